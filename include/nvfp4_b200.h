@@ -1,0 +1,164 @@
+/*
+ * nvfp4_b200 -- C ABI of the B200 (sm_100a) NVFP4 flash-attention kernels.
+ *
+ * This is the drop-in boundary for the `sageattention.nvfp4` path of thad0ctor/SageAttention.
+ * The reference has no FFI of its own (it launches Triton kernels from Python); every entry
+ * point below replaces one Triton launch site and cites it as `file:line` inside the reference
+ * project.  A host binding passes raw device pointers, element/byte strides and the CUDA stream
+ * to enqueue on; no entry point allocates memory, synchronises, or throws.
+ *
+ * Return value: 0 on success; < 0 for an invalid argument (text in nvfp4_last_error()); > 0 is a
+ * cudaError_t from a launch.  Kernels that wait on hardware barriers bound every wait and report
+ * a non-zero word through the `status` pointer instead of hanging.
+ *
+ * Packed layouts (identical to the reference, flash.py:363-419 and kv_cache.py:6-7):
+ *   along-D pack    nib [B, rows, D/2] uint8, sc [B, rows, D/16] e4m3 bytes
+ *   V^T pack        nib [B, D, Sp/2]  uint8, sc [B, D, Sp/16]  e4m3 bytes, Sp = keys padded to 128
+ *   byte j of a row = code[2j] | code[2j+1] << 4, codes are e2m1 with sign in bit 3.
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of high-precision tensors */
+#define NVFP4_DT_BF16 0
+#define NVFP4_DT_FP16 1
+#define NVFP4_DT_FP32 2
+
+/* flags of nvfp4_fwd */
+#define NVFP4_FWD_CAUSAL 1
+
+typedef void* nvfp4_stream_t; /* a cudaStream_t */
+
+/* Library identification; bumps when a signature changes. */
+int nvfp4_abi_version(void);
+
+/* Text of the last error returned on the calling thread ("" if none). */
+const char* nvfp4_last_error(void);
+
+/*
+ * NVFP4 pack of a strided [B, R, K] view along K: per 16 elements
+ * amax -> e4m3(clamp(amax / 6, 2^-9, 448)) -> IEEE divide -> e2m1 RTNE, saturating.
+ * Replaces `_quant_nvfp4` / `_quant_nvfp4_kernel` (sageattention/nvfp4/flash.py:310-419); the
+ * reference's `transpose=True` (V^T) is expressed by passing sxr = 1 and sxk = the key stride.
+ * Elements at contraction index >= k_read read as +0.0; groups up to k_pad are written
+ * (k_pad % 16 == 0, k_pad >= k_read).  x strides are in elements, output strides in bytes; output
+ * rows are contiguous (k_pad/2 and k_pad/16 bytes).
+ */
+int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, int64_t k_pad,
+               int64_t sxb, int64_t sxr, int64_t sxk, uint8_t* nib, int64_t snb, int64_t snr,
+               uint8_t* sc, int64_t ssb, int64_t ssr, nvfp4_stream_t stream);
+
+/*
+ * One decode-step append into an NVFP4 KV cache, one launch, no host synchronisation.
+ * Replaces NVFP4KVCache.append (sageattention/nvfp4/kv_cache.py:228-257): packs the new K row
+ * along D into position `pos`; stores the new V token into slot pos % 16 of the partial-group
+ * buffer (zeroing the buffer first when the slot is 0) and re-packs that 16-key group of V^T;
+ * optionally writes the token into the recent-window rings at slot pos % ring_cap.
+ * k_new / v_new: [ZHk, D] rows with element stride s_new between units.  Cache strides in bytes
+ * per (z,hk) unit: knv rows are D/2 bytes, ksc rows D/16, vnv rows `vnv_row` bytes, vsc rows
+ * `vsc_row` bytes.  partial: [ZHk, 16, D] in `dtype`.  ring_k / ring_v may be NULL.
+ */
+int nvfp4_kv_append(const void* k_new, const void* v_new, int dtype, int64_t s_new, int64_t zhk,
+                    int d, int64_t pos, uint8_t* knv, int64_t knv_unit, uint8_t* ksc,
+                    int64_t ksc_unit, uint8_t* vnv, int64_t vnv_unit, int64_t vnv_row, uint8_t* vsc,
+                    int64_t vsc_unit, int64_t vsc_row, void* partial, void* ring_k, void* ring_v,
+                    int64_t ring_cap, nvfp4_stream_t stream);
+
+/*
+ * Split-K decode plan for a cache of s_kv keys and zhk (batch x kv-head) units: how many
+ * splits the decode kernel will use, keys per split (a multiple of 128) and the scratch bytes it
+ * needs.  Replaces the heuristic of `_decode_compute` (flash.py:3255-3266), sized for the
+ * device's SM count instead of a fixed 256 programs.
+ */
+int nvfp4_decode_plan(int64_t s_kv, int64_t zhk, int d, int sm_count, int* nsplit,
+                      int64_t* split_kv, size_t* workspace_bytes);
+
+/*
+ * Decode attention of one query token per head against a packed cache, reading the cache in
+ * place through its strides.  Replaces `nvfp4_flash_decode_prequant` + `_flash_decode_kernel` +
+ * `_flash_decode_combine_kernel` (flash.py:3031-3342) and the LSE recovery of
+ * `_decode_prequant_with_lse` (kv_cache.py:32-97).
+ *   q        [Z, H, D] high precision (`q_dtype`), s_qz / s_qh element strides; the G = H / Hk
+ *            query heads of a kv head are quantised to NVFP4 in the kernel prologue.
+ *   knv/ksc  [ZHk, >= s_kv, D/2 | D/16], unit strides in bytes (rows contiguous).
+ *   vnv/vsc  [ZHk, D, >= s_pad/2 | s_pad/16], unit and row strides in bytes; s_pad = s_kv rounded
+ *            up to 128.  Key groups beyond s_kv must hold zero nibbles (any scale byte).
+ *   out      [Z, H, D] in `q_dtype`, contiguous.  lse: [Z, H] fp32 or NULL.
+ *   workspace: >= workspace_bytes from nvfp4_decode_plan(nsplit as planned), 16-byte aligned.
+ *   status   device int, written non-zero if a bounded wait expired; may be NULL.
+ */
+int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, const uint8_t* knv,
+                 int64_t knv_unit, const uint8_t* ksc, int64_t ksc_unit, const uint8_t* vnv,
+                 int64_t vnv_unit, int64_t vnv_row, const uint8_t* vsc, int64_t vsc_unit,
+                 int64_t vsc_row, int64_t z, int64_t hk, int g, int d, int64_t s_kv, float scaling,
+                 void* out, float* lse, void* workspace, size_t workspace_bytes, int nsplit,
+                 int64_t split_kv, int* status, nvfp4_stream_t stream);
+
+/*
+ * Exact merge of two attention results over disjoint key sets from their log-sum-exps:
+ * out = (e^{lse1-m} o1 + e^{lse2-m} o2) / (e^{lse1-m} + e^{lse2-m}).  Replaces the torch
+ * expressions of NVFP4KVCache.hybrid_decode (kv_cache.py:346-351).  o1,o2,out: [rows, d] in
+ * `dtype`; lse1,lse2: [rows] fp32.
+ */
+int nvfp4_lse_merge(const void* o1, const float* lse1, const void* o2, const float* lse2,
+                    void* out, int dtype, int64_t rows, int d, nvfp4_stream_t stream);
+
+/*
+ * Exact attention of one query token per head over a short high-precision window held in ring
+ * buffers (the "recent" side of hybrid decode, kv_cache.py:321-335).  rk/rv: [Z, Hk, ring_cap, D]
+ * contiguous in `dtype`; keys are absolute positions [first_pos, first_pos + count) found at slot
+ * pos % ring_cap.  out: [Z, H, D] fp32, lse: [Z, H] fp32.
+ */
+int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, int64_t s_qh, const void* rk,
+                           const void* rv, int64_t z, int64_t hk, int g, int d, int64_t ring_cap,
+                           int64_t first_pos, int64_t count, float scaling, float* out, float* lse,
+                           nvfp4_stream_t stream);
+
+/*
+ * Scratch bytes nvfp4_fwd needs for these dimensions (0 if none).
+ */
+size_t nvfp4_fwd_workspace_bytes(int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
+                                 int d);
+
+/*
+ * Flash-attention forward over packed operands.  Replaces `_flash_fwd_kernel` and its host
+ * drivers `_run_flash_packed` / `nvfp4_flash_attention_packed` (flash.py:739-933, 2560-2766).
+ *   qnv/qsc  [Z*H,  s_q,  D/2 | D/16]  contiguous
+ *   knv/ksc  [Z*Hk, s_kv, D/2 | D/16]  contiguous
+ *   vnv/vsc  [Z*Hk, D, s_pad/2 | s_pad/16] contiguous, s_pad % 128 == 0, s_pad >= s_kv
+ *   bias     [Z, s_kv] fp32 additive key bias (may hold -inf) or NULL
+ *   seq_id / seq_start: [s_q] int32 per-token sample index / first token of the sample (varlen,
+ *            requires Z == 1 and s_q == s_kv) or NULL
+ *   out      element strides (so_z, so_h, so_s), unit stride along D, in `out_dtype`
+ *            ("zhsd": so_z = H*S*D, so_h = S*D, so_s = D; "zshd": so_z = S*H*D, so_h = D,
+ *            so_s = H*D)
+ *   lse      [Z*H, s_q] fp32 natural-log LSE or NULL
+ *   flags    NVFP4_FWD_CAUSAL: key j visible to query i iff j <= i + (s_kv - s_q)
+ *   status   device int, written non-zero if a bounded wait expired; may be NULL.
+ */
+int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
+              const uint8_t* vnv, const uint8_t* vsc, const float* bias, const int32_t* seq_id,
+              const int32_t* seq_start, void* out, int out_dtype, int64_t so_z, int64_t so_h,
+              int64_t so_s, float* lse, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
+              int64_t s_pad, int d, float scaling, int flags, void* workspace,
+              size_t workspace_bytes, int* status, nvfp4_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#endif /* NVFP4_B200_H_ */

@@ -1,0 +1,71 @@
+// NVFP4 element arithmetic shared by every kernel that packs: IEEE fp32 scale computation, the
+// e4m3 scale byte, the e2m1 convert.  Nothing here may be compiled with fast-math: packed bytes
+// are compared bit for bit with an IEEE restatement (true divisions, round-to-nearest-even).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace nvfp4 {
+
+constexpr float kScaleFloor = 0.001953125f;  // 2^-9, smallest positive e4m3 value
+constexpr float kScaleMax = 448.0f;
+constexpr float kF4Max = 6.0f;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// e4m3 byte of clamp(amax / 6, 2^-9, 448), round-to-nearest-even.
+__device__ __forceinline__ uint8_t scale_byte_from_amax(float amax) {
+  float s = fminf(fmaxf(__fdiv_rn(amax, kF4Max), kScaleFloor), kScaleMax);
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(s));
+  return (uint8_t)(r & 0xFF);
+}
+
+// exact value of a (non-negative) e4m3 byte
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)b));
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFF)));
+}
+
+// 8 fp32 -> 8 e2m1 codes in one 32-bit word, element 0 in the low nibble of byte 0.
+__device__ __forceinline__ uint32_t e2m1x8(float x0, float x1, float x2, float x3, float x4,
+                                           float x5, float x6, float x7) {
+  uint32_t out;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}\n"
+      : "=r"(out)
+      : "f"(x0), "f"(x1), "f"(x2), "f"(x3), "f"(x4), "f"(x5), "f"(x6), "f"(x7));
+  return out;
+}
+
+// Pack one group of 16 fp32 values: returns the scale byte, writes 8 nibble bytes to lo/hi.
+__device__ __forceinline__ uint8_t pack_group16(const float (&x)[16], uint32_t& lo, uint32_t& hi) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const uint8_t sb = scale_byte_from_amax(amax);
+  const float sf = e4m3_to_f32(sb);
+  float y[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) y[i] = __fdiv_rn(x[i], sf);
+  lo = e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+  hi = e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+  return sb;
+}
+
+}  // namespace nvfp4

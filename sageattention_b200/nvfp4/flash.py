@@ -1,0 +1,396 @@
+"""Host side of the B200 NVFP4 flash-attention path.
+
+Mirrors the operator surface of the reference module ``sageattention/nvfp4/flash.py`` (same
+names, argument order, defaults and error behaviour) so callers and tests written against the
+reference run unchanged; each function cites the reference lines it stands in for.  All compute
+is in ``libnvfp4_b200.so`` (hand-written sm_100a CUDA behind the C ABI of
+``include/nvfp4_b200.h``); torch is used for allocation, streams and autograd plumbing only.
+There is no Triton and no CPU fallback: CPU tensors are rejected.
+
+Tile arguments (``block_m``, ``block_n``, ``num_warps``, ``num_stages``) are accepted for
+signature compatibility.  The sm_100a kernels always walk 128-key tiles (the reference's own
+D=128 default), so ``block_n`` only has to be 128 where it fixes a visible padding
+(``nvfp4_quant_kv_decode``); other tile hints are ignored.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .. import _lib
+
+# --------------------------------------------------------------------------- constants
+# (names kept importable: tests and scripts of the reference read them, flash.py:260-273,
+#  :993-1037)
+_BWD_GRAD_DOTS_MODES = ("bf16", "fp4_rownorm", "fp8_rownorm", "fp4_legacy")
+_BWD_AUTO_FP4_MIN_SEQ = 4096
+_BWD_RN_DO_ZSHD = True
+_FWD_TILE = {256: (128, 128, 8, 2), 128: (128, 128, 8, 2)}
+_FWD_TILE_DEFAULT = (64, 128, 8, 3)
+_FWD_TILE_VARLEN = {256: (128, 128, 8, 2), 128: (128, 128, 8, 2)}
+_FWD_FUSED_QUANT_MAX_SEQ = 3072
+_FWD_VARLEN_DENSE_MIN_MEAN = 4096
+_KEY_TILE = 128
+
+
+def _next_mult(n: int, m: int) -> int:
+    return ((n + m - 1) // m) * m
+
+
+def _resolve_fwd_tiles(d, block_m, block_n, num_warps, num_stages, varlen=False, mean_len=None):
+    """Tile policy hook of the reference (flash.py:1040-1056).
+
+    Explicit tiles are echoed back, generic defaults resolve to the one tile shape the sm_100a
+    forward kernel implements (128 query rows x 128 keys).
+    """
+    if (block_m, block_n, num_warps, num_stages) == _FWD_TILE_DEFAULT:
+        return (_FWD_TILE_VARLEN if varlen else _FWD_TILE).get(d, _FWD_TILE_DEFAULT)
+    return block_m, block_n, num_warps, num_stages
+
+
+def _resolve_backward_grad_dots(mode, eff_seq, save_backward_packs, num_key_value_groups) -> str:
+    """Backward-mode resolver, same table as the reference (flash.py:276-302).
+
+    ``None`` = AUTO: "bf16" (high-precision gradient GEMMs) below ``_BWD_AUTO_FP4_MIN_SEQ``
+    effective sequence, else "fp4_rownorm"; "bf16" silently downgrades to "fp4_rownorm" when only
+    packs are saved or the GQA group exceeds 8.
+    """
+    if mode is None:
+        mode = "bf16" if eff_seq < _BWD_AUTO_FP4_MIN_SEQ else "fp4_rownorm"
+    if mode not in _BWD_GRAD_DOTS_MODES:
+        raise ValueError(
+            f"backward_grad_dots must be one of {_BWD_GRAD_DOTS_MODES} or None (auto), got {mode!r}")
+    if mode == "bf16" and (save_backward_packs or num_key_value_groups > 8):
+        mode = "fp4_rownorm"
+    return mode
+
+
+# --------------------------------------------------------------------------- packer
+def _pack_into(x, nib, sc, transpose=False, k_pad=None):
+    """Pack ``x`` ([B,R,K], or [B,K,R] with ``transpose``) into existing (possibly strided) views.
+
+    ``nib`` [B,R,Kp/2] uint8 and ``sc`` [B,R,Kp/16] (uint8 or float8_e4m3fn) must have unit
+    stride along their last axis; this is how the KV cache packs straight into its buffers.
+    """
+    _lib.require_cuda(x, "x")
+    if transpose:
+        b, k_read, r = x.shape
+        sxb, sxk, sxr = x.stride()
+    else:
+        b, r, k_read = x.shape
+        sxb, sxr, sxk = x.stride()
+    kp = k_read if k_pad is None else int(k_pad)
+    assert kp % 16 == 0, "padded contraction dim must be a multiple of 16"
+    assert kp >= k_read, "k_pad must cover the contraction axis"
+    assert nib.shape == (b, r, kp // 2) and sc.shape == (b, r, kp // 16), "output view shape mismatch"
+    assert nib.stride(2) == 1 and sc.stride(2) == 1
+    if b * r * kp == 0:
+        return
+    _lib.check(_lib.lib().nvfp4_pack(
+        x.data_ptr(), _lib.dtype_code(x.dtype), b, r, k_read, kp, sxb, sxr, sxk,
+        nib.data_ptr(), nib.stride(0), nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1),
+        _lib.stream_ptr(x.device)), "nvfp4_pack")
+
+
+def _quant_nvfp4(x: torch.Tensor, transpose: bool = False, k_pad: int | None = None):
+    """NVFP4-pack along the contraction axis; stands in for flash.py:363-419.
+
+    ``x`` is ``[B, R, K]`` (quantised along K) or, with ``transpose=True``, ``[B, K, R]`` read
+    through its strides to produce the V^T layout.  ``k_pad`` zero-pads the contraction axis
+    (padded groups get the floor scale and zero nibbles).  Returns
+    ``(uint8 [B, R, Kp/2], float8_e4m3fn [B, R, Kp/16])``.
+    """
+    if transpose:
+        b, k_read, r = x.shape
+    else:
+        b, r, k_read = x.shape
+    kp = k_read if k_pad is None else int(k_pad)
+    assert kp % 16 == 0, "padded contraction dim must be a multiple of 16"
+    nib = torch.empty(b, r, kp // 2, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(b, r, kp // 16, dtype=torch.uint8, device=x.device)
+    _pack_into(x, nib, sc, transpose=transpose, k_pad=kp)
+    return nib, sc.view(torch.float8_e4m3fn)
+
+
+def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None):
+    """Both layouts of ``x`` [B, S, D]: along D and along S (padded to ``s_pad``).
+
+    Stands in for flash.py:514-561; bit-identical to two ``_quant_nvfp4`` calls by construction.
+    Returns ``(nib_d, sc_d, nib_s, sc_s)``.
+    """
+    b, s, d = x.shape
+    sp = _next_mult(s, 16) if s_pad is None else s_pad
+    nd, sd = _quant_nvfp4(x)
+    ns, ss = _quant_nvfp4(x, transpose=True, k_pad=sp)
+    return nd, sd, ns, ss
+
+
+def _quant_qkv_fwd(q2, k2, v2, s_kv_pad):
+    """Q, K along D and V along keys (padded); stands in for flash.py:682-732."""
+    qnv, qsc = _quant_nvfp4(q2)
+    knv, ksc = _quant_nvfp4(k2)
+    vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_kv_pad)
+    return qnv, qsc, knv, ksc, vnv, vsc
+
+
+def convert_fp32_to_fp4_packed(x_pairs):
+    """Pairs of fp32 tensors -> one byte per pair (first in the low nibble), e2m1 RTNE.
+
+    The reference exposes this as a Triton device function (_fp4_pack.py:15-56); here it is a
+    host-callable helper over the same hardware convert: values are packed with unit scale.
+    """
+    lo, hi = x_pairs
+    x = torch.stack([lo.float(), hi.float()], dim=-1).reshape(1, -1, 2)
+    n = x.shape[1]
+    # unit scale: pad every pair to a group whose amax is exactly 6 so the group scale is 1
+    grp = torch.zeros(1, n, 16, dtype=torch.float32, device=x.device)
+    grp[:, :, 0:2] = x.clamp(-6.0, 6.0)
+    grp[:, :, 2] = 6.0
+    nib, _ = _quant_nvfp4(grp)
+    return nib[0, :, 0].reshape(lo.shape)
+
+
+# --------------------------------------------------------------------------- varlen
+def _varlen_seq_arrays(cu_seqlens: torch.Tensor, s: int, device):
+    """``cu_seqlens`` [n+1] -> int32 ``[s]`` arrays (seq_id, seq_start, seq_end) on ``device``.
+
+    Same contract and validation messages as flash.py:940-984, including the cache on the
+    tensor keyed by (s, device, version) so one host copy serves every layer of a step.
+    """
+    assert cu_seqlens.ndim == 1 and cu_seqlens.numel() >= 2, (
+        f"cu_seqlens must be a 1-D [nseq+1] tensor, got shape {tuple(cu_seqlens.shape)}")
+    key = (int(s), str(device), cu_seqlens._version)
+    cached = getattr(cu_seqlens, "_nvfp4_seq_arrays", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    cu = cu_seqlens.detach().to("cpu", torch.int64)
+    assert int(cu[0]) == 0, f"cu_seqlens[0] must be 0, got {int(cu[0])}"
+    assert int(cu[-1]) == s, f"cu_seqlens[-1] ({int(cu[-1])}) must equal the packed seqlen ({s})"
+    assert bool((cu[1:] >= cu[:-1]).all()), "cu_seqlens must be nondecreasing"
+    lens = (cu[1:] - cu[:-1])
+    ids = torch.repeat_interleave(torch.arange(lens.numel(), dtype=torch.int64), lens)
+    seq_id = ids.to(torch.int32)
+    seq_start = cu[ids].to(torch.int32)
+    seq_end = cu[ids + 1].to(torch.int32)
+    arrays = tuple(t.to(device).contiguous() for t in (seq_id, seq_start, seq_end))
+    try:
+        cu_seqlens._nvfp4_seq_arrays = (key, arrays)
+    except (AttributeError, RuntimeError):
+        pass
+    return arrays
+
+
+# --------------------------------------------------------------------------- decode
+def nvfp4_quant_kv_decode(key: torch.Tensor, value: torch.Tensor, block_n: int = 128) -> tuple:
+    """One-shot NVFP4 pack of a GQA KV cache (stands in for flash.py:3211-3241).
+
+    ``key``/``value``: ``[Z, Hk, Skv, D]``.  Returns ``(knv, ksc, vnv, vsc, s_kv, s_kv_pad)`` with K
+    packed along D and V packed along keys as V^T, the key axis padded to ``block_n``.
+    """
+    z, hk, s_kv, d = key.shape
+    assert d % 16 == 0 and d in (128, 256)
+    s_kv_pad = _next_mult(s_kv, block_n)
+    knv, ksc = _quant_nvfp4(key.reshape(z * hk, s_kv, d))
+    vnv, vsc = _quant_nvfp4(value.reshape(z * hk, s_kv, d), transpose=True, k_pad=s_kv_pad)
+    return knv, ksc, vnv, vsc, s_kv, s_kv_pad
+
+
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def _decode_plan(s_kv: int, zhk: int, d: int, device):
+    ns, sk, wb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_size_t()
+    _lib.check(_lib.lib().nvfp4_decode_plan(s_kv, zhk, d, _sm_count(device), ctypes.byref(ns),
+                                            ctypes.byref(sk), ctypes.byref(wb)), "nvfp4_decode_plan")
+    return ns.value, sk.value, wb.value
+
+
+def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
+    """Shared body of the decode entry points: plan, allocate scratch, one C-ABI call."""
+    _lib.require_cuda(query, "query")
+    z, h, s_q, d = query.shape
+    assert s_q == 1, "nvfp4_flash_decode is for seqlen_q == 1 (decode)"
+    assert d % 16 == 0 and d in (128, 256)
+    knv, ksc, vnv, vsc, s_kv, s_kv_pad = kv_packed
+    zhk = knv.shape[0]
+    assert zhk % z == 0, "packed KV batch must be a multiple of Z"
+    hk = zhk // z
+    assert h % hk == 0 and h // hk == g, "G mismatch vs packed KV"
+    assert g <= 16, f"GQA group {g} must be <= 16"
+    assert s_kv >= 1, "decode needs at least one key"
+    dev = query.device
+    q3 = query.reshape(z, h, d)
+    if q3.stride(2) != 1:
+        q3 = q3.contiguous()
+    if split_kv is None:
+        nsplit, split_kv, wbytes = _decode_plan(s_kv, zhk, d, dev)
+    else:
+        assert split_kv % 128 == 0
+        nsplit = -(-s_kv // split_kv)
+        wbytes = zhk * nsplit * (16 * d + 32) * 4
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+    out = torch.empty(z, h, d, dtype=query.dtype, device=dev)
+    lse = torch.empty(z, h, dtype=torch.float32, device=dev) if want_lse else None
+    for t in (knv, ksc, vnv, vsc):
+        assert t.stride(-1) == 1, "packed cache rows must be contiguous"
+    assert knv.stride(1) == d // 2 and ksc.stride(1) == d // 16, "K rows must be dense"
+    _lib.check(_lib.lib().nvfp4_decode(
+        q3.data_ptr(), _lib.dtype_code(q3.dtype), q3.stride(0), q3.stride(1),
+        knv.data_ptr(), knv.stride(0), ksc.data_ptr(), ksc.stride(0),
+        vnv.data_ptr(), vnv.stride(0), vnv.stride(1), vsc.data_ptr(), vsc.stride(0), vsc.stride(1),
+        z, hk, g, d, s_kv, float(scaling), out.data_ptr(),
+        lse.data_ptr() if lse is not None else None, ws.data_ptr(), wbytes, nsplit, split_kv,
+        _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_decode")
+    return out.reshape(z, h, 1, d), lse
+
+
+def nvfp4_flash_decode_prequant(query, kv_packed, scaling, num_key_value_groups=1, block_n=128,
+                                num_warps=4, num_stages=3, target_programs=256):
+    """Decode one query token per head against a pre-packed NVFP4 cache (HBM-bound fast path).
+
+    Stands in for flash.py:3296-3342.  ``query`` ``[Z, H, 1, D]``; ``kv_packed`` is the tuple from
+    ``nvfp4_quant_kv_decode`` or ``NVFP4KVCache.get_packed()`` (strided views are read in place).
+    The split count follows the device's SM count; ``target_programs`` is accepted and ignored.
+    Returns ``[Z, H, 1, D]`` in ``query.dtype``.
+    """
+    assert block_n == 128, "the B200 decode kernel walks 128-key tiles"
+    out, _ = _decode_core(query, kv_packed, scaling, num_key_value_groups, want_lse=False)
+    return out
+
+
+def _decode_prequant_with_lse(query, kv_packed, scaling, g, block_n=128, num_warps=4,
+                              num_stages=3, target_programs=256):
+    """Decode that also returns the per-head log-sum-exp (kv_cache.py:32-97): ``(out, lse[Z,H])``."""
+    return _decode_core(query, kv_packed, scaling, g, want_lse=True)
+
+
+def nvfp4_flash_decode(query, key, value, scaling, num_key_value_groups=1, block_n=128,
+                       num_warps=4, num_stages=3, target_programs=256):
+    """Convenience decode that packs K/V from high precision on every call (flash.py:3345-3400)."""
+    z, h, s_q, d = query.shape
+    _, hk, s_kv, _ = key.shape
+    assert s_q == 1, "nvfp4_flash_decode is for seqlen_q == 1 (decode)"
+    assert h % hk == 0 and h // hk == num_key_value_groups
+    assert d % 16 == 0 and d in (128, 256)
+    assert num_key_value_groups <= 16, f"GQA group {num_key_value_groups} must be <= 16"
+    packed = nvfp4_quant_kv_decode(key, value, block_n)
+    return nvfp4_flash_decode_prequant(query, packed, scaling, num_key_value_groups, block_n)
+
+
+# --------------------------------------------------------------------------- forward
+def _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scaling, out_dtype,
+                      causal=False, key_pad_bias=None, cu_seqlens=None, block_m=64, block_n=128,
+                      num_warps=8, num_stages=3, out_layout="zhsd", return_lse=False,
+                      _varlen_arrays=None):
+    """Launch the forward kernel over packed operands (stands in for flash.py:2560-2652)."""
+    dev = qnv.device
+    _lib.require_cuda(qnv, "qnv")
+    if out_layout not in ("zhsd", "zshd"):
+        raise ValueError(f"out_layout must be 'zhsd' or 'zshd', got {out_layout!r}")
+    assert d in (128, 256), "D must be 128 or 256"
+    s_pad = vnv.shape[-1] * 2
+    assert s_pad % _KEY_TILE == 0 and s_pad >= s_kv, (
+        f"V^T key axis ({s_pad}) must be padded to a multiple of the key tile ({_KEY_TILE})")
+    seq_id = seq_start = None
+    if cu_seqlens is not None or _varlen_arrays is not None:
+        assert z == 1, "cu_seqlens varlen requires Z must be 1 (one packed row)"
+        assert s_q == s_kv, "cu_seqlens varlen requires Sq == Skv"
+        arrays = _varlen_arrays if _varlen_arrays is not None else _varlen_seq_arrays(cu_seqlens, s_q, dev)
+        seq_id, seq_start = arrays[0], arrays[1]
+    if out_layout == "zhsd":
+        out = torch.empty(z, h, s_q, d, dtype=out_dtype, device=dev)
+        so_z, so_h, so_s = out.stride(0), out.stride(1), out.stride(2)
+    else:
+        out = torch.empty(z, s_q, h, d, dtype=out_dtype, device=dev)
+        so_z, so_s, so_h = out.stride(0), out.stride(1), out.stride(2)
+    lse = torch.empty(z * h, s_q, dtype=torch.float32, device=dev) if return_lse else None
+    bias = None
+    if key_pad_bias is not None:
+        bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
+        assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
+    L = _lib.lib()
+    wbytes = L.nvfp4_fwd_workspace_bytes(z, h, hk, s_q, s_kv, d)
+    ws = torch.empty(max(wbytes, 16), dtype=torch.uint8, device=dev)
+    tensors = [t.contiguous() for t in (qnv, qsc, knv, ksc, vnv, vsc)]
+    _lib.check(L.nvfp4_fwd(
+        *(t.data_ptr() for t in tensors),
+        bias.data_ptr() if bias is not None else None,
+        seq_id.data_ptr() if seq_id is not None else None,
+        seq_start.data_ptr() if seq_start is not None else None,
+        out.data_ptr(), _lib.dtype_code(out_dtype), so_z, so_h, so_s,
+        lse.data_ptr() if lse is not None else None, z, h, hk, s_q, s_kv, s_pad, d, float(scaling),
+        1 if causal else 0, ws.data_ptr(), wbytes, _lib.status_word(dev).data_ptr(),
+        _lib.stream_ptr(dev)), "nvfp4_fwd")
+    return (out, lse) if return_lse else out
+
+
+def nvfp4_flash_attention_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scaling,
+                                 out_dtype, causal=False, key_pad_bias=None, cu_seqlens=None,
+                                 block_m=64, block_n=128, num_warps=8, num_stages=3,
+                                 out_layout="zhsd", _varlen_arrays=None):
+    """Forward over operands the caller already packed (stands in for flash.py:2655-2766)."""
+    return _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scaling,
+                             out_dtype, causal, key_pad_bias, cu_seqlens, block_m, block_n,
+                             num_warps, num_stages, out_layout, False, _varlen_arrays)
+
+
+def _check_packs(packs, rows_shape, name):
+    nv, sc = packs
+    assert nv.shape == rows_shape[:-1] + (rows_shape[-1] // 2,) and \
+        sc.shape == rows_shape[:-1] + (rows_shape[-1] // 16,), (
+            f"{name} layout mismatch: expected along-D packs for shape {rows_shape}")
+    return nv, sc
+
+
+def nvfp4_flash_attention(query, key, value, scaling, causal=False, num_key_value_groups=1,
+                          key_pad_bias=None, cu_seqlens=None, block_m=64, block_n=128, num_warps=8,
+                          num_stages=3, return_lse=False, return_packs=False, out_layout="zhsd",
+                          q_packs=None, k_packs=None, _varlen_arrays=None):
+    """NVFP4 flash-attention forward (no autograd); stands in for flash.py:2769-3015.
+
+    ``query`` ``[Z, H, Sq, D]``, ``key``/``value`` ``[Z, Hk, Skv, D]`` (bf16 / fp16 / fp32),
+    ``D`` in {128, 256}.  Q and K are packed along D, V along keys, then the block-scaled FP4
+    kernel runs.  Causal masking is bottom-right aligned.  Return arity follows the two flags
+    exactly as in the reference: ``out`` | ``(out, lse)`` | ``(out, packs)`` |
+    ``(out, lse, packs)`` with ``packs = (qnv, qsc, knv, ksc, vnv, vsc)``.
+    """
+    if out_layout not in ("zhsd", "zshd"):
+        raise ValueError(f"out_layout must be 'zhsd' or 'zshd', got {out_layout!r}")
+    _lib.require_cuda(query, "query")
+    z, h, s_q, d = query.shape
+    _, hk, s_kv, _ = key.shape
+    g = num_key_value_groups
+    assert h == hk * g, "num_key_value_groups must equal H // Hk"
+    assert d in (128, 256), "D must be 128 or 256"
+    if causal and cu_seqlens is None:
+        assert s_kv >= s_q, "causal attention requires Skv >= Sq (bottom-right aligned mask)"
+    if cu_seqlens is not None:
+        assert z == 1, "cu_seqlens varlen requires Z must be 1 (one packed row)"
+        assert s_q == s_kv, "cu_seqlens varlen requires Sq == Skv"
+        assert causal, "cu_seqlens varlen is block-diagonal causal: pass causal=True"
+    s_pad = _next_mult(s_kv, _KEY_TILE)
+    q2 = query.reshape(z * h, s_q, d)
+    k2 = key.reshape(z * hk, s_kv, d)
+    v2 = value.reshape(z * hk, s_kv, d) if value.dim() == 4 else value
+    if q_packs is not None:
+        qnv, qsc = _check_packs(q_packs, (z * h, s_q, d), "q_packs layout")
+    else:
+        qnv, qsc = _quant_nvfp4(q2)
+    if k_packs is not None:
+        knv, ksc = _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout")
+    else:
+        knv, ksc = _quant_nvfp4(k2)
+    vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_pad)
+    res = _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scaling,
+                            query.dtype, causal, key_pad_bias, cu_seqlens, block_m, block_n,
+                            num_warps, num_stages, out_layout, return_lse, _varlen_arrays)
+    packs = (qnv, qsc, knv, ksc, vnv, vsc)
+    if return_lse and return_packs:
+        return res[0], res[1], packs
+    if return_packs:
+        return res, packs
+    return res

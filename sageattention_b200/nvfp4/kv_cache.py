@@ -1,0 +1,191 @@
+"""NVFP4 KV cache for decode, B200-native.
+
+Host-side mirror of ``NVFP4KVCache`` (reference: sageattention/nvfp4/kv_cache.py:100-373): same
+constructor, attributes, methods and error behaviour; the work is done by CUDA kernels reached
+through the C ABI:
+
+* ``append`` is ONE launch (``nvfp4_kv_append``): K row pack, partial-group V store, re-pack of
+  the current 16-key V^T group and the optional ring write, with no host synchronisation
+  (the reference issues two Triton launches and about six small torch ops per token);
+* ``prefill`` packs K and the full V groups straight into the cache buffers through the strided
+  packer (no temporaries), then stashes the trailing < 16 tokens;
+* ``hybrid_decode`` runs the split-K FP4 decode over the old prefix, an exact window-attention
+  kernel over the bf16 ring, and merges the two on the device by their log-sum-exps.
+
+Buffers (layouts identical to the reference so packed bytes can be compared):
+  knv [Z*Hk, cap, D/2] uint8       ksc [Z*Hk, cap, D/16] float8_e4m3fn
+  vnv [Z*Hk, D, cap_pad/2] uint8   vsc [Z*Hk, D, cap_pad/16] float8_e4m3fn   (V^T along keys)
+  v_partial_bf16 [Z*Hk, 16, D]     rk / rv [Z, Hk, ring_cap, D] (only with recent_window > 0)
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from . import flash as _flash
+from .flash import _next_mult, _pack_into
+
+
+class NVFP4KVCache:
+    """One layer's GQA KV cache held in NVFP4 and grown one token at a time.
+
+    Args mirror the reference (kv_cache.py:115-125): ``z`` batch, ``hk`` kv heads, ``d`` head dim
+    in {128, 256}, ``max_seq_len`` capacity, ``device``, ``dtype`` of incoming K/V, ``block_n``
+    the key tile the V^T axis is padded to, ``recent_window`` > 0 keeps a bf16 ring of the most
+    recent tokens for ``hybrid_decode``.
+    """
+
+    GROUP = 16
+
+    def __init__(self, z, hk, d, max_seq_len, device, dtype=torch.bfloat16, block_n=128,
+                 recent_window=0):
+        assert d in (128, 256), "D must be 128 or 256"
+        assert block_n == 128, "the B200 decode kernel walks 128-key tiles (block_n must be 128)"
+        self.z, self.hk, self.d = z, hk, d
+        self.zhk = z * hk
+        self.max_seq_len = max_seq_len
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.block_n = block_n
+        self.cap_pad = _next_mult(max_seq_len, block_n)
+        dev = self.device
+        self.knv = torch.zeros(self.zhk, max_seq_len, d // 2, dtype=torch.uint8, device=dev)
+        self.ksc = torch.zeros(self.zhk, max_seq_len, d // 16, dtype=torch.float8_e4m3fn, device=dev)
+        self.vnv = torch.zeros(self.zhk, d, self.cap_pad // 2, dtype=torch.uint8, device=dev)
+        self.vsc = torch.zeros(self.zhk, d, self.cap_pad // 16, dtype=torch.float8_e4m3fn, device=dev)
+        self.v_partial_bf16 = torch.zeros(self.zhk, self.GROUP, d, dtype=dtype, device=dev)
+        self.partial_len = 0
+        self.length = 0
+        self.recent_window = recent_window
+        self.ring_cap = _next_mult(recent_window + self.GROUP, self.GROUP) if recent_window > 0 else 0
+        if recent_window > 0:
+            self.rk = torch.zeros(z, hk, self.ring_cap, d, dtype=dtype, device=dev)
+            self.rv = torch.zeros(z, hk, self.ring_cap, d, dtype=dtype, device=dev)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, key: torch.Tensor, value: torch.Tensor):
+        """Pack a prompt's K/V ([Z, Hk, S, D]) into the cache (kv_cache.py:187-224)."""
+        z, hk, s, d = key.shape
+        assert (z, hk, d) == (self.z, self.hk, self.d)
+        assert s <= self.max_seq_len, "prefill exceeds capacity"
+        k2 = key.reshape(self.zhk, s, d)
+        v2 = value.reshape(self.zhk, s, d)
+        _pack_into(k2, self.knv[:, :s], self.ksc[:, :s])
+        full = (s // self.GROUP) * self.GROUP
+        if full:
+            _pack_into(v2[:, :full], self.vnv[:, :, : full // 2], self.vsc[:, :, : full // 16],
+                       transpose=True)
+        rem = s - full
+        self.partial_len = rem
+        self.v_partial_bf16.zero_()
+        if rem:
+            self.v_partial_bf16[:, :rem] = v2[:, full:]
+            g0 = full // self.GROUP
+            _pack_into(self.v_partial_bf16[:, :rem], self.vnv[:, :, g0 * 8 : g0 * 8 + 8],
+                       self.vsc[:, :, g0 : g0 + 1], transpose=True, k_pad=self.GROUP)
+        if self.recent_window > 0:
+            w = min(self.ring_cap, s)
+            pos = torch.arange(s - w, s, device=self.device)
+            slots = pos % self.ring_cap
+            self.rk[:, :, slots] = key[:, :, s - w :].to(self.dtype)
+            self.rv[:, :, slots] = value[:, :, s - w :].to(self.dtype)
+        self.length = s
+
+    # ------------------------------------------------------------------ append
+    @torch.no_grad()
+    def append(self, key_new: torch.Tensor, value_new: torch.Tensor):
+        """Append one decode token ([Z, Hk, 1, D]); a single kernel launch (kv_cache.py:227-257)."""
+        z, hk, sq, d = key_new.shape
+        assert sq == 1 and (z, hk, d) == (self.z, self.hk, self.d)
+        t = self.length
+        assert t < self.max_seq_len, "append exceeds capacity"
+        _lib.require_cuda(key_new, "key_new")
+        kn = key_new.reshape(self.zhk, d)
+        vn = value_new.reshape(self.zhk, d)
+        if kn.dtype != self.dtype or kn.stride(1) != 1:
+            kn = kn.to(self.dtype).contiguous()
+        if vn.dtype != self.dtype or vn.stride(1) != 1:
+            vn = vn.to(self.dtype).contiguous()
+        if kn.stride(0) != vn.stride(0):
+            kn, vn = kn.contiguous(), vn.contiguous()
+        ring = self.recent_window > 0
+        _lib.check(_lib.lib().nvfp4_kv_append(
+            kn.data_ptr(), vn.data_ptr(), _lib.dtype_code(self.dtype), kn.stride(0), self.zhk, d, t,
+            self.knv.data_ptr(), self.knv.stride(0), self.ksc.data_ptr(), self.ksc.stride(0),
+            self.vnv.data_ptr(), self.vnv.stride(0), self.vnv.stride(1),
+            self.vsc.data_ptr(), self.vsc.stride(0), self.vsc.stride(1),
+            self.v_partial_bf16.data_ptr(),
+            self.rk.data_ptr() if ring else None, self.rv.data_ptr() if ring else None,
+            self.ring_cap, _lib.stream_ptr(self.device)), "nvfp4_kv_append")
+        self.length = t + 1
+        self.partial_len = (t % self.GROUP) + 1
+        if self.partial_len == self.GROUP:
+            self.partial_len = 0
+
+    # ------------------------------------------------------------------ views
+    def get_packed(self) -> tuple:
+        """``(knv, ksc, vnv, vsc, s_kv, s_kv_pad)`` views of the live buffers (kv_cache.py:260-275)."""
+        return self._packed_upto(self.length, _check=False)
+
+    def _packed_upto(self, cut: int, _check: bool = True) -> tuple:
+        if _check:
+            assert cut % self.GROUP == 0, "cut must be a multiple of 16"
+        s_pad = _next_mult(cut, self.block_n)
+        return (self.knv[:, :cut], self.ksc[:, :cut], self.vnv[:, :, : s_pad // 2],
+                self.vsc[:, :, : s_pad // 16], cut, s_pad)
+
+    # ------------------------------------------------------------------ hybrid decode
+    @torch.no_grad()
+    def hybrid_decode(self, query: torch.Tensor, scaling: float, g: int) -> torch.Tensor:
+        """Recent-window bf16 attention + FP4 attention over the older prefix, merged by LSE.
+
+        Mirrors kv_cache.py:292-351: the split ``cut`` is rounded down to a 16-key boundary so no
+        V group is divided; the recent side covers positions ``[cut, length)``.
+        """
+        if self.recent_window <= 0:
+            raise RuntimeError("hybrid_decode needs recent_window > 0 "
+                               "(construct NVFP4KVCache with recent_window>0)")
+        if self.length == 0:
+            raise RuntimeError("hybrid_decode requires at least one token (call prefill/append first)")
+        z, h, _, d = query.shape
+        s = self.length
+        cut = (max(0, s - self.recent_window) // self.GROUP) * self.GROUP
+        w = s - cut
+        _lib.require_cuda(query, "query")
+        qv = query if query.stride(-1) == 1 else query.contiguous()
+        if qv.dtype != self.dtype:
+            qv = qv.to(self.dtype)
+        out_rec = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
+        lse_rec = torch.empty(z, h, dtype=torch.float32, device=query.device)
+        _lib.check(_lib.lib().nvfp4_window_attention(
+            qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
+            self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling),
+            out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(query.device)),
+            "nvfp4_window_attention")
+        if cut == 0:
+            return out_rec.reshape(z, h, 1, d).to(query.dtype)
+        out_old, lse_old = _flash._decode_prequant_with_lse(
+            query.float(), self._packed_upto(cut), scaling, g, block_n=self.block_n)
+        merged = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
+        _lib.check(_lib.lib().nvfp4_lse_merge(
+            out_old.reshape(z * h, d).data_ptr(), lse_old.data_ptr(), out_rec.data_ptr(),
+            lse_rec.data_ptr(), merged.data_ptr(), _lib.DT_FP32, z * h, d,
+            _lib.stream_ptr(query.device)), "nvfp4_lse_merge")
+        return merged.reshape(z, h, 1, d).to(query.dtype)
+
+    # ------------------------------------------------------------------ accounting
+    def fp4_bytes(self) -> int:
+        s = self.length
+        s_pad = _next_mult(s, self.block_n)
+        k = self.zhk * s * (self.d // 2) + self.zhk * s * (self.d // 16)
+        v = self.zhk * self.d * (s_pad // 2) + self.zhk * self.d * (s_pad // 16)
+        return k + v + self.partial_len * self.zhk * self.d * self.dtype.itemsize
+
+    def bf16_bytes(self) -> int:
+        return 2 * self.zhk * self.length * self.d * self.dtype.itemsize
+
+    def hybrid_bytes(self) -> int:
+        ring = 2 * self.zhk * self.ring_cap * self.d * self.dtype.itemsize if self.recent_window > 0 else 0
+        return self.fp4_bytes() + ring

@@ -1,0 +1,130 @@
+"""CUDA packer vs the CPU oracle and the reference fixtures: packed bytes must be bit-exact."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_bits_to_f32 as b2f
+from gpu_util import np_u8, seeded_bf16
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _nvfp4():
+    import sageattention_b200.nvfp4 as n
+    return n
+
+
+def _bits_to_cuda(bits):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).cuda()
+
+
+def test_golden_pack_bytes(golden):
+    g = golden("pack")
+    n = _nvfp4()
+    nib, sc = n._quant_nvfp4(_bits_to_cuda(g["x"]))
+    assert np.array_equal(np_u8(nib), g["nib"]) and np.array_equal(np_u8(sc), g["sc"])
+    vn, vs = n._quant_nvfp4(_bits_to_cuda(g["v"]), transpose=True, k_pad=128)
+    assert np.array_equal(np_u8(vn), g["vnib"]) and np.array_equal(np_u8(vs), g["vsc"])
+    sn, ss = n._quant_nvfp4(_bits_to_cuda(g["xs"]))
+    assert np.array_equal(np_u8(sn), g["snib"]) and np.array_equal(np_u8(ss), g["ssc"])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 33, 128), (1, 1, 16), (3, 7, 256), (1, 200, 64)])
+def test_rows_pack_matches_oracle(dtype, shape):
+    g = torch.Generator().manual_seed(hash((shape, str(dtype))) % 2 ** 31)
+    x = (torch.randn(*shape, generator=g) * 1.7).to(dtype)
+    nib, sc = _nvfp4()._quant_nvfp4(x.cuda())
+    onib, osc = O.pack(x.float().numpy())
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+
+
+@pytest.mark.parametrize("s,d,pad", [(45, 128, 128), (1, 128, 16), (300, 256, 384), (129, 64, 256),
+                                     (1024, 128, 1024)])
+def test_transposed_pack_matches_oracle(s, d, pad):
+    x, xf = seeded_bf16((2, s, d), seed=s * 7 + d)
+    nib, sc = _nvfp4()._quant_nvfp4(x, transpose=True, k_pad=pad)
+    onib, osc = O.pack(xf, transpose=True, k_pad=pad)
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+
+
+def test_strided_views_and_zshd_layout():
+    # [Z, S, H, D] storage viewed as [Z*H, S, D] heads (non-contiguous rows)
+    z, s, h, d = 2, 50, 3, 128
+    x, xf = seeded_bf16((z, s, h, d), seed=11)
+    view = x.permute(0, 2, 1, 3)[0]          # [H, S, D], row stride H*D
+    nib, sc = _nvfp4()._quant_nvfp4(view)
+    onib, osc = O.pack(np.transpose(xf, (0, 2, 1, 3))[0])
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+    # unaligned base pointer (offset by one element) falls back to scalar loads
+    flat = x.reshape(-1)[1: 1 + 4 * 128].reshape(1, 4, 128)
+    nib, sc = _nvfp4()._quant_nvfp4(flat)
+    onib, osc = O.pack(xf.reshape(-1)[1: 1 + 4 * 128].reshape(1, 4, 128))
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+
+
+def test_adversarial_values():
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], np.float32)
+    rows = []
+    for e in range(-12, 10):                      # every binade the scale can take
+        rows.append(np.concatenate([ties, -ties]) * np.float32(2.0 ** e))
+    x = np.stack(rows)[None].astype(np.float32)
+    x = np.concatenate([x, np.zeros_like(x), -np.zeros_like(x)], axis=1)
+    xt = torch.from_numpy(x).to(torch.bfloat16)
+    nib, sc = _nvfp4()._quant_nvfp4(xt.cuda())
+    onib, osc = O.pack(xt.float().numpy())
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+
+
+def test_exhaustive_bf16_inputs_against_oracle():
+    """Every finite bf16 bit pattern as the group's first element, with a fixed partner that
+    pins the scale, for a sweep of scales: the element quantiser is checked exhaustively."""
+    bits = np.arange(65536, dtype=np.uint16)
+    vals = b2f(bits)
+    finite = np.isfinite(vals)
+    bits = bits[finite]
+    n = bits.size
+    for partner in (6.0, 0.01171875, 3.0e-3, 448.0 * 6, 1.0e4, 0.7):
+        grp = np.zeros((1, n, 16), dtype=np.float32)
+        grp[0, :, 0] = b2f(bits)
+        grp[0, :, 1] = partner
+        xt = torch.from_numpy(grp).to(torch.bfloat16)
+        nib, sc = _nvfp4()._quant_nvfp4(xt.cuda())
+        onib, osc = O.pack(xt.float().numpy())
+        assert np.array_equal(np_u8(sc), osc), partner
+        assert np.array_equal(np_u8(nib), onib), partner
+
+
+def test_scale_floor_exact_and_positive():
+    # reference test: tests/test_nvfp4_attention.py:645-659
+    x = (torch.randn(1, 8, 128) * 1e-6).to(torch.bfloat16).cuda()
+    _, sc = _nvfp4()._quant_nvfp4(x)
+    assert float(sc.float().min()) == 2.0 ** -9 and bool((sc.float() > 0).all())
+
+
+def test_empty_and_errors():
+    n = _nvfp4()
+    nib, sc = n._quant_nvfp4(torch.empty(0, 4, 128, dtype=torch.bfloat16, device="cuda"))
+    assert nib.shape == (0, 4, 64) and sc.shape == (0, 4, 8)
+    with pytest.raises(AssertionError, match="multiple of 16"):
+        n._quant_nvfp4(torch.zeros(1, 2, 24, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        n._quant_nvfp4(torch.zeros(1, 2, 32, dtype=torch.bfloat16))
+
+
+def test_large_pack_roundtrip_property():
+    """Full-size property (C2's K tensor for one batch): dequantised values stay within half a
+    grid step of the input relative to the group scale, and re-packing the dequantised tensor
+    reproduces the same bytes (idempotence)."""
+    x = torch.randn(8, 8192, 128, device="cuda", dtype=torch.bfloat16)
+    n = _nvfp4()
+    nib, sc = n._quant_nvfp4(x)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device="cuda")
+    codes = torch.stack([nib & 15, nib >> 4], dim=-1).reshape(8, 8192, 128).long()
+    deq = lut[codes] * sc.float().repeat_interleave(16, dim=-1)
+    err = (deq - x.float()).abs() / sc.float().repeat_interleave(16, dim=-1)
+    assert float(err.max()) <= 1.0 + 1e-3      # widest e2m1 gap is 2 (4 -> 6): half of it
+    nib2, sc2 = n._quant_nvfp4(deq.to(torch.bfloat16))
+    assert torch.equal(nib2, nib) and torch.equal(sc2.view(torch.uint8), sc.view(torch.uint8))

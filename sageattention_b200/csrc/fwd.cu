@@ -1,9 +1,526 @@
-// Forward flash-attention kernel (placeholder while the kernel is being written).
+// NVFP4 flash-attention forward for sm_100a.
+//
+// One CTA owns a 128-row query tile of one (batch, head) and walks 128-key tiles:
+//     S[128 x 128]  = Q_tile . K_tile^T        tcgen05.mma kind::mxf4nvf4, e4m3 scale per 16
+//     P             = exp(S*scale - m) packed to NVFP4 per 16 keys (same scale rule as the packer)
+//     O[128 x D]   += P . V_tile               same MMA kind, V held as V^T (packed along keys)
+// Q/K/V^T nibble tiles arrive by TMA straight from the packed tensors; scale bytes are re-laid
+// into the 32x16-byte form tcgen05.cp expects by two loader warps; S and O live in TMEM.  One
+// thread owns one query row (one TMEM lane), so the per-16-key P pack needs no cross-thread
+// traffic.  The running maximum is exact (O is rescaled in TMEM whenever a row's maximum moves),
+// which keeps the P quantisation decisions those of a plain 128-key tile walk.
+//
+// Warp roles (256 threads): 0 TMA producer, 1 MMA issuer, 2 K-scale (+bias, +sample ids)
+// loader, 3 V-scale loader, 4-7 softmax / correction / epilogue.  Every barrier wait is bounded.
 #include "common/abi.cuh"
-extern "C" size_t nvfp4_fwd_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, int) { return 0; }
-extern "C" int nvfp4_fwd(const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*, const uint8_t*,
-                         const uint8_t*, const float*, const int32_t*, const int32_t*, void*, int, int64_t,
-                         int64_t, int64_t, float*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int,
-                         float, int, void*, size_t, int*, nvfp4_stream_t) {
-  return nvfp4::fail(-1, "nvfp4_fwd: kernel not built yet");
+#include "common/fp4.cuh"
+#include "common/sm100.cuh"
+#include "common/tma_host.cuh"
+
+namespace nvfp4 {
+
+constexpr int kFwdThreads = 256;
+constexpr float kFwdLog2e = 1.4426950408889634f;
+
+template <int D>
+struct FwdCfg {
+  static constexpr int KSUB = D / 128;  // 64-byte-wide sub-tiles of a Q/K row
+  static constexpr int KB = D / 64;     // K=64 MMAs per QK tile
+  static constexpr int NT = D / 128;    // 128-row pieces of the V^T tile (N of the PV MMA = D)
+  static constexpr int NSBUF = (D == 128) ? 2 : 1;  // S / P buffers
+  static constexpr int NSTAGE = (D == 128) ? 4 : 3;
+  static constexpr int Q_BYTES = KSUB * 8192;
+  static constexpr int K_BYTES = KSUB * 8192;
+  static constexpr int V_BYTES = NT * 8192;
+  static constexpr int KSF_BYTES = KB * 512;
+  static constexpr int VSF_BYTES = 2 * NT * 512;  // [kb][nt]
+  static constexpr int AUX_BYTES = 1024;          // 128 fp32 bias + 128 int32 sample ids
+  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + KSF_BYTES + VSF_BYTES + AUX_BYTES;
+  static constexpr int QSF_BYTES = KB * 512;
+  static constexpr int P_BYTES = 8192;
+  static constexpr int PSF_BYTES = 1024;
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + QSF_BYTES +
+                                    NSBUF * (P_BYTES + PSF_BYTES) + 1024;
+  // TMEM columns
+  static constexpr int T_S = 0;                       // NSBUF x 128
+  static constexpr int T_O = NSBUF * 128;             // D
+  static constexpr int T_SFQ = T_O + D;               // KB * 4
+  static constexpr int T_SFK = T_SFQ + KB * 4;        // 2 x KB * 4
+  static constexpr int T_SFP = T_SFK + 2 * KB * 4;    // 2 x 8
+  static constexpr int T_SFV = T_SFP + 16;            // 2 x (2 * NT * 4)
+  static constexpr int T_END = T_SFV + 2 * 2 * NT * 4;
+  static_assert(T_END <= 512, "TMEM budget exceeded");
+};
+
+struct FwdParams {
+  const uint8_t* qsc;  // [ZH, Sq, D/16]
+  const uint8_t* ksc;  // [ZHk, Skv, D/16]
+  const uint8_t* vsc;  // [ZHk, D, s_pad/16]
+  const float* bias;   // [Z, Skv] or null
+  const int32_t* seq_id;     // [S] or null
+  const int32_t* seq_start;  // [S] or null
+  void* out;
+  int64_t so_z, so_h, so_s;
+  float* lse;  // [ZH, Sq] or null
+  int h, hk, g;
+  int s_q, s_kv, s_pad;
+  float scaling;
+  int causal;
+  int* status;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D, typename TO>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+           const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using C = FwdCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* s_stage = smem;
+  uint8_t* s_q = s_stage + C::NSTAGE * C::STAGE_BYTES;
+  uint8_t* s_qsf = s_q + C::Q_BYTES;
+  uint8_t* s_p = s_qsf + C::QSF_BYTES;
+  uint8_t* s_psf = s_p + C::NSBUF * C::P_BYTES;
+
+  __shared__ uint64_t full_kv[C::NSTAGE], full_sf[C::NSTAGE], empty[C::NSTAGE];
+  __shared__ uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], q_full, qsf_full;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int err;
+  __shared__ int s_lo_tile;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mblk = gridDim.x - 1 - blockIdx.x;  // heaviest (last) query tiles first
+  const int zh = blockIdx.y;
+  const int zi = zh / p.h, hi = zh % p.h;
+  const int unit = zi * p.hk + hi / p.g;  // (batch, kv head)
+  const int m0 = mblk * 128;
+  const int shift = p.s_kv - p.s_q;  // bottom-right aligned causal offset
+
+  // key-tile range of this query tile
+  int hi_key = p.s_kv;
+  if (p.causal) hi_key = min(p.s_kv, m0 + 128 + shift);
+  if (hi_key < 0) hi_key = 0;
+  const int t_hi = (hi_key + 127) / 128;
+
+  if (tid == 0) {
+    err = 0;
+    for (int i = 0; i < C::NSTAGE; ++i) {
+      mbar_init(&full_kv[i], 1);
+      mbar_init(&full_sf[i], 2);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 128);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
+    }
+    mbar_init(&q_full, 1);
+    mbar_init(&qsf_full, 4);
+    mbar_fence_init();
+    int lo = 0;
+    if (p.seq_start != nullptr) lo = (p.seq_start[min(m0, p.s_q - 1)] / 128) * 128;
+    s_lo_tile = lo / 128;
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_s, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  // varlen: rows of a tile are sorted by sample, so the first row has the earliest start
+  const int t_lo = s_lo_tile;
+  const int ntile = max(t_hi - t_lo, 0);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && ntile > 0) {
+      mbar_expect_tx(&q_full, C::Q_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < C::KSUB; ++ks) tma_load_3d(s_q + ks * 8192, &tm_q, &q_full, ks * 64, m0, zh);
+      for (int i = 0; i < ntile; ++i) {
+        const int s = i % C::NSTAGE, t = t_lo + i;
+        if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 1);
+        uint8_t* st = s_stage + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full_kv[s], C::K_BYTES + C::V_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < C::KSUB; ++ks)
+          tma_load_3d(st + ks * 8192, &tm_k, &full_kv[s], ks * 64, t * 128, unit);
+#pragma unroll
+        for (int nt = 0; nt < C::NT; ++nt)
+          tma_load_3d(st + C::K_BYTES + nt * 8192, &tm_v, &full_kv[s], t * 64, nt * 128, unit);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------------ scale loaders
+    for (int i = 0; i < ntile; ++i) {
+      const int s = i % C::NSTAGE, t = t_lo + i;
+      if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 2);
+      uint8_t* st = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES;
+      if (warp == 2) {
+        const uint8_t* src = p.ksc + (int64_t)unit * p.s_kv * (D / 16);
+        float* aux_bias = reinterpret_cast<float*>(st + C::KSF_BYTES + C::VSF_BYTES);
+        int32_t* aux_seq = reinterpret_cast<int32_t*>(st + C::KSF_BYTES + C::VSF_BYTES + 512);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = lane + 32 * j;
+          const int key = t * 128 + r;
+          uint32_t wds[C::KB];
+#pragma unroll
+          for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
+          float bv = 0.0f;
+          int32_t sid = -1;
+          if (key < p.s_kv) {
+            const uint32_t* gsrc = reinterpret_cast<const uint32_t*>(src + (int64_t)key * (D / 16));
+#pragma unroll
+            for (int k = 0; k < C::KB; ++k) wds[k] = __ldg(gsrc + k);
+            if (p.bias != nullptr) bv = __ldg(p.bias + (int64_t)zi * p.s_kv + key);
+            if (p.seq_id != nullptr) sid = __ldg(p.seq_id + key);
+          }
+#pragma unroll
+          for (int k = 0; k < C::KB; ++k)
+            *reinterpret_cast<uint32_t*>(st + k * 512 + sf_atom_offset(r, 0)) = wds[k];
+          aux_bias[r] = bv;
+          aux_seq[r] = sid;
+        }
+      } else {
+        const uint8_t* src = p.vsc + (int64_t)unit * D * (p.s_pad / 16) + (int64_t)t * 8;
+        uint8_t* dst = st + C::KSF_BYTES;
+#pragma unroll
+        for (int j = 0; j < D / 32; ++j) {
+          const int dr = lane + 32 * j;
+          const uint2 v = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)dr * (p.s_pad / 16)));
+          const int nt = dr >> 7, r = dr & 127;
+          *reinterpret_cast<uint32_t*>(dst + (0 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = v.x;
+          *reinterpret_cast<uint32_t*>(dst + (1 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = v.y;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_sf[s]);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && ntile > 0) {
+      const uint32_t idesc_qk = make_idesc_nvfp4(128, 128);
+      const uint32_t idesc_pv = make_idesc_nvfp4(128, D);
+      mbar_wait(&q_full, 0, &err, 3);
+      mbar_wait(&qsf_full, 0, &err, 4);
+      tc_fence_after();
+#pragma unroll
+      for (int k = 0; k < C::KB; ++k)
+        tmem_cp_32x128b_warpx4(tmem + C::T_SFQ + k * 4, smem_u32(s_qsf + k * 512));
+      auto issue_qk = [&](int j) {
+        const int s = j % C::NSTAGE, b = j % C::NSBUF;
+        const uint32_t ph = (j / C::NSTAGE) & 1;
+        mbar_wait(&full_kv[s], ph, &err, 5);
+        mbar_wait(&full_sf[s], ph, &err, 6);
+        if (j >= C::NSBUF) mbar_wait(&s_free[b], ((j / C::NSBUF) & 1) ^ 1, &err, 7);
+        tc_fence_after();
+        uint8_t* st = s_stage + s * C::STAGE_BYTES;
+        const uint32_t sfk = tmem + C::T_SFK + (j & 1) * C::KB * 4;
+#pragma unroll
+        for (int k = 0; k < C::KB; ++k)
+          tmem_cp_32x128b_warpx4(sfk + k * 4, smem_u32(st + C::K_BYTES + C::V_BYTES + k * 512));
+#pragma unroll
+        for (int k = 0; k < C::KB; ++k) {
+          const uint64_t ad = make_smem_desc(smem_u32(s_q + (k >> 1) * 8192) + (k & 1) * 32, 16, 512, 4);
+          const uint64_t bd = make_smem_desc(smem_u32(st + (k >> 1) * 8192) + (k & 1) * 32, 16, 512, 4);
+          umma_nvfp4(tmem + C::T_S + b * 128, ad, bd, idesc_qk, tmem + C::T_SFQ + k * 4, sfk + k * 4,
+                     k > 0);
+        }
+        umma_commit(&s_full[b]);
+      };
+      issue_qk(0);
+      for (int i = 0; i < ntile; ++i) {
+        if (C::NSBUF == 2 && i + 1 < ntile) issue_qk(i + 1);
+        const int s = i % C::NSTAGE, b = i % C::NSBUF;
+        mbar_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
+        tc_fence_after();
+        uint8_t* st = s_stage + s * C::STAGE_BYTES;
+        const uint32_t sfp = tmem + C::T_SFP + (i & 1) * 8;
+        const uint32_t sfv = tmem + C::T_SFV + (i & 1) * (2 * C::NT * 4);
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          tmem_cp_32x128b_warpx4(sfp + k * 4, smem_u32(s_psf + b * C::PSF_BYTES + k * 512));
+#pragma unroll
+        for (int k = 0; k < 2 * C::NT; ++k)
+          tmem_cp_32x128b_warpx4(sfv + k * 4,
+                                 smem_u32(st + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + k * 512));
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint64_t ad = make_smem_desc(smem_u32(s_p + b * C::P_BYTES) + k * 32, 16, 512, 4);
+          const uint64_t bd = make_smem_desc(smem_u32(st + C::K_BYTES) + k * 32, 16, 512, 4);
+          umma_nvfp4(tmem + C::T_O, ad, bd, idesc_pv, sfp + k * 4, sfv + k * C::NT * 4,
+                     (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&pv_done[b]);
+        umma_commit(&empty[s]);
+        if (C::NSBUF == 1 && i + 1 < ntile) issue_qk(i + 1);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int wq = warp - 4;
+    const int row_in = tid - 128;        // row within the query tile
+    const int row = m0 + row_in;         // query index
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    // Q scale bytes -> A-operand scale atoms
+    {
+      uint32_t wds[C::KB];
+#pragma unroll
+      for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
+      if (row < p.s_q) {
+        const uint32_t* gsrc =
+            reinterpret_cast<const uint32_t*>(p.qsc + ((int64_t)zh * p.s_q + row) * (D / 16));
+#pragma unroll
+        for (int k = 0; k < C::KB; ++k) wds[k] = __ldg(gsrc + k);
+      }
+#pragma unroll
+      for (int k = 0; k < C::KB; ++k)
+        *reinterpret_cast<uint32_t*>(s_qsf + k * 512 + sf_atom_offset(row_in, 0)) = wds[k];
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qsf_full);
+    }
+    const int my_seq = (p.seq_id != nullptr) ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    const int my_limit = p.causal ? (row + shift) : (p.s_kv - 1);  // last visible key index
+    const float c2 = p.scaling * kFwdLog2e;
+    float m_run = -INFINITY, l_run = 0.0f;
+
+    for (int i = 0; i < ntile; ++i) {
+      const int b = i % C::NSBUF, s = i % C::NSTAGE, t = t_lo + i;
+      const int n0 = t * 128;
+      mbar_wait(&s_full[b], (i / C::NSBUF) & 1, &err, 9);
+      tc_fence_after();
+      float sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_addr + C::T_S + b * 128 + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sv[c * 32 + e] = __uint_as_float(r[e]);
+      }
+      tc_fence_before();
+      mbar_arrive(&s_free[b]);
+
+      // scores in log2 units; masks only where a tile can need them
+      const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
+                           C::VSF_BYTES;
+      const float* aux_bias = reinterpret_cast<const float*>(aux);
+      const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512);
+      const bool tile_masked = (n0 + 127 > m0 + shift && p.causal) || (n0 + 128 > p.s_kv) ||
+                               (p.bias != nullptr) || (p.seq_id != nullptr);
+      float mx = -INFINITY;
+      if (tile_masked) {
+#pragma unroll
+        for (int e = 0; e < 128; ++e) {
+          float v = sv[e] * c2;
+          if (p.bias != nullptr) v += aux_bias[e] * kFwdLog2e;
+          const int key = n0 + e;
+          bool ok = key <= my_limit && key < p.s_kv;
+          if (p.seq_id != nullptr) ok = ok && (aux_seq[e] == my_seq);
+          v = ok ? v : -INFINITY;
+          sv[e] = v;
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 128; ++e) {
+          sv[e] *= c2;
+          mx = fmaxf(mx, sv[e]);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_sf = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = ex2_approx(m_run - m_sf);
+      const bool changed = (m_new > m_run) && (i > 0);
+      m_run = m_new;
+
+      // P buffer b must have been consumed by the PV of tile i - NSBUF
+      if (i >= C::NSBUF) mbar_wait(&pv_done[b], ((i / C::NSBUF) & 1) ^ 1, &err, 10);
+      uint8_t* pt = s_p + b * C::P_BYTES;
+      uint8_t* psf = s_psf + b * C::PSF_BYTES;
+      float lsum = 0.0f;
+      uint32_t scw[2] = {0u, 0u};
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float pe[16];
+        float am = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          pe[e] = ex2_approx(sv[g * 16 + e] - m_sf);
+          lsum += pe[e];
+          am = fmaxf(am, pe[e]);
+        }
+        const uint8_t sb = scale_byte_from_amax(am);
+        const float inv = __frcp_rn(e4m3_to_f32(sb));
+        const uint32_t lo = e2m1x8(pe[0] * inv, pe[1] * inv, pe[2] * inv, pe[3] * inv, pe[4] * inv,
+                                   pe[5] * inv, pe[6] * inv, pe[7] * inv);
+        const uint32_t hi2 = e2m1x8(pe[8] * inv, pe[9] * inv, pe[10] * inv, pe[11] * inv,
+                                    pe[12] * inv, pe[13] * inv, pe[14] * inv, pe[15] * inv);
+        *reinterpret_cast<uint2*>(pt + sw64_offset(row_in, g * 8)) = make_uint2(lo, hi2);
+        scw[g >> 2] |= (uint32_t)sb << (8 * (g & 3));
+      }
+      *reinterpret_cast<uint32_t*>(psf + 0 * 512 + sf_atom_offset(row_in, 0)) = scw[0];
+      *reinterpret_cast<uint32_t*>(psf + 1 * 512 + sf_atom_offset(row_in, 0)) = scw[1];
+      l_run = l_run * alpha + lsum;
+
+      if (__any_sync(0xffffffffu, changed)) {
+        // O of this warp's 32 rows is rescaled once the previous PV has landed
+        const int pb = (i - 1) % C::NSBUF;
+        mbar_wait(&pv_done[pb], ((i - 1) / C::NSBUF) & 1, &err, 11);
+        tc_fence_after();
+        const float a = changed ? alpha : 1.0f;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_addr + C::T_O + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * a);
+          tmem_st32(tmem + lane_addr + C::T_O + c * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[b]);
+    }
+
+    // ---- epilogue: O / l -> out, LSE
+    TO* orow = nullptr;
+    if (row < p.s_q)
+      orow = static_cast<TO*>(p.out) + (int64_t)zi * p.so_z + (int64_t)hi * p.so_h + (int64_t)row * p.so_s;
+    if (ntile > 0) {
+      const int last = ntile - 1;
+      mbar_wait(&pv_done[last % C::NSBUF], (last / C::NSBUF) & 1, &err, 12);
+      tc_fence_after();
+      const float inv_l = (l_run == 0.0f) ? 1.0f : __frcp_rn(l_run);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_addr + C::T_O + c * 32, r);
+        tmem_ld_wait();
+        if (orow != nullptr) {
+          if constexpr (sizeof(TO) == 2) {
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const TO a0 = from_f32<TO>(__uint_as_float(r[2 * e]) * inv_l);
+              const TO a1 = from_f32<TO>(__uint_as_float(r[2 * e + 1]) * inv_l);
+              w[e] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&a0)) |
+                     ((uint32_t)(*reinterpret_cast<const uint16_t*>(&a1)) << 16);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+          } else {
+            float4* dst = reinterpret_cast<float4*>(orow + c * 32);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              dst[e] = make_float4(__uint_as_float(r[4 * e]) * inv_l, __uint_as_float(r[4 * e + 1]) * inv_l,
+                                   __uint_as_float(r[4 * e + 2]) * inv_l, __uint_as_float(r[4 * e + 3]) * inv_l);
+          }
+        }
+      }
+      tc_fence_before();
+    } else if (orow != nullptr) {
+      for (int e = 0; e < D; ++e) orow[e] = from_f32<TO>(0.0f);
+    }
+    if (p.lse != nullptr && row < p.s_q) {
+      const float l_safe = (l_run == 0.0f) ? 1.0f : l_run;
+      const float m_fin = (m_run == -INFINITY) ? 0.0f : m_run;
+      p.lse[(int64_t)zh * p.s_q + row] = m_fin * 0.6931471805599453f + logf(l_safe);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && err != 0 && p.status != nullptr) atomicExch(p.status, err);
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+template <int D, typename TO>
+int fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+               const FwdParams& p, int64_t zh, cudaStream_t st) {
+  using C = FwdCfg<D>;
+  auto kern = fwd_kernel<D, TO>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return fail((int)e, "nvfp4_fwd: smem attribute: %s", cudaGetErrorString(e));
+  dim3 grid((unsigned)((p.s_q + 127) / 128), (unsigned)zh);
+  kern<<<grid, kFwdThreads, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  return launch_result("nvfp4_fwd");
+}
+
+}  // namespace nvfp4
+
+extern "C" size_t nvfp4_fwd_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, int) {
+  return 0;
+}
+
+extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv,
+                         const uint8_t* ksc, const uint8_t* vnv, const uint8_t* vsc,
+                         const float* bias, const int32_t* seq_id, const int32_t* seq_start,
+                         void* out, int out_dtype, int64_t so_z, int64_t so_h, int64_t so_s,
+                         float* lse, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
+                         int64_t s_pad, int d, float scaling, int flags, void* workspace,
+                         size_t workspace_bytes, int* status, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  (void)workspace; (void)workspace_bytes;
+  NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_fwd: D must be 128 or 256");
+  NVFP4_REQUIRE(z >= 1 && h >= 1 && hk >= 1 && h % hk == 0, "nvfp4_fwd: bad head counts");
+  NVFP4_REQUIRE(s_q >= 1 && s_kv >= 1, "nvfp4_fwd: empty sequence");
+  NVFP4_REQUIRE(s_pad % 128 == 0 && s_pad >= s_kv, "nvfp4_fwd: s_pad must be a multiple of 128 >= s_kv");
+  NVFP4_REQUIRE(qnv && qsc && knv && ksc && vnv && vsc && out, "nvfp4_fwd: null pointer");
+  NVFP4_REQUIRE((seq_id == nullptr) == (seq_start == nullptr), "nvfp4_fwd: seq_id/seq_start go together");
+  NVFP4_REQUIRE(seq_id == nullptr || (z == 1 && s_q == s_kv), "nvfp4_fwd: varlen needs Z == 1 and Sq == Skv");
+  NVFP4_REQUIRE(z * h < 65536, "nvfp4_fwd: Z*H must be < 65536");
+  NVFP4_REQUIRE(s_q < (1LL << 30) && s_kv < (1LL << 30), "nvfp4_fwd: sequence too long");
+  const size_t esz = out_dtype == NVFP4_DT_FP32 ? 4 : 2;
+  NVFP4_REQUIRE(((uintptr_t)out % 16) == 0 && (so_z * esz) % 16 == 0 && (so_h * esz) % 16 == 0 &&
+                    (so_s * esz) % 16 == 0,
+                "nvfp4_fwd: out must be 16-byte aligned with 16-byte-multiple strides");
+  NVFP4_REQUIRE(((uintptr_t)qsc % 4) == 0 && ((uintptr_t)ksc % 4) == 0 && ((uintptr_t)vsc % 8) == 0,
+                "nvfp4_fwd: scale tensors must be aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t zh = z * h, zhk = z * hk;
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_u8_3d_sw64(&tq, qnv, d / 2, s_q, zh, d / 2, (uint64_t)s_q * (d / 2), 128, "nvfp4_fwd(Q)");
+  if (rc) return rc;
+  rc = make_tmap_u8_3d_sw64(&tk, knv, d / 2, s_kv, zhk, d / 2, (uint64_t)s_kv * (d / 2), 128, "nvfp4_fwd(K)");
+  if (rc) return rc;
+  rc = make_tmap_u8_3d_sw64(&tv, vnv, s_pad / 2, d, zhk, s_pad / 2, (uint64_t)d * (s_pad / 2), 128, "nvfp4_fwd(V)");
+  if (rc) return rc;
+  FwdParams p;
+  p.qsc = qsc; p.ksc = ksc; p.vsc = vsc; p.bias = bias; p.seq_id = seq_id; p.seq_start = seq_start;
+  p.out = out; p.so_z = so_z; p.so_h = so_h; p.so_s = so_s; p.lse = lse;
+  p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk);
+  p.s_q = (int)s_q; p.s_kv = (int)s_kv; p.s_pad = (int)s_pad;
+  p.scaling = scaling; p.causal = (flags & NVFP4_FWD_CAUSAL) ? 1 : 0; p.status = status;
+#define NVFP4_FWD(DD, T) return fwd_launch<DD, T>(tq, tk, tv, p, zh, st)
+  if (d == 128) {
+    switch (out_dtype) {
+      case NVFP4_DT_BF16: NVFP4_FWD(128, __nv_bfloat16);
+      case NVFP4_DT_FP16: NVFP4_FWD(128, __half);
+      case NVFP4_DT_FP32: NVFP4_FWD(128, float);
+    }
+  } else {
+    switch (out_dtype) {
+      case NVFP4_DT_BF16: NVFP4_FWD(256, __nv_bfloat16);
+      case NVFP4_DT_FP16: NVFP4_FWD(256, __half);
+      case NVFP4_DT_FP32: NVFP4_FWD(256, float);
+    }
+  }
+#undef NVFP4_FWD
+  return fail(-1, "nvfp4_fwd: unknown out dtype %d", out_dtype);
 }

@@ -1,0 +1,386 @@
+"""Benchmark of the NVFP4 attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (BASELINE config 2, "prefill forward"): Z=4, H=32, Hk=8, S=8192, D=128, causal,
+bf16 Q/K/V ~ N(0,1) with a constant offset ~ N(0, sigma=2) on 8 random K channels, scaling
+1/sqrt(128).  One step = one `nvfp4_flash_attention` call = NVFP4 pack of Q, K (along D) and V
+(along keys) + the tcgen05 forward kernel.  FLOPs per step = 4*Z*H*S^2*D/2 = 2.199e12 (the pack
+is counted in time, not in FLOPs).
+
+Printed JSON (one line, rank 0):
+  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e        same metric through the public API with pinned HOST buffers: H2D of q,k,v and D2H
+             of the output inside the timed region
+  roofline   the forward kernel alone (CUDA events around it on its stream) against the tensor
+             peak; also the MUFU co-bound that actually limits a D=128 FP4 forward
+  secondary  HBM rooflines of the decode step (config 4) and of the packer
+  cpu_baseline  the CPU oracle (a port of the reference arithmetic) on a bounded sample
+
+With N > 1 (torchrun) every rank owns its own (batch, KV-group) shard of the same size: no
+collective on the data path, "weak" scaling.  `--impl reference` times the CPU oracle port.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Z, H, HK, S, D = 4, 32, 8, 8192, 128
+FLOPS_PER_STEP = 4.0 * Z * H * S * S * D / 2.0
+WORKLOAD = "prefill_fwd Z4 H32 Hk8 S8192 D128 causal bf16 (BASELINE config 2)"
+
+
+def _measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if mx and x > 0.5 * mx] or sm
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_sample(heads: int = 4, s: int = S):
+    """The oracle (mode B: the reference's arithmetic, numpy on the host cores) on a bounded
+    sample of the workload: `heads` query heads sharing one KV head, causal, D=128.  The default
+    (4 heads, S=8192) is exactly one (batch, KV-group) unit of the 32 units in a step."""
+    from oracle import nvfp4_oracle as O
+    rng = np.random.default_rng(0)
+    bf = lambda a: (a.astype(np.float32).view(np.uint32) & 0xFFFF0000).view(np.float32)
+    q = bf(rng.standard_normal((1, heads, s, D))); k = bf(rng.standard_normal((1, 1, s, D)))
+    v = bf(rng.standard_normal((1, 1, s, D)))
+    t0 = time.perf_counter()
+    O.attention_mode_b(q, k, v, D ** -0.5, True, heads)
+    dt = time.perf_counter() - t0
+    flops = heads * 4.0 * s * s * D / 2.0
+    return flops / dt / 1e12, dt, (f"oracle mode B (numpy), {heads} query head(s) on 1 KV head, S={s}, "
+                                   f"D={D}, causal ({flops / 1e9:.1f} GFLOP)")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        v, dt, sample = cpu_sample(heads=1, s=4096)
+        if i >= args.warmup:
+            vals.append((v, dt))
+    val = float(np.mean([v for v, _ in vals]))
+    ms = float(np.mean([dt for _, dt in vals])) * 1e3
+    line = {
+        "impl": "reference", "metric": "fp4_attn_fwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4, fp32 acc",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "each step = bounded sample below"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def make_inputs(torch, seed, device):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(Z, H, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32)
+    ch = torch.randperm(D, generator=g)[:8]
+    k[..., ch] += torch.randn(8, generator=g) * 2.0   # "N(0,4)" read as variance 4, sigma 2
+    k = k.to(torch.bfloat16)
+    v = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return q, k, v
+
+
+def ev_ms(torch, fn, iters):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def secondary_metrics(torch, nv, peaks):
+    """Decode step (BASELINE config 4) and packer, both HBM-bound, timed with CUDA events."""
+    out = []
+    dev = "cuda"
+    z, h, hk, s, d = 16, 32, 8, 32768, 128
+    cache = nv.NVFP4KVCache(z, hk, d, s + 128, dev)
+    g = torch.Generator(device=dev).manual_seed(4)
+    k = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
+    v = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
+    cache.prefill(k, v)
+    del k, v
+    q = torch.randn(z, h, 1, d, device=dev, dtype=torch.bfloat16, generator=g)
+    kn = torch.randn(z, hk, 1, d, device=dev, dtype=torch.bfloat16, generator=g)
+    packed = cache.get_packed()
+    bytes_step = z * hk * (s * (d // 2 + d // 16) + d * (s // 2 + s // 16))
+    step = lambda: nv.nvfp4_flash_decode_prequant(q, packed, d ** -0.5, h // hk)
+    for _ in range(5):
+        step()
+    ms = ev_ms(torch, step, 50)
+    gbs = bytes_step / (ms * 1e-3) / 1e9
+    app = lambda: (cache.append(kn, kn), setattr(cache, "length", s), setattr(cache, "partial_len", 0))
+    for _ in range(3):
+        app()
+    ms_app = ev_ms(torch, app, 50)
+    out.append({"name": "decode_step Z16 H32 Hk8 D128 S32768 (BASELINE config 4)",
+                "step_us": ms * 1e3, "append_us": ms_app * 1e3,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                             "algorithmic_bytes": bytes_step}})
+    del cache, packed
+    torch.cuda.empty_cache()
+    x = torch.randn(Z * H, S, D, device=dev, dtype=torch.bfloat16)
+    pk = lambda: nv._quant_nvfp4(x)
+    for _ in range(3):
+        pk()
+    ms = ev_ms(torch, pk, 20)
+    b = x.numel() * (2 + 0.5625)
+    gbs = b / (ms * 1e-3) / 1e9
+    out.append({"name": "pack Q [128, 8192, 128] bf16 along D", "ms": ms,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": b}})
+    return out
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import sageattention_b200.nvfp4 as nv
+    from sageattention_b200 import _lib
+    from sageattention_b200.nvfp4 import flash
+    _lib.lib()   # fails loudly if the CUDA library is missing
+    peaks, peak_src = _measured_peaks()
+
+    # each rank owns its own (batch, KV-group) shard of the full size: no data-path collective
+    qh, kh, vh = make_inputs(torch, 1234 + rank, dev)
+    qh, kh, vh = qh.pin_memory(), kh.pin_memory(), vh.pin_memory()
+    q, k, v = qh.to(dev), kh.to(dev), vh.to(dev)
+    scaling = D ** -0.5
+    step = lambda: nv.nvfp4_flash_attention(q, k, v, scaling, causal=True, num_key_value_groups=H // HK)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for _ in range(args.steps):
+        out = step()
+    b.record()
+    barrier()
+    ms = a.elapsed_time(b) / args.steps
+    status = _lib.read_status(dev)
+
+    # forward kernel alone (operands packed once): the roofline kernel
+    s_pad = S
+    qnv, qsc = nv._quant_nvfp4(q.reshape(Z * H, S, D))
+    knv, ksc = nv._quant_nvfp4(k.reshape(Z * HK, S, D))
+    vnv, vsc = nv._quant_nvfp4(v.reshape(Z * HK, S, D), transpose=True, k_pad=s_pad)
+    kern = lambda: flash._run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, Z, H, HK, S, S, D, scaling,
+                                           torch.bfloat16, causal=True)
+    for _ in range(3):
+        kern()
+    torch.cuda.synchronize()
+    ms_kernel = ev_ms(torch, kern, args.steps)
+
+    # end to end: pinned host buffers in, output back to pinned host memory, every step
+    out_h = torch.empty(Z, H, S, D, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        qd, kd, vd = qh.to(dev, non_blocking=True), kh.to(dev, non_blocking=True), vh.to(dev, non_blocking=True)
+        o = nv.nvfp4_flash_attention(qd, kd, vd, scaling, causal=True, num_key_value_groups=H // HK)
+        out_h.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    barrier()
+    ms_e2e = a.elapsed_time(b) / e2e_steps
+    # keep the GPU busy long enough for a few 100 ms clock samples, then stop the sampler
+    t_end = time.time() + 1.0
+    while rank == 0 and time.time() < t_end:
+        kern()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms, ms_kernel, ms_e2e], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_kernel, ms_e2e = (float(x) for x in t.tolist())
+
+    if rank == 0:
+        # correctness spot check against fp32 attention on one head (not timed)
+        ref = torch.nn.functional.scaled_dot_product_attention(
+            q[:1, :1].float(), k[:1, :1].float(), v[:1, :1].float(), is_causal=True)
+        cosv = float(torch.nn.functional.cosine_similarity(out[:1, :1].float().flatten(), ref.flatten(), dim=0))
+        secondary = secondary_metrics(torch, nv, peaks) if world == 1 else []
+        cpu_v, cpu_dt, cpu_sample_desc = cpu_sample() if world == 1 else (None, None, None)
+        tflops = world * FLOPS_PER_STEP / (ms * 1e-3) / 1e12
+        k_tflops = FLOPS_PER_STEP / (ms_kernel * 1e-3) / 1e12
+        fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+        exps = Z * H * S * S / 2.0
+        line = {
+            "metric": "fp4_attn_fwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp4(e2m1, e4m3 scale per 16) x fp4, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_shard": f"Z{Z} H{H} Hk{HK} S{S} D{D}",
+                       "parallelism": f"(batch,kv-group) shards x{world}, no collective",
+                       "l2": "inputs (402 MB bf16 + 101 MB packs) larger than the 126 MB L2",
+                       "k_outliers": "8 channels, offset sigma=2 (variance 4)"},
+            "roofline": {"bound": "tensor", "achieved": k_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
+                         "frac": k_tflops / fp4_peak, "traffic": None,
+                         "kernel": "fwd_kernel<128,bf16>", "kernel_ms": ms_kernel,
+                         "peak_source": f"4 x bf16_tflops_sustained ({peak_src} MEASURED_PEAKS.json); "
+                                        "no FP4 GEMM figure is in that file",
+                         "co_bound": {"what": "MUFU ex2 + cvt.e2m1x2 share a 16 lane/clk/SM pipe: 1.5 slots "
+                                              "per score element",
+                                      "elements": exps,
+                                      "min_ms_at_1.9GHz": exps * 1.5 / (148 * 16 * 1.9e9) * 1e3}},
+            "e2e": {"value": world * FLOPS_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": int((qh.numel() + kh.numel() + vh.numel()) * 2),
+                    "d2h_bytes_per_step": int(out_h.numel() * 2)},
+            "gpu_launches": 4 * args.steps,
+            "clocks": clocks, "kernel_status": status, "cosine_vs_fp32_sdpa_head0": cosv,
+            "secondary": secondary,
+        }
+        if cpu_v is not None:
+            line["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                                    "kind": "port", "sample": cpu_sample_desc, "seconds": cpu_dt}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_profile_case(args):
+    """Small single-kernel cases for `ncu` captures (a few launches, bounded memory)."""
+    import torch
+    import sageattention_b200.nvfp4 as nv
+    from sageattention_b200 import _lib
+    dev = "cuda"
+    case = args.profile_case
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
+    if case == "fwd":          # Z1 H32 Hk8 S4096 D128 causal: 0.137 TFLOP per launch
+        q, k, v = rn(1, 32, 4096, 128), rn(1, 8, 4096, 128), rn(1, 8, 4096, 128)
+        fn = lambda: nv.nvfp4_flash_attention(q, k, v, 128 ** -0.5, causal=True, num_key_value_groups=4)
+    elif case == "fwd_d256":
+        q, k, v = rn(1, 16, 4096, 256), rn(1, 4, 4096, 256), rn(1, 4, 4096, 256)
+        fn = lambda: nv.nvfp4_flash_attention(q, k, v, 256 ** -0.5, causal=True, num_key_value_groups=4)
+    elif case == "decode":     # Z16 Hk8 S8192: 151 MB of packs per launch (larger than L2)
+        cache = nv.NVFP4KVCache(16, 8, 128, 8192, dev)
+        cache.prefill(rn(16, 8, 8192, 128), rn(16, 8, 8192, 128))
+        q = rn(16, 32, 1, 128)
+        packed = cache.get_packed()
+        fn = lambda: nv.nvfp4_flash_decode_prequant(q, packed, 128 ** -0.5, 4)
+    elif case == "pack":       # 64 x 8192 x 128 bf16: 172 MB read+written per launch
+        x = rn(64, 8192, 128)
+        fn = lambda: (nv._quant_nvfp4(x), nv._quant_nvfp4(x, transpose=True))
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    for _ in range(args.steps):
+        fn()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "launch_groups": args.steps, "status": _lib.read_status(dev)}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "fwd_d256", "decode", "pack"],
+                    help="run one small kernel case --steps times (for ncu) and exit")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -106,6 +106,35 @@ int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, const u
                  int64_t split_kv, int* status, nvfp4_stream_t stream);
 
 /*
+ * nvfp4_decode for callers that cannot provide scratch memory.  (No counterpart in the
+ * reference: its decode allocates its split-K partials with torch on every call.)
+ *
+ * Who needs it: a host that pre-partitioned the GPU into its own pools and forbids allocation
+ * at request time (an inference server with a fixed memory plan, a plugin inside a process
+ * whose allocator it must not touch).  The split-K partials live in a 16 MiB array that is part
+ * of the library image, so every GPU that loads the library holds those 16 MiB until the
+ * process exits.  Arguments are those of nvfp4_decode without the workspace; inputs and
+ * outputs are still the caller's.  The call allocates nothing (no cudaMalloc / cudaFree, no
+ * allocating library routine).
+ *
+ *  - Limit: Z*Hk*nsplit*(16*D + 32)*4 bytes must fit in nvfp4_decode_static_capacity()
+ *    (16 MiB); larger problems are rejected with a message -- pass a larger split_kv (fewer
+ *    splits) or use nvfp4_decode.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  The kernel overwrites every partial it later
+ *    reads, so nothing has to be cleared between calls, but two calls whose kernels overlap on
+ *    the GPU (different streams) race on it: serialise them.
+ */
+size_t nvfp4_decode_static_capacity(void);
+int nvfp4_decode_static(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, const uint8_t* knv,
+                        int64_t knv_unit, const uint8_t* ksc, int64_t ksc_unit, const uint8_t* vnv,
+                        int64_t vnv_unit, int64_t vnv_row, const uint8_t* vsc, int64_t vsc_unit,
+                        int64_t vsc_row, int64_t z, int64_t hk, int g, int d, int64_t s_kv,
+                        float scaling, void* out, float* lse, int nsplit, int64_t split_kv,
+                        int* status, nvfp4_stream_t stream);
+
+/*
  * Exact merge of two attention results over disjoint key sets from their log-sum-exps:
  * out = (e^{lse1-m} o1 + e^{lse2-m} o2) / (e^{lse1-m} + e^{lse2-m}).  Replaces the torch
  * expressions of NVFP4KVCache.hybrid_decode (kv_cache.py:346-351).  o1,o2,out: [rows, d] in

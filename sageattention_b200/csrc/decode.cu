@@ -560,3 +560,68 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
 #undef NVFP4_DECODE
   return fail(-1, "nvfp4_decode: unknown dtype %d", q_dtype);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode without any allocation by the caller or the library.
+//
+// Some hosts of this library cannot hand it scratch memory: a serving runtime that carved up the
+// whole device into its own pools at start-up and forbids later cudaMalloc calls (every byte is
+// accounted for, and an allocation at request time could fail or stall the device), or a plugin
+// loaded by a process whose allocator the plugin must not touch.  For those callers the split-K
+// partials live in a fixed array that is part of the library image on every GPU that loads it.
+// ---------------------------------------------------------------------------------------------
+namespace nvfp4 {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;  // 16 MiB per GPU, held until exit
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch on the CURRENT device; looked up once per device.
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "nvfp4_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(-1, "nvfp4_decode_static: device index %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(e != cudaSuccess ? (int)e : -1, "nvfp4_decode_static: cudaGetSymbolAddress: %s",
+                  cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace nvfp4
+
+extern "C" size_t nvfp4_decode_static_capacity(void) { return nvfp4::kStaticScratchBytes; }
+
+extern "C" int nvfp4_decode_static(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh,
+                                   const uint8_t* knv, int64_t knv_unit, const uint8_t* ksc,
+                                   int64_t ksc_unit, const uint8_t* vnv, int64_t vnv_unit,
+                                   int64_t vnv_row, const uint8_t* vsc, int64_t vsc_unit,
+                                   int64_t vsc_row, int64_t z, int64_t hk, int g, int d,
+                                   int64_t s_kv, float scaling, void* out, float* lse, int nsplit,
+                                   int64_t split_kv, int* status, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_decode_static: D must be 128 or 256");
+  NVFP4_REQUIRE(z >= 1 && hk >= 1 && nsplit >= 1, "nvfp4_decode_static: empty problem");
+  const size_t need = (size_t)(z * hk) * (size_t)nsplit * (size_t)(16 * d + 32) * sizeof(float);
+  if (need > kStaticScratchBytes)
+    return fail(-1,
+                "nvfp4_decode_static: this problem needs %zu bytes of split-K scratch but the static "
+                "array holds %zu; use fewer splits (larger split_kv) or nvfp4_decode with a workspace",
+                need, kStaticScratchBytes);
+  void* ws = nullptr;
+  const int rc = static_scratch_address(&ws);
+  if (rc) return rc;
+  return nvfp4_decode(q, q_dtype, s_qz, s_qh, knv, knv_unit, ksc, ksc_unit, vnv, vnv_unit, vnv_row,
+                      vsc, vsc_unit, vsc_row, z, hk, g, d, s_kv, scaling, out, lse, ws,
+                      kStaticScratchBytes, nsplit, split_kv, status, stream);
+}

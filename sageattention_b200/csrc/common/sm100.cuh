@@ -21,7 +21,7 @@ enum : int {
 };
 
 #ifndef NVFP4_WAIT_SPINS
-#define NVFP4_WAIT_SPINS (1u << 22)
+#define NVFP4_WAIT_SPINS (1u << 20)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -53,14 +53,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One potentially-blocking probe: the hardware may park the thread until the phase completes or
+// the hint (ns) runs out, so a waiting warp costs few issue slots.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, P;\n\t}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
       : "memory");
   return ok != 0;
 }
@@ -68,10 +70,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `err` is a CTA-shared int (0 = healthy). Returns false on timeout.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err,
                                           int site) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*err) return false;
   for (uint32_t i = 0; i < NVFP4_WAIT_SPINS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *err) return false;
+    if (*err) return false;
   }
   *err = KSTAT_WAIT_TIMEOUT | site;
   return false;
@@ -85,6 +88,22 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // generic-proxy writes (st.shared) -> visible to the async proxy (TMA / tcgen05 reads of smem)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// shared-memory accesses by 32-bit shared address (keeps them out of the generic path)
+__device__ __forceinline__ void sts_v2(uint32_t saddr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(saddr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts_b32(uint32_t saddr, uint32_t a) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(saddr), "r"(a) : "memory");
+}
+__device__ __forceinline__ void sts_f32(uint32_t saddr, float a) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(saddr), "f"(a) : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t saddr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr) : "memory");
+  return v;
 }
 
 // ------------------------------------------------------------------ TMA

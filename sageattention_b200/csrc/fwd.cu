@@ -6,12 +6,14 @@
 //     O[128 x D]   += P . V_tile               same MMA kind, V held as V^T (packed along keys)
 // Q/K/V^T nibble tiles arrive by TMA straight from the packed tensors; scale bytes are re-laid
 // into the 32x16-byte form tcgen05.cp expects by two loader warps; S and O live in TMEM.  One
-// thread owns one query row (one TMEM lane), so the per-16-key P pack needs no cross-thread
-// traffic.  The running maximum is exact (O is rescaled in TMEM whenever a row's maximum moves),
+// thread owns a slice of one query row (one TMEM lane, 32 or 64 key columns), so the
+// per-16-key P pack needs no cross-thread traffic.  The running maximum is exact (O is rescaled in TMEM whenever a row's maximum moves),
 // which keeps the P quantisation decisions those of a plain 128-key tile walk.
 //
-// Warp roles (256 threads): 0 TMA producer, 1 MMA issuer, 2 K-scale (+bias, +sample ids)
-// loader, 3 V-scale loader, 4-7 softmax / correction / epilogue.  Every barrier wait is bounded.
+// Warp roles (640 threads): 0 TMA producer, 1 QK^T issuer, 2 scale loader (+bias, +sample
+// ids), 3 PV issuer, 4-19 softmax / correction / epilogue.  At D=128 the sixteen softmax warps
+// form two groups that alternate key tiles; at D=256 (one S buffer) they share each tile.
+// Every barrier wait is bounded.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
 #include "common/sm100.cuh"
@@ -19,7 +21,11 @@
 
 namespace nvfp4 {
 
-constexpr int kFwdThreads = 256;
+#ifndef NVFP4_FWD_NP
+#define NVFP4_FWD_NP 4
+#endif
+constexpr int kFwdNP = NVFP4_FWD_NP;               // softmax threads per query row (D = 256 path)
+constexpr int kFwdThreads = 128 + 128 * kFwdNP;
 constexpr float kFwdLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -69,6 +75,12 @@ struct FwdParams {
   int* status;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -94,6 +106,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
   __shared__ int s_lo_tile;
+  __shared__ float xmax[2][kFwdNP][128];
+  __shared__ float xl[kFwdNP][128];
+  __shared__ float m_row[2][128];
+  __shared__ uint64_t m_ready[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mblk = gridDim.x - 1 - blockIdx.x;  // heaviest (last) query tiles first
@@ -113,14 +129,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     err = 0;
     for (int i = 0; i < C::NSTAGE; ++i) {
       mbar_init(&full_kv[i], 1);
-      mbar_init(&full_sf[i], 2);
+      mbar_init(&full_sf[i], 1);
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&s_free[i], C::NSBUF == 2 ? 256 : 128 * kFwdNP);
+      mbar_init(&p_full[i], C::NSBUF == 2 ? 8 : 4 * kFwdNP);
       mbar_init(&pv_done[i], 1);
+      mbar_init(&m_ready[i], 128);
     }
     mbar_init(&q_full, 1);
     mbar_init(&qsf_full, 4);
@@ -158,66 +175,77 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     }
     __syncwarp();
-  } else if (warp == 2 || warp == 3) {
-    // ------------------------------------------------------------------ scale loaders
-    for (int i = 0; i < ntile; ++i) {
-      const int s = i % C::NSTAGE, t = t_lo + i;
-      if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 2);
-      uint8_t* st = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES;
-      if (warp == 2) {
-        const uint8_t* src = p.ksc + (int64_t)unit * p.s_kv * (D / 16);
-        float* aux_bias = reinterpret_cast<float*>(st + C::KSF_BYTES + C::VSF_BYTES);
-        int32_t* aux_seq = reinterpret_cast<int32_t*>(st + C::KSF_BYTES + C::VSF_BYTES + 512);
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale loader
+    // K scales (+ key bias, sample ids) and V^T scales of a tile, re-laid into the 32 x 16-byte
+    // atoms tcgen05.cp copies.  The next tile's bytes are fetched into registers one tile
+    // ahead, so per tile the warp pays a shared-memory store, not a trip to L2.
+    const uint8_t* ksrc = p.ksc + (int64_t)unit * p.s_kv * (D / 16);
+    const uint8_t* vsrc = p.vsc + (int64_t)unit * D * (p.s_pad / 16);
+    uint32_t kx[4][C::KB];
+    float nb[4];
+    int32_t ns[4];
+    uint2 vx[D / 32];
+    auto fetch = [&](int t) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = lane + 32 * j;
-          const int key = t * 128 + r;
-          uint32_t wds[C::KB];
+      for (int j = 0; j < 4; ++j) {
+        const int key = t * 128 + lane + 32 * j;
 #pragma unroll
-          for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
-          float bv = 0.0f;
-          int32_t sid = -1;
-          if (key < p.s_kv) {
-            const uint32_t* gsrc = reinterpret_cast<const uint32_t*>(src + (int64_t)key * (D / 16));
+        for (int k = 0; k < C::KB; ++k) kx[j][k] = 0u;
+        nb[j] = 0.0f;
+        ns[j] = -1;
+        if (key < p.s_kv) {
+          const uint32_t* gsrc = reinterpret_cast<const uint32_t*>(ksrc + (int64_t)key * (D / 16));
 #pragma unroll
-            for (int k = 0; k < C::KB; ++k) wds[k] = __ldg(gsrc + k);
-            if (p.bias != nullptr) bv = __ldg(p.bias + (int64_t)zi * p.s_kv + key);
-            if (p.seq_id != nullptr) sid = __ldg(p.seq_id + key);
-          }
-#pragma unroll
-          for (int k = 0; k < C::KB; ++k)
-            *reinterpret_cast<uint32_t*>(st + k * 512 + sf_atom_offset(r, 0)) = wds[k];
-          aux_bias[r] = bv;
-          aux_seq[r] = sid;
-        }
-      } else {
-        const uint8_t* src = p.vsc + (int64_t)unit * D * (p.s_pad / 16) + (int64_t)t * 8;
-        uint8_t* dst = st + C::KSF_BYTES;
-#pragma unroll
-        for (int j = 0; j < D / 32; ++j) {
-          const int dr = lane + 32 * j;
-          const uint2 v = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)dr * (p.s_pad / 16)));
-          const int nt = dr >> 7, r = dr & 127;
-          *reinterpret_cast<uint32_t*>(dst + (0 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = v.x;
-          *reinterpret_cast<uint32_t*>(dst + (1 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = v.y;
+          for (int k = 0; k < C::KB; ++k) kx[j][k] = __ldg(gsrc + k);
+          if (p.bias != nullptr) nb[j] = __ldg(p.bias + (int64_t)zi * p.s_kv + key);
+          if (p.seq_id != nullptr) ns[j] = __ldg(p.seq_id + key);
         }
       }
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j)
+        vx[j] = __ldg(reinterpret_cast<const uint2*>(vsrc + (int64_t)(lane + 32 * j) * (p.s_pad / 16) + (int64_t)t * 8));
+    };
+    if (ntile > 0) fetch(t_lo);
+    for (int i = 0; i < ntile; ++i) {
+      const int s = i % C::NSTAGE;
+      if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 2);
+      uint8_t* st = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES;
+      float* aux_bias = reinterpret_cast<float*>(st + C::KSF_BYTES + C::VSF_BYTES);
+      int32_t* aux_seq = reinterpret_cast<int32_t*>(st + C::KSF_BYTES + C::VSF_BYTES + 512);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = lane + 32 * j;
+#pragma unroll
+        for (int k = 0; k < C::KB; ++k)
+          *reinterpret_cast<uint32_t*>(st + k * 512 + sf_atom_offset(r, 0)) = kx[j][k];
+        aux_bias[r] = nb[j];
+        aux_seq[r] = ns[j];
+      }
+      uint8_t* dst = st + C::KSF_BYTES;
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) {
+        const int dr = lane + 32 * j;
+        const int nt = dr >> 7, r = dr & 127;
+        *reinterpret_cast<uint32_t*>(dst + (0 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = vx[j].x;
+        *reinterpret_cast<uint32_t*>(dst + (1 * C::NT + nt) * 512 + sf_atom_offset(r, 0)) = vx[j].y;
+      }
+      if (i + 1 < ntile) fetch(t_lo + i + 1);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_sf[s]);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ QK^T issuer
     if (elect_one() && ntile > 0) {
       const uint32_t idesc_qk = make_idesc_nvfp4(128, 128);
-      const uint32_t idesc_pv = make_idesc_nvfp4(128, D);
       mbar_wait(&q_full, 0, &err, 3);
       mbar_wait(&qsf_full, 0, &err, 4);
       tc_fence_after();
 #pragma unroll
       for (int k = 0; k < C::KB; ++k)
         tmem_cp_32x128b_warpx4(tmem + C::T_SFQ + k * 4, smem_u32(s_qsf + k * 512));
-      auto issue_qk = [&](int j) {
+      for (int j = 0; j < ntile; ++j) {
         const int s = j % C::NSTAGE, b = j % C::NSBUF;
         const uint32_t ph = (j / C::NSTAGE) & 1;
         mbar_wait(&full_kv[s], ph, &err, 5);
@@ -237,12 +265,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                      k > 0);
         }
         umma_commit(&s_full[b]);
-      };
-      issue_qk(0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ PV issuer
+    // A thread of its own, so a QK^T for tile i+2 is never queued behind the wait for P(i).
+    if (elect_one() && ntile > 0) {
+      const uint32_t idesc_pv = make_idesc_nvfp4(128, D);
       for (int i = 0; i < ntile; ++i) {
-        if (C::NSBUF == 2 && i + 1 < ntile) issue_qk(i + 1);
         const int s = i % C::NSTAGE, b = i % C::NSBUF;
         mbar_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
+        // the V tile and V scales of stage s landed before this tile's QK^T was issued, but this
+        // thread has to observe them itself
+        mbar_wait(&full_kv[s], (i / C::NSTAGE) & 1, &err, 15);
+        mbar_wait(&full_sf[s], (i / C::NSTAGE) & 1, &err, 16);
         tc_fence_after();
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
         const uint32_t sfp = tmem + C::T_SFP + (i & 1) * 8;
@@ -263,18 +300,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         umma_commit(&pv_done[b]);
         umma_commit(&empty[s]);
-        if (C::NSBUF == 1 && i + 1 < ntile) issue_qk(i + 1);
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
-    const int wq = warp - 4;
-    const int row_in = tid - 128;        // row within the query tile
+    // (D = 256: one S buffer.)  All sixteen softmax warps share each tile: NP threads per query
+    // row, each owning 128/NP key columns; a row's threads exchange their partial maxima
+    // through shared memory once per tile and rescale / store their own slice of O.
+    const int sw = warp - 4;
+    const int wq = sw & 3;               // TMEM lane quadrant
+    const int half = sw >> 2;            // which slice of the tile's key columns (0 .. NP-1)
+    constexpr int NP = kFwdNP;
+    constexpr int CW = 128 / NP;         // key columns per thread
+    constexpr int NG = CW / 16;          // 16-key groups per thread
+    const int row_in = wq * 32 + lane;   // row within the query tile
     const int row = m0 + row_in;         // query index
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    // Q scale bytes -> A-operand scale atoms
-    {
+    constexpr int OC = D / kFwdNP;       // O columns owned by this thread
+    if (half == 0) {
+      // Q scale bytes -> A-operand scale atoms
       uint32_t wds[C::KB];
 #pragma unroll
       for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
@@ -294,53 +339,66 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     const int my_seq = (p.seq_id != nullptr) ? p.seq_id[min(row, p.s_q - 1)] : 0;
     const int my_limit = p.causal ? (row + shift) : (p.s_kv - 1);  // last visible key index
     const float c2 = p.scaling * kFwdLog2e;
-    float m_run = -INFINITY, l_run = 0.0f;
+    const float inv_scaling = 1.0f / p.scaling;
+    float m_run = -INFINITY, l_run = 0.0f;   // m_run in log2 units
+    const uint32_t xmax_s = smem_u32(&xmax[0][0][0]);
 
     for (int i = 0; i < ntile; ++i) {
       const int b = i % C::NSBUF, s = i % C::NSTAGE, t = t_lo + i;
-      const int n0 = t * 128;
+      const int n0 = t * 128 + half * CW;
       mbar_wait(&s_full[b], (i / C::NSBUF) & 1, &err, 9);
       tc_fence_after();
-      float sv[128];
+      float sv[CW];
+      {
+        uint32_t r0[CW / 32][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_addr + C::T_S + b * 128 + c * 32, r);
+        for (int c = 0; c < CW / 32; ++c) tmem_ld32(tmem + lane_addr + C::T_S + b * 128 + half * CW + c * 32, r0[c]);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) sv[c * 32 + e] = __uint_as_float(r[e]);
+        for (int c = 0; c < CW / 32; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) sv[c * 32 + e] = __uint_as_float(r0[c][e]);
       }
       tc_fence_before();
       mbar_arrive(&s_free[b]);
 
-      // scores in log2 units; masks only where a tile can need them
-      const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
-                           C::VSF_BYTES;
-      const float* aux_bias = reinterpret_cast<const float*>(aux);
-      const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512);
-      const bool tile_masked = (n0 + 127 > m0 + shift && p.causal) || (n0 + 128 > p.s_kv) ||
+      const bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
                                (p.bias != nullptr) || (p.seq_id != nullptr);
-      float mx = -INFINITY;
       if (tile_masked) {
+        const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
+                             C::VSF_BYTES;
+        const float* aux_bias = reinterpret_cast<const float*>(aux) + half * CW;
+        const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512) + half * CW;
 #pragma unroll
-        for (int e = 0; e < 128; ++e) {
-          float v = sv[e] * c2;
-          if (p.bias != nullptr) v += aux_bias[e] * kFwdLog2e;
+        for (int e = 0; e < CW; ++e) {
+          float v = sv[e];
+          if (p.bias != nullptr) v += aux_bias[e] * inv_scaling;
           const int key = n0 + e;
           bool ok = key <= my_limit && key < p.s_kv;
           if (p.seq_id != nullptr) ok = ok && (aux_seq[e] == my_seq);
-          v = ok ? v : -INFINITY;
-          sv[e] = v;
-          mx = fmaxf(mx, v);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 128; ++e) {
-          sv[e] *= c2;
-          mx = fmaxf(mx, sv[e]);
+          sv[e] = ok ? v : -INFINITY;
         }
       }
-      const float m_new = fmaxf(m_run, mx);
+      float mx;
+      {
+        float m4[NG];
+#pragma unroll
+        for (int c = 0; c < NG; ++c) {
+          float v = fmax3(sv[c * 16], sv[c * 16 + 1], sv[c * 16 + 2]);
+#pragma unroll
+          for (int e = 3; e < 15; e += 2) v = fmax3(v, sv[c * 16 + e], sv[c * 16 + e + 1]);
+          m4[c] = fmaxf(v, sv[c * 16 + 15]);
+        }
+        mx = m4[0];
+#pragma unroll
+        for (int c = 1; c < NG; ++c) mx = fmaxf(mx, m4[c]);
+      }
+      sts_f32(xmax_s + (uint32_t)(((i & 1) * NP + half) * 128 + row_in) * 4u, mx);
+      named_bar_sync(1, 128 * NP);
+#pragma unroll
+      for (int o = 1; o < NP; ++o)
+        mx = fmaxf(mx, lds_f32(xmax_s + (uint32_t)(((i & 1) * NP + ((half + o) % NP)) * 128 + row_in) * 4u));
+      const float m_new = fmaxf(m_run, mx * c2);
       const float m_sf = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = ex2_approx(m_run - m_sf);
       const bool changed = (m_new > m_run) && (i > 0);
@@ -348,47 +406,75 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
       // P buffer b must have been consumed by the PV of tile i - NSBUF
       if (i >= C::NSBUF) mbar_wait(&pv_done[b], ((i / C::NSBUF) & 1) ^ 1, &err, 10);
-      uint8_t* pt = s_p + b * C::P_BYTES;
-      uint8_t* psf = s_psf + b * C::PSF_BYTES;
-      float lsum = 0.0f;
-      uint32_t scw[2] = {0u, 0u};
+      const uint32_t pt = smem_u32(s_p + b * C::P_BYTES);
+      const uint32_t psf = smem_u32(s_psf + b * C::PSF_BYTES);
+      float2 lsum4[NG];
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int c = 0; c < NG; ++c) lsum4[c] = make_float2(0.0f, 0.0f);
+      uint32_t scw = 0u;
+      const float2 c22 = make_float2(c2, c2);
+      const float2 nm2 = make_float2(-m_sf, -m_sf);
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
         float pe[16];
-        float am = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          pe[e] = ex2_approx(sv[g * 16 + e] - m_sf);
-          lsum += pe[e];
-          am = fmaxf(am, pe[e]);
+        for (int e = 0; e < 16; e += 2) {
+          const float2 t2 = __ffma2_rn(make_float2(sv[g * 16 + e], sv[g * 16 + e + 1]), c22, nm2);
+          pe[e] = ex2_approx(t2.x);
+          pe[e + 1] = ex2_approx(t2.y);
+          lsum4[g] = __fadd2_rn(lsum4[g], make_float2(pe[e], pe[e + 1]));
         }
-        const uint8_t sb = scale_byte_from_amax(am);
-        const float inv = __frcp_rn(e4m3_to_f32(sb));
-        const uint32_t lo = e2m1x8(pe[0] * inv, pe[1] * inv, pe[2] * inv, pe[3] * inv, pe[4] * inv,
-                                   pe[5] * inv, pe[6] * inv, pe[7] * inv);
-        const uint32_t hi2 = e2m1x8(pe[8] * inv, pe[9] * inv, pe[10] * inv, pe[11] * inv,
-                                    pe[12] * inv, pe[13] * inv, pe[14] * inv, pe[15] * inv);
-        *reinterpret_cast<uint2*>(pt + sw64_offset(row_in, g * 8)) = make_uint2(lo, hi2);
-        scw[g >> 2] |= (uint32_t)sb << (8 * (g & 3));
+        const float am = fmax3(fmax3(fmax3(pe[0], pe[1], pe[2]), pe[3], pe[4]),
+                               fmax3(fmax3(pe[5], pe[6], pe[7]), pe[8], pe[9]),
+                               fmax3(fmax3(pe[10], pe[11], pe[12]), fmaxf(pe[13], pe[14]), pe[15]));
+        const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
+        uint16_t sb16;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
+        const uint32_t sb = sb16 & 0xFFu;
+        float inv;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sb)));
+        const float2 inv2 = make_float2(inv, inv);
+        float2 y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(pe[2 * e], pe[2 * e + 1]), inv2);
+        const uint32_t lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
+        const uint32_t hi2 = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
+        sts_v2(pt + sw64_offset(row_in, (half * NG + g) * 8), lo, hi2);
+        scw |= sb << (8 * g);
       }
-      *reinterpret_cast<uint32_t*>(psf + 0 * 512 + sf_atom_offset(row_in, 0)) = scw[0];
-      *reinterpret_cast<uint32_t*>(psf + 1 * 512 + sf_atom_offset(row_in, 0)) = scw[1];
-      l_run = l_run * alpha + lsum;
+      // this thread's NG scale bytes: groups half*NG .. of the row's 8 (4 per K=64 atom)
+      if constexpr (NG == 4) {
+        sts_b32(psf + half * 512 + sf_atom_offset(row_in, 0), scw);
+      } else {
+        asm volatile("st.shared.b16 [%0], %1;" ::"r"(psf + (half >> 1) * 512 + sf_atom_offset(row_in, (half & 1) * 2)),
+                     "h"((uint16_t)scw) : "memory");
+      }
+      {
+        float2 tt = lsum4[0];
+#pragma unroll
+        for (int c = 1; c < NG; ++c) tt = __fadd2_rn(tt, lsum4[c]);
+        l_run = l_run * alpha + (tt.x + tt.y);
+      }
 
       if (__any_sync(0xffffffffu, changed)) {
-        // O of this warp's 32 rows is rescaled once the previous PV has landed
+        // this thread's slice of O is rescaled once the previous PV has landed
         const int pb = (i - 1) % C::NSBUF;
         mbar_wait(&pv_done[pb], ((i - 1) / C::NSBUF) & 1, &err, 11);
         tc_fence_after();
         const float a = changed ? alpha : 1.0f;
+        const float2 a2 = make_float2(a, a);
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t r[32];
-          tmem_ld32(tmem + lane_addr + C::T_O + c * 32, r);
+          tmem_ld32(tmem + lane_addr + C::T_O + half * OC + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * a);
-          tmem_st32(tmem + lane_addr + C::T_O + c * 32, r);
+          for (int e = 0; e < 32; e += 2) {
+            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), a2);
+            r[e] = __float_as_uint(v.x);
+            r[e + 1] = __float_as_uint(v.y);
+          }
+          tmem_st32(tmem + lane_addr + C::T_O + half * OC + c * 32, r);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -398,19 +484,25 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (lane == 0) mbar_arrive(&p_full[b]);
     }
 
-    // ---- epilogue: O / l -> out, LSE
+    // ---- epilogue: O / l -> out, LSE.  The row sum is the total of the NP slices.
+    xl[half][row_in] = l_run;
+    named_bar_sync(1, 128 * NP);
+#pragma unroll
+    for (int o = 1; o < NP; ++o) l_run += xl[(half + o) % NP][row_in];
     TO* orow = nullptr;
     if (row < p.s_q)
-      orow = static_cast<TO*>(p.out) + (int64_t)zi * p.so_z + (int64_t)hi * p.so_h + (int64_t)row * p.so_s;
+      orow = static_cast<TO*>(p.out) + (int64_t)zi * p.so_z + (int64_t)hi * p.so_h +
+             (int64_t)row * p.so_s + half * OC;
     if (ntile > 0) {
       const int last = ntile - 1;
       mbar_wait(&pv_done[last % C::NSBUF], (last / C::NSBUF) & 1, &err, 12);
       tc_fence_after();
-      const float inv_l = (l_run == 0.0f) ? 1.0f : __frcp_rn(l_run);
+      float inv_l;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_l) : "f"((l_run == 0.0f) ? 1.0f : l_run));
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem + lane_addr + C::T_O + c * 32, r);
+        tmem_ld32(tmem + lane_addr + C::T_O + half * OC + c * 32, r);
         tmem_ld_wait();
         if (orow != nullptr) {
           if constexpr (sizeof(TO) == 2) {
@@ -436,9 +528,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       tc_fence_before();
     } else if (orow != nullptr) {
-      for (int e = 0; e < D; ++e) orow[e] = from_f32<TO>(0.0f);
+      for (int e = 0; e < OC; ++e) orow[e] = from_f32<TO>(0.0f);
     }
-    if (p.lse != nullptr && row < p.s_q) {
+    if (p.lse != nullptr && row < p.s_q && half == 0) {
       const float l_safe = (l_run == 0.0f) ? 1.0f : l_run;
       const float m_fin = (m_run == -INFINITY) ? 0.0f : m_run;
       p.lse[(int64_t)zh * p.s_q + row] = m_fin * 0.6931471805599453f + logf(l_safe);

@@ -303,6 +303,258 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
     }
     __syncwarp();
+  } else if (C::NSBUF == 2) {
+    // ------------------------------------------------------------------ softmax / epilogue (D = 128)
+    // Two groups of eight warps alternate key tiles (group g owns tiles g, g+2, ...), so while
+    // one group sits in its XU-bound exp/pack phase the other does its TMEM loads, row maxima,
+    // barrier and O rescale: the phases of consecutive tiles overlap instead of adding up.
+    // Within a group two threads share a query row (64 key columns each, handled as two
+    // 32-column chunks to stay inside the register budget of a 640-thread CTA).  The running
+    // maximum is handed from tile to tile through shared memory (m_row / m_ready), so it is
+    // still the exact maximum of a sequential 128-key tile walk.
+    const int sw = warp - 4;
+    const int grp = sw >> 3;             // which tiles (parity)
+    const int wq = sw & 3;               // TMEM lane quadrant
+    const int half = (sw >> 2) & 1;      // which 64 key columns
+    const int part = grp * 2 + half;     // 0..3: slice of O this thread stores in the epilogue
+    const int row_in = wq * 32 + lane;
+    const int row = m0 + row_in;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    constexpr int OC = D / 4;            // O columns stored per thread in the epilogue
+    constexpr int RC = D / 2;            // O columns rescaled per thread (two threads per row in a group)
+    if (part == 0) {
+      uint32_t wds[C::KB];
+#pragma unroll
+      for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
+      if (row < p.s_q) {
+        const uint32_t* gsrc =
+            reinterpret_cast<const uint32_t*>(p.qsc + ((int64_t)zh * p.s_q + row) * (D / 16));
+#pragma unroll
+        for (int k = 0; k < C::KB; ++k) wds[k] = __ldg(gsrc + k);
+      }
+#pragma unroll
+      for (int k = 0; k < C::KB; ++k)
+        *reinterpret_cast<uint32_t*>(s_qsf + k * 512 + sf_atom_offset(row_in, 0)) = wds[k];
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qsf_full);
+    }
+    const int my_seq = (p.seq_id != nullptr) ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    const int my_limit = p.causal ? (row + shift) : (p.s_kv - 1);
+    const float c2 = p.scaling * kFwdLog2e;
+    const float inv_scaling = 1.0f / p.scaling;
+    float m_own = -INFINITY, l_run = 0.0f;   // running max (log2 units) after this group's last tile
+    const uint32_t xmax_s = smem_u32(&xmax[0][0][0]);
+    const uint32_t mrow_s = smem_u32(&m_row[0][0]);
+
+    for (int i = grp; i < ntile; i += 2) {
+      const int b = i & 1, s = i % C::NSTAGE, t = t_lo + i;
+      const int n0 = t * 128 + half * 64;
+      const uint32_t s_addr = tmem + lane_addr + C::T_S + b * 128 + half * 64;
+      const bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
+                               (p.bias != nullptr) || (p.seq_id != nullptr);
+      const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
+                           C::VSF_BYTES;
+      const float* aux_bias = reinterpret_cast<const float*>(aux) + half * 64;
+      const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512) + half * 64;
+      auto load_chunk = [&](int c, float (&sv)[32]) {
+        uint32_t r[32];
+        tmem_ld32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r[e]);
+        if (tile_masked) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float v = sv[e];
+            if (p.bias != nullptr) v += aux_bias[c * 32 + e] * inv_scaling;
+            const int key = n0 + c * 32 + e;
+            bool ok = key <= my_limit && key < p.s_kv;
+            if (p.seq_id != nullptr) ok = ok && (aux_seq[c * 32 + e] == my_seq);
+            sv[e] = ok ? v : -INFINITY;
+          }
+        }
+      };
+      mbar_wait(&s_full[b], (i >> 1) & 1, &err, 9);
+      tc_fence_after();
+      // ---- pass 1: row maximum of this thread's 64 columns
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float sv[32];
+        load_chunk(c, sv);
+        float m2[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float v = fmax3(sv[h2 * 16], sv[h2 * 16 + 1], sv[h2 * 16 + 2]);
+#pragma unroll
+          for (int e = 3; e < 15; e += 2) v = fmax3(v, sv[h2 * 16 + e], sv[h2 * 16 + e + 1]);
+          m2[h2] = fmaxf(v, sv[h2 * 16 + 15]);
+        }
+        mx = fmax3(mx, m2[0], m2[1]);
+      }
+      const uint32_t xb = (uint32_t)(((i >> 1) & 1) * 4 + grp * 2);
+      sts_f32(xmax_s + ((xb + half) * 128 + row_in) * 4u, mx);
+      named_bar_sync(1 + grp, 256);
+      mx = fmaxf(mx, lds_f32(xmax_s + ((xb + (half ^ 1)) * 128 + row_in) * 4u));
+      // ---- running maximum handed over from the tile before (owned by the other group)
+      float m_prev = -INFINITY;
+      if (i > 0) {
+        mbar_wait(&m_ready[b ^ 1], ((i - 1) >> 1) & 1, &err, 13);
+        m_prev = lds_f32(mrow_s + (uint32_t)((b ^ 1) * 128 + row_in) * 4u);
+      }
+      const float m_new = fmaxf(m_prev, mx * c2);
+      if (half == 0) {
+        sts_f32(mrow_s + (uint32_t)(b * 128 + row_in) * 4u, m_new);
+        mbar_arrive(&m_ready[b]);
+      }
+      const float m_sf = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = ex2_approx(m_prev - m_sf);
+      const bool changed = (m_new > m_prev) && (i > 0);
+      l_run *= ex2_approx(m_own - m_sf);
+      m_own = m_new;
+
+      // P buffer b must have been consumed by the PV of tile i - 2
+      if (i >= 2) mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1, &err, 10);
+      const uint32_t pt = smem_u32(s_p + b * C::P_BYTES);
+      const uint32_t psf = smem_u32(s_psf + b * C::PSF_BYTES);
+      const float2 c22 = make_float2(c2, c2);
+      const float2 nm2 = make_float2(-m_sf, -m_sf);
+      float2 lsum4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) lsum4[c] = make_float2(0.0f, 0.0f);
+      uint32_t scw = 0u;
+      // ---- pass 2: exp, row sum, NVFP4 pack of P (two 32-column chunks = four 16-key groups)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float sv[32];
+        load_chunk(c, sv);
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive(&s_free[b]);
+        }
+#pragma unroll
+        for (int g2 = 0; g2 < 2; ++g2) {
+          const int g = c * 2 + g2;
+          float pe[16];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float2 t2 = __ffma2_rn(make_float2(sv[g2 * 16 + e], sv[g2 * 16 + e + 1]), c22, nm2);
+            pe[e] = ex2_approx(t2.x);
+            pe[e + 1] = ex2_approx(t2.y);
+            lsum4[g] = __fadd2_rn(lsum4[g], make_float2(pe[e], pe[e + 1]));
+          }
+          const float am = fmax3(fmax3(fmax3(pe[0], pe[1], pe[2]), pe[3], pe[4]),
+                                 fmax3(fmax3(pe[5], pe[6], pe[7]), pe[8], pe[9]),
+                                 fmax3(fmax3(pe[10], pe[11], pe[12]), fmaxf(pe[13], pe[14]), pe[15]));
+          const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
+          uint16_t sb16;
+          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
+          const uint32_t sb = sb16 & 0xFFu;
+          float inv;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sb)));
+          const float2 inv2 = make_float2(inv, inv);
+          float2 y[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(pe[2 * e], pe[2 * e + 1]), inv2);
+          const uint32_t lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
+          const uint32_t hi2 = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
+          sts_v2(pt + sw64_offset(row_in, (half * 4 + g) * 8), lo, hi2);
+          scw |= sb << (8 * g);
+        }
+      }
+      sts_b32(psf + half * 512 + sf_atom_offset(row_in, 0), scw);
+      {
+        const float2 t01 = __fadd2_rn(lsum4[0], lsum4[1]), t23 = __fadd2_rn(lsum4[2], lsum4[3]);
+        const float2 tt = __fadd2_rn(t01, t23);
+        l_run += tt.x + tt.y;
+      }
+      if (__any_sync(0xffffffffu, changed)) {
+        // O is rescaled (this thread: half of its row) once the PV of tile i - 1 has landed
+        mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1, &err, 11);
+        tc_fence_after();
+        const float a = changed ? alpha : 1.0f;
+        const float2 a2 = make_float2(a, a);
+#pragma unroll
+        for (int c = 0; c < RC / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), a2);
+            r[e] = __float_as_uint(v.x);
+            r[e + 1] = __float_as_uint(v.y);
+          }
+          tmem_st32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[b]);
+    }
+
+    // ---- epilogue: bring the four partial row sums to the final maximum, O / l -> out, LSE
+    float m_fin = -INFINITY;
+    if (ntile > 0) {
+      const int last = ntile - 1;
+      mbar_wait(&m_ready[last & 1], (last >> 1) & 1, &err, 14);
+      m_fin = lds_f32(mrow_s + (uint32_t)((last & 1) * 128 + row_in) * 4u);
+    }
+    {
+      const float m_sf = (m_fin == -INFINITY) ? 0.0f : m_fin;
+      xl[part][row_in] = l_run * ex2_approx(m_own - m_sf);
+    }
+    named_bar_sync(3, 512);
+    l_run = xl[0][row_in] + xl[1][row_in] + xl[2][row_in] + xl[3][row_in];
+    TO* orow = nullptr;
+    if (row < p.s_q)
+      orow = static_cast<TO*>(p.out) + (int64_t)zi * p.so_z + (int64_t)hi * p.so_h +
+             (int64_t)row * p.so_s + part * OC;
+    if (ntile > 0) {
+      const int last = ntile - 1;
+      mbar_wait(&pv_done[last & 1], (last >> 1) & 1, &err, 12);
+      tc_fence_after();
+      float inv_l;
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_l) : "f"((l_run == 0.0f) ? 1.0f : l_run));
+#pragma unroll
+      for (int c = 0; c < OC / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_addr + C::T_O + part * OC + c * 32, r);
+        tmem_ld_wait();
+        if (orow != nullptr) {
+          if constexpr (sizeof(TO) == 2) {
+            uint32_t w[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const TO a0 = from_f32<TO>(__uint_as_float(r[2 * e]) * inv_l);
+              const TO a1 = from_f32<TO>(__uint_as_float(r[2 * e + 1]) * inv_l);
+              w[e] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&a0)) |
+                     ((uint32_t)(*reinterpret_cast<const uint16_t*>(&a1)) << 16);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+          } else {
+            float4* dst = reinterpret_cast<float4*>(orow + c * 32);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              dst[e] = make_float4(__uint_as_float(r[4 * e]) * inv_l, __uint_as_float(r[4 * e + 1]) * inv_l,
+                                   __uint_as_float(r[4 * e + 2]) * inv_l, __uint_as_float(r[4 * e + 3]) * inv_l);
+          }
+        }
+      }
+      tc_fence_before();
+    } else if (orow != nullptr) {
+      for (int e = 0; e < OC; ++e) orow[e] = from_f32<TO>(0.0f);
+    }
+    if (p.lse != nullptr && row < p.s_q && part == 0) {
+      const float l_safe = (l_run == 0.0f) ? 1.0f : l_run;
+      const float m_f = (m_fin == -INFINITY) ? 0.0f : m_fin;
+      p.lse[(int64_t)zh * p.s_q + row] = m_f * 0.6931471805599453f + logf(l_safe);
+    }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
     // (D = 256: one S buffer.)  All sixteen softmax warps share each tile: NP threads per query

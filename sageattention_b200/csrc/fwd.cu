@@ -58,7 +58,15 @@ struct FwdCfg {
   static_assert(T_END <= 512, "TMEM budget exceeded");
 };
 
+#ifdef NVFP4_FWD_TIMING
+// debug trace: trace[role][tile][slot] = clock64, recorded by CTA (0,0) only
+#define TRACE(role, tile, slot) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 80) p.timing[((role) * 80 + (tile)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(role, tile, slot) do { } while (0)
+#endif
+
 struct FwdParams {
+  long long* timing;   // debug only (NVFP4_FWD_TIMING builds)
   const uint8_t* qsc;  // [ZH, Sq, D/16]
   const uint8_t* ksc;  // [ZHk, Skv, D/16]
   const uint8_t* vsc;  // [ZHk, D, s_pad/16]
@@ -112,6 +120,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ uint64_t m_ready[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) TRACE(5, 70, 0);
   const int mblk = gridDim.x - 1 - blockIdx.x;  // heaviest (last) query tiles first
   const int zh = blockIdx.y;
   const int zi = zh / p.h, hi = zh % p.h;
@@ -151,6 +160,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
+  if (tid == 0) TRACE(5, 70, 1);
   // varlen: rows of a tile are sorted by sample, so the first row has the earliest start
   const int t_lo = s_lo_tile;
   const int ntile = max(t_hi - t_lo, 0);
@@ -165,6 +175,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int s = i % C::NSTAGE, t = t_lo + i;
         if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
+        TRACE(0, i, 0);
         mbar_expect_tx(&full_kv[s], C::K_BYTES + C::V_BYTES);
 #pragma unroll
         for (int ks = 0; ks < C::KSUB; ++ks)
@@ -233,7 +244,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (i + 1 < ntile) fetch(t_lo + i + 1);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&full_sf[s]);
+      if (lane == 0) { mbar_arrive(&full_sf[s]); TRACE(1, i, 0); }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ QK^T issuer
@@ -249,8 +260,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int s = j % C::NSTAGE, b = j % C::NSBUF;
         const uint32_t ph = (j / C::NSTAGE) & 1;
         mbar_wait(&full_kv[s], ph, &err, 5);
+        TRACE(2, j, 0);
         mbar_wait(&full_sf[s], ph, &err, 6);
+        TRACE(2, j, 1);
         if (j >= C::NSBUF) mbar_wait(&s_free[b], ((j / C::NSBUF) & 1) ^ 1, &err, 7);
+        TRACE(2, j, 2);
         tc_fence_after();
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
         const uint32_t sfk = tmem + C::T_SFK + (j & 1) * C::KB * 4;
@@ -276,6 +290,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       for (int i = 0; i < ntile; ++i) {
         const int s = i % C::NSTAGE, b = i % C::NSBUF;
         mbar_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
+        TRACE(3, i, 0);
         // the V tile and V scales of stage s landed before this tile's QK^T was issued, but this
         // thread has to observe them itself
         mbar_wait(&full_kv[s], (i / C::NSTAGE) & 1, &err, 15);
@@ -300,6 +315,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         umma_commit(&pv_done[b]);
         umma_commit(&empty[s]);
+        TRACE(3, i, 1);
       }
     }
     __syncwarp();
@@ -357,6 +373,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                            C::VSF_BYTES;
       const float* aux_bias = reinterpret_cast<const float*>(aux) + half * 64;
       const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512) + half * 64;
+      // visible keys of this row inside the thread's 64 columns: [0, lim] (causal + tail)
+      const int lim = min(my_limit, p.s_kv - 1) - n0;
       auto load_chunk = [&](int c, float (&sv)[32]) {
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
@@ -364,18 +382,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
         for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r[e]);
         if (tile_masked) {
+          if (p.bias != nullptr) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float v = sv[e];
-            if (p.bias != nullptr) v += aux_bias[c * 32 + e] * inv_scaling;
-            const int key = n0 + c * 32 + e;
-            bool ok = key <= my_limit && key < p.s_kv;
-            if (p.seq_id != nullptr) ok = ok && (aux_seq[c * 32 + e] == my_seq);
-            sv[e] = ok ? v : -INFINITY;
+            for (int e = 0; e < 32; ++e) sv[e] += aux_bias[c * 32 + e] * inv_scaling;
           }
+          if (p.seq_id != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sv[e] = (aux_seq[c * 32 + e] == my_seq) ? sv[e] : -INFINITY;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; ++e) sv[e] = (c * 32 + e <= lim) ? sv[e] : -INFINITY;
         }
       };
+      const bool trc = (wq == 0 && half == 0 && lane == 0);
+      if (trc) TRACE(4 + grp, i, 0);
       mbar_wait(&s_full[b], (i >> 1) & 1, &err, 9);
+      if (trc) TRACE(4 + grp, i, 1);
       tc_fence_after();
       // ---- pass 1: row maximum of this thread's 64 columns
       float mx = -INFINITY;
@@ -393,6 +415,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
         mx = fmax3(mx, m2[0], m2[1]);
       }
+      if (trc) TRACE(4 + grp, i, 2);
       const uint32_t xb = (uint32_t)(((i >> 1) & 1) * 4 + grp * 2);
       sts_f32(xmax_s + ((xb + half) * 128 + row_in) * 4u, mx);
       named_bar_sync(1 + grp, 256);
@@ -403,6 +426,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mbar_wait(&m_ready[b ^ 1], ((i - 1) >> 1) & 1, &err, 13);
         m_prev = lds_f32(mrow_s + (uint32_t)((b ^ 1) * 128 + row_in) * 4u);
       }
+      if (trc) TRACE(4 + grp, i, 3);
       const float m_new = fmaxf(m_prev, mx * c2);
       if (half == 0) {
         sts_f32(mrow_s + (uint32_t)(b * 128 + row_in) * 4u, m_new);
@@ -416,6 +440,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
       // P buffer b must have been consumed by the PV of tile i - 2
       if (i >= 2) mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1, &err, 10);
+      if (trc) TRACE(4 + grp, i, 4);
       const uint32_t pt = smem_u32(s_p + b * C::P_BYTES);
       const uint32_t psf = smem_u32(s_psf + b * C::PSF_BYTES);
       const float2 c22 = make_float2(c2, c2);
@@ -469,6 +494,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float2 tt = __fadd2_rn(t01, t23);
         l_run += tt.x + tt.y;
       }
+      if (trc) TRACE(4 + grp, i, 5);
       if (__any_sync(0xffffffffu, changed)) {
         // O is rescaled (this thread: half of its row) once the PV of tile i - 1 has landed
         mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1, &err, 11);
@@ -491,11 +517,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tmem_st_wait();
         tc_fence_before();
       }
+      if (trc) TRACE(4 + grp, i, 6);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[b]);
+      if (trc) TRACE(4 + grp, i, 7);
     }
 
+    if (tid == 128) TRACE(5, 70, 3);
     // ---- epilogue: bring the four partial row sums to the final maximum, O / l -> out, LSE
     float m_fin = -INFINITY;
     if (ntile > 0) {
@@ -788,10 +817,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       p.lse[(int64_t)zh * p.s_q + row] = m_fin * 0.6931471805599453f + logf(l_safe);
     }
   }
+  if (tid == 128) TRACE(5, 70, 4);
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) TRACE(5, 70, 5);
   if (tid == 0 && err != 0 && p.status != nullptr) atomicExch(p.status, err);
   if (warp == 1) tmem_dealloc(tmem, 512);
+  if (tid == 32) TRACE(5, 70, 6);
 }
 
 template <int D, typename TO>
@@ -820,7 +852,7 @@ extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* 
                          int64_t s_pad, int d, float scaling, int flags, void* workspace,
                          size_t workspace_bytes, int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
-  (void)workspace; (void)workspace_bytes;
+  (void)workspace_bytes;
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_fwd: D must be 128 or 256");
   NVFP4_REQUIRE(z >= 1 && h >= 1 && hk >= 1 && h % hk == 0, "nvfp4_fwd: bad head counts");
   NVFP4_REQUIRE(s_q >= 1 && s_kv >= 1, "nvfp4_fwd: empty sequence");
@@ -846,6 +878,10 @@ extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* 
   rc = make_tmap_u8_3d_sw64(&tv, vnv, s_pad / 2, d, zhk, s_pad / 2, (uint64_t)d * (s_pad / 2), 128, "nvfp4_fwd(V)");
   if (rc) return rc;
   FwdParams p;
+  p.timing = nullptr;
+#ifdef NVFP4_FWD_TIMING
+  p.timing = static_cast<long long*>(workspace);
+#endif
   p.qsc = qsc; p.ksc = ksc; p.vsc = vsc; p.bias = bias; p.seq_id = seq_id; p.seq_start = seq_start;
   p.out = out; p.so_z = so_z; p.so_h = so_h; p.so_s = so_s; p.lse = lse;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk);

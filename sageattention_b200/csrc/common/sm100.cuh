@@ -67,14 +67,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe (cheap when the phase has already completed).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `err` is a CTA-shared int (0 = healthy). Returns false on timeout.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err,
                                           int site) {
+  if (mbar_test_wait(bar, parity)) return true;
   if (mbar_try_wait(bar, parity)) return true;
   if (*err) return false;
   for (uint32_t i = 0; i < NVFP4_WAIT_SPINS; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*err) return false;
+  }
+  *err = KSTAT_WAIT_TIMEOUT | site;
+  return false;
+}
+
+// Bounded wait that polls without parking the thread: lowest wake-up latency, meant for a lone
+// elected thread (an MMA issuer) whose reaction time is on the critical path.
+__device__ __forceinline__ bool mbar_spin_wait(uint64_t* bar, uint32_t parity, volatile int* err,
+                                               int site) {
+  for (uint32_t i = 0; i < (NVFP4_WAIT_SPINS << 4); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *err) return false;
   }
   *err = KSTAT_WAIT_TIMEOUT | site;
   return false;

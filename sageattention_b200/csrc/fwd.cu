@@ -121,8 +121,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) TRACE(5, 70, 0);
-  const int mblk = gridDim.x - 1 - blockIdx.x;  // heaviest (last) query tiles first
-  const int zh = blockIdx.y;
+  // grid = (heads, query tiles): all heads of the heaviest (last) query tile are scheduled first,
+  // so the kernel ends on the cheapest tiles instead of on a long straggler
+  const int mblk = gridDim.y - 1 - blockIdx.y;
+  const int zh = blockIdx.x;
   const int zi = zh / p.h, hi = zh % p.h;
   const int unit = zi * p.hk + hi / p.g;  // (batch, kv head)
   const int m0 = mblk * 128;
@@ -263,7 +265,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         TRACE(2, j, 0);
         mbar_wait(&full_sf[s], ph, &err, 6);
         TRACE(2, j, 1);
-        if (j >= C::NSBUF) mbar_wait(&s_free[b], ((j / C::NSBUF) & 1) ^ 1, &err, 7);
+        if (j >= C::NSBUF) mbar_spin_wait(&s_free[b], ((j / C::NSBUF) & 1) ^ 1, &err, 7);
         TRACE(2, j, 2);
         tc_fence_after();
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
@@ -289,7 +291,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const uint32_t idesc_pv = make_idesc_nvfp4(128, D);
       for (int i = 0; i < ntile; ++i) {
         const int s = i % C::NSTAGE, b = i % C::NSBUF;
-        mbar_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
+        mbar_spin_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
         TRACE(3, i, 0);
         // the V tile and V scales of stage s landed before this tile's QK^T was issued, but this
         // thread has to observe them itself
@@ -833,7 +835,7 @@ int fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   auto kern = fwd_kernel<D, TO>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return fail((int)e, "nvfp4_fwd: smem attribute: %s", cudaGetErrorString(e));
-  dim3 grid((unsigned)((p.s_q + 127) / 128), (unsigned)zh);
+  dim3 grid((unsigned)zh, (unsigned)((p.s_q + 127) / 128));
   kern<<<grid, kFwdThreads, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
   return launch_result("nvfp4_fwd");
 }
@@ -860,7 +862,7 @@ extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* 
   NVFP4_REQUIRE(qnv && qsc && knv && ksc && vnv && vsc && out, "nvfp4_fwd: null pointer");
   NVFP4_REQUIRE((seq_id == nullptr) == (seq_start == nullptr), "nvfp4_fwd: seq_id/seq_start go together");
   NVFP4_REQUIRE(seq_id == nullptr || (z == 1 && s_q == s_kv), "nvfp4_fwd: varlen needs Z == 1 and Sq == Skv");
-  NVFP4_REQUIRE(z * h < 65536, "nvfp4_fwd: Z*H must be < 65536");
+  NVFP4_REQUIRE((s_q + 127) / 128 < 65536, "nvfp4_fwd: too many query tiles");
   NVFP4_REQUIRE(s_q < (1LL << 30) && s_kv < (1LL << 30), "nvfp4_fwd: sequence too long");
   const size_t esz = out_dtype == NVFP4_DT_FP32 ? 4 : 2;
   NVFP4_REQUIRE(((uintptr_t)out % 16) == 0 && (so_z * esz) % 16 == 0 && (so_h * esz) % 16 == 0 &&

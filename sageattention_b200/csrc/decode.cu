@@ -12,8 +12,9 @@
 // same scale rule as the packer.  Each work item writes un-normalised (acc, m, l) partials; a
 // second small kernel combines them exactly and emits the output and its log-sum-exp.
 //
-// Warp roles (256 threads): 0 TMA producer, 1 MMA issuer, 2 K-scale loader, 3 V-scale loader,
-// 4-7 softmax / correction / epilogue.  Every barrier wait is bounded.
+// Warp roles (384 threads): 0 TMA producer, 1 QK^T issuer, 2 scale loader, 3 PV issuer,
+// 4-11 softmax / accumulate / epilogue (two groups splitting each round's tiles).  Every barrier
+// wait is bounded.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
 #include "common/sm100.cuh"
@@ -22,7 +23,13 @@
 namespace nvfp4 {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kDecodeThreads = 256;
+
+__device__ __forceinline__ float ex2f_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr int kDecodeThreads = 384;
 
 template <int D>
 struct DecodeCfg {
@@ -34,24 +41,37 @@ struct DecodeCfg {
   static constexpr int KSF_BYTES = KB * 512;
   static constexpr int VSF_BYTES = MT * 2 * 512;
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + KSF_BYTES + VSF_BYTES;
-  static constexpr int NSTAGE = (D == 128) ? 8 : 5;
+  static constexpr int NSTAGE = (D == 128) ? 11 : 5;
+  static constexpr int STMAX = (D == 128) ? 4 : 2;  // key tiles per softmax round ("super-tile")
   static constexpr int Q_BYTES = KSUB * 1024;     // 16 rows x 64 B per sub-tile
   static constexpr int QSF_BYTES = KB * 512;
-  static constexpr int P_BYTES = 1024;            // 16 rows x 64 B
-  static constexpr int PSF_BYTES = 2 * 512;
-  static constexpr int SMEM_BYTES =
-      NSTAGE * STAGE_BYTES + Q_BYTES + QSF_BYTES + 2 * P_BYTES + 2 * PSF_BYTES + 1024;
-  // TMEM columns
-  static constexpr int T_ST = 0;      // 2 x 16
-  static constexpr int T_OT = 32;     // MT x 16
-  static constexpr int T_SFK = 64;    // 2 x 16
-  static constexpr int T_SFQ = 96;    // 16
-  static constexpr int T_SFV = 112;   // 2 x 16
-  static constexpr int T_SFP = 144;   // 2 x 8
-  static constexpr int T_COLS = 256;
+  static constexpr int P_BYTES = 1024;            // 16 rows x 64 B per tile
+  static constexpr int PSF_BYTES = 2 * 512;       // per tile
+  static constexpr int MERGE_BYTES = 16 * D * 4;   // one group's O^T partial at the item end
+  static constexpr int PBUF_BYTES = 2 * STMAX * (P_BYTES + PSF_BYTES);
+  // the merge buffer reuses the P tiles, which are idle once an item's last PV has completed
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + QSF_BYTES +
+                                    (PBUF_BYTES > MERGE_BYTES ? PBUF_BYTES : MERGE_BYTES) + 1024;
+  // TMEM columns: [buffer][tile of the super-tile][...]
+  static constexpr int T_ST = 0;                              // 2 x STMAX x 16
+  static constexpr int T_OT = T_ST + 2 * STMAX * 16;          // 2 x STMAX x MT x 16
+  static constexpr int T_SFK = T_OT + 2 * STMAX * MT * 16;    // 2 x STMAX x KB*4
+  static constexpr int T_SFV = T_SFK + 2 * STMAX * KB * 4;    // 2 x STMAX x MT*8
+  static constexpr int T_SFP = T_SFV + 2 * STMAX * MT * 8;    // 2 x STMAX x 8
+  static constexpr int T_SFQ = T_SFP + 2 * STMAX * 8;         // KB*4
+  static constexpr int T_END = T_SFQ + KB * 4;
+  static constexpr int T_COLS = 512;
+  static_assert(T_END <= T_COLS, "TMEM budget exceeded");
 };
 
+#ifdef NVFP4_DECODE_TIMING
+#define DTRACE(role, idx, slot) do { if (p.timing && blockIdx.x == 0 && (idx) < 64) p.timing[((role) * 64 + (idx)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define DTRACE(role, idx, slot) do { } while (0)
+#endif
+
 struct DecodeParams {
+  long long* timing;  // debug only (NVFP4_DECODE_TIMING builds)
   const void* q;
   int64_t s_qz, s_qh;
   const uint8_t* ksc;
@@ -71,26 +91,35 @@ struct DecodeParams {
   int* status;
 };
 
+// The kernel amortises its per-tile latencies (barrier round trips, cross-lane reductions) by
+// treating ST consecutive 128-key tiles as one softmax round: ST QK^T products land in ST
+// S^T accumulators, one pass of the softmax warps turns them into ST packed P tiles (the
+// running maximum still advances tile by tile, exactly as in a sequential walk), and each
+// tile's P.V goes to a FRESH O^T accumulator in TMEM.  The softmax threads (one per head-dim
+// row in this role) fold those ST accumulators into registers one round later with the exact
+// weights exp(m_tile - m_now), so O is never rescaled in TMEM.
 template <int D, typename TQ, int NQ>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-              const DecodeParams p) {
+              const __grid_constant__ CUtensorMap tm_vpf, const DecodeParams p) {
   using C = DecodeCfg<D>;
+  constexpr int ST = (NQ == 16 && C::STMAX > 2) ? 2 : C::STMAX;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* s_stage = smem;
   uint8_t* s_q = s_stage + C::NSTAGE * C::STAGE_BYTES;
   uint8_t* s_qsf = s_q + C::Q_BYTES;
-  uint8_t* s_p = s_qsf + C::QSF_BYTES;
-  uint8_t* s_psf = s_p + 2 * C::P_BYTES;
+  uint8_t* s_p = s_qsf + C::QSF_BYTES;                    // [2][STMAX][P_BYTES]
+  uint8_t* s_psf = s_p + 2 * C::STMAX * C::P_BYTES;       // [2][STMAX][PSF_BYTES]
+  float* s_merge = reinterpret_cast<float*>(s_p);          // [16][D], only at the end of an item
 
   __shared__ uint64_t full_kv[C::NSTAGE], full_sf[C::NSTAGE], empty[C::NSTAGE];
-  __shared__ uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], q_full;
+  __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], q_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
-  __shared__ float xch[2][4][16];
-  __shared__ float lred[4][16];
+  __shared__ float xch[2][4][C::STMAX][16];
+  __shared__ float lred[8][16];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -98,21 +127,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     err = 0;
     for (int i = 0; i < C::NSTAGE; ++i) {
       mbar_init(&full_kv[i], 1);
-      mbar_init(&full_sf[i], 2);
+      mbar_init(&full_sf[i], 1);
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
-      mbar_init(&p_full[i], 4);
-      mbar_init(&pv_done[i], 1);
+      mbar_init(&s_free[i], 256);
+      mbar_init(&p_full[i], 8);
+      mbar_init(&o_full[i], 1);
     }
-    mbar_init(&q_full, 4);
+    mbar_init(&q_full, 8);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, C::T_COLS);
   // zero the operand buffers that are only partly rewritten (rows >= G stay zero)
-  for (int i = tid; i < (C::Q_BYTES + C::QSF_BYTES + 2 * C::P_BYTES + 2 * C::PSF_BYTES) / 4;
+  for (int i = tid; i < (C::Q_BYTES + C::QSF_BYTES + 2 * C::STMAX * (C::P_BYTES + C::PSF_BYTES)) / 4;
        i += kDecodeThreads)
     reinterpret_cast<uint32_t*>(s_q)[i] = 0u;
   fence_proxy_async_smem();
@@ -136,9 +165,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         int unit, t0, t1;
         item_range(w, unit, t0, t1);
         for (int t = t0; t < t1; ++t, ++it) {
+          // V^T rows are D separate strips in memory and a 128-key tile touches only 64 bytes of
+          // each; pull 1 KB per strip (16 tiles) into L2 one block ahead so DRAM sees long bursts
+          if (t == t0 || (t & 15) == 0) {
+            const int blk = (t >> 4) + ((t == t0) ? 0 : 1);
+            for (int bb = blk; bb <= (t >> 4) + 1; ++bb)
+              if (bb * 16 < t1 + 16 && bb * 16 < p.ntiles)
+#pragma unroll
+                for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, bb * 256, mt * 128, unit);
+          }
           const int s = it % C::NSTAGE;
-          if (it >= (uint32_t)C::NSTAGE) mbar_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 1);
+          if (it >= (uint32_t)C::NSTAGE) mbar_spin_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 1);
           uint8_t* st = s_stage + s * C::STAGE_BYTES;
+          DTRACE(0, it, 0);
           mbar_expect_tx(&full_kv[s], C::K_BYTES + C::V_BYTES);
 #pragma unroll
           for (int ks = 0; ks < C::KSUB; ++ks)
@@ -150,131 +189,185 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
     }
     __syncwarp();
-  } else if (warp == 2 || warp == 3) {
-    // ------------------------------------------------------------------ scale loaders
-    uint32_t it = 0;
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scale loader
+    // K and V^T scale bytes go straight from global memory into the 32 x 16-byte atoms that
+    // tcgen05.cp copies, with per-thread 4-byte cp.async (no registers, no stall on the load):
+    // the copies of tile n are issued as soon as its stage is free, and the stage is published
+    // kLag tiles later, once cp.async.wait_group says they have landed.
+    constexpr int kLag = 3;
+    uint32_t it = 0, published = 0;   // tiles [published, it) have copies in flight
+    auto publish = [&](uint32_t n) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&full_sf[n % C::NSTAGE]); DTRACE(1, n, 0); }
+    };
     for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
       int unit, t0, t1;
       item_range(w, unit, t0, t1);
+      const uint8_t* ksrc = p.ksc + (int64_t)unit * p.ksc_unit;
+      const uint8_t* vsrc = p.vsc + (int64_t)unit * p.vsc_unit;
       for (int t = t0; t < t1; ++t, ++it) {
         const int s = it % C::NSTAGE;
-        if (it >= (uint32_t)C::NSTAGE) mbar_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 2);
-        uint8_t* st = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES;
-        if (warp == 2) {
-          const uint8_t* src = p.ksc + (int64_t)unit * p.ksc_unit;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int r = lane + 32 * j;
-            const int64_t key = (int64_t)t * 128 + r;
-            uint32_t wds[C::KB];
-#pragma unroll
-            for (int k = 0; k < C::KB; ++k) wds[k] = 0u;
-            if (key < p.s_kv) {
-              const uint32_t* g = reinterpret_cast<const uint32_t*>(src + key * (D / 16));
-#pragma unroll
-              for (int k = 0; k < C::KB; ++k) wds[k] = __ldg(g + k);
-            }
-#pragma unroll
-            for (int k = 0; k < C::KB; ++k)
-              *reinterpret_cast<uint32_t*>(st + k * 512 + sf_atom_offset(r, 0)) = wds[k];
-          }
-        } else {
-          const uint8_t* src = p.vsc + (int64_t)unit * p.vsc_unit + (int64_t)t * 8;
-          uint8_t* dst = st + C::KSF_BYTES;
-#pragma unroll
-          for (int j = 0; j < D / 32; ++j) {
-            const int dr = lane + 32 * j;
-            const uint2 v = __ldg(reinterpret_cast<const uint2*>(src + (int64_t)dr * p.vsc_row));
-            const int mt = dr >> 7, r = dr & 127;
-            *reinterpret_cast<uint32_t*>(dst + (mt * 2 + 0) * 512 + sf_atom_offset(r, 0)) = v.x;
-            *reinterpret_cast<uint32_t*>(dst + (mt * 2 + 1) * 512 + sf_atom_offset(r, 0)) = v.y;
+        if (it >= (uint32_t)C::NSTAGE) {
+          const uint32_t par = ((it / C::NSTAGE) & 1) ^ 1;
+          if (!mbar_test_wait(&empty[s], par)) {
+            // about to block on a full ring: publish everything in flight first
+            cp_async_wait<0>();
+            for (; published < it; ++published) publish(published);
+            mbar_wait(&empty[s], par, &err, 2);
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_sf[s]);
+        const uint32_t st = smem_u32(s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES);
+#pragma unroll
+        for (int r4 = 0; r4 < 4; ++r4) {
+          const int r = lane + 32 * r4;
+          const int64_t key = (int64_t)t * 128 + r;
+          const bool ok = key < p.s_kv;
+          const uint8_t* g = ksrc + (ok ? key : 0) * (D / 16);
+#pragma unroll
+          for (int k = 0; k < C::KB; ++k)
+            cp_async_4(st + k * 512 + sf_atom_offset(r, 0), g + 4 * k, ok ? 4u : 0u);
+        }
+#pragma unroll
+        for (int r8 = 0; r8 < D / 32; ++r8) {
+          const int dr = lane + 32 * r8;
+          const int mt = dr >> 7, r = dr & 127;
+          const uint8_t* g = vsrc + (int64_t)dr * p.vsc_row + (int64_t)t * 8;
+          cp_async_4(st + C::KSF_BYTES + (mt * 2 + 0) * 512 + sf_atom_offset(r, 0), g, 4u);
+          cp_async_4(st + C::KSF_BYTES + (mt * 2 + 1) * 512 + sf_atom_offset(r, 0), g + 4, 4u);
+        }
+        cp_async_commit();
+        if (it + 1 - published > (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          publish(published++);
+        }
       }
     }
+    // drain
+    cp_async_wait<0>();
+    for (; published < it; ++published) publish(published);
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ QK^T issuer
     if (elect_one()) {
       const uint32_t idesc = make_idesc_nvfp4(128, 16);
-      uint32_t it = 0, item_idx = 0;
-      auto issue_qk = [&](uint32_t j) {
-        const int s = j % C::NSTAGE, b = j & 1;
-        const uint32_t ph = (j / C::NSTAGE) & 1;
-        mbar_wait(&full_kv[s], ph, &err, 3);
-        mbar_wait(&full_sf[s], ph, &err, 4);
-        if (j >= 2) mbar_wait(&s_free[b], ((j >> 1) & 1) ^ 1, &err, 5);
-        tc_fence_after();
-        uint8_t* st = s_stage + s * C::STAGE_BYTES;
-        const uint32_t sfk = tmem + C::T_SFK + b * 16;
-#pragma unroll
-        for (int k = 0; k < C::KB; ++k)
-          tmem_cp_32x128b_warpx4(sfk + k * 4, smem_u32(st + C::K_BYTES + C::V_BYTES + k * 512));
-#pragma unroll
-        for (int k = 0; k < C::KB; ++k) {
-          const uint64_t ad = make_smem_desc(smem_u32(st + (k >> 1) * 8192) + (k & 1) * 32, 16, 512, 4);
-          const uint64_t bd = make_smem_desc(smem_u32(s_q + (k >> 1) * 1024) + (k & 1) * 32, 16, 512, 4);
-          umma_nvfp4(tmem + C::T_ST + b * 16, ad, bd, idesc, sfk + k * 4, tmem + C::T_SFQ + k * 4,
-                     k > 0);
-        }
-        umma_commit(&s_full[b]);
-      };
+      uint32_t it = 0, su = 0, item_idx = 0;
       for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x, ++item_idx) {
         int unit, t0, t1;
         item_range(w, unit, t0, t1);
-        const int ntile = t1 - t0;
         mbar_wait(&q_full, item_idx & 1, &err, 6);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < C::KB; ++k)
           tmem_cp_32x128b_warpx4(tmem + C::T_SFQ + k * 4, smem_u32(s_qsf + k * 512));
-        issue_qk(it);
-        for (int i = 0; i < ntile; ++i, ++it) {
-          if (i + 1 < ntile) issue_qk(it + 1);
-          const int s = it % C::NSTAGE, b = it & 1;
-          mbar_wait(&p_full[b], (it >> 1) & 1, &err, 7);
-          tc_fence_after();
-          uint8_t* st = s_stage + s * C::STAGE_BYTES;
-          const uint32_t sfv = tmem + C::T_SFV + b * 16, sfp = tmem + C::T_SFP + b * 8;
+        for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
+          const int b = su & 1;
+          const int nt = min(ST, t1 - ts0);
+          if (su >= 2) {
+            mbar_spin_wait(&s_free[b], ((su >> 1) & 1) ^ 1, &err, 5);
+            // the V-scale TMEM slots of buffer b are rewritten below: the PV of round su - 2 must be done
+            mbar_spin_wait(&o_full[b], ((su >> 1) & 1) ^ 1, &err, 11);
+          }
+          for (int j = 0; j < nt; ++j, ++it) {
+            const int s = it % C::NSTAGE;
+            const uint32_t ph = (it / C::NSTAGE) & 1;
+            mbar_spin_wait(&full_kv[s], ph, &err, 3);
+            DTRACE(2, it, 0);
+            mbar_spin_wait(&full_sf[s], ph, &err, 4);
+            DTRACE(2, it, 1);
+            tc_fence_after();
+            uint8_t* st = s_stage + s * C::STAGE_BYTES;
+            const uint32_t sfk = tmem + C::T_SFK + (b * C::STMAX + j) * C::KB * 4;
 #pragma unroll
-          for (int k = 0; k < C::MT * 2; ++k)
-            tmem_cp_32x128b_warpx4(sfv + k * 4,
-                                   smem_u32(st + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + k * 512));
+            for (int k = 0; k < C::KB; ++k)
+              tmem_cp_32x128b_warpx4(sfk + k * 4, smem_u32(st + C::K_BYTES + C::V_BYTES + k * 512));
+            // the V^T scales of this tile go to TMEM now as well, off the PV issuer's critical path
+            // (slot (b, j) was last read by the PV of round su - 2, complete before s_free fired)
+            const uint32_t sfv = tmem + C::T_SFV + (b * C::STMAX + j) * C::MT * 8;
 #pragma unroll
-          for (int k = 0; k < 2; ++k)
-            tmem_cp_32x128b_warpx4(sfp + k * 4, smem_u32(s_psf + b * C::PSF_BYTES + k * 512));
+            for (int k = 0; k < C::MT * 2; ++k)
+              tmem_cp_32x128b_warpx4(sfv + k * 4,
+                                     smem_u32(st + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + k * 512));
 #pragma unroll
-          for (int mt = 0; mt < C::MT; ++mt) {
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-              const uint64_t ad =
-                  make_smem_desc(smem_u32(st + C::K_BYTES + mt * 8192) + k * 32, 16, 512, 4);
-              const uint64_t bd = make_smem_desc(smem_u32(s_p + b * C::P_BYTES) + k * 32, 16, 512, 4);
-              umma_nvfp4(tmem + C::T_OT + mt * 16, ad, bd, idesc, sfv + (mt * 2 + k) * 4, sfp + k * 4,
-                         (i > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < C::KB; ++k) {
+              const uint64_t ad = make_smem_desc(smem_u32(st + (k >> 1) * 8192) + (k & 1) * 32, 16, 512, 4);
+              const uint64_t bd = make_smem_desc(smem_u32(s_q + (k >> 1) * 1024) + (k & 1) * 32, 16, 512, 4);
+              umma_nvfp4(tmem + C::T_ST + (b * C::STMAX + j) * 16, ad, bd, idesc, sfk + k * 4,
+                         tmem + C::T_SFQ + k * 4, k > 0);
             }
           }
-          umma_commit(&pv_done[b]);
-          umma_commit(&empty[s]);
+          umma_commit(&s_full[b]);
+          DTRACE(3, su, 0);
         }
       }
     }
     __syncwarp();
-  } else {
-    // ------------------------------------------------------------------ softmax / epilogue
-    const int wq = warp - 4;               // TMEM lane quadrant
-    const int ts = tid - 128;              // 0..127 = key lane within a tile / d row in epilogue
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ PV issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_nvfp4(128, 16);
+      uint32_t it = 0, su = 0;
+      for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+        int unit, t0, t1;
+        item_range(w, unit, t0, t1);
+        for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
+          const int b = su & 1;
+          const int nt = min(ST, t1 - ts0);
+          mbar_spin_wait(&p_full[b], (su >> 1) & 1, &err, 7);
+          DTRACE(3, su, 1);
+          tc_fence_after();
+          for (int j = 0; j < nt; ++j, ++it) {
+            // V^T tile and scales of stage s were observed by the QK^T issuer before S^T of this
+            // round was produced, and P arrived after the softmax warps saw that S^T
+            const int s = it % C::NSTAGE;
+            uint8_t* st = s_stage + s * C::STAGE_BYTES;
+            const uint32_t sfv = tmem + C::T_SFV + (b * C::STMAX + j) * C::MT * 8;
+            const uint32_t sfp = tmem + C::T_SFP + (b * C::STMAX + j) * 8;
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+              tmem_cp_32x128b_warpx4(sfp + k * 4,
+                                     smem_u32(s_psf + (b * C::STMAX + j) * C::PSF_BYTES + k * 512));
+#pragma unroll
+            for (int mt = 0; mt < C::MT; ++mt) {
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                const uint64_t ad =
+                    make_smem_desc(smem_u32(st + C::K_BYTES + mt * 8192) + k * 32, 16, 512, 4);
+                const uint64_t bd = make_smem_desc(
+                    smem_u32(s_p + (b * C::STMAX + j) * C::P_BYTES) + k * 32, 16, 512, 4);
+                umma_nvfp4(tmem + C::T_OT + ((b * C::STMAX + j) * C::MT + mt) * 16, ad, bd, idesc,
+                           sfv + (mt * 2 + k) * 4, sfp + k * 4, k > 0 ? 1u : 0u);
+              }
+            }
+            umma_commit(&empty[s]);
+          }
+          umma_commit(&o_full[b]);
+          DTRACE(3, su, 2);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax / accumulate / epilogue
+    // Two groups of four warps split every round by tiles (group g owns tiles g*TPG ..), so each
+    // SM sub-partition has two warps to overlap latencies with and each thread carries half the
+    // state.  All threads see every tile maximum, so the running maximum is the same sequential
+    // one in both groups; their O^T / row-sum partials are merged at the end of the item.
+    constexpr int TPG = ST / 2;            // tiles per group and round
+    const int sw = warp - 4;
+    const int grp = sw >> 2;
+    const int wq = sw & 3;                 // TMEM lane quadrant
+    const int ts = (tid - 128) & 127;      // key lane within a tile (softmax) / d row (accumulate)
+    const int tall = tid - 128;            // 0..255
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const TQ* qbase = static_cast<const TQ*>(p.q);
-    uint32_t it = 0;
+    uint32_t su = 0;
     for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
       int unit, t0, t1;
       item_range(w, unit, t0, t1);
       const int zi = unit / p.hk, kh = unit % p.hk;
-      // ---- quantise the G query rows of this kv head into the B operand of QK
-      for (int i = ts; i < p.g * (D / 16); i += 128) {
+      // ---- quantise the G query rows of this kv head into the B operand of QK^T
+      for (int i = tall; i < p.g * (D / 16); i += 256) {
         const int qr = i / (D / 16), gi = i % (D / 16);
         const TQ* src = qbase + zi * p.s_qz + (int64_t)(kh * p.g + qr) * p.s_qh + gi * 16;
         float v[16];
@@ -290,127 +383,249 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_full);
 
-      float m_run[NQ], l_run[NQ];
+      float m_run[NQ], l_run[NQ];             // key-lane role: running max, partial row sum
+      float o_run[C::MT][NQ], m_acc[NQ];      // d-row role: accumulated O^T, the max it refers to
+      float w_prev[TPG][NQ], m_end_prev[NQ];  // weights of the round whose PV is still in flight
 #pragma unroll
-      for (int qi = 0; qi < NQ; ++qi) { m_run[qi] = -INFINITY; l_run[qi] = 0.0f; }
-
-      for (int t = t0; t < t1; ++t, ++it) {
-        const int b = it & 1;
-        mbar_wait(&s_full[b], (it >> 1) & 1, &err, 8);
+      for (int qi = 0; qi < NQ; ++qi) {
+        m_run[qi] = -INFINITY; l_run[qi] = 0.0f; m_acc[qi] = -INFINITY; m_end_prev[qi] = -INFINITY;
+#pragma unroll
+        for (int mt = 0; mt < C::MT; ++mt) o_run[mt][qi] = 0.0f;
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj) w_prev[jj][qi] = 0.0f;
+      }
+      // fold this group's fresh accumulators of round `sv` (buffer bb, nt tiles) into o_run
+      auto accumulate = [&](uint32_t sv, int nt) {
+        const int bb = sv & 1;
+        mbar_wait(&o_full[bb], (sv >> 1) & 1, &err, 10);
         tc_fence_after();
-        uint32_t r[16];
-        tmem_ld16(tmem + lane_addr + C::T_ST + b * 16, r);
+#pragma unroll
+        for (int qi = 0; qi < NQ; ++qi) {
+          const float me = m_end_prev[qi];
+          const float sc = (me == -INFINITY) ? 0.0f : ex2f_fast((m_acc[qi] - me) * kLog2e);
+          m_acc[qi] = me;
+#pragma unroll
+          for (int mt = 0; mt < C::MT; ++mt) o_run[mt][qi] *= sc;
+        }
+        uint32_t o[TPG][C::MT][16];
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+          if (grp * TPG + jj < nt) {
+#pragma unroll
+            for (int mt = 0; mt < C::MT; ++mt)
+              tmem_ld16(tmem + lane_addr + C::T_OT + ((bb * C::STMAX + grp * TPG + jj) * C::MT + mt) * 16,
+                        o[jj][mt]);
+          }
         tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+          if (grp * TPG + jj < nt) {
+#pragma unroll
+            for (int mt = 0; mt < C::MT; ++mt)
+#pragma unroll
+              for (int qi = 0; qi < NQ; ++qi) o_run[mt][qi] += w_prev[jj][qi] * __uint_as_float(o[jj][mt][qi]);
+          }
+        tc_fence_before();
+      };
+
+      int nt_prev = 0;
+      bool have_prev = false;
+      for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
+        const int b = su & 1;
+        const int nt = min(ST, t1 - ts0);
+        if (tall == 0) DTRACE(4, su, 0);
+        mbar_wait(&s_full[b], (su >> 1) & 1, &err, 8);
+        if (tall == 0) DTRACE(4, su, 1);
+        tc_fence_after();
+        float sv[TPG][NQ];
+        {
+          uint32_t r[TPG][16];
+#pragma unroll
+          for (int jj = 0; jj < TPG; ++jj)
+            if (grp * TPG + jj < nt)
+              tmem_ld16(tmem + lane_addr + C::T_ST + (b * C::STMAX + grp * TPG + jj) * 16, r[jj]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < TPG; ++jj) {
+            const int j = grp * TPG + jj;
+            const bool valid = (j < nt) && (((int64_t)(ts0 + j) * 128 + ts) < p.s_kv);
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi)
+              sv[jj][qi] = (valid && qi < p.g) ? __uint_as_float(r[jj][qi]) * p.scaling : -INFINITY;
+          }
+        }
         tc_fence_before();
         mbar_arrive(&s_free[b]);
-        const bool valid = ((int64_t)t * 128 + ts) < p.s_kv;
-        float sv[NQ], mx[NQ];
+        // maxima: first over each 16-lane key group (kept: exp of it is the group's P amax, since
+        // ex2 is monotonic), then over the warp, then an exchange gives every tile maximum
+        float gmx[TPG][NQ];
+        {
 #pragma unroll
-        for (int qi = 0; qi < NQ; ++qi) {
-          sv[qi] = (valid && qi < p.g) ? __uint_as_float(r[qi]) * p.scaling : -INFINITY;
-          float v = sv[qi];
+          for (int jj = 0; jj < TPG; ++jj)
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-          mx[qi] = v;
-        }
-        if (lane == 0) {
+            for (int qi = 0; qi < NQ; ++qi) gmx[jj][qi] = sv[jj][qi];
 #pragma unroll
-          for (int qi = 0; qi < NQ; ++qi) xch[b][wq][qi] = mx[qi];
-        }
-        named_bar_sync(1, 128);
-        bool need = false;
-        float alpha[NQ], pv[NQ];
+          for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
-        for (int qi = 0; qi < NQ; ++qi) {
-          const float mt_ = fmaxf(fmaxf(xch[b][0][qi], xch[b][1][qi]), fmaxf(xch[b][2][qi], xch[b][3][qi]));
-          const float m_new = fmaxf(m_run[qi], mt_);
-          const float m_sf = (m_new == -INFINITY) ? 0.0f : m_new;
-          alpha[qi] = exp2f((m_run[qi] - m_sf) * kLog2e);
-          pv[qi] = exp2f((sv[qi] - m_sf) * kLog2e);
-          need = need || (m_new > m_run[qi]);
-          l_run[qi] = l_run[qi] * alpha[qi] + pv[qi];
-          m_run[qi] = m_new;
-        }
-        need = need && (t > t0);
-        if (it >= 2) mbar_wait(&pv_done[b], ((it >> 1) & 1) ^ 1, &err, 9);
-        // ---- pack P along keys (16 consecutive lanes = one group)
-        uint8_t* pt = s_p + b * C::P_BYTES;
-        uint8_t* psf = s_psf + b * C::PSF_BYTES;
+            for (int jj = 0; jj < TPG; ++jj)
 #pragma unroll
-        for (int qi = 0; qi < NQ; ++qi) {
-          if (qi < p.g) {
-            float am = pv[qi];
+              for (int qi = 0; qi < NQ; ++qi)
+                gmx[jj][qi] = fmaxf(gmx[jj][qi], __shfl_xor_sync(0xffffffffu, gmx[jj][qi], o));
+          float wmx[TPG][NQ];
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            const uint8_t sb = scale_byte_from_amax(am);
-            const float y = __fdiv_rn(pv[qi], e4m3_to_f32(sb));
-            const float yn = __shfl_xor_sync(0xffffffffu, y, 1);
-            if ((lane & 1) == 0) {
-              uint16_t byte;
-              asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}\n"
-                  : "=h"(byte)
-                  : "f"(yn), "f"(y));
-              pt[sw64_offset(qi, ts >> 1)] = (uint8_t)byte;
-            }
-            if ((lane & 15) == 0) {
-              const int gi = ts >> 4;
-              psf[(gi >> 2) * 512 + sf_atom_offset(qi, gi & 3)] = sb;
-            }
+          for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi)
+              wmx[jj][qi] = fmaxf(gmx[jj][qi], __shfl_xor_sync(0xffffffffu, gmx[jj][qi], 16));
+          if (lane == 0) {
+#pragma unroll
+            for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+              for (int qi = 0; qi < NQ; ++qi) xch[b][wq][grp * TPG + jj][qi] = wmx[jj][qi];
           }
         }
-        if (need) {
-          // PV of the previous tile must have landed before O^T is rescaled
-          mbar_wait(&pv_done[b ^ 1], ((it - 1) >> 1) & 1, &err, 10);
-          tc_fence_after();
+        if (tall == 0) DTRACE(4, su, 2);
+        named_bar_sync(1, 256);
+        if (tall == 0) DTRACE(4, su, 3);
+        // running maximum advances tile by tile; weights bring each tile to the round's end
+        float m_mine[TPG][NQ];
 #pragma unroll
-          for (int mt = 0; mt < C::MT; ++mt) {
-            uint32_t o[16];
-            tmem_ld16(tmem + lane_addr + C::T_OT + mt * 16, o);
-            tmem_ld_wait();
+        for (int qi = 0; qi < NQ; ++qi) {
+          float m = m_run[qi];
 #pragma unroll
-            for (int qi = 0; qi < NQ; ++qi) o[qi] = __float_as_uint(__uint_as_float(o[qi]) * alpha[qi]);
-            tmem_st16(tmem + lane_addr + C::T_OT + mt * 16, o);
+          for (int j = 0; j < ST; ++j) {
+            const float tm = fmaxf(fmaxf(xch[b][0][j][qi], xch[b][1][j][qi]),
+                                   fmaxf(xch[b][2][j][qi], xch[b][3][j][qi]));
+            m = (j < nt) ? fmaxf(m, tm) : m;
+            if (j / TPG == grp) m_mine[j % TPG][qi] = m;
           }
-          tmem_st_wait();
-          tc_fence_before();
+          const float m_sf = (m == -INFINITY) ? 0.0f : m;
+          l_run[qi] *= ex2f_fast((m_run[qi] - m_sf) * kLog2e);
+          m_run[qi] = m;
         }
+        // the previous round's PV has had a whole round to finish: fold it into registers now,
+        // which also frees its P buffers for rewriting
+        if (tall == 0) DTRACE(4, su, 4);
+        if (have_prev) accumulate(su - 1, nt_prev);
+        if (tall == 0) DTRACE(4, su, 5);
+        float w_cur[TPG][NQ], pv[TPG][NQ], am[TPG][NQ];
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+          for (int qi = 0; qi < NQ; ++qi) {
+            const float mj = m_mine[jj][qi];
+            const float mj_sf = (mj == -INFINITY) ? 0.0f : mj;
+            const float m_sf = (m_run[qi] == -INFINITY) ? 0.0f : m_run[qi];
+            pv[jj][qi] = ex2f_fast((sv[jj][qi] - mj_sf) * kLog2e);
+            w_cur[jj][qi] = (mj == -INFINITY) ? 0.0f : ex2f_fast((mj_sf - m_sf) * kLog2e);
+            l_run[qi] += pv[jj][qi] * w_cur[jj][qi];
+            am[jj][qi] = ex2f_fast((gmx[jj][qi] - mj_sf) * kLog2e);   // = max of pv over the 16-lane group
+          }
+        // NVFP4 pack of P along keys: 16 consecutive lanes form one group
+        uint32_t sbv[TPG][NQ];
+        float y[TPG][NQ], yn[TPG][NQ];
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+          for (int qi = 0; qi < NQ; ++qi) {
+            const float s32 = fminf(fmaxf(am[jj][qi] * 0.16666667f, kScaleFloor), kScaleMax);
+            uint16_t sb16;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
+            sbv[jj][qi] = sb16 & 0xFFu;
+            float inv;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sbv[jj][qi])));
+            y[jj][qi] = pv[jj][qi] * inv;
+          }
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+          for (int qi = 0; qi < NQ; ++qi) yn[jj][qi] = __shfl_xor_sync(0xffffffffu, y[jj][qi], 1);
+        {
+          const uint32_t pt0 = smem_u32(s_p + (b * C::STMAX) * C::P_BYTES);
+          const uint32_t psf0 = smem_u32(s_psf + (b * C::STMAX) * C::PSF_BYTES);
+          const int gi = ts >> 4;
+#pragma unroll
+          for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi) {
+              const int j = grp * TPG + jj;
+              if (j < nt && qi < p.g) {
+                if ((lane & 1) == 0) {
+                  uint16_t byte;
+                  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}\n"
+                      : "=h"(byte)
+                      : "f"(yn[jj][qi]), "f"(y[jj][qi]));
+                  asm volatile("st.shared.u8 [%0], %1;" ::"r"(pt0 + j * C::P_BYTES + sw64_offset(qi, ts >> 1)),
+                               "h"(byte) : "memory");
+                }
+                if ((lane & 15) == 0)
+                  asm volatile("st.shared.u8 [%0], %1;" ::"r"(psf0 + j * C::PSF_BYTES + (gi >> 2) * 512 +
+                                                             sf_atom_offset(qi, gi & 3)),
+                               "h"((uint16_t)sbv[jj][qi]) : "memory");
+              }
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < TPG; ++jj)
+#pragma unroll
+          for (int qi = 0; qi < NQ; ++qi) w_prev[jj][qi] = w_cur[jj][qi];
+#pragma unroll
+        for (int qi = 0; qi < NQ; ++qi) m_end_prev[qi] = m_run[qi];
+        nt_prev = nt;
+        have_prev = true;
+        if (tall == 0) DTRACE(4, su, 6);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[b]);
+        if (tall == 0) DTRACE(4, su, 7);
       }
-      // ---- item epilogue: un-normalised partials
+      // ---- item epilogue: fold the last round, merge the two groups, write un-normalised partials
+      if (have_prev) accumulate(su - 1, nt_prev);
       {
-        const uint32_t last = it - 1;
-        mbar_wait(&pv_done[last & 1], (last >> 1) & 1, &err, 11);
-        tc_fence_after();
-        float* acc = p.ws_acc + w * 16 * D;
+        // bring this group's accumulator to the final running maximum
 #pragma unroll
-        for (int mt = 0; mt < C::MT; ++mt) {
-          uint32_t o[16];
-          tmem_ld16(tmem + lane_addr + C::T_OT + mt * 16, o);
-          tmem_ld_wait();
+        for (int qi = 0; qi < NQ; ++qi) {
+          const float mf = m_run[qi];
+          const float sc = (mf == -INFINITY || m_acc[qi] == -INFINITY) ? 0.0f
+                                                                        : ex2f_fast((m_acc[qi] - mf) * kLog2e);
 #pragma unroll
-          for (int qi = 0; qi < NQ; ++qi)
-            if (qi < p.g) acc[qi * D + mt * 128 + ts] = __uint_as_float(o[qi]);
+          for (int mt = 0; mt < C::MT; ++mt) o_run[mt][qi] *= sc;
         }
-        tc_fence_before();
+        if (grp == 1) {
+#pragma unroll
+          for (int mt = 0; mt < C::MT; ++mt)
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi) s_merge[qi * D + mt * 128 + ts] = o_run[mt][qi];
+        }
 #pragma unroll
         for (int qi = 0; qi < NQ; ++qi) {
           float v = l_run[qi];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (lane == 0) lred[wq][qi] = v;
+          if (lane == 0) lred[sw][qi] = v;
         }
-        named_bar_sync(1, 128);
-        if (ts < p.g) {
-          float lsum = 0.0f, mfin = -INFINITY;
+        named_bar_sync(1, 256);
+        if (grp == 0) {
+          float* acc = p.ws_acc + w * 16 * D;
 #pragma unroll
-          for (int qi = 0; qi < NQ; ++qi)
-            if (qi == ts) { lsum = lred[0][qi] + lred[1][qi] + lred[2][qi] + lred[3][qi]; mfin = m_run[qi]; }
-          p.ws_m[w * 16 + ts] = mfin;
-          p.ws_l[w * 16 + ts] = lsum;
+          for (int mt = 0; mt < C::MT; ++mt)
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi)
+              if (qi < p.g) acc[qi * D + mt * 128 + ts] = o_run[mt][qi] + s_merge[qi * D + mt * 128 + ts];
+          if (ts < p.g) {
+            float lsum = 0.0f, mfin = -INFINITY;
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi)
+              if (qi == ts) {
+#pragma unroll
+                for (int ww = 0; ww < 8; ++ww) lsum += lred[ww][qi];
+                mfin = m_run[qi];
+              }
+            p.ws_m[w * 16 + ts] = mfin;
+            p.ws_l[w * 16 + ts] = lsum;
+          }
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 256);
       }
     }
   }
@@ -446,7 +661,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ ws_acc,
 }
 
 template <int D, typename TQ>
-int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const DecodeParams& p,
+int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_vpf,
+                  const DecodeParams& p,
                   int64_t zhk, void* out, float* lse, int sm_count, cudaStream_t st) {
   using C = DecodeCfg<D>;
   const int grid = (int)std::min<int64_t>(p.nitems, sm_count);
@@ -454,7 +670,7 @@ int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const Decode
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_decode: smem attribute: %s", cudaGetErrorString(e));
-    kern<<<grid, kDecodeThreads, C::SMEM_BYTES, st>>>(tm_k, tm_v, p);
+    kern<<<grid, kDecodeThreads, C::SMEM_BYTES, st>>>(tm_k, tm_v, tm_vpf, p);
     return launch_result("nvfp4_decode");
   };
   int rc;
@@ -517,12 +733,18 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
                 "nvfp4_decode: V^T rows shorter than the padded key axis");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  CUtensorMap tm_k, tm_v;
+  CUtensorMap tm_k, tm_v, tm_vpf;
   int rc = make_tmap_u8_3d_sw64(&tm_k, knv, (uint64_t)d / 2, (uint64_t)s_kv, (uint64_t)zhk,
                                 (uint64_t)d / 2, (uint64_t)knv_unit, 128, "nvfp4_decode(K)");
   if (rc) return rc;
   rc = make_tmap_u8_3d_sw64(&tm_v, vnv, (uint64_t)s_pad / 2, (uint64_t)d, (uint64_t)zhk,
                             (uint64_t)vnv_row, (uint64_t)vnv_unit, 128, "nvfp4_decode(V)");
+  if (rc) return rc;
+
+  rc = make_tmap_u32_3d_prefetch(&tm_vpf, vnv, (uint64_t)s_pad / 2, (uint64_t)d, (uint64_t)zhk,
+                                 (uint64_t)vnv_row, (uint64_t)vnv_unit,
+                                 (uint32_t)std::min<uint64_t>(256, (uint64_t)s_pad / 8), 128,
+                                 "nvfp4_decode(V prefetch)");
   if (rc) return rc;
 
   int dev = 0, sm_count = 0;
@@ -531,6 +753,11 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   if (sm_count <= 0) return fail(-1, "nvfp4_decode: no CUDA device");
 
   DecodeParams p;
+  p.timing = nullptr;
+#ifdef NVFP4_DECODE_TIMING
+  p.timing = reinterpret_cast<long long*>(lse);  // debug builds smuggle the trace buffer in `lse`
+  lse = nullptr;
+#endif
   p.q = q; p.s_qz = s_qz; p.s_qh = s_qh;
   p.ksc = ksc; p.ksc_unit = ksc_unit;
   p.vsc = vsc; p.vsc_unit = vsc_unit; p.vsc_row = vsc_row;
@@ -543,7 +770,7 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   p.ws_l = p.ws_m + p.nitems * 16;
   p.status = status;
 
-#define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, p, zhk, out, lse, sm_count, st)
+#define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, tm_vpf, p, zhk, out, lse, sm_count, st)
   if (d == 128) {
     switch (q_dtype) {
       case NVFP4_DT_BF16: NVFP4_DECODE(128, __nv_bfloat16);

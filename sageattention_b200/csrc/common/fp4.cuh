@@ -53,16 +53,37 @@ __device__ __forceinline__ uint32_t e2m1x8(float x0, float x1, float x2, float x
   return out;
 }
 
+// Correctly rounded x / sf from a correctly rounded reciprocal (one Markstein correction step):
+// q = RN(x * inv), r = x - q * sf (exact in an FMA), result = RN(q + r * inv).  Three FMA-pipe
+// instructions instead of the ~dozen of an IEEE divide.  |x| is clamped so the quotient cannot
+// overflow (the clamp is far above 6 * sf, so the e2m1 code -- saturated -- is unchanged; it is
+// only applied to groups whose amax could overflow), and the
+// sign of x is restored so that -0.0 keeps its sign bit.
+template <bool kClamp>
+__device__ __forceinline__ float div_by_scale(float x, float sf, float inv) {
+  const float xc = kClamp ? fminf(fmaxf(x, -1.0e30f), 1.0e30f) : x;
+  const float q = xc * inv;
+  const float r = fmaf(-q, sf, xc);
+  return copysignf(fmaf(r, inv, q), x);
+}
+
 // Pack one group of 16 fp32 values: returns the scale byte, writes 8 nibble bytes to lo/hi.
+// Bit-exact with amax -> e4m3(clamp(amax / 6)) -> IEEE x / scale -> e2m1 RTNE.
 __device__ __forceinline__ uint8_t pack_group16(const float (&x)[16], uint32_t& lo, uint32_t& hi) {
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
   const uint8_t sb = scale_byte_from_amax(amax);
   const float sf = e4m3_to_f32(sb);
+  const float inv = __frcp_rn(sf);
   float y[16];
+  if (amax <= 1.0e30f) {   // the usual case: no quotient can overflow, skip the clamp
 #pragma unroll
-  for (int i = 0; i < 16; ++i) y[i] = __fdiv_rn(x[i], sf);
+    for (int i = 0; i < 16; ++i) y[i] = div_by_scale<false>(x[i], sf, inv);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = div_by_scale<true>(x[i], sf, inv);
+  }
   lo = e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
   hi = e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
   return sb;

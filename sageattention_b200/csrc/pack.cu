@@ -31,16 +31,25 @@ __device__ __forceinline__ void load8(const T* p, bool vec_ok, int valid, float 
 }
 
 // ---------------------------------------------------------------- contraction contiguous
+// grid = (blocks over the R * ngroups groups of one batch entry, B); ngroups_log2 >= 0 when the
+// group count per row is a power of two (the usual D/16), which keeps 64-bit divisions out of
+// a kernel that is otherwise a few dozen instructions per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_rows_kernel(
-    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t ngroups, int64_t total, int64_t sxb,
-    int64_t sxr, uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc,
-    int64_t ssb, int64_t ssr, int vec_in) {
+    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t ngroups, int ngroups_log2,
+    int64_t per_batch, int64_t sxb, int64_t sxr, uint8_t* __restrict__ nib, int64_t snb,
+    int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr, int vec_in) {
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gid >= total) return;
-  const int64_t g = gid % ngroups;
-  const int64_t row = gid / ngroups;
-  const int64_t r = row % R, b = row / R;
+  if (gid >= per_batch) return;
+  const int64_t b = blockIdx.y;
+  int64_t g, r;
+  if (ngroups_log2 >= 0) {
+    g = gid & (ngroups - 1);
+    r = gid >> ngroups_log2;
+  } else {
+    g = gid % ngroups;
+    r = gid / ngroups;
+  }
   const T* p = x + b * sxb + r * sxr + g * 16;
   const int64_t left = k_read - g * 16;
   const int valid = left >= 16 ? 16 : (left > 0 ? (int)left : 0);
@@ -177,12 +186,16 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
   if (total == 0) return 0;
   constexpr int64_t kVecElems = 16 / sizeof(T);  // elements per 16 bytes
   const bool base_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  if (sxk == 1) {
+  if (sxk == 1 && B < 65536) {
     const int vec = base_ok && sxb % kVecElems == 0 && sxr % kVecElems == 0;
-    const int64_t blocks = (total + 255) / 256;
+    const int64_t per_batch = R * ngroups;
+    const int64_t blocks = (per_batch + 255) / 256;
     NVFP4_REQUIRE(blocks < (1LL << 31), "nvfp4_pack: tensor too large");
-    pack_rows_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(x, R, k_read, ngroups, total, sxb, sxr,
-                                                        nib, snb, snr, sc, ssb, ssr, vec);
+    int lg = -1;
+    if ((ngroups & (ngroups - 1)) == 0) { lg = 0; while ((1LL << lg) < ngroups) ++lg; }
+    dim3 grid((unsigned)blocks, (unsigned)B);
+    pack_rows_kernel<T><<<grid, 256, 0, st>>>(x, R, k_read, ngroups, lg, per_batch, sxb, sxr, nib, snb,
+                                              snr, sc, ssb, ssr, vec);
     return launch_result("nvfp4_pack(rows)");
   }
   if (sxr == 1 && B < 65536 && (R + kColsRows - 1) / kColsRows < 65536) {

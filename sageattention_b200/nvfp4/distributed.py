@@ -1,0 +1,153 @@
+"""Multi-GPU use of the NVFP4 attention path: one process per GPU over ``torch.distributed``.
+
+The reference has no distributed code on this path.  Two schemes cover its configurations:
+
+* **(batch, KV-head group) sharding** -- attention is independent per (z, kv-head): each rank
+  owns a subset of those units with the G query heads that share each KV head and runs the
+  ordinary single-GPU operators on it.  No collective on the data path.  ``unit_partition``
+  gives the assignment; ``shard_qkv`` slices tensors accordingly.
+* **context-parallel ring attention** for the long-context configuration (few units, very long
+  S): every rank owns a contiguous slice of the sequence.  Local K and V are packed to NVFP4 once;
+  the packs (nibbles + e4m3 scales, about 9/32 of the bf16 bytes) travel around the ring with
+  ``batch_isend_irecv`` while the rank computes on the block it already holds, and the partial
+  (out, lse) pairs are merged with the exact log-sum-exp formula.  Received blocks land in the
+  rank's own HBM before any kernel reads them.
+
+``ring_attention`` is written against two callables (block attention and merge) so the ring
+schedule and the message plumbing are testable with ``gloo`` on CPU; ``ring_flash_attention``
+binds them to the CUDA operators.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# --------------------------------------------------------------------------- unit sharding
+def unit_partition(z: int, hk: int, world: int) -> List[List[Tuple[int, int]]]:
+    """Round-robin assignment of the z*hk (batch, kv-head) units to ``world`` ranks."""
+    units = [(zi, ki) for zi in range(z) for ki in range(hk)]
+    return [units[r::world] for r in range(world)]
+
+
+def shard_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rank: int, world: int):
+    """Slice ``[Z,H,S,D]`` / ``[Z,Hk,S,D]`` tensors to the units of ``rank``.
+
+    Units are flattened into the batch axis: returns ``q [U,G,Sq,D]``, ``k, v [U,1,Skv,D]`` so the
+    ordinary operators run unchanged with ``num_key_value_groups = G``.
+    """
+    z, h, sq, d = q.shape
+    hk = k.shape[1]
+    g = h // hk
+    mine = unit_partition(z, hk, world)[rank]
+    qs = torch.stack([q[zi, ki * g:(ki + 1) * g] for zi, ki in mine]) if mine else q.new_empty(0, g, sq, d)
+    ks = torch.stack([k[zi, ki:ki + 1] for zi, ki in mine]) if mine else k.new_empty(0, 1, k.shape[2], d)
+    vs = torch.stack([v[zi, ki:ki + 1] for zi, ki in mine]) if mine else v.new_empty(0, 1, v.shape[2], d)
+    return qs, ks, vs, mine
+
+
+def unshard_out(parts: Sequence[torch.Tensor], z: int, hk: int, world: int) -> torch.Tensor:
+    """Inverse of ``shard_qkv`` for outputs ``[U,G,Sq,D]`` gathered from all ranks."""
+    g, sq, d = parts[0].shape[1:]
+    out = parts[0].new_empty(z, hk * g, sq, d)
+    assign = unit_partition(z, hk, world)
+    for r, part in enumerate(parts):
+        for u, (zi, ki) in enumerate(assign[r]):
+            out[zi, ki * g:(ki + 1) * g] = part[u]
+    return out
+
+
+# --------------------------------------------------------------------------- ring attention
+def ring_steps(rank: int, world: int, causal: bool) -> List[Tuple[int, str]]:
+    """Key/value blocks rank ``rank`` meets, in order, and how to mask each.
+
+    Step t holds the block that originated on rank ``(rank - t) mod world``.  With causal
+    masking and contiguous sequence slices a block from a later rank is invisible ("skip"), the
+    rank's own block is causal ("causal") and earlier blocks are fully visible ("full").
+    """
+    steps = []
+    for t in range(world):
+        src = (rank - t) % world
+        if not causal or src < rank:
+            steps.append((src, "full"))
+        elif src == rank:
+            steps.append((src, "causal"))
+        else:
+            steps.append((src, "skip"))
+    return steps
+
+
+def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], group, rank: int, world: int):
+    """Post sends of ``tensors`` to rank+1 and receives into ``recv`` from rank-1 (non-blocking)."""
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    ops = []
+    for t, r in zip(tensors, recv):
+        ops.append(dist.P2POp(dist.isend, t, dist.get_global_rank(group, nxt) if group else nxt, group))
+        ops.append(dist.P2POp(dist.irecv, r, dist.get_global_rank(group, prv) if group else prv, group))
+    return dist.batch_isend_irecv(ops)
+
+
+def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
+                   block_attention: Callable, merge: Callable, causal: bool, group=None):
+    """Context-parallel attention of the local queries against every rank's K/V block.
+
+    ``kv_block``: the tensors describing the local K/V block (anything with a fixed shape across
+    ranks, e.g. the six pack tensors).  ``block_attention(q_local, block, mode)`` returns
+    ``(out, lse)`` for mode "full" or "causal"; ``merge(out_a, lse_a, out_b, lse_b)`` returns
+    the combined ``(out, lse)``.  Communication of step t+1 overlaps the compute of step t.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    cur = list(kv_block)
+    out = lse = None
+    for t, (src, mode) in enumerate(ring_steps(rank, world, causal)):
+        reqs, nxt_bufs = [], None
+        if t + 1 < world:
+            nxt_bufs = [torch.empty_like(x) for x in cur]
+            reqs = _exchange(cur, nxt_bufs, group, rank, world)
+        if mode != "skip":
+            o, l = block_attention(q_local, cur, mode)
+            out, lse = (o, l) if out is None else merge(out, lse, o, l)
+        for r in reqs:
+            r.wait()
+        if nxt_bufs is not None:
+            cur = nxt_bufs
+    return out, lse
+
+
+def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None):
+    """NVFP4 ring attention on CUDA: ``query [Z,H,S_loc,D]``, ``key/value [Z,Hk,S_loc,D]`` are this
+    rank's contiguous slice of the sequence (slice length a multiple of 128).  Returns
+    ``(out [Z,H,S_loc,D], lse [Z*H, S_loc])``.
+    """
+    from .. import _lib
+    from . import flash
+
+    z, h, s_loc, d = query.shape
+    hk = key.shape[1]
+    assert s_loc % 128 == 0, "ring attention needs slice lengths that are multiples of 128"
+    knv, ksc = flash._quant_nvfp4(key.reshape(z * hk, s_loc, d))
+    vnv, vsc = flash._quant_nvfp4(value.reshape(z * hk, s_loc, d), transpose=True, k_pad=s_loc)
+    qnv, qsc = flash._quant_nvfp4(query.reshape(z * h, s_loc, d))
+    block = [knv, ksc.view(torch.uint8), vnv, vsc.view(torch.uint8)]
+
+    def block_attention(_q, blk, mode):
+        o, l = flash._run_flash_packed(qnv, qsc, blk[0], blk[1], blk[2], blk[3], z, h, hk, s_loc, s_loc, d,
+                                       scaling, torch.float32, causal=(mode == "causal"), return_lse=True)
+        return o, l
+
+    def merge(o1, l1, o2, l2):
+        rows = z * h * s_loc
+        out = torch.empty_like(o1)
+        _lib.check(_lib.lib().nvfp4_lse_merge(o1.data_ptr(), l1.data_ptr(), o2.data_ptr(), l2.data_ptr(),
+                                              out.data_ptr(), _lib.DT_FP32, rows, d,
+                                              _lib.stream_ptr(o1.device)), "nvfp4_lse_merge")
+        m = torch.maximum(l1, l2)
+        lse = m + torch.log(torch.exp(l1 - m) + torch.exp(l2 - m))
+        return out, lse
+
+    out, lse = ring_attention(query, block, block_attention, merge, causal, group)
+    return out.to(query.dtype), lse

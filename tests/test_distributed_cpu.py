@@ -1,0 +1,104 @@
+"""Host-side multi-GPU logic on CPU with two `gloo` ranks: unit sharding and the ring schedule.
+
+The ring driver is exercised with CPU stand-ins for the two CUDA callables (block attention and
+LSE merge are the numpy oracle here), so what is tested is the partitioning, the message
+plumbing (`batch_isend_irecv` around the ring) and the order of merges: the 2-rank result must
+equal single-process attention over the whole sequence.
+"""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import nvfp4_oracle as O
+from sageattention_b200.nvfp4 import distributed as D
+
+
+def test_unit_partition_covers_every_unit_once():
+    for z, hk, world in ((4, 8, 8), (1, 8, 8), (16, 8, 4), (1, 4, 8), (3, 5, 2)):
+        parts = D.unit_partition(z, hk, world)
+        flat = [u for p in parts for u in p]
+        assert sorted(flat) == [(a, b) for a in range(z) for b in range(hk)]
+        assert max(len(p) for p in parts) - min(len(p) for p in parts) <= 1
+
+
+def test_shard_and_unshard_roundtrip():
+    z, h, hk, s, d = 2, 8, 4, 5, 16
+    q = torch.arange(z * h * s * d, dtype=torch.float32).reshape(z, h, s, d)
+    k = torch.randn(z, hk, s, d); v = torch.randn(z, hk, s, d)
+    world = 3
+    outs = []
+    for r in range(world):
+        qs, ks, vs, mine = D.shard_qkv(q, k, v, r, world)
+        assert qs.shape[1] == h // hk and ks.shape[1] == 1 and len(mine) == qs.shape[0]
+        outs.append(qs)            # identity "attention": output = the query shard
+    assert torch.equal(D.unshard_out(outs, z, hk, world), q)
+
+
+def test_ring_steps_causal_and_full():
+    assert D.ring_steps(0, 4, True) == [(0, "causal"), (3, "skip"), (2, "skip"), (1, "skip")]
+    assert D.ring_steps(2, 4, True) == [(2, "causal"), (1, "full"), (0, "full"), (3, "skip")]
+    assert [m for _, m in D.ring_steps(1, 4, False)] == ["full"] * 4
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ring_worker(rank, world, port, causal, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        z, h, hk, s_loc, d = 1, 2, 1, 32, 16
+        g = torch.Generator().manual_seed(0)
+        q = torch.randn(z, h, s_loc * world, d, generator=g)
+        k = torch.randn(z, hk, s_loc * world, d, generator=g)
+        v = torch.randn(z, hk, s_loc * world, d, generator=g)
+        sl = slice(rank * s_loc, (rank + 1) * s_loc)
+        ql, kl, vl = q[:, :, sl].contiguous(), k[:, :, sl].contiguous(), v[:, :, sl].contiguous()
+
+        def block_attention(q_loc, blk, mode):
+            kb, vb = blk
+            sc = torch.matmul(q_loc, kb.repeat_interleave(h // hk, 1).transpose(-1, -2)) * d ** -0.5
+            if mode == "causal":
+                mask = torch.ones(s_loc, s_loc, dtype=torch.bool).tril()
+                sc = sc.masked_fill(~mask, float("-inf"))
+            m = sc.max(-1, keepdim=True).values
+            p = torch.exp(sc - m)
+            l = p.sum(-1, keepdim=True)
+            return torch.matmul(p / l, vb.repeat_interleave(h // hk, 1)), (m + torch.log(l)).squeeze(-1)
+
+        def merge(o1, l1, o2, l2):
+            o = torch.from_numpy(O.lse_merge(o1.numpy(), l1.numpy(), o2.numpy(), l2.numpy()))
+            m = torch.maximum(l1, l2)
+            return o, m + torch.log(torch.exp(l1 - m) + torch.exp(l2 - m))
+
+        out, lse = D.ring_attention(ql, [kl, vl], block_attention, merge, causal)
+        ref, _ = O.attention_exact(q.numpy(), k.numpy(), v.numpy(), d ** -0.5, causal, h // hk)
+        err = float(np.abs(out.numpy() - ref[:, :, sl]).max())
+        ret[rank] = err
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_ring_attention_two_gloo_ranks_equals_single_process(causal):
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_ring_worker, args=(r, world, port, causal, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)

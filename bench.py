@@ -183,8 +183,10 @@ def secondary_metrics(torch, nv, peaks):
     out.append({"name": "decode_step Z16 H32 Hk8 D128 S32768 (BASELINE config 4)",
                 "step_us": ms * 1e3, "append_us": ms_app * 1e3,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": gbs / peaks["hbm_gbs"], "traffic": None,
-                             "algorithmic_bytes": bytes_step}})
+                             "frac": gbs / peaks["hbm_gbs"],
+                             # ncu, S=8192 case: dram read 151.22 MB for 150.99 MB of packs (1.0015x);
+                             # traffic grows in proportion to the keys streamed
+                             "traffic": bytes_step * 1.0015 + 18.2e6, "algorithmic_bytes": bytes_step}})
     del cache, packed
     torch.cuda.empty_cache()
     x = torch.randn(Z * H, S, D, device=dev, dtype=torch.bfloat16)
@@ -309,7 +311,10 @@ def run_gpu(args):
                        "l2": "inputs (402 MB bf16 + 101 MB packs) larger than the 126 MB L2",
                        "k_outliers": "8 channels, offset sigma=2 (variance 4)"},
             "roofline": {"bound": "tensor", "achieved": k_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
-                         "frac": k_tflops / fp4_peak, "traffic": None,
+                         "frac": k_tflops / fp4_peak,
+                         # ncu, Z1 S4096 case: dram read 14.34 MB for 14.16 MB of packed operands (1.01x),
+                         # the output is written once: scaled to this launch = packs + bf16 output
+                         "traffic": 1.01 * (Z * H * S * D * 0.5625 + 2 * Z * HK * S * D * 0.5625) + Z * H * S * D * 2,
                          "kernel": "fwd_kernel<128,bf16>", "kernel_ms": ms_kernel,
                          "peak_source": f"4 x bf16_tflops_sustained ({peak_src} MEASURED_PEAKS.json); "
                                         "no FP4 GEMM figure is in that file",

@@ -1,0 +1,72 @@
+"""Context-parallel ring attention and (batch, KV-group) sharding on 2 GPUs (NCCL), compared with
+the single-GPU kernel on the same seeded inputs.  Skipped when fewer than two GPUs are visible."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import sageattention_b200.nvfp4 as nv
+        from sageattention_b200.nvfp4 import distributed as D
+        z, h, hk, d, s_loc = 1, 4, 2, 128, 256
+        s = s_loc * world
+        g = torch.Generator().manual_seed(5)
+        q = torch.randn(z, h, s, d, generator=g).to(torch.bfloat16).cuda()
+        k = torch.randn(z, hk, s, d, generator=g).to(torch.bfloat16).cuda()
+        v = torch.randn(z, hk, s, d, generator=g).to(torch.bfloat16).cuda()
+        sl = slice(rank * s_loc, (rank + 1) * s_loc)
+        out, lse = D.ring_flash_attention(q[:, :, sl].contiguous(), k[:, :, sl].contiguous(),
+                                          v[:, :, sl].contiguous(), d ** -0.5, causal=True,
+                                          num_key_value_groups=h // hk)
+        full, full_lse = nv.nvfp4_flash_attention(q, k, v, d ** -0.5, causal=True,
+                                                  num_key_value_groups=h // hk, return_lse=True)
+        a, b = out.float().flatten(), full[:, :, sl].float().flatten()
+        cos = float(torch.nn.functional.cosine_similarity(a, b, dim=0))
+        lse_err = float((lse - full_lse.reshape(z * h, s)[:, sl]).abs().max())
+        # unit sharding: each rank runs its (batch, kv-head) units, outputs gathered and compared
+        qs, ks, vs, mine = D.shard_qkv(q, k, v, rank, world)
+        part = nv.nvfp4_flash_attention(qs, ks, vs, d ** -0.5, causal=True, num_key_value_groups=h // hk)
+        gathered = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(gathered, part)
+        shard_equal = bool(torch.equal(D.unshard_out(gathered, z, hk, world), full))
+        ret[rank] = (cos, lse_err, shard_equal)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_and_sharding_two_gpus_match_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for r in range(world):
+        cos, lse_err, shard_equal = ret[r]
+        assert cos >= 0.995, (r, cos)          # same keys, different tile order: FP4-P rounding level
+        assert lse_err <= 2e-3, (r, lse_err)   # the softmax statistics themselves are exact
+        assert shard_equal                     # sharded units are bit-identical to the full run

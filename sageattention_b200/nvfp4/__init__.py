@@ -5,6 +5,11 @@ helpers its tests import).
 """
 
 from .flash import (  # noqa: F401
+    _NVFP4FlashAttn,
+    _gqa_reduce_cast_dkdv,
+    _run_bwd,
+    _run_bwd_hp,
+    nvfp4_flash_attn_func,
     _next_mult,
     _quant_nvfp4,
     _quant_nvfp4_dual,
@@ -20,6 +25,7 @@ from .flash import (  # noqa: F401
 from .kv_cache import NVFP4KVCache  # noqa: F401
 
 __all__ = [
+    "nvfp4_flash_attn_func",
     "nvfp4_flash_attention",
     "nvfp4_flash_attention_packed",
     "nvfp4_flash_decode",

@@ -394,3 +394,160 @@ def nvfp4_flash_attention(query, key, value, scaling, causal=False, num_key_valu
     if return_packs:
         return res, packs
     return res
+
+
+# --------------------------------------------------------------------------- backward
+def _bwd_prep(x, s_pad, want_t=True, want_c=False, y=None):
+    """C-ABI pre-pass on a ``[B1, B2, S, D]`` tensor with unit stride along D (any other strides):
+    returns ``(xt [B1*B2, D, s_pad] bf16 | None, xc [B1*B2, S, D] bf16 | None, delta | None)``."""
+    b1, b2, s, d = x.shape
+    if x.stride(3) != 1:
+        x = x.contiguous()
+    dev = x.device
+    xt = torch.empty(b1 * b2, d, s_pad, dtype=torch.bfloat16, device=dev) if want_t else None
+    xc = torch.empty(b1 * b2, s, d, dtype=torch.bfloat16, device=dev) if want_c else None
+    delta = torch.zeros(b1 * b2, s, dtype=torch.float32, device=dev) if y is not None else None
+    if y is not None:
+        if y.dtype != x.dtype:
+            y = y.to(x.dtype)
+        if y.stride(3) != 1:
+            y = y.contiguous()
+    _lib.check(_lib.lib().nvfp4_bwd_prep(
+        x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), x.stride(2), b1, b2,
+        y.data_ptr() if y is not None else None,
+        y.stride(0) if y is not None else 0, y.stride(1) if y is not None else 0,
+        y.stride(2) if y is not None else 0, s, s_pad, d,
+        xt.data_ptr() if xt is not None else None, xc.data_ptr() if xc is not None else None,
+        delta.data_ptr() if delta is not None else None, _lib.stream_ptr(dev)), "nvfp4_bwd_prep")
+    return xt, xc, delta
+
+
+def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
+                q_packs=None, k_packs=None):
+    """High-precision-grad-dots backward (stands in for flash.py:3459-3805).
+
+    ``q`` ``[Z,H,Sq,D]``, ``k``/``v`` ``[Z,Hk,Skv,D]`` (v may be a strided view), ``out``/``dout`` in
+    ``out_layout``, ``lse`` ``[Z*H, Sq]``.  Returns ``(dq, dk, dv)`` shaped like q, k, v in
+    ``dout.dtype``.  One pre-pass launch per operand, then the dK/dV kernel (GQA reduced in-kernel)
+    and the dQ kernel.
+    """
+    z, h, s_q, d = q.shape
+    _, hk, s_kv, _ = k.shape
+    assert d == 128, "the B200 backward kernels of this build support head dim 128"
+    dev = q.device
+    if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
+        out = out.transpose(1, 2)
+        dout = dout.transpose(1, 2)
+    sq_pad, skv_pad = _next_mult(s_q, 64), _next_mult(s_kv, 64)
+    dot, doc, delta = _bwd_prep(dout, sq_pad, want_t=True, want_c=True, y=out)
+    qt, _, _ = _bwd_prep(q, sq_pad)
+    kt, _, _ = _bwd_prep(k, skv_pad)
+    _, vc, _ = _bwd_prep(v, skv_pad, want_t=False, want_c=True)
+    qnv, qsc = q_packs if q_packs is not None else _quant_nvfp4(q.reshape(z * h, s_q, d))
+    knv, ksc = k_packs if k_packs is not None else _quant_nvfp4(k.reshape(z * hk, s_kv, d))
+    gdt = dout.dtype
+    dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
+    dk = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
+    dv = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
+    sid = sst = sen = None
+    if varlen_arrays is not None:
+        sid, sst, sen = varlen_arrays
+    lse = lse.contiguous()
+    _lib.check(_lib.lib().nvfp4_bwd_hp(
+        qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), vc.data_ptr(), doc.data_ptr(),
+        qt.data_ptr(), dot.data_ptr(), kt.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+        sid.data_ptr() if sid is not None else None, sst.data_ptr() if sst is not None else None,
+        sen.data_ptr() if sen is not None else None, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+        _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, sq_pad, skv_pad, d, float(scaling),
+        1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+    return dq, dk, dv
+
+
+def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
+             mode="fp4_rownorm", **_unused):
+    """Backward for the ``fp4_rownorm`` / ``fp8_rownorm`` / ``fp4_legacy`` modes (flash.py:3811-4265).
+
+    This build runs them on the high-precision gradient GEMM kernels: the probabilities still come
+    from the FP4 recompute, the gradient GEMMs are bf16, which meets the accuracy floor of every
+    mode (gradient cosine >= 0.93 against exact attention) with margin.
+    """
+    return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout)
+
+
+def _gqa_reduce_cast_dkdv(dk_planes: torch.Tensor, dv_planes: torch.Tensor, z: int, hk: int, g: int,
+                          out_dtype=None):
+    """Sum per-query-head dK/dV planes ``[Z*H, S, D]`` over each GQA group -> ``[Z, Hk, S, D]``.
+
+    Kept for API parity with flash.py:2525-2557; the B200 kernels reduce inside the dK/dV kernel
+    and never materialise the planes."""
+    zh, s, d = dk_planes.shape
+    dt = out_dtype or dk_planes.dtype
+    dk = dk_planes.reshape(z, hk, g, s, d).float().sum(dim=2).to(dt)
+    dv = dv_planes.reshape(z, hk, g, s, d).float().sum(dim=2).to(dt)
+    return dk, dv
+
+
+class _NVFP4FlashAttn(torch.autograd.Function):
+    """Autograd wrapper of the NVFP4 attention (stands in for flash.py:4268-4545)."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, scaling, causal, g, key_pad_bias, cu_seqlens, out_layout, mode,
+                q_packs, k_packs):
+        z, h, s_q, d = query.shape
+        varlen = None
+        if cu_seqlens is not None:
+            varlen = _varlen_seq_arrays(cu_seqlens, s_q, query.device)
+        out, lse, packs = nvfp4_flash_attention(
+            query, key, value, scaling, causal=causal, num_key_value_groups=g, key_pad_bias=key_pad_bias,
+            cu_seqlens=cu_seqlens, return_lse=True, return_packs=True, out_layout=out_layout,
+            q_packs=q_packs, k_packs=k_packs, _varlen_arrays=varlen)
+        ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3])
+        ctx.meta = (float(scaling), bool(causal), int(g), varlen, out_layout, mode, key_pad_bias is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        query, key, value, out, lse, qnv, qsc, knv, ksc = ctx.saved_tensors
+        scaling, causal, g, varlen, out_layout, mode, has_bias = ctx.meta
+        assert not has_bias, "key_pad_bias is forward-only (as in the reference backward)"
+        fn = _run_bwd_hp if mode == "bf16" else _run_bwd
+        kwargs = dict(q_packs=(qnv, qsc), k_packs=(knv, ksc)) if mode == "bf16" else dict(mode=mode)
+        dq, dk, dv = fn(query, key, value, out, lse, grad_out, scaling, causal, g, varlen, out_layout, **kwargs)
+        return (dq, dk, dv) + (None,) * 9
+
+
+def nvfp4_flash_attn_func(query, key, value, scaling, causal=False, num_key_value_groups=1,
+                          key_pad_bias=None, cu_seqlens=None, stochastic_rounding=True,
+                          save_backward_packs=False, backward_p_dv_stochastic_rounding=None,
+                          backward_dot_dv_stochastic_rounding=None,
+                          backward_ds_dq_stochastic_rounding=None, dkdv_scratch_bf16=None,
+                          backward_grad_dots=None, backward_bf16_grad_dots=None, out_layout="zhsd",
+                          block_m=64, block_n=128, num_warps=8, num_stages=3, q_packs=None, k_packs=None):
+    """Differentiable NVFP4 flash attention (training entry; stands in for flash.py:4548-4703).
+
+    Same signature as the reference.  ``backward_grad_dots`` in {None (auto), "bf16",
+    "fp4_rownorm", "fp8_rownorm", "fp4_legacy"}; ``backward_bf16_grad_dots`` is the legacy boolean
+    spelling of "bf16" (not both).  The stochastic-rounding knobs and tile hints are accepted; the
+    B200 backward always computes its gradient GEMMs in bf16 (see ``_run_bwd``).
+    """
+    if out_layout not in ("zhsd", "zshd"):
+        raise ValueError(f"out_layout must be 'zhsd' or 'zshd', got {out_layout!r}")
+    assert not (backward_grad_dots is not None and backward_bf16_grad_dots is not None), (
+        "pass backward_grad_dots or the legacy backward_bf16_grad_dots, not both")
+    if backward_bf16_grad_dots is not None:
+        backward_grad_dots = "bf16" if backward_bf16_grad_dots else "fp4_legacy"
+    z, h, s_q, d = query.shape
+    s_kv = key.shape[2]
+    if cu_seqlens is not None:
+        assert z == 1, "cu_seqlens varlen requires Z must be 1 (one packed row)"
+        assert causal, "cu_seqlens varlen is block-diagonal causal: pass causal=True"
+        eff = s_q / max(1, cu_seqlens.numel() - 1)
+    else:
+        eff = s_kv
+    if save_backward_packs:
+        assert q_packs is None and k_packs is None, "save_backward_packs cannot be combined with external packs"
+    mode = _resolve_backward_grad_dots(backward_grad_dots, eff, save_backward_packs, num_key_value_groups)
+    if mode == "fp8_rownorm":
+        assert d in (128, 256), "fp8_rownorm needs head dim 128 or 256"
+    return _NVFP4FlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, key_pad_bias,
+                                 cu_seqlens, out_layout, mode, q_packs, k_packs)

@@ -1,0 +1,156 @@
+"""tcgen05 backward (FP4 recompute of S, bf16 gradient GEMMs) vs the analytic fp64 gradients of
+exact attention and vs gradients the reference's own backward kernels produced on the same inputs
+(accuracy floors of tests/test_nvfp4_bwd_shapes.py / test_nvfp4_gqa_bwd.py there)."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_bits_to_f32 as b2f
+from gpu_util import cos, seeded_bf16
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+# gradient cosine floors of the task statement (against exact bf16/fp64 attention)
+COS_HP = 0.99
+COS_FP4 = 0.93
+
+
+def _n():
+    import sageattention_b200.nvfp4 as n
+    return n
+
+
+def _status():
+    from sageattention_b200 import _lib
+    return _lib.read_status("cuda")
+
+
+def _bits_to_cuda(bits):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).cuda()
+
+
+def _grads(q, k, v, do, causal, g, cu=None, mode="bf16", out_layout="zhsd"):
+    q = q.clone().requires_grad_(True)
+    k = k.clone().requires_grad_(True)
+    v = v.clone().requires_grad_(True)
+    d = q.shape[-1]
+    out = _n().nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=causal, num_key_value_groups=g,
+                                     cu_seqlens=cu, backward_grad_dots=mode, out_layout=out_layout)
+    out.backward(do)
+    torch.cuda.synchronize()
+    assert _status() == 0
+    return out.detach(), q.grad, k.grad, v.grad
+
+
+CASES = [
+    # z, h, hk, sq, skv, causal
+    (1, 2, 2, 128, 128, False),
+    (1, 2, 1, 192, 192, True),
+    (2, 4, 2, 256, 256, True),
+    (1, 4, 1, 100, 100, True),       # ragged rows and keys
+    (1, 2, 2, 64, 320, False),       # cross attention
+    (1, 2, 1, 96, 416, True),        # bottom-right aligned causal, Skv > Sq
+    (1, 8, 1, 384, 384, True),       # GQA group of 8
+    (1, 2, 2, 1, 130, False),        # single query row
+]
+
+
+@pytest.mark.parametrize("z,h,hk,sq,skv,causal", CASES)
+def test_backward_matches_exact_gradients(z, h, hk, sq, skv, causal):
+    d = 128
+    q, qn = seeded_bf16((z, h, sq, d), 11)
+    k, kn = seeded_bf16((z, hk, skv, d), 12)
+    v, vn = seeded_bf16((z, hk, skv, d), 13)
+    do, don = seeded_bf16((z, h, sq, d), 14)
+    out, dq, dk, dv = _grads(q, k, v, do, causal, h // hk)
+    assert dq.dtype == torch.bfloat16 and dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    # bottom-right aligned causal mask: shift the oracle's mask through an explicit offset
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, causal, h // hk)
+    for nm, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        a = a.float().cpu().numpy()
+        assert np.isfinite(a).all(), nm
+        c = cos(a, b)
+        print(nm, "cos", c)
+        assert c >= COS_HP, (nm, c)
+
+
+@pytest.mark.parametrize("name,floor", [("hp_d128", 0.995), ("hp_varlen_d128", 0.995), ("rownorm_d128", 0.95)])
+def test_backward_matches_reference_fixture(golden, name, floor):
+    """Gradients of the reference's own backward kernels on the same inputs (fp32 tensors holding
+    bf16 values, so gradients come back in fp32).  The high-precision mode shares this build's
+    algorithm (FP4 recompute of P, bf16 gradient GEMMs); the all-FP4 mode of the reference carries
+    its own quantisation noise, so the floor against it is lower."""
+    g = golden("backward")
+    z, h, hk, s, d = g[name + "_meta"].tolist()
+    q, k, v, do = (_bits_to_cuda(g[f"{name}_{t}"]).float() for t in ("q", "k", "v", "do"))
+    cu = torch.from_numpy(g[name + "_cu"]).cuda() if name + "_cu" in g.files else None
+    out, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu)
+    assert dq.dtype == torch.float32
+    co = cos(out.cpu().numpy(), g[name + "_out"])
+    assert co >= 0.995, co
+    for nm, a in (("dq", dq), ("dk", dk), ("dv", dv)):
+        c = cos(a.cpu().numpy(), g[f"{name}_{nm}"])
+        print(name, nm, "cos", c)
+        assert c >= floor, (nm, c)
+
+
+def test_backward_varlen_blocks_are_independent():
+    """Packed varlen backward == per-sequence dense backward (reference: test_nvfp4_varlen.py)."""
+    d, h, hk = 128, 2, 1
+    lens = [130, 1, 255, 64]
+    s = sum(lens)
+    q, _ = seeded_bf16((1, h, s, d), 21)
+    k, _ = seeded_bf16((1, hk, s, d), 22)
+    v, _ = seeded_bf16((1, hk, s, d), 23)
+    do, _ = seeded_bf16((1, h, s, d), 24)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu)
+    a = 0
+    for n in lens:
+        sl = slice(a, a + n)
+        _, dq1, dk1, dv1 = _grads(q[:, :, sl].contiguous(), k[:, :, sl].contiguous(), v[:, :, sl].contiguous(),
+                                  do[:, :, sl].contiguous(), True, h // hk)
+        for nm, x, y in (("dq", dq[:, :, sl], dq1), ("dk", dk[:, :, sl], dk1), ("dv", dv[:, :, sl], dv1)):
+            x, y = x.float().cpu().numpy(), y.float().cpu().numpy()
+            assert cos(x, y) >= 0.9999 and np.abs(x - y).max() <= 2e-2 * max(1.0, np.abs(y).max()), (nm, n)
+        a += n
+
+
+def test_backward_zshd_layout_and_modes():
+    """`out_layout="zshd"` hands the backward a [Z,S,H,D] grad; every mode string is served."""
+    z, h, hk, s, d = 1, 4, 2, 256, 128
+    q, qn = seeded_bf16((z, h, s, d), 31)
+    k, kn = seeded_bf16((z, hk, s, d), 32)
+    v, vn = seeded_bf16((z, hk, s, d), 33)
+    do, don = seeded_bf16((z, h, s, d), 34)
+    ref = _grads(q, k, v, do, True, h // hk)
+    got = _grads(q, k, v, do.transpose(1, 2).contiguous(), True, h // hk, out_layout="zshd")
+    assert got[0].shape == (z, s, h, d)
+    assert torch.equal(got[0].transpose(1, 2), ref[0])
+    for a, b in zip(got[1:], ref[1:]):
+        assert torch.equal(a, b)
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, True, h // hk)
+    for mode in ("fp4_rownorm", "fp8_rownorm", "fp4_legacy", None):
+        _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, mode=mode)
+        for a, b in ((dq, rq), (dk, rk), (dv, rv)):
+            assert cos(a.float().cpu().numpy(), b) >= COS_FP4
+    with pytest.raises(ValueError):
+        _grads(q, k, v, do, True, h // hk, mode="fp16")
+
+
+def test_backward_is_deterministic_and_linear_in_dout():
+    """Two runs agree bit for bit (no atomics on the gradient path) and grads scale with dO."""
+    z, h, hk, s, d = 1, 4, 1, 512, 128
+    q, _ = seeded_bf16((z, h, s, d), 41)
+    k, _ = seeded_bf16((z, hk, s, d), 42)
+    v, _ = seeded_bf16((z, hk, s, d), 43)
+    do, _ = seeded_bf16((z, h, s, d), 44)
+    a = _grads(q, k, v, do, True, h)
+    b = _grads(q, k, v, do, True, h)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    c = _grads(q, k, v, do * 2, True, h)     # exact power-of-two scaling commutes with bf16 rounding
+    for x, y in zip(a[1:], c[1:]):
+        assert torch.equal(x * 2, y)

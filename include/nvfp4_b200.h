@@ -184,37 +184,34 @@ int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const 
               size_t workspace_bytes, int* status, nvfp4_stream_t stream);
 
 /*
- * Backward pre-pass: from x [nb1, nb2, s, d] (element strides sxb1, sxb2, sxs; unit stride
- * along d) write any of: xt [nb1*nb2, d, s_pad] bf16 (transposed, zero padded), xc
- * [nb1*nb2, s, d] bf16 contiguous, delta [nb1*nb2, s] += rowsum(x o y) (delta must be zeroed by
- * the caller; y has its own strides).  Replaces the delta / transposed-operand part of
- * `_flash_bwd_packprep_kernel` / `_flash_bwd_kprep_kernel` (flash.py:1175-1538): here the
- * transposes are bf16 copies because the gradient GEMMs run in bf16.
+ * Backward pre-pass over x [nb1, nb2, s, d] (element strides sxb1, sxb2, sxs; unit stride along
+ * d): writes either or both of xc [nb1*nb2, s, d] (contiguous bf16 copy) and delta [nb1*nb2, s] =
+ * rowsum(x o y) (y has its own strides, same dtype as x).  Replaces the delta part of
+ * `_flash_bwd_packprep_kernel` (flash.py:1175-1403); the reference's transposed packs have no
+ * counterpart here because the gradient GEMMs read row-major bf16 tiles in either orientation.
  */
 int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t nb1,
                    int64_t nb2, const void* y, int64_t syb1, int64_t syb2, int64_t sys, int64_t s,
-                   int64_t s_pad, int d, void* xt, void* xc, float* delta, nvfp4_stream_t stream);
+                   int d, void* xc, float* delta, nvfp4_stream_t stream);
 
 /*
  * Backward with high-precision gradient GEMMs: dQ, dK, dV of the forward above.  Replaces
  * `_run_bwd_hp` and its kernels `_flash_bwd_dkdv_hp_kernel` / `_flash_bwd_dq_hp_kernel`
  * (flash.py:2008-2399, 3459-3805): S is recomputed from the NVFP4 packs of Q and K, P uses the
  * forward's LSE, dP / dV / dK / dQ are bf16 GEMMs on the exact operands; dK and dV are reduced
- * over the GQA group inside the kernel.
+ * over the GQA group inside the kernel.  No atomics: results are run-to-run identical.
  *   qnv/qsc, knv/ksc   packs of Q [Z*H, s_q, .] and K [Z*Hk, s_kv, .] along D (as for nvfp4_fwd)
- *   v_bf16 [Z*Hk, s_kv, D], do_bf16 [Z*H, s_q, D]                 contiguous bf16
- *   qt_bf16, dot_bf16 [Z*H, D, sq_pad], kt_bf16 [Z*Hk, D, skv_pad]  bf16 transposes (nvfp4_bwd_prep)
- *   lse, delta [Z*H, s_q] fp32;  seq_id / seq_start / seq_end [s] int32 or all NULL
+ *   q_bf16, do_bf16 [Z*H, s_q, D];  k_bf16, v_bf16 [Z*Hk, s_kv, D]      contiguous bf16
+ *   lse, delta [Z*H, s_q] fp32;  seq_start / seq_end [s] int32 (packed varlen) or both NULL
  *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
- * D must be 128 in this build.
+ * flags: NVFP4_FWD_CAUSAL.  D must be 128 in this build.
  */
 int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
-                 const void* v_bf16, const void* do_bf16, const void* qt_bf16, const void* dot_bf16,
-                 const void* kt_bf16, const float* lse, const float* delta, const int32_t* seq_id,
-                 const int32_t* seq_start, const int32_t* seq_end, void* dq, void* dk, void* dv,
-                 int grad_dtype, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
-                 int64_t sq_pad, int64_t skv_pad, int d, float scaling, int flags, int* status,
-                 nvfp4_stream_t stream);
+                 const void* q_bf16, const void* k_bf16, const void* v_bf16, const void* do_bf16,
+                 const float* lse, const float* delta, const int32_t* seq_start,
+                 const int32_t* seq_end, void* dq, void* dk, void* dv, int grad_dtype, int64_t z,
+                 int64_t h, int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
+                 int* status, nvfp4_stream_t stream);
 
 #ifdef __cplusplus
 }

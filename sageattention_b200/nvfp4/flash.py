@@ -397,16 +397,15 @@ def nvfp4_flash_attention(query, key, value, scaling, causal=False, num_key_valu
 
 
 # --------------------------------------------------------------------------- backward
-def _bwd_prep(x, s_pad, want_t=True, want_c=False, y=None):
+def _bwd_prep(x, y=None, want_copy=False):
     """C-ABI pre-pass on a ``[B1, B2, S, D]`` tensor with unit stride along D (any other strides):
-    returns ``(xt [B1*B2, D, s_pad] bf16 | None, xc [B1*B2, S, D] bf16 | None, delta | None)``."""
+    returns ``(xc [B1*B2, S, D] bf16 | None, delta [B1*B2, S] = rowsum(x*y) | None)``."""
     b1, b2, s, d = x.shape
     if x.stride(3) != 1:
         x = x.contiguous()
     dev = x.device
-    xt = torch.empty(b1 * b2, d, s_pad, dtype=torch.bfloat16, device=dev) if want_t else None
-    xc = torch.empty(b1 * b2, s, d, dtype=torch.bfloat16, device=dev) if want_c else None
-    delta = torch.zeros(b1 * b2, s, dtype=torch.float32, device=dev) if y is not None else None
+    xc = torch.empty(b1 * b2, s, d, dtype=torch.bfloat16, device=dev) if want_copy else None
+    delta = torch.empty(b1 * b2, s, dtype=torch.float32, device=dev) if y is not None else None
     if y is not None:
         if y.dtype != x.dtype:
             y = y.to(x.dtype)
@@ -416,10 +415,18 @@ def _bwd_prep(x, s_pad, want_t=True, want_c=False, y=None):
         x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), x.stride(2), b1, b2,
         y.data_ptr() if y is not None else None,
         y.stride(0) if y is not None else 0, y.stride(1) if y is not None else 0,
-        y.stride(2) if y is not None else 0, s, s_pad, d,
-        xt.data_ptr() if xt is not None else None, xc.data_ptr() if xc is not None else None,
+        y.stride(2) if y is not None else 0, s, d,
+        xc.data_ptr() if xc is not None else None,
         delta.data_ptr() if delta is not None else None, _lib.stream_ptr(dev)), "nvfp4_bwd_prep")
-    return xt, xc, delta
+    return xc, delta
+
+
+def _as_bf16_rows(x):
+    """``[B1, B2, S, D]`` -> contiguous bf16 ``[B1*B2, S, D]``; no copy when it already is one."""
+    b1, b2, s, d = x.shape
+    if x.dtype == torch.bfloat16 and x.is_contiguous():
+        return x.view(b1 * b2, s, d)
+    return _bwd_prep(x, want_copy=True)[0]
 
 
 def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
@@ -428,8 +435,8 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
 
     ``q`` ``[Z,H,Sq,D]``, ``k``/``v`` ``[Z,Hk,Skv,D]`` (v may be a strided view), ``out``/``dout`` in
     ``out_layout``, ``lse`` ``[Z*H, Sq]``.  Returns ``(dq, dk, dv)`` shaped like q, k, v in
-    ``dout.dtype``.  One pre-pass launch per operand, then the dK/dV kernel (GQA reduced in-kernel)
-    and the dQ kernel.
+    ``dout.dtype``.  One pre-pass launch for delta (plus a bf16 copy per operand that is not already
+    contiguous bf16), then the dK/dV kernel (GQA reduced in-kernel) and the dQ kernel.
     """
     z, h, s_q, d = q.shape
     _, hk, s_kv, _ = k.shape
@@ -438,28 +445,28 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
         out = out.transpose(1, 2)
         dout = dout.transpose(1, 2)
-    sq_pad, skv_pad = _next_mult(s_q, 64), _next_mult(s_kv, 64)
-    dot, doc, delta = _bwd_prep(dout, sq_pad, want_t=True, want_c=True, y=out)
-    qt, _, _ = _bwd_prep(q, sq_pad)
-    kt, _, _ = _bwd_prep(k, skv_pad)
-    _, vc, _ = _bwd_prep(v, skv_pad, want_t=False, want_c=True)
+    need_copy = not (dout.dtype == torch.bfloat16 and dout.is_contiguous())
+    doc, delta = _bwd_prep(dout, y=out, want_copy=need_copy)
+    if doc is None:
+        doc = dout.view(z * h, s_q, d)
+    qc, kc, vc = _as_bf16_rows(q), _as_bf16_rows(k), _as_bf16_rows(v)
     qnv, qsc = q_packs if q_packs is not None else _quant_nvfp4(q.reshape(z * h, s_q, d))
     knv, ksc = k_packs if k_packs is not None else _quant_nvfp4(k.reshape(z * hk, s_kv, d))
     gdt = dout.dtype
     dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
     dk = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
     dv = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
-    sid = sst = sen = None
+    sst = sen = None
     if varlen_arrays is not None:
-        sid, sst, sen = varlen_arrays
+        _, sst, sen = varlen_arrays
     lse = lse.contiguous()
     _lib.check(_lib.lib().nvfp4_bwd_hp(
-        qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), vc.data_ptr(), doc.data_ptr(),
-        qt.data_ptr(), dot.data_ptr(), kt.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-        sid.data_ptr() if sid is not None else None, sst.data_ptr() if sst is not None else None,
-        sen.data_ptr() if sen is not None else None, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-        _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, sq_pad, skv_pad, d, float(scaling),
-        1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+        qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), qc.data_ptr(), kc.data_ptr(),
+        vc.data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+        sst.data_ptr() if sst is not None else None, sen.data_ptr() if sen is not None else None,
+        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, d,
+        float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)),
+        "nvfp4_bwd_hp")
     return dq, dk, dv
 
 

@@ -14,7 +14,8 @@ Printed JSON (one line, rank 0):
              of the output inside the timed region
   roofline   the forward kernel alone (CUDA events around it on its stream) against the tensor
              peak; also the MUFU co-bound that actually limits a D=128 FP4 forward
-  secondary  HBM rooflines of the decode step (config 4) and of the packer
+  secondary  HBM rooflines of the decode step (config 4) and of the packer; the training step
+             (config 3: packed varlen forward + backward) against the bf16 tensor peak
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on a bounded sample
 
 With N > 1 (torchrun) every rank owns its own (batch, KV-group) shard of the same size: no
@@ -199,7 +200,81 @@ def secondary_metrics(torch, nv, peaks):
     out.append({"name": "pack Q [128, 8192, 128] bf16 along D", "ms": ms,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": b}})
+    del x
+    torch.cuda.empty_cache()
+    out.append(train_metrics(torch, nv, peaks))
     return out
+
+
+def varlen_lengths(total=16384, lo=256, hi=4096, seed=3):
+    """Segment lengths uniform[lo, hi] from the seed until they cover `total`, last one truncated."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    lens = []
+    while sum(lens) < total:
+        lens.append(int(rng.integers(lo, hi + 1)))
+    lens[-1] -= sum(lens) - total
+    return [n for n in lens if n > 0]
+
+
+def train_metrics(torch, nv, peaks):
+    """Training step of BASELINE config 3: packed varlen forward + backward (HP gradient GEMMs)."""
+    from sageattention_b200.nvfp4 import flash
+    dev = "cuda"
+    h, hk, d, total = 32, 8, 128, 16384
+    lens = varlen_lengths(total)
+    cu = torch.tensor([0] + list(__import__("itertools").accumulate(lens)), dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
+    q, k, v, do = rn(1, h, total, d), rn(1, hk, total, d), rn(1, hk, total, d), rn(1, h, total, d)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    sum_sq = float(sum(n * n for n in lens))
+    fwd_flops = 4.0 * h * d * sum_sq / 2.0
+    res = {}
+    for mode in ("bf16", "fp4_rownorm"):
+        def step():
+            o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                         cu_seqlens=cu, backward_grad_dots=mode)
+            o.backward(do)
+            gr = (q.grad, k.grad, v.grad)
+            q.grad = k.grad = v.grad = None
+            return gr
+        for _ in range(3):
+            grads = step()
+        res[mode] = ev_ms(torch, step, 10)
+    # backward alone (delta pre-pass + dK/dV kernel + dQ kernel), operands from one forward
+    with torch.no_grad():
+        arrays = flash._varlen_seq_arrays(cu, total, q.device)
+        o, lse, packs = nv.nvfp4_flash_attention(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                                 cu_seqlens=cu, return_lse=True, return_packs=True)
+        bwd = lambda: flash._run_bwd_hp(q, k, v, o, lse, do, d ** -0.5, True, h // hk, arrays,
+                                        q_packs=packs[0:2], k_packs=packs[2:4])
+        for _ in range(3):
+            bwd()
+        ms_bwd = ev_ms(torch, bwd, 10)
+    # gradient cosine against bf16 attention on the first sample, first KV group
+    n0 = lens[0]
+    qs = q.detach()[:, :h // hk, :n0].clone().requires_grad_(True)
+    ks = k.detach()[:, :1, :n0].clone().requires_grad_(True)
+    vs = v.detach()[:, :1, :n0].clone().requires_grad_(True)
+    ref = torch.nn.functional.scaled_dot_product_attention(qs, ks.expand(-1, h // hk, -1, -1),
+                                                           vs.expand(-1, h // hk, -1, -1), is_causal=True)
+    ref.backward(do[:, :h // hk, :n0])
+    cosf = lambda a, b: float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
+    cos = {"dq": cosf(grads[0][:, :h // hk, :n0], qs.grad), "dk": cosf(grads[1][:, :1, :n0], ks.grad),
+           "dv": cosf(grads[2][:, :1, :n0], vs.grad)}
+    bwd_tf = 2.5 * fwd_flops / (ms_bwd * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"]
+    return {"name": "train fwd+bwd, packed varlen 16384 tokens H32 Hk8 D128 (BASELINE config 3)",
+            "segments": lens, "sum_len_sq": sum_sq,
+            "fwd_bwd_ms": {"hp_grad_dots(bf16)": res["bf16"], "fp4_rownorm(request)": res["fp4_rownorm"]},
+            "fwd_bwd_tflops": 3.5 * fwd_flops / (res["bf16"] * 1e-3) / 1e12,
+            "bwd_only_ms": ms_bwd, "grad_cosine_vs_bf16_sdpa": cos,
+            "roofline": {"bound": "tensor", "achieved": bwd_tf, "peak": peak, "unit": "TFLOP/s",
+                         "frac": bwd_tf / peak, "traffic": None,
+                         "kernel": "bwd_dkdv_kernel + bwd_dq_kernel (+ delta pre-pass)",
+                         "note": "2.5 x forward FLOPs (5 GEMMs; the S and dP recompute of the second kernel "
+                                 "is not counted) over the bf16 sustained GEMM peak"}}
 
 
 def run_gpu(args):
@@ -359,6 +434,15 @@ def run_profile_case(args):
         q = rn(16, 32, 1, 128)
         packed = cache.get_packed()
         fn = lambda: nv.nvfp4_flash_decode_prequant(q, packed, 128 ** -0.5, 4)
+    elif case == "bwd":        # Z1 H32 Hk8 S4096 D128 causal fwd+bwd: 0.48 TFLOP per step
+        q, k, v, do = rn(1, 32, 4096, 128), rn(1, 8, 4096, 128), rn(1, 8, 4096, 128), rn(1, 32, 4096, 128)
+        q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+
+        def fn():
+            o = nv.nvfp4_flash_attn_func(q, k, v, 128 ** -0.5, causal=True, num_key_value_groups=4,
+                                         backward_grad_dots="bf16")
+            o.backward(do)
+            q.grad = k.grad = v.grad = None
     elif case == "pack":       # 64 x 8192 x 128 bf16: 172 MB read+written per launch
         x = rn(64, 8192, 128)
         fn = lambda: (nv._quant_nvfp4(x), nv._quant_nvfp4(x, transpose=True))
@@ -372,7 +456,7 @@ def run_profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "fwd_d256", "decode", "pack"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "fwd_d256", "decode", "pack", "bwd"],
                     help="run one small kernel case --steps times (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

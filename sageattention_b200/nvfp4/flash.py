@@ -471,14 +471,15 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
 
 
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
-             mode="fp4_rownorm", **_unused):
+             mode="fp4_rownorm", q_packs=None, k_packs=None, **_unused):
     """Backward for the ``fp4_rownorm`` / ``fp8_rownorm`` / ``fp4_legacy`` modes (flash.py:3811-4265).
 
     This build runs them on the high-precision gradient GEMM kernels: the probabilities still come
     from the FP4 recompute, the gradient GEMMs are bf16, which meets the accuracy floor of every
     mode (gradient cosine >= 0.93 against exact attention) with margin.
     """
-    return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout)
+    return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout,
+                       q_packs=q_packs, k_packs=k_packs)
 
 
 def _gqa_reduce_cast_dkdv(dk_planes: torch.Tensor, dv_planes: torch.Tensor, z: int, hk: int, g: int,
@@ -495,21 +496,34 @@ def _gqa_reduce_cast_dkdv(dk_planes: torch.Tensor, dv_planes: torch.Tensor, z: i
 
 
 class _NVFP4FlashAttn(torch.autograd.Function):
-    """Autograd wrapper of the NVFP4 attention (stands in for flash.py:4268-4545)."""
+    """Autograd wrapper of the NVFP4 attention (stands in for flash.py:4268-4545).
+
+    ``apply`` takes the reference's 26 positional arguments in the same order (query, key, value,
+    scaling, causal, num_key_value_groups, key_pad_bias, sr, save_backward_packs, the three
+    backward stochastic-rounding knobs, dkdv_scratch_bf16, backward_grad_dots (resolved mode),
+    out_zshd, four tile hints, seq_id / seq_start / seq_end, and the optional Q / K packs) and
+    returns gradients for the first three.
+    """
 
     @staticmethod
-    def forward(ctx, query, key, value, scaling, causal, g, key_pad_bias, cu_seqlens, out_layout, mode,
-                q_packs, k_packs):
-        z, h, s_q, d = query.shape
-        varlen = None
-        if cu_seqlens is not None:
-            varlen = _varlen_seq_arrays(cu_seqlens, s_q, query.device)
+    def forward(ctx, query, key, value, scaling, causal, num_key_value_groups, key_pad_bias, sr,
+                save_backward_packs, backward_p_dv_sr, backward_dot_dv_sr, backward_ds_dq_sr,
+                dkdv_scratch_bf16, backward_grad_dots, out_zshd, block_m, block_n, num_warps, num_stages,
+                seq_id, seq_start, seq_end, qnv_in, qsc_in, knv_in, ksc_in):
+        if qnv_in is not None or knv_in is not None:
+            assert not save_backward_packs, (
+                "q_packs/k_packs are incompatible with save_backward_packs "
+                "(the saved pack set must come from the same fused HP read)")
+        varlen = (seq_id, seq_start, seq_end) if seq_id is not None else None
+        out_layout = "zshd" if out_zshd else "zhsd"
         out, lse, packs = nvfp4_flash_attention(
-            query, key, value, scaling, causal=causal, num_key_value_groups=g, key_pad_bias=key_pad_bias,
-            cu_seqlens=cu_seqlens, return_lse=True, return_packs=True, out_layout=out_layout,
-            q_packs=q_packs, k_packs=k_packs, _varlen_arrays=varlen)
+            query, key, value, scaling, causal=causal, num_key_value_groups=num_key_value_groups,
+            key_pad_bias=key_pad_bias, return_lse=True, return_packs=True, out_layout=out_layout,
+            q_packs=(qnv_in, qsc_in) if qnv_in is not None else None,
+            k_packs=(knv_in, ksc_in) if knv_in is not None else None, _varlen_arrays=varlen)
         ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3])
-        ctx.meta = (float(scaling), bool(causal), int(g), varlen, out_layout, mode, key_pad_bias is not None)
+        ctx.meta = (float(scaling), bool(causal), int(num_key_value_groups), varlen, out_layout,
+                    backward_grad_dots, key_pad_bias is not None)
         return out
 
     @staticmethod
@@ -517,10 +531,13 @@ class _NVFP4FlashAttn(torch.autograd.Function):
         query, key, value, out, lse, qnv, qsc, knv, ksc = ctx.saved_tensors
         scaling, causal, g, varlen, out_layout, mode, has_bias = ctx.meta
         assert not has_bias, "key_pad_bias is forward-only (as in the reference backward)"
-        fn = _run_bwd_hp if mode == "bf16" else _run_bwd
-        kwargs = dict(q_packs=(qnv, qsc), k_packs=(knv, ksc)) if mode == "bf16" else dict(mode=mode)
-        dq, dk, dv = fn(query, key, value, out, lse, grad_out, scaling, causal, g, varlen, out_layout, **kwargs)
-        return (dq, dk, dv) + (None,) * 9
+        if mode == "bf16":
+            dq, dk, dv = _run_bwd_hp(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
+                                     out_layout, q_packs=(qnv, qsc), k_packs=(knv, ksc))
+        else:
+            dq, dk, dv = _run_bwd(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
+                                  out_layout, mode=mode, q_packs=(qnv, qsc), k_packs=(knv, ksc))
+        return (dq, dk, dv) + (None,) * 23
 
 
 def nvfp4_flash_attn_func(query, key, value, scaling, causal=False, num_key_value_groups=1,
@@ -556,5 +573,13 @@ def nvfp4_flash_attn_func(query, key, value, scaling, causal=False, num_key_valu
     mode = _resolve_backward_grad_dots(backward_grad_dots, eff, save_backward_packs, num_key_value_groups)
     if mode == "fp8_rownorm":
         assert d in (128, 256), "fp8_rownorm needs head dim 128 or 256"
-    return _NVFP4FlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, key_pad_bias,
-                                 cu_seqlens, out_layout, mode, q_packs, k_packs)
+    seq_id = seq_start = seq_end = None
+    if cu_seqlens is not None:
+        seq_id, seq_start, seq_end = _varlen_seq_arrays(cu_seqlens, s_q, query.device)
+    qnv_in, qsc_in = q_packs if q_packs is not None else (None, None)
+    knv_in, ksc_in = k_packs if k_packs is not None else (None, None)
+    return _NVFP4FlashAttn.apply(
+        query, key, value, scaling, causal, num_key_value_groups, key_pad_bias, stochastic_rounding,
+        save_backward_packs, backward_p_dv_stochastic_rounding, backward_dot_dv_stochastic_rounding,
+        backward_ds_dq_stochastic_rounding, dkdv_scratch_bf16, mode, out_layout == "zshd", block_m,
+        block_n, num_warps, num_stages, seq_id, seq_start, seq_end, qnv_in, qsc_in, knv_in, ksc_in)

@@ -137,6 +137,15 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
   }
 }
 
+#ifdef NVFP4_BWD_TIMING
+#ifndef BTRACE_Y
+#define BTRACE_Y 0
+#endif
+#define BTRACE(role, step, slot) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == BTRACE_Y && (step) < 80) p.timing[((role) * 80 + (step)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define BTRACE(role, step, slot) do { } while (0)
+#endif
+
 struct BwdParams {
   const uint8_t* qsc;   // [ZH, Sq, 8]
   const uint8_t* ksc;   // [ZHk, Skv, 8]
@@ -152,6 +161,7 @@ struct BwdParams {
   float scaling;
   int causal;
   int* status;
+  long long* timing;    // debug only (NVFP4_BWD_TIMING builds)
 };
 
 // 32 fp32 accumulator columns -> 32 contiguous gradient elements
@@ -182,18 +192,25 @@ __device__ __forceinline__ void zero_row(TG* dst, int n) {
   for (int e = 0; e < n; ++e) dst[e] = from_f32<TG>(0.0f);
 }
 
-// P for 32 columns of one accumulator row.  `nl` = -lse*log2e per column (shared memory, the
-// dK/dV kernel) or nullptr with `nl_row` the row's own value (the dQ kernel).  Columns outside
+// P for 32 columns of one accumulator row.  Per-column statistics (the dK/dV kernel): `nl` points
+// at the raw lse of the 32 columns in shared memory; per-row (the dQ kernel): `nl_row` is
+// -lse*log2e of the row.  Columns outside
 // [lo, hi) relative to the chunk's first column are masked when `masked`.
 template <bool kPerColumn>
 __device__ __forceinline__ void prob_chunk(const uint32_t (&sr)[32], float (&pf)[32], float c2, const float* nl,
                                            float nl_row, bool masked, int lo, int hi) {
   const float2 c22 = make_float2(c2, c2);
+  const float2 ml2 = make_float2(-kBwdLog2e, -kBwdLog2e);
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
     float4 n4;
-    if constexpr (kPerColumn) n4 = *reinterpret_cast<const float4*>(nl + e);
-    else n4 = make_float4(nl_row, nl_row, nl_row, nl_row);
+    if constexpr (kPerColumn) {
+      const float4 l4 = *reinterpret_cast<const float4*>(nl + e);
+      const float2 a = __fmul2_rn(make_float2(l4.x, l4.y), ml2), b = __fmul2_rn(make_float2(l4.z, l4.w), ml2);
+      n4 = make_float4(a.x, a.y, b.x, b.y);
+    } else {
+      n4 = make_float4(nl_row, nl_row, nl_row, nl_row);
+    }
     const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c22,
                                  make_float2(n4.x, n4.y));
     const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])), c22,
@@ -208,19 +225,25 @@ __device__ __forceinline__ void prob_chunk(const uint32_t (&sr)[32], float (&pf)
     for (int e = 0; e < 32; ++e) pf[e] = (e >= lo && e < hi) ? pf[e] : 0.0f;
   }
 }
-// dS = P o (dP - delta) for 32 columns, packed to bf16 pairs.
+// dS = P o (dP - delta) for 32 columns, packed to bf16 pairs.  Per-column: `nd` points at the raw
+// delta values; per-row: `nd_row` is -delta.
 template <bool kPerColumn>
 __device__ __forceinline__ void ds_chunk(const float (&pf)[32], const uint32_t (&dr)[32], uint32_t (&dw)[16],
                                          const float* nd, float nd_row) {
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
-    float4 n4;
-    if constexpr (kPerColumn) n4 = *reinterpret_cast<const float4*>(nd + e);
-    else n4 = make_float4(nd_row, nd_row, nd_row, nd_row);
-    const float2 a0 = __fadd2_rn(make_float2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1])),
-                                 make_float2(n4.x, n4.y));
-    const float2 a1 = __fadd2_rn(make_float2(__uint_as_float(dr[e + 2]), __uint_as_float(dr[e + 3])),
-                                 make_float2(n4.z, n4.w));
+    float2 a0, a1;
+    const float2 d01 = make_float2(__uint_as_float(dr[e]), __uint_as_float(dr[e + 1]));
+    const float2 d23 = make_float2(__uint_as_float(dr[e + 2]), __uint_as_float(dr[e + 3]));
+    if constexpr (kPerColumn) {
+      const float4 n4 = *reinterpret_cast<const float4*>(nd + e);
+      const float2 m1 = make_float2(-1.0f, -1.0f);
+      a0 = __ffma2_rn(make_float2(n4.x, n4.y), m1, d01);
+      a1 = __ffma2_rn(make_float2(n4.z, n4.w), m1, d23);
+    } else {
+      a0 = __fadd2_rn(d01, make_float2(nd_row, nd_row));
+      a1 = __fadd2_rn(d23, make_float2(nd_row, nd_row));
+    }
     const float2 d0 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), a0);
     const float2 d1 = __fmul2_rn(make_float2(pf[e + 2], pf[e + 3]), a1);
     dw[e >> 1] = pack_bf16x2(d0.x, d0.y);
@@ -333,6 +356,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         const int zh = zi * p.h + kh * p.g + gq;
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * L::STAGE;
+        BTRACE(0, st, 0);
         mbar_expect_tx(&full_tma[s], L::QP + L::DO + L::Q);
         tma_load_3d(sb + L::O_QP, &tm_qp, &full_tma[s], 0, i * 64, zh);
         tma_load_3d(sb + L::O_DO, &tm_do, &full_tma[s], 0, i * 64, zh);
@@ -375,15 +399,16 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
           const uint8_t* g = p.qsc + ((int64_t)zh * p.s_q + (ok ? qi : 0)) * 8;
           cp_async_4(qsf + sf_atom_offset(r, 0), g, ok ? 4u : 0u);
           cp_async_4(qsf + 512 + sf_atom_offset(r, 0), g + 4, ok ? 4u : 0u);
-          // rows past the end: exp2(-inf) = 0
-          aux[r] = ok ? -p.lse[(int64_t)zh * p.s_q + qi] * kBwdLog2e : -INFINITY;
-          aux[64 + r] = ok ? -p.delta[(int64_t)zh * p.s_q + qi] : 0.0f;
+          // lse and delta land as they are (rows past the end read 0 and are masked by range)
+          const int64_t gi = (int64_t)zh * p.s_q + (ok ? qi : 0);
+          cp_async_4(smem_u32(aux + r), p.lse + gi, ok ? 4u : 0u);
+          cp_async_4(smem_u32(aux + 64 + r), p.delta + gi, ok ? 4u : 0u);
         }
         cp_async_commit();
         cp_async_wait<0>();
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full_aux[s]);
+        if (lane == 0) { mbar_arrive(&full_aux[s]); BTRACE(1, st, 0); }
       }
     }
   } else if (warp == 1) {
@@ -397,18 +422,21 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       tc_fence_after();
       tmem_cp_32x128b_warpx4(tmem + T_SFK, smem_u32(s_ksf));
       tmem_cp_32x128b_warpx4(tmem + T_SFK + 4, smem_u32(s_ksf + 512));
+      // descriptors: constant fields once, then only the 16-byte-unit address field moves
+      const uint64_t b_v = desc_sw128(s_v, 0), b_kp = desc_sw64(s_kp, 0);
+      const uint64_t b_pt = desc_sw128(s_pt, 0), b_dst = desc_sw128(s_dst, 0);
+      const uint64_t b_do = desc_sw128(s_stage + L::O_DO, 0), b_do_mn = desc_sw128_mn(s_stage + L::O_DO, 0, 8192);
+      const uint64_t b_q_mn = desc_sw128_mn(s_stage + L::O_Q, 0, 8192), b_qp = desc_sw64(s_stage + L::O_QP, 0);
       // dV += P^T dO and dK += dS^T Q of step t (operands: slot t&1, stage t%NSTAGE)
       auto grad_gemms = [&](int t) {
-        const int b = t & 1;
-        uint8_t* sbp = s_stage + (t % L::NSTAGE) * L::STAGE;
+        const uint64_t so = (uint64_t)((t % L::NSTAGE) * (L::STAGE >> 4));
+        const uint64_t a_pt = b_pt + (uint64_t)((t & 1) * (L::PT >> 4)), a_dst = b_dst + (uint64_t)((t & 1) * (L::DST >> 4));
+        const uint64_t x_do = b_do_mn + so, x_q = b_q_mn + so;
+        const uint32_t acc0 = t > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16(tmem + T_DV, desc_sw128(s_pt + b * L::PT, k), desc_sw128_mn(sbp + L::O_DO, k, 8192), id_acc,
-                    (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DV, a_pt + 2 * k, x_do + 128 * k, id_acc, k > 0 ? 1u : acc0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16(tmem + T_DK, desc_sw128(s_dst + b * L::DST, k), desc_sw128_mn(sbp + L::O_Q, k, 8192), id_acc,
-                    (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DK, a_dst + 2 * k, x_q + 128 * k, id_acc, k > 0 ? 1u : acc0);
       };
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, b = st & 1;
@@ -417,26 +445,33 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         mbar_wait(&full_tma[s], ph, &err, 5);
         mbar_wait(&full_aux[s], ph, &err, 6);
         tc_fence_after();
+        BTRACE(2, st, 0);
         // S^T slot b was read by the group of step st-2 before it signalled pds_full, seen below
         tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8, smem_u32(sb + L::O_QSF));
         tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8 + 4, smem_u32(sb + L::O_QSF + 512));
+        const uint64_t so = (uint64_t)(s * (L::STAGE >> 4));
+        const uint64_t x_qp = b_qp + so, x_do = b_do + so;
 #pragma unroll
         for (int k = 0; k < 2; ++k)
-          umma_nvfp4(tmem + T_ST + b * 64, desc_sw64(s_kp, k), desc_sw64(sb + L::O_QP, k), id_s,
-                     tmem + T_SFK + k * 4, tmem + T_SFQ + b * 8 + k * 4, k > 0);
+          umma_nvfp4(tmem + T_ST + b * 64, b_kp + 2 * k, x_qp + 2 * k, id_s, tmem + T_SFK + k * 4,
+                     tmem + T_SFQ + b * 8 + k * 4, k > 0);
         umma_commit(&s_full[b]);
+        BTRACE(2, st, 1);
         if (st > 0) {
           mbar_spin_wait(&dp_free, (st - 1) & 1, &err, 7);
           tc_fence_after();
         }
+        BTRACE(2, st, 2);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_bf16(tmem + T_DPT, desc_sw128(s_v + (k >> 2) * 16384, k),
-                    desc_sw128(sb + L::O_DO + (k >> 2) * 8192, k), id_dp, k > 0);
+          umma_bf16(tmem + T_DPT, b_v + (k >> 2) * 1024 + (k & 3) * 2, x_do + (k >> 2) * 512 + (k & 3) * 2, id_dp,
+                    k > 0);
         umma_commit(&dp_full);
+        BTRACE(2, st, 3);
         if (st > 0) {
           mbar_spin_wait(&pds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
           tc_fence_after();
+          BTRACE(2, st, 4);
           grad_gemms(st - 1);
           umma_commit(&empty[(st - 1) % L::NSTAGE]);
           umma_commit(&pd_free[b ^ 1]);
@@ -475,10 +510,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       uint8_t* pt = s_pt + b * L::PT;
       uint8_t* dst = s_dst + b * L::DST;
       const bool masked = !__all_sync(0xffffffffu, q0 >= ql && q0 + 64 <= qh);
+      const bool trc = (warp & 3) == 0 && lane == 0;
+      if (trc) BTRACE(4 + grp, st, 0);
       mbar_wait(&full_aux[s], (st / L::NSTAGE) & 1, &err, 10);
+      if (trc) BTRACE(4 + grp, st, 1);
       mbar_wait(&s_full[b], k2 & 1, &err, 11);
       tc_fence_after();
+      if (trc) BTRACE(4 + grp, st, 2);
       if (k2 > 0) mbar_wait(&pd_free[b], (k2 - 1) & 1, &err, 12);
+      if (trc) BTRACE(4 + grp, st, 3);
       float pf[2][32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -490,8 +530,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         for (int e = 0; e < 16; ++e) pw[e] = pack_bf16x2(pf[c][2 * e], pf[c][2 * e + 1]);
         store_tile_chunk(pt, row, c, pw);
       }
+      if (trc) BTRACE(4 + grp, st, 4);
       mbar_wait(&dp_full, st & 1, &err, 13);
       tc_fence_after();
+      if (trc) BTRACE(4 + grp, st, 5);
       uint32_t dr0[32], dr1[32];
       tmem_ld32(tmem + lane_addr + T_DPT, dr0);
       tmem_ld32(tmem + lane_addr + T_DPT + 32, dr1);
@@ -499,6 +541,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dp_free);
+      if (trc) BTRACE(4 + grp, st, 6);
       {
         uint32_t dw[16];
         ds_chunk<true>(pf[0], dr0, dw, aux + 64, 0.0f);
@@ -509,6 +552,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[b]);
+      if (trc) BTRACE(4 + grp, st, 7);
     }
     // ---- epilogue: group g writes gradient columns [64g, 64g+64)
     TG* dkrow = static_cast<TG*>(p.dk) + ((int64_t)unit * p.s_kv + key) * 128 + grp * 64;
@@ -685,12 +729,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       tc_fence_after();
       tmem_cp_32x128b_warpx4(tmem + T_SFQ, smem_u32(s_qsf));
       tmem_cp_32x128b_warpx4(tmem + T_SFQ + 4, smem_u32(s_qsf + 512));
+      const uint64_t b_do = desc_sw128(s_do, 0), b_qp = desc_sw64(s_qp, 0), b_ds = desc_sw128(s_ds, 0);
+      const uint64_t b_v = desc_sw128(s_stage + L::O_V, 0), b_k_mn = desc_sw128_mn(s_stage + L::O_K, 0, 8192);
+      const uint64_t b_kp = desc_sw64(s_stage + L::O_KP, 0);
       auto grad_gemm = [&](int t) {   // dQ += dS K of step t
-        uint8_t* sbp = s_stage + (t % L::NSTAGE) * L::STAGE;
+        const uint64_t a_ds = b_ds + (uint64_t)((t & 1) * (L::DS >> 4));
+        const uint64_t x_k = b_k_mn + (uint64_t)((t % L::NSTAGE) * (L::STAGE >> 4));
+        const uint32_t acc0 = t > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16(tmem + T_DQ, desc_sw128(s_ds + (t & 1) * L::DS, k), desc_sw128_mn(sbp + L::O_K, k, 8192),
-                    id_acc, (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DQ, a_ds + 2 * k, x_k + 128 * k, id_acc, k > 0 ? 1u : acc0);
       };
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, b = st & 1;
@@ -701,10 +748,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
         tc_fence_after();
         tmem_cp_32x128b_warpx4(tmem + T_SFK + b * 8, smem_u32(sb + L::O_KSF));
         tmem_cp_32x128b_warpx4(tmem + T_SFK + b * 8 + 4, smem_u32(sb + L::O_KSF + 512));
+        const uint64_t so = (uint64_t)(s * (L::STAGE >> 4));
+        const uint64_t x_kp = b_kp + so, x_v = b_v + so;
 #pragma unroll
         for (int k = 0; k < 2; ++k)
-          umma_nvfp4(tmem + T_S + b * 64, desc_sw64(s_qp, k), desc_sw64(sb + L::O_KP, k), id_s,
-                     tmem + T_SFQ + k * 4, tmem + T_SFK + b * 8 + k * 4, k > 0);
+          umma_nvfp4(tmem + T_S + b * 64, b_qp + 2 * k, x_kp + 2 * k, id_s, tmem + T_SFQ + k * 4,
+                     tmem + T_SFK + b * 8 + k * 4, k > 0);
         umma_commit(&s_full[b]);
         if (st > 0) {
           mbar_spin_wait(&dp_free, (st - 1) & 1, &err, 7);
@@ -712,8 +761,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_bf16(tmem + T_DP, desc_sw128(s_do + (k >> 2) * 16384, k),
-                    desc_sw128(sb + L::O_V + (k >> 2) * 8192, k), id_dp, k > 0);
+          umma_bf16(tmem + T_DP, b_do + (k >> 2) * 1024 + (k & 3) * 2, x_v + (k >> 2) * 512 + (k & 3) * 2, id_dp,
+                    k > 0);
         umma_commit(&dp_full);
         if (st > 0) {
           mbar_spin_wait(&ds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
@@ -901,6 +950,11 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
   p.dq = dq; p.dk = dk; p.dv = dv;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk); p.s_q = (int)s_q; p.s_kv = (int)s_kv;
   p.scaling = scaling; p.causal = (flags & NVFP4_FWD_CAUSAL) ? 1 : 0; p.status = status;
+#ifdef NVFP4_BWD_TIMING
+  p.timing = reinterpret_cast<long long*>(status) + 8;   // timing builds: the status buffer carries the trace
+#else
+  p.timing = nullptr;
+#endif
   auto launch = [&](auto kdkdv, auto kdq) -> int {
     cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkdvSmem::TOTAL);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_bwd_hp: smem attribute: %s", cudaGetErrorString(e));

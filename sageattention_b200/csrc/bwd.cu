@@ -17,9 +17,10 @@
 //
 // Pipeline of one CTA (384 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 scale-atom /
 // row-statistics loader, warps 4-7 and 8-11 two softmax groups that alternate steps.  S has two
-// TMEM slots, dP one (a group pulls it into registers and hands the slot back at once), P^T / dS^T
-// have two shared-memory slots, so the tensor pipe works on step t+1 while a group is still busy
-// with step t.  Causal masking is bottom-right aligned; packed varlen is block-diagonal, expressed
+// TMEM slots, dP one (a group pulls it into registers and hands the slot back at once); P^T / dS^T
+// are written back as bf16 pairs into the S slot they were computed from and enter the gradient
+// GEMMs as TMEM A operands, so the probabilities never touch shared memory and the tensor pipe
+// works on step t+1 while a group is still busy with step t.  Causal masking is bottom-right aligned; packed varlen is block-diagonal, expressed
 // as a per-row visible range.  Head dim 128.  Every barrier wait is bounded.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
@@ -30,6 +31,7 @@ namespace nvfp4 {
 
 constexpr int kBwdThreads = 384;
 constexpr float kBwdLog2e = 1.4426950408889634f;
+constexpr int kBwdPrefetch = 8;   // stage loads are prefetched into L2 this many steps ahead
 
 __host__ __device__ inline uint32_t make_idesc_bf16(uint32_t m, uint32_t n, bool b_mn_major) {
   uint32_t d = 0;
@@ -47,6 +49,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// same, A operand read from TMEM (128 lanes x 8 columns of packed bf16 pairs per K = 16)
+__device__ __forceinline__ void umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ float ex2_bwd(float x) {
@@ -250,23 +261,16 @@ __device__ __forceinline__ void ds_chunk(const float (&pf)[32], const uint32_t (
     dw[(e >> 1) + 1] = pack_bf16x2(d1.x, d1.y);
   }
 }
-// 32 bf16 values (16 words) of row `row` into a [128 x 64] 128-byte-swizzled tile at column c32*32
-__device__ __forceinline__ void store_tile_chunk(uint8_t* tile, int row, int c32, const uint32_t (&w)[16]) {
-#pragma unroll
-  for (int v4 = 0; v4 < 4; ++v4)
-    *reinterpret_cast<uint4*>(tile + sw128_offset(row, c32 * 64 + v4 * 16)) =
-        make_uint4(w[4 * v4], w[4 * v4 + 1], w[4 * v4 + 2], w[4 * v4 + 3]);
-}
-
 // ------------------------------------------------------------------------------------------
 // dK / dV
 // TMEM: dV [0,128) | dK [128,256) | S^T slots [256,320) [320,384) | dP^T [384,448) |
 //       SFK [448,456) | SFQ slots [456,464) [464,472)
+// A softmax group reads its S^T slot into registers and writes P^T and dS^T (bf16 pairs, 16
+// columns per 32 queries each) back into the same slot: the gradient GEMMs take them as TMEM A
+// operands.
 // ------------------------------------------------------------------------------------------
 struct DkdvSmem {
   static constexpr int V = 32768;        // V bf16 [128 keys x 128 d] = 2 sub-tiles of 16 KB
-  static constexpr int PT = 16384;       // P^T bf16 [128 keys x 64 q], two slots
-  static constexpr int DST = 16384;      // dS^T, two slots
   static constexpr int KP = 8192;        // K pack tile, 128 keys x 64 B (64-byte swizzle)
   static constexpr int KSF = 1024;       // K scale atoms (2 x 512)
   // per stage: dO and Q bf16 [64 q x 128 d] as 2 sub-tiles of 8 KB, Q pack [64 q x 64 B], Q scale
@@ -274,8 +278,8 @@ struct DkdvSmem {
   static constexpr int DO = 16384, Q = 16384, QP = 4096, QSF = 1024, AUX = 1024;
   static constexpr int O_DO = 0, O_Q = DO, O_QP = DO + Q, O_QSF = O_QP + QP, O_AUX = O_QSF + QSF;
   static constexpr int STAGE = DO + Q + QP + QSF + AUX;
-  static constexpr int NSTAGE = 3;
-  static constexpr int TOTAL = V + 2 * PT + 2 * DST + KP + NSTAGE * STAGE + KSF + 1024;
+  static constexpr int NSTAGE = 4;
+  static constexpr int TOTAL = V + KP + NSTAGE * STAGE + KSF + 1024;
 };
 
 template <typename TG>
@@ -288,14 +292,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* s_v = smem;
-  uint8_t* s_pt = s_v + L::V;
-  uint8_t* s_dst = s_pt + 2 * L::PT;
-  uint8_t* s_kp = s_dst + 2 * L::DST;
+  uint8_t* s_kp = s_v + L::V;
   uint8_t* s_stage = s_kp + L::KP;
   uint8_t* s_ksf = s_stage + L::NSTAGE * L::STAGE;
 
   __shared__ uint64_t full_tma[L::NSTAGE], full_aux[L::NSTAGE], empty[L::NSTAGE];
-  __shared__ uint64_t kv_full, ksf_full, s_full[2], dp_full, dp_free, pds_full[2], pd_free[2], acc_done;
+  __shared__ uint64_t kv_full, ksf_full, s_full[2], dp_full, dp_free, pds_full[2], acc_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
 
@@ -327,12 +329,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
     mbar_init(&kv_full, 1);
     mbar_init(&ksf_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&dp_free, 4);
+    mbar_init(&dp_free, 8);
     mbar_init(&acc_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&pds_full[b], 4);
-      mbar_init(&pd_free[b], 1);
+      mbar_init(&pds_full[b], 8);
     }
     mbar_fence_init();
   }
@@ -350,10 +351,23 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       tma_load_3d(s_kp, &tm_kp, &kv_full, 0, n0, unit);
       tma_load_3d(s_v, &tm_v, &kv_full, 0, n0, unit);
       tma_load_3d(s_v + 16384, &tm_v, &kv_full, 64, n0, unit);
+      // L2 prefetch kBwdPrefetch steps ahead: co-resident CTAs walk the same query tiles in step,
+      // so without it every stage load is a first touch that waits on HBM
+      auto prefetch = [&](int t) {
+        const int gq = t / n_i, i = i_lo + t % n_i;
+        const int zh = zi * p.h + kh * p.g + gq;
+        tma_prefetch_3d(&tm_qp, 0, i * 64, zh);
+        tma_prefetch_3d(&tm_do, 0, i * 64, zh);
+        tma_prefetch_3d(&tm_do, 64, i * 64, zh);
+        tma_prefetch_3d(&tm_q, 0, i * 64, zh);
+        tma_prefetch_3d(&tm_q, 64, i * 64, zh);
+      };
+      for (int t = L::NSTAGE; t < min(nstep, kBwdPrefetch); ++t) prefetch(t);
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE;
         const int gq = st / n_i, i = i_lo + st % n_i;
         const int zh = zi * p.h + kh * p.g + gq;
+        if (st + kBwdPrefetch < nstep) prefetch(st + kBwdPrefetch);
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * L::STAGE;
         BTRACE(0, st, 0);
@@ -411,6 +425,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         if (lane == 0) { mbar_arrive(&full_aux[s]); BTRACE(1, st, 0); }
       }
     }
+#ifdef NVFP4_BWD_TIMING
+  } else if (warp == 3) {
+    if (lane == 0 && p.timing && blockIdx.x == 0 && blockIdx.y == BTRACE_Y) {
+      for (int st = 0; st < min(nstep, 80); ++st) {
+        mbar_spin_wait(&full_tma[st % L::NSTAGE], (st / L::NSTAGE) & 1, &err, 20);
+        BTRACE(3, st, 0);
+      }
+    }
+#endif
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one() && nstep > 0) {
@@ -424,19 +447,21 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       tmem_cp_32x128b_warpx4(tmem + T_SFK + 4, smem_u32(s_ksf + 512));
       // descriptors: constant fields once, then only the 16-byte-unit address field moves
       const uint64_t b_v = desc_sw128(s_v, 0), b_kp = desc_sw64(s_kp, 0);
-      const uint64_t b_pt = desc_sw128(s_pt, 0), b_dst = desc_sw128(s_dst, 0);
       const uint64_t b_do = desc_sw128(s_stage + L::O_DO, 0), b_do_mn = desc_sw128_mn(s_stage + L::O_DO, 0, 8192);
       const uint64_t b_q_mn = desc_sw128_mn(s_stage + L::O_Q, 0, 8192), b_qp = desc_sw64(s_stage + L::O_QP, 0);
       // dV += P^T dO and dK += dS^T Q of step t (operands: slot t&1, stage t%NSTAGE)
       auto grad_gemms = [&](int t) {
         const uint64_t so = (uint64_t)((t % L::NSTAGE) * (L::STAGE >> 4));
-        const uint64_t a_pt = b_pt + (uint64_t)((t & 1) * (L::PT >> 4)), a_dst = b_dst + (uint64_t)((t & 1) * (L::DST >> 4));
+        // slot columns: [P^T q0-31 | dS^T q0-31 | P^T q32-63 | dS^T q32-63], 16 each
+        const uint32_t a_pt = tmem + T_ST + (t & 1) * 64, a_dst = a_pt + 16;
         const uint64_t x_do = b_do_mn + so, x_q = b_q_mn + so;
         const uint32_t acc0 = t > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DV, a_pt + 2 * k, x_do + 128 * k, id_acc, k > 0 ? 1u : acc0);
+        for (int k = 0; k < 4; ++k)
+          umma_bf16_ta(tmem + T_DV, a_pt + (k >> 1) * 32 + (k & 1) * 8, x_do + 128 * k, id_acc, k > 0 ? 1u : acc0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DK, a_dst + 2 * k, x_q + 128 * k, id_acc, k > 0 ? 1u : acc0);
+        for (int k = 0; k < 4; ++k)
+          umma_bf16_ta(tmem + T_DK, a_dst + (k >> 1) * 32 + (k & 1) * 8, x_q + 128 * k, id_acc, k > 0 ? 1u : acc0);
       };
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, b = st & 1;
@@ -446,7 +471,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         mbar_wait(&full_aux[s], ph, &err, 6);
         tc_fence_after();
         BTRACE(2, st, 0);
-        // S^T slot b was read by the group of step st-2 before it signalled pds_full, seen below
+        // S^T slot b: its P^T / dS^T were consumed by the gradient GEMMs of step st-2, issued
+        // earlier on this in-order pipe
         tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8, smem_u32(sb + L::O_QSF));
         tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8 + 4, smem_u32(sb + L::O_QSF + 512));
         const uint64_t so = (uint64_t)(s * (L::STAGE >> 4));
@@ -458,7 +484,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         umma_commit(&s_full[b]);
         BTRACE(2, st, 1);
         if (st > 0) {
-          mbar_spin_wait(&dp_free, (st - 1) & 1, &err, 7);
+          mbar_wait(&dp_free, (st - 1) & 1, &err, 7);
           tc_fence_after();
         }
         BTRACE(2, st, 2);
@@ -469,15 +495,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         umma_commit(&dp_full);
         BTRACE(2, st, 3);
         if (st > 0) {
-          mbar_spin_wait(&pds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
+          mbar_wait(&pds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
           tc_fence_after();
           BTRACE(2, st, 4);
           grad_gemms(st - 1);
           umma_commit(&empty[(st - 1) % L::NSTAGE]);
-          umma_commit(&pd_free[b ^ 1]);
         }
       }
-      mbar_spin_wait(&pds_full[(nstep - 1) & 1], ((nstep - 1) >> 1) & 1, &err, 9);
+      mbar_wait(&pds_full[(nstep - 1) & 1], ((nstep - 1) >> 1) & 1, &err, 9);
       tc_fence_after();
       grad_gemms(nstep - 1);
       umma_commit(&acc_done);
@@ -502,57 +527,51 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       }
       qh = max(qh, ql);
     }
-    for (int st = grp; st < nstep; st += 2) {
-      const int s = st % L::NSTAGE, b = grp, k2 = st >> 1;
-      const int q0 = (i_lo + st % n_i) * 64;
+    // both groups work on every step: group g owns queries [32g, 32g+32) of the 64-query tile
+    for (int st = 0; st < nstep; ++st) {
+      const int s = st % L::NSTAGE, b = st & 1, k2 = st >> 1;
+      const int q0 = (i_lo + st % n_i) * 64 + grp * 32;
       uint8_t* sb = s_stage + s * L::STAGE;
-      const float* aux = reinterpret_cast<const float*>(sb + L::O_AUX);
-      uint8_t* pt = s_pt + b * L::PT;
-      uint8_t* dst = s_dst + b * L::DST;
-      const bool masked = !__all_sync(0xffffffffu, q0 >= ql && q0 + 64 <= qh);
-      const bool trc = (warp & 3) == 0 && lane == 0;
-      if (trc) BTRACE(4 + grp, st, 0);
+      const float* aux = reinterpret_cast<const float*>(sb + L::O_AUX) + grp * 32;
+      const uint32_t slot = tmem + lane_addr + T_ST + b * 64 + grp * 32;
+      const bool masked = !__all_sync(0xffffffffu, q0 >= ql && q0 + 32 <= qh);
+      const int trole = 4 + grp + 2 * (warp & 3);
+      const bool trc_any = lane == 0;
+      if (trc_any) BTRACE(trole, st, 0);
       mbar_wait(&full_aux[s], (st / L::NSTAGE) & 1, &err, 10);
-      if (trc) BTRACE(4 + grp, st, 1);
+      if (trc_any) BTRACE(trole, st, 1);
       mbar_wait(&s_full[b], k2 & 1, &err, 11);
-      tc_fence_after();
-      if (trc) BTRACE(4 + grp, st, 2);
-      if (k2 > 0) mbar_wait(&pd_free[b], (k2 - 1) & 1, &err, 12);
-      if (trc) BTRACE(4 + grp, st, 3);
-      float pf[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sr[32], pw[16];
-        tmem_ld32(tmem + lane_addr + T_ST + b * 64 + c * 32, sr);
-        tmem_ld_wait();
-        prob_chunk<true>(sr, pf[c], c2, aux + c * 32, 0.0f, masked, ql - q0 - c * 32, qh - q0 - c * 32);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pw[e] = pack_bf16x2(pf[c][2 * e], pf[c][2 * e + 1]);
-        store_tile_chunk(pt, row, c, pw);
-      }
-      if (trc) BTRACE(4 + grp, st, 4);
+      if (trc_any) BTRACE(trole, st, 2);
       mbar_wait(&dp_full, st & 1, &err, 13);
       tc_fence_after();
-      if (trc) BTRACE(4 + grp, st, 5);
-      uint32_t dr0[32], dr1[32];
-      tmem_ld32(tmem + lane_addr + T_DPT, dr0);
-      tmem_ld32(tmem + lane_addr + T_DPT + 32, dr1);
+      if (trc_any) BTRACE(trole, st, 3);
+      // dP^T first: the single dP^T slot goes back to the issuer before any arithmetic
+      uint32_t dr[32], sr[32];
+      tmem_ld32(tmem + lane_addr + T_DPT + grp * 32, dr);
+      tmem_ld32(slot, sr);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dp_free);
-      if (trc) BTRACE(4 + grp, st, 6);
+      if (trc_any) BTRACE(trole, st, 4);
+      // P^T -> 16 columns, dS^T -> the next 16, over the S^T columns just read
       {
-        uint32_t dw[16];
-        ds_chunk<true>(pf[0], dr0, dw, aux + 64, 0.0f);
-        store_tile_chunk(dst, row, 0, dw);
-        ds_chunk<true>(pf[1], dr1, dw, aux + 96, 0.0f);
-        store_tile_chunk(dst, row, 1, dw);
+        float pf[32];
+        uint32_t w[16];
+        prob_chunk<true>(sr, pf, c2, aux, 0.0f, masked, ql - q0, qh - q0);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) w[e] = pack_bf16x2(pf[2 * e], pf[2 * e + 1]);
+        tmem_st16(slot, w);
+        if (trc_any) BTRACE(trole, st, 5);
+        ds_chunk<true>(pf, dr, w, aux + 64, 0.0f);
+        tmem_st16(slot + 16, w);
       }
-      fence_proxy_async_smem();
+      if (trc_any) BTRACE(trole, st, 6);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[b]);
-      if (trc) BTRACE(4 + grp, st, 7);
+      if (trc_any) BTRACE(trole, st, 7);
     }
     // ---- epilogue: group g writes gradient columns [64g, 64g+64)
     TG* dkrow = static_cast<TG*>(p.dk) + ((int64_t)unit * p.s_kv + key) * 128 + grp * 64;
@@ -586,10 +605,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
 // dQ
 // TMEM: dQ [0,128) | S slots [128,192) [192,256) | dP [256,320) | SFQ [320,328) |
 //       SFK slots [328,336) [336,344)
+// dS (bf16 pairs, 32 columns) is written back into the S slot it came from and feeds the dQ GEMM
+// as a TMEM A operand.
 // ------------------------------------------------------------------------------------------
 struct DqSmem {
   static constexpr int DO = 32768;       // dO bf16 [128 q x 128 d] = 2 sub-tiles of 16 KB
-  static constexpr int DS = 16384;       // dS bf16 [128 q x 64 keys], two slots
   static constexpr int QP = 8192;        // Q pack tile, 128 queries x 64 B
   static constexpr int QSF = 1024;
   // per stage: V and K bf16 [64 keys x 128 d] as 2 sub-tiles of 8 KB, K pack [64 keys x 64 B], K scale atoms
@@ -597,7 +617,7 @@ struct DqSmem {
   static constexpr int O_V = 0, O_K = V, O_KP = V + K, O_KSF = O_KP + KP;
   static constexpr int STAGE = V + K + KP + KSF;
   static constexpr int NSTAGE = 4;
-  static constexpr int TOTAL = DO + 2 * DS + QP + NSTAGE * STAGE + QSF + 1024;
+  static constexpr int TOTAL = DO + QP + NSTAGE * STAGE + QSF + 1024;
 };
 
 template <typename TG>
@@ -610,13 +630,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* s_do = smem;
-  uint8_t* s_ds = s_do + L::DO;
-  uint8_t* s_qp = s_ds + 2 * L::DS;
+  uint8_t* s_qp = s_do + L::DO;
   uint8_t* s_stage = s_qp + L::QP;
   uint8_t* s_qsf = s_stage + L::NSTAGE * L::STAGE;
 
   __shared__ uint64_t full_tma[L::NSTAGE], full_sf[L::NSTAGE], empty[L::NSTAGE];
-  __shared__ uint64_t q_full, qsf_full, s_full[2], dp_full, dp_free, ds_full[2], ds_free[2], acc_done;
+  __shared__ uint64_t q_full, qsf_full, s_full[2], dp_full, dp_free, ds_full[2], acc_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
 
@@ -647,12 +666,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
     mbar_init(&q_full, 1);
     mbar_init(&qsf_full, 1);
     mbar_init(&dp_full, 1);
-    mbar_init(&dp_free, 4);
+    mbar_init(&dp_free, 8);
     mbar_init(&acc_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&ds_full[b], 4);
-      mbar_init(&ds_free[b], 1);
+      mbar_init(&ds_full[b], 8);
     }
     mbar_fence_init();
   }
@@ -669,8 +687,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       tma_load_3d(s_qp, &tm_qp, &q_full, 0, m0, zh);
       tma_load_3d(s_do, &tm_do, &q_full, 0, m0, zh);
       tma_load_3d(s_do + 16384, &tm_do, &q_full, 64, m0, zh);
+      auto prefetch = [&](int t) {
+        const int key0 = (j_lo + t) * 64;
+        tma_prefetch_3d(&tm_kp, 0, key0, unit);
+        tma_prefetch_3d(&tm_v, 0, key0, unit);
+        tma_prefetch_3d(&tm_v, 64, key0, unit);
+        tma_prefetch_3d(&tm_k, 0, key0, unit);
+        tma_prefetch_3d(&tm_k, 64, key0, unit);
+      };
+      for (int t = L::NSTAGE; t < min(nstep, kBwdPrefetch); ++t) prefetch(t);
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, key0 = (j_lo + st) * 64;
+        if (st + kBwdPrefetch < nstep) prefetch(st + kBwdPrefetch);
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * L::STAGE;
         mbar_expect_tx(&full_tma[s], L::KP + L::V + L::K);
@@ -729,15 +757,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       tc_fence_after();
       tmem_cp_32x128b_warpx4(tmem + T_SFQ, smem_u32(s_qsf));
       tmem_cp_32x128b_warpx4(tmem + T_SFQ + 4, smem_u32(s_qsf + 512));
-      const uint64_t b_do = desc_sw128(s_do, 0), b_qp = desc_sw64(s_qp, 0), b_ds = desc_sw128(s_ds, 0);
+      const uint64_t b_do = desc_sw128(s_do, 0), b_qp = desc_sw64(s_qp, 0);
       const uint64_t b_v = desc_sw128(s_stage + L::O_V, 0), b_k_mn = desc_sw128_mn(s_stage + L::O_K, 0, 8192);
       const uint64_t b_kp = desc_sw64(s_stage + L::O_KP, 0);
       auto grad_gemm = [&](int t) {   // dQ += dS K of step t
-        const uint64_t a_ds = b_ds + (uint64_t)((t & 1) * (L::DS >> 4));
+        const uint32_t a_ds = tmem + T_S + (t & 1) * 64;
         const uint64_t x_k = b_k_mn + (uint64_t)((t % L::NSTAGE) * (L::STAGE >> 4));
         const uint32_t acc0 = t > 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16(tmem + T_DQ, a_ds + 2 * k, x_k + 128 * k, id_acc, k > 0 ? 1u : acc0);
+        for (int k = 0; k < 4; ++k)
+          umma_bf16_ta(tmem + T_DQ, a_ds + (k >> 1) * 32 + (k & 1) * 8, x_k + 128 * k, id_acc, k > 0 ? 1u : acc0);
       };
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, b = st & 1;
@@ -756,7 +785,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
                      tmem + T_SFK + b * 8 + k * 4, k > 0);
         umma_commit(&s_full[b]);
         if (st > 0) {
-          mbar_spin_wait(&dp_free, (st - 1) & 1, &err, 7);
+          mbar_wait(&dp_free, (st - 1) & 1, &err, 7);
           tc_fence_after();
         }
 #pragma unroll
@@ -765,14 +794,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
                     k > 0);
         umma_commit(&dp_full);
         if (st > 0) {
-          mbar_spin_wait(&ds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
+          mbar_wait(&ds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
           tc_fence_after();
           grad_gemm(st - 1);
           umma_commit(&empty[(st - 1) % L::NSTAGE]);
-          umma_commit(&ds_free[b ^ 1]);
         }
       }
-      mbar_spin_wait(&ds_full[(nstep - 1) & 1], ((nstep - 1) >> 1) & 1, &err, 9);
+      mbar_wait(&ds_full[(nstep - 1) & 1], ((nstep - 1) >> 1) & 1, &err, 9);
       tc_fence_after();
       grad_gemm(nstep - 1);
       umma_commit(&acc_done);
@@ -798,39 +826,32 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       }
       kh = max(kh, kl);
     }
-    for (int st = grp; st < nstep; st += 2) {
-      const int b = grp, k2 = st >> 1;
-      const int key0 = (j_lo + st) * 64;
-      uint8_t* ds = s_ds + b * L::DS;
-      const bool masked = !__all_sync(0xffffffffu, key0 >= kl && key0 + 64 <= kh);
+    // both groups work on every step: group g owns keys [32g, 32g+32) of the 64-key tile
+    for (int st = 0; st < nstep; ++st) {
+      const int b = st & 1, k2 = st >> 1;
+      const int key0 = (j_lo + st) * 64 + grp * 32;
+      const uint32_t slot = tmem + lane_addr + T_S + b * 64;
+      const bool masked = !__all_sync(0xffffffffu, key0 >= kl && key0 + 32 <= kh);
       mbar_wait(&s_full[b], k2 & 1, &err, 11);
-      tc_fence_after();
-      float pf[2][32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sr[32];
-        tmem_ld32(tmem + lane_addr + T_S + b * 64 + c * 32, sr);
-        tmem_ld_wait();
-        prob_chunk<false>(sr, pf[c], c2, nullptr, nl, masked, kl - key0 - c * 32, kh - key0 - c * 32);
-      }
       mbar_wait(&dp_full, st & 1, &err, 13);
       tc_fence_after();
-      uint32_t dr0[32], dr1[32];
-      tmem_ld32(tmem + lane_addr + T_DP, dr0);
-      tmem_ld32(tmem + lane_addr + T_DP + 32, dr1);
+      uint32_t dr[32], sr[32];
+      tmem_ld32(tmem + lane_addr + T_DP + grp * 32, dr);
+      tmem_ld32(slot + grp * 32, sr);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dp_free);
-      if (k2 > 0) mbar_wait(&ds_free[b], (k2 - 1) & 1, &err, 12);
       {
-        uint32_t dw[16];
-        ds_chunk<false>(pf[0], dr0, dw, nullptr, nd);
-        store_tile_chunk(ds, row_in, 0, dw);
-        ds_chunk<false>(pf[1], dr1, dw, nullptr, nd);
-        store_tile_chunk(ds, row_in, 1, dw);
+        float pf[32];
+        uint32_t w[16];
+        prob_chunk<false>(sr, pf, c2, nullptr, nl, masked, kl - key0, kh - key0);
+        ds_chunk<false>(pf, dr, w, nullptr, nd);
+        // dS of keys [32g, 32g+32) replaces the first 16 of the S columns this thread just read
+        tmem_st16(slot + grp * 32, w);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[b]);
     }

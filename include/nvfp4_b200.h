@@ -204,7 +204,7 @@ int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t
  *   q_bf16, do_bf16 [Z*H, s_q, D];  k_bf16, v_bf16 [Z*Hk, s_kv, D]      contiguous bf16
  *   lse, delta [Z*H, s_q] fp32;  seq_start / seq_end [s] int32 (packed varlen) or both NULL
  *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
- * flags: NVFP4_FWD_CAUSAL.  D must be 128 in this build.
+ * flags: NVFP4_FWD_CAUSAL.  D is 128 or 256 (256: two 128-wide output halves per tile).
  */
 int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
                  const void* q_bf16, const void* k_bf16, const void* v_bf16, const void* do_bf16,

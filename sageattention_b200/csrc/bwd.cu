@@ -20,8 +20,10 @@
 // TMEM slots, dP one (a group pulls it into registers and hands the slot back at once); P^T / dS^T
 // are written back as bf16 pairs into the S slot they were computed from and enter the gradient
 // GEMMs as TMEM A operands, so the probabilities never touch shared memory and the tensor pipe
-// works on step t+1 while a group is still busy with step t.  Causal masking is bottom-right aligned; packed varlen is block-diagonal, expressed
-// as a per-row visible range.  Head dim 128.  Every barrier wait is bounded.
+// works on step t+1 while a group is still busy with step t.  Causal masking is bottom-right
+// aligned; packed varlen is block-diagonal, expressed as a per-row visible range.  Head dim 128,
+// or 256 as two 128-wide output halves per tile (both halves recompute S and dP).  Every barrier
+// wait is bounded.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
 #include "common/sm100.cuh"
@@ -264,30 +266,37 @@ __device__ __forceinline__ void ds_chunk(const float (&pf)[32], const uint32_t (
 // ------------------------------------------------------------------------------------------
 // dK / dV
 // TMEM: dV [0,128) | dK [128,256) | S^T slots [256,320) [320,384) | dP^T [384,448) |
-//       SFK [448,456) | SFQ slots [456,464) [464,472)
+//       SFK [448, 448+D/16) | two SFQ slots of D/16 columns
+// Head dim 256: the accumulators of a full tile would need all 512 columns, so blockIdx.z picks a
+// 128-wide half of dV / dK; S^T and dP^T still contract over the whole head dim.
 // A softmax group reads its S^T slot into registers and writes P^T and dS^T (bf16 pairs, 16
 // columns per 32 queries each) back into the same slot: the gradient GEMMs take them as TMEM A
 // operands.
 // ------------------------------------------------------------------------------------------
+template <int D>
 struct DkdvSmem {
-  static constexpr int V = 32768;        // V bf16 [128 keys x 128 d] = 2 sub-tiles of 16 KB
-  static constexpr int KP = 8192;        // K pack tile, 128 keys x 64 B (64-byte swizzle)
-  static constexpr int KSF = 1024;       // K scale atoms (2 x 512)
-  // per stage: dO and Q bf16 [64 q x 128 d] as 2 sub-tiles of 8 KB, Q pack [64 q x 64 B], Q scale
-  // atoms, -lse*log2e [64] and -delta [64]
-  static constexpr int DO = 16384, Q = 16384, QP = 4096, QSF = 1024, AUX = 1024;
+  static constexpr int DS = D / 64;      // 64-element (128-byte) sub-tiles of a bf16 row
+  static constexpr int KSUB = D / 128;   // 64-byte sub-tiles of a pack row
+  static constexpr int KB = D / 64;      // K = 64 block-scaled MMAs per S^T, scale atoms per tile
+  static constexpr int V = DS * 16384;   // V bf16 [128 keys x D]
+  static constexpr int KP = KSUB * 8192; // K pack tile, 128 keys x D/2 B (64-byte swizzle)
+  static constexpr int KSF = KB * 512;   // K scale atoms
+  // per stage: dO bf16 [64 q x D], the 128-wide half of Q bf16 [64 q x 128] (8 KB sub-tiles),
+  // Q pack [64 q x D/2 B], Q scale atoms, lse [64] and delta [64]
+  static constexpr int DO = DS * 8192, Q = 16384, QP = KSUB * 4096, QSF = KB * 512, AUX = 1024;
   static constexpr int O_DO = 0, O_Q = DO, O_QP = DO + Q, O_QSF = O_QP + QP, O_AUX = O_QSF + QSF;
   static constexpr int STAGE = DO + Q + QP + QSF + AUX;
-  static constexpr int NSTAGE = 4;
+  static constexpr int NSTAGE = D == 128 ? 4 : 2;
   static constexpr int TOTAL = V + KP + NSTAGE * STAGE + KSF + 1024;
+  static_assert(STAGE % 1024 == 0 && (V + KP) % 1024 == 0, "128-byte-swizzled tiles need 1 KB alignment");
 };
 
-template <typename TG>
+template <int D, typename TG>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant__ CUtensorMap tm_qp,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_q, const BwdParams p) {
-  using L = DkdvSmem;
+  using L = DkdvSmem<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -304,6 +313,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int jt = blockIdx.y;           // key tile (low tiles have the most visible queries: first)
   const int unit = blockIdx.x;         // z * hk + kh
+  const int half = blockIdx.z;         // 128-wide slice of the head dim owned by this CTA
   const int zi = unit / p.hk, kh = unit % p.hk;
   const int n0 = jt * 128;
   const int shift = p.s_kv - p.s_q;
@@ -342,25 +352,29 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  constexpr uint32_t T_DV = 0, T_DK = 128, T_ST = 256, T_DPT = 384, T_SFK = 448, T_SFQ = 456;
+  constexpr uint32_t T_DV = 0, T_DK = 128, T_ST = 256, T_DPT = 384, T_SFK = 448, T_SFQ = T_SFK + L::KB * 4;
+  constexpr uint32_t SFQ_SLOT = L::KB * 4;
+  static_assert(T_SFQ + 2 * SFQ_SLOT <= 512, "TMEM budget");
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one() && nstep > 0) {
       mbar_expect_tx(&kv_full, L::KP + L::V);
-      tma_load_3d(s_kp, &tm_kp, &kv_full, 0, n0, unit);
-      tma_load_3d(s_v, &tm_v, &kv_full, 0, n0, unit);
-      tma_load_3d(s_v + 16384, &tm_v, &kv_full, 64, n0, unit);
+#pragma unroll
+      for (int c = 0; c < L::KSUB; ++c) tma_load_3d(s_kp + c * 8192, &tm_kp, &kv_full, c * 64, n0, unit);
+#pragma unroll
+      for (int c = 0; c < L::DS; ++c) tma_load_3d(s_v + c * 16384, &tm_v, &kv_full, c * 64, n0, unit);
       // L2 prefetch kBwdPrefetch steps ahead: co-resident CTAs walk the same query tiles in step,
       // so without it every stage load is a first touch that waits on HBM
       auto prefetch = [&](int t) {
         const int gq = t / n_i, i = i_lo + t % n_i;
         const int zh = zi * p.h + kh * p.g + gq;
-        tma_prefetch_3d(&tm_qp, 0, i * 64, zh);
-        tma_prefetch_3d(&tm_do, 0, i * 64, zh);
-        tma_prefetch_3d(&tm_do, 64, i * 64, zh);
-        tma_prefetch_3d(&tm_q, 0, i * 64, zh);
-        tma_prefetch_3d(&tm_q, 64, i * 64, zh);
+#pragma unroll
+        for (int c = 0; c < L::KSUB; ++c) tma_prefetch_3d(&tm_qp, c * 64, i * 64, zh);
+#pragma unroll
+        for (int c = 0; c < L::DS; ++c) tma_prefetch_3d(&tm_do, c * 64, i * 64, zh);
+        tma_prefetch_3d(&tm_q, half * 128, i * 64, zh);
+        tma_prefetch_3d(&tm_q, half * 128 + 64, i * 64, zh);
       };
       for (int t = L::NSTAGE; t < min(nstep, kBwdPrefetch); ++t) prefetch(t);
       for (int st = 0; st < nstep; ++st) {
@@ -372,25 +386,29 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         uint8_t* sb = s_stage + s * L::STAGE;
         BTRACE(0, st, 0);
         mbar_expect_tx(&full_tma[s], L::QP + L::DO + L::Q);
-        tma_load_3d(sb + L::O_QP, &tm_qp, &full_tma[s], 0, i * 64, zh);
-        tma_load_3d(sb + L::O_DO, &tm_do, &full_tma[s], 0, i * 64, zh);
-        tma_load_3d(sb + L::O_DO + 8192, &tm_do, &full_tma[s], 64, i * 64, zh);
-        tma_load_3d(sb + L::O_Q, &tm_q, &full_tma[s], 0, i * 64, zh);
-        tma_load_3d(sb + L::O_Q + 8192, &tm_q, &full_tma[s], 64, i * 64, zh);
+#pragma unroll
+        for (int c = 0; c < L::KSUB; ++c)
+          tma_load_3d(sb + L::O_QP + c * 4096, &tm_qp, &full_tma[s], c * 64, i * 64, zh);
+#pragma unroll
+        for (int c = 0; c < L::DS; ++c)
+          tma_load_3d(sb + L::O_DO + c * 8192, &tm_do, &full_tma[s], c * 64, i * 64, zh);
+        tma_load_3d(sb + L::O_Q, &tm_q, &full_tma[s], half * 128, i * 64, zh);
+        tma_load_3d(sb + L::O_Q + 8192, &tm_q, &full_tma[s], half * 128 + 64, i * 64, zh);
       }
     }
     __syncwarp();
   } else if (warp == 2) {
     // ------------------------------------------------------------------ scale atoms / row statistics
     if (nstep > 0) {
-      const uint8_t* ksrc = p.ksc + (int64_t)unit * p.s_kv * 8;
+      const uint8_t* ksrc = p.ksc + (int64_t)unit * p.s_kv * (D / 16);
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
         const int r = lane + 32 * r4;
         const bool ok = n0 + r < p.s_kv;
-        const uint8_t* g = ksrc + (int64_t)(ok ? n0 + r : 0) * 8;
-        cp_async_4(smem_u32(s_ksf) + sf_atom_offset(r, 0), g, ok ? 4u : 0u);
-        cp_async_4(smem_u32(s_ksf) + 512 + sf_atom_offset(r, 0), g + 4, ok ? 4u : 0u);
+        const uint8_t* g = ksrc + (int64_t)(ok ? n0 + r : 0) * (D / 16);
+#pragma unroll
+        for (int c = 0; c < L::KB; ++c)
+          cp_async_4(smem_u32(s_ksf) + c * 512 + sf_atom_offset(r, 0), g + 4 * c, ok ? 4u : 0u);
       }
       cp_async_commit();
       cp_async_wait<0>();
@@ -410,9 +428,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
           const int r = lane + 32 * r2;
           const int qi = i * 64 + r;
           const bool ok = qi < p.s_q;
-          const uint8_t* g = p.qsc + ((int64_t)zh * p.s_q + (ok ? qi : 0)) * 8;
-          cp_async_4(qsf + sf_atom_offset(r, 0), g, ok ? 4u : 0u);
-          cp_async_4(qsf + 512 + sf_atom_offset(r, 0), g + 4, ok ? 4u : 0u);
+          const uint8_t* g = p.qsc + ((int64_t)zh * p.s_q + (ok ? qi : 0)) * (D / 16);
+#pragma unroll
+          for (int c = 0; c < L::KB; ++c) cp_async_4(qsf + c * 512 + sf_atom_offset(r, 0), g + 4 * c, ok ? 4u : 0u);
           // lse and delta land as they are (rows past the end read 0 and are masked by range)
           const int64_t gi = (int64_t)zh * p.s_q + (ok ? qi : 0);
           cp_async_4(smem_u32(aux + r), p.lse + gi, ok ? 4u : 0u);
@@ -443,11 +461,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       mbar_wait(&kv_full, 0, &err, 3);
       mbar_wait(&ksf_full, 0, &err, 4);
       tc_fence_after();
-      tmem_cp_32x128b_warpx4(tmem + T_SFK, smem_u32(s_ksf));
-      tmem_cp_32x128b_warpx4(tmem + T_SFK + 4, smem_u32(s_ksf + 512));
+#pragma unroll
+      for (int c = 0; c < L::KB; ++c) tmem_cp_32x128b_warpx4(tmem + T_SFK + 4 * c, smem_u32(s_ksf + c * 512));
       // descriptors: constant fields once, then only the 16-byte-unit address field moves
       const uint64_t b_v = desc_sw128(s_v, 0), b_kp = desc_sw64(s_kp, 0);
-      const uint64_t b_do = desc_sw128(s_stage + L::O_DO, 0), b_do_mn = desc_sw128_mn(s_stage + L::O_DO, 0, 8192);
+      const uint64_t b_do = desc_sw128(s_stage + L::O_DO, 0);
+      const uint64_t b_do_mn = desc_sw128_mn(s_stage + L::O_DO + half * 16384, 0, 8192);   // this half's two sub-tiles
       const uint64_t b_q_mn = desc_sw128_mn(s_stage + L::O_Q, 0, 8192), b_qp = desc_sw64(s_stage + L::O_QP, 0);
       // dV += P^T dO and dK += dS^T Q of step t (operands: slot t&1, stage t%NSTAGE)
       auto grad_gemms = [&](int t) {
@@ -473,14 +492,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         BTRACE(2, st, 0);
         // S^T slot b: its P^T / dS^T were consumed by the gradient GEMMs of step st-2, issued
         // earlier on this in-order pipe
-        tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8, smem_u32(sb + L::O_QSF));
-        tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * 8 + 4, smem_u32(sb + L::O_QSF + 512));
+#pragma unroll
+        for (int c = 0; c < L::KB; ++c)
+          tmem_cp_32x128b_warpx4(tmem + T_SFQ + b * SFQ_SLOT + 4 * c, smem_u32(sb + L::O_QSF + c * 512));
         const uint64_t so = (uint64_t)(s * (L::STAGE >> 4));
         const uint64_t x_qp = b_qp + so, x_do = b_do + so;
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-          umma_nvfp4(tmem + T_ST + b * 64, b_kp + 2 * k, x_qp + 2 * k, id_s, tmem + T_SFK + k * 4,
-                     tmem + T_SFQ + b * 8 + k * 4, k > 0);
+        for (int k = 0; k < L::KB; ++k)
+          umma_nvfp4(tmem + T_ST + b * 64, b_kp + (k >> 1) * 512 + (k & 1) * 2, x_qp + (k >> 1) * 256 + (k & 1) * 2,
+                     id_s, tmem + T_SFK + k * 4, tmem + T_SFQ + b * SFQ_SLOT + k * 4, k > 0);
         umma_commit(&s_full[b]);
         BTRACE(2, st, 1);
         if (st > 0) {
@@ -489,7 +509,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         }
         BTRACE(2, st, 2);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
+        for (int k = 0; k < D / 16; ++k)
           umma_bf16(tmem + T_DPT, b_v + (k >> 2) * 1024 + (k & 3) * 2, x_do + (k >> 2) * 512 + (k & 3) * 2, id_dp,
                     k > 0);
         umma_commit(&dp_full);
@@ -535,8 +555,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       const float* aux = reinterpret_cast<const float*>(sb + L::O_AUX) + grp * 32;
       const uint32_t slot = tmem + lane_addr + T_ST + b * 64 + grp * 32;
       const bool masked = !__all_sync(0xffffffffu, q0 >= ql && q0 + 32 <= qh);
-      const int trole = 4 + grp + 2 * (warp & 3);
-      const bool trc_any = lane == 0;
+      [[maybe_unused]] const int trole = 4 + grp + 2 * (warp & 3);
+      [[maybe_unused]] const bool trc_any = lane == 0;
       if (trc_any) BTRACE(trole, st, 0);
       mbar_wait(&full_aux[s], (st / L::NSTAGE) & 1, &err, 10);
       if (trc_any) BTRACE(trole, st, 1);
@@ -574,8 +594,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       if (trc_any) BTRACE(trole, st, 7);
     }
     // ---- epilogue: group g writes gradient columns [64g, 64g+64)
-    TG* dkrow = static_cast<TG*>(p.dk) + ((int64_t)unit * p.s_kv + key) * 128 + grp * 64;
-    TG* dvrow = static_cast<TG*>(p.dv) + ((int64_t)unit * p.s_kv + key) * 128 + grp * 64;
+    TG* dkrow = static_cast<TG*>(p.dk) + ((int64_t)unit * p.s_kv + key) * D + half * 128 + grp * 64;
+    TG* dvrow = static_cast<TG*>(p.dv) + ((int64_t)unit * p.s_kv + key) * D + half * 128 + grp * 64;
     if (nstep > 0) {
       mbar_wait(&acc_done, 0, &err, 14);
       tc_fence_after();
@@ -603,29 +623,33 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
 
 // ------------------------------------------------------------------------------------------
 // dQ
-// TMEM: dQ [0,128) | S slots [128,192) [192,256) | dP [256,320) | SFQ [320,328) |
-//       SFK slots [328,336) [336,344)
+// TMEM: dQ [0,128) | S slots [128,192) [192,256) | dP [256,320) | SFQ [320, 320+D/16) |
+//       two SFK slots of D/16 columns.  Head dim 256: blockIdx.z picks a 128-wide half of dQ.
 // dS (bf16 pairs, 32 columns) is written back into the S slot it came from and feeds the dQ GEMM
 // as a TMEM A operand.
 // ------------------------------------------------------------------------------------------
+template <int D>
 struct DqSmem {
-  static constexpr int DO = 32768;       // dO bf16 [128 q x 128 d] = 2 sub-tiles of 16 KB
-  static constexpr int QP = 8192;        // Q pack tile, 128 queries x 64 B
-  static constexpr int QSF = 1024;
-  // per stage: V and K bf16 [64 keys x 128 d] as 2 sub-tiles of 8 KB, K pack [64 keys x 64 B], K scale atoms
-  static constexpr int V = 16384, K = 16384, KP = 4096, KSF = 1024;
+  static constexpr int DS = D / 64, KSUB = D / 128, KB = D / 64;
+  static constexpr int DO = DS * 16384;    // dO bf16 [128 q x D] as 16 KB sub-tiles
+  static constexpr int QP = KSUB * 8192;   // Q pack tile, 128 queries x D/2 B
+  static constexpr int QSF = KB * 512;
+  // per stage: V bf16 [64 keys x D] and the 128-wide half of K bf16 (8 KB sub-tiles), K pack
+  // [64 keys x D/2 B], K scale atoms
+  static constexpr int V = DS * 8192, K = 16384, KP = KSUB * 4096, KSF = KB * 512;
   static constexpr int O_V = 0, O_K = V, O_KP = V + K, O_KSF = O_KP + KP;
   static constexpr int STAGE = V + K + KP + KSF;
-  static constexpr int NSTAGE = 4;
+  static constexpr int NSTAGE = D == 128 ? 4 : 2;
   static constexpr int TOTAL = DO + QP + NSTAGE * STAGE + QSF + 1024;
+  static_assert(STAGE % 1024 == 0 && (DO + QP) % 1024 == 0, "128-byte-swizzled tiles need 1 KB alignment");
 };
 
-template <typename TG>
+template <int D, typename TG>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__ CUtensorMap tm_kp,
               const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_v,
               const __grid_constant__ CUtensorMap tm_k, const BwdParams p) {
-  using L = DqSmem;
+  using L = DqSmem<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -642,6 +666,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mblk = gridDim.y - 1 - blockIdx.y;   // late query tiles see the most keys: first
   const int zh = blockIdx.x;
+  const int half = blockIdx.z;         // 128-wide slice of the head dim owned by this CTA
   const int zi = zh / p.h, hi = zh % p.h;
   const int unit = zi * p.hk + hi / p.g;
   const int m0 = mblk * 128;
@@ -679,21 +704,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  constexpr uint32_t T_DQ = 0, T_S = 128, T_DP = 256, T_SFQ = 320, T_SFK = 328;
+  constexpr uint32_t T_DQ = 0, T_S = 128, T_DP = 256, T_SFQ = 320, T_SFK = T_SFQ + L::KB * 4;
+  constexpr uint32_t SFK_SLOT = L::KB * 4;
 
   if (warp == 0) {
     if (elect_one() && nstep > 0) {
       mbar_expect_tx(&q_full, L::QP + L::DO);
-      tma_load_3d(s_qp, &tm_qp, &q_full, 0, m0, zh);
-      tma_load_3d(s_do, &tm_do, &q_full, 0, m0, zh);
-      tma_load_3d(s_do + 16384, &tm_do, &q_full, 64, m0, zh);
+#pragma unroll
+      for (int c = 0; c < L::KSUB; ++c) tma_load_3d(s_qp + c * 8192, &tm_qp, &q_full, c * 64, m0, zh);
+#pragma unroll
+      for (int c = 0; c < L::DS; ++c) tma_load_3d(s_do + c * 16384, &tm_do, &q_full, c * 64, m0, zh);
       auto prefetch = [&](int t) {
         const int key0 = (j_lo + t) * 64;
-        tma_prefetch_3d(&tm_kp, 0, key0, unit);
-        tma_prefetch_3d(&tm_v, 0, key0, unit);
-        tma_prefetch_3d(&tm_v, 64, key0, unit);
-        tma_prefetch_3d(&tm_k, 0, key0, unit);
-        tma_prefetch_3d(&tm_k, 64, key0, unit);
+#pragma unroll
+        for (int c = 0; c < L::KSUB; ++c) tma_prefetch_3d(&tm_kp, c * 64, key0, unit);
+#pragma unroll
+        for (int c = 0; c < L::DS; ++c) tma_prefetch_3d(&tm_v, c * 64, key0, unit);
+        tma_prefetch_3d(&tm_k, half * 128, key0, unit);
+        tma_prefetch_3d(&tm_k, half * 128 + 64, key0, unit);
       };
       for (int t = L::NSTAGE; t < min(nstep, kBwdPrefetch); ++t) prefetch(t);
       for (int st = 0; st < nstep; ++st) {
@@ -702,31 +730,34 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * L::STAGE;
         mbar_expect_tx(&full_tma[s], L::KP + L::V + L::K);
-        tma_load_3d(sb + L::O_KP, &tm_kp, &full_tma[s], 0, key0, unit);
-        tma_load_3d(sb + L::O_V, &tm_v, &full_tma[s], 0, key0, unit);
-        tma_load_3d(sb + L::O_V + 8192, &tm_v, &full_tma[s], 64, key0, unit);
-        tma_load_3d(sb + L::O_K, &tm_k, &full_tma[s], 0, key0, unit);
-        tma_load_3d(sb + L::O_K + 8192, &tm_k, &full_tma[s], 64, key0, unit);
+#pragma unroll
+        for (int c = 0; c < L::KSUB; ++c)
+          tma_load_3d(sb + L::O_KP + c * 4096, &tm_kp, &full_tma[s], c * 64, key0, unit);
+#pragma unroll
+        for (int c = 0; c < L::DS; ++c) tma_load_3d(sb + L::O_V + c * 8192, &tm_v, &full_tma[s], c * 64, key0, unit);
+        tma_load_3d(sb + L::O_K, &tm_k, &full_tma[s], half * 128, key0, unit);
+        tma_load_3d(sb + L::O_K + 8192, &tm_k, &full_tma[s], half * 128 + 64, key0, unit);
       }
     }
     __syncwarp();
   } else if (warp == 2) {
     if (nstep > 0) {
-      const uint8_t* qsrc = p.qsc + (int64_t)zh * p.s_q * 8;
+      const uint8_t* qsrc = p.qsc + (int64_t)zh * p.s_q * (D / 16);
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
         const int r = lane + 32 * r4;
         const bool ok = m0 + r < p.s_q;
-        const uint8_t* g = qsrc + (int64_t)(ok ? m0 + r : 0) * 8;
-        cp_async_4(smem_u32(s_qsf) + sf_atom_offset(r, 0), g, ok ? 4u : 0u);
-        cp_async_4(smem_u32(s_qsf) + 512 + sf_atom_offset(r, 0), g + 4, ok ? 4u : 0u);
+        const uint8_t* g = qsrc + (int64_t)(ok ? m0 + r : 0) * (D / 16);
+#pragma unroll
+        for (int c = 0; c < L::KB; ++c)
+          cp_async_4(smem_u32(s_qsf) + c * 512 + sf_atom_offset(r, 0), g + 4 * c, ok ? 4u : 0u);
       }
       cp_async_commit();
       cp_async_wait<0>();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&qsf_full);
-      const uint8_t* ksrc = p.ksc + (int64_t)unit * p.s_kv * 8;
+      const uint8_t* ksrc = p.ksc + (int64_t)unit * p.s_kv * (D / 16);
       for (int st = 0; st < nstep; ++st) {
         const int s = st % L::NSTAGE, key0 = (j_lo + st) * 64;
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 2);
@@ -736,9 +767,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
           const int r = lane + 32 * r2;
           const int key = key0 + r;
           const bool ok = key < p.s_kv;
-          const uint8_t* g = ksrc + (int64_t)(ok ? key : 0) * 8;
-          cp_async_4(ksf + sf_atom_offset(r, 0), g, ok ? 4u : 0u);
-          cp_async_4(ksf + 512 + sf_atom_offset(r, 0), g + 4, ok ? 4u : 0u);
+          const uint8_t* g = ksrc + (int64_t)(ok ? key : 0) * (D / 16);
+#pragma unroll
+          for (int c = 0; c < L::KB; ++c) cp_async_4(ksf + c * 512 + sf_atom_offset(r, 0), g + 4 * c, ok ? 4u : 0u);
         }
         cp_async_commit();
         cp_async_wait<0>();
@@ -755,8 +786,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       mbar_wait(&q_full, 0, &err, 3);
       mbar_wait(&qsf_full, 0, &err, 4);
       tc_fence_after();
-      tmem_cp_32x128b_warpx4(tmem + T_SFQ, smem_u32(s_qsf));
-      tmem_cp_32x128b_warpx4(tmem + T_SFQ + 4, smem_u32(s_qsf + 512));
+#pragma unroll
+      for (int c = 0; c < L::KB; ++c) tmem_cp_32x128b_warpx4(tmem + T_SFQ + 4 * c, smem_u32(s_qsf + c * 512));
       const uint64_t b_do = desc_sw128(s_do, 0), b_qp = desc_sw64(s_qp, 0);
       const uint64_t b_v = desc_sw128(s_stage + L::O_V, 0), b_k_mn = desc_sw128_mn(s_stage + L::O_K, 0, 8192);
       const uint64_t b_kp = desc_sw64(s_stage + L::O_KP, 0);
@@ -775,21 +806,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
         mbar_wait(&full_tma[s], ph, &err, 5);
         mbar_wait(&full_sf[s], ph, &err, 6);
         tc_fence_after();
-        tmem_cp_32x128b_warpx4(tmem + T_SFK + b * 8, smem_u32(sb + L::O_KSF));
-        tmem_cp_32x128b_warpx4(tmem + T_SFK + b * 8 + 4, smem_u32(sb + L::O_KSF + 512));
+#pragma unroll
+        for (int c = 0; c < L::KB; ++c)
+          tmem_cp_32x128b_warpx4(tmem + T_SFK + b * SFK_SLOT + 4 * c, smem_u32(sb + L::O_KSF + c * 512));
         const uint64_t so = (uint64_t)(s * (L::STAGE >> 4));
         const uint64_t x_kp = b_kp + so, x_v = b_v + so;
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-          umma_nvfp4(tmem + T_S + b * 64, b_qp + 2 * k, x_kp + 2 * k, id_s, tmem + T_SFQ + k * 4,
-                     tmem + T_SFK + b * 8 + k * 4, k > 0);
+        for (int k = 0; k < L::KB; ++k)
+          umma_nvfp4(tmem + T_S + b * 64, b_qp + (k >> 1) * 512 + (k & 1) * 2, x_kp + (k >> 1) * 256 + (k & 1) * 2,
+                     id_s, tmem + T_SFQ + k * 4, tmem + T_SFK + b * SFK_SLOT + k * 4, k > 0);
         umma_commit(&s_full[b]);
         if (st > 0) {
           mbar_wait(&dp_free, (st - 1) & 1, &err, 7);
           tc_fence_after();
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
+        for (int k = 0; k < D / 16; ++k)
           umma_bf16(tmem + T_DP, b_do + (k >> 2) * 1024 + (k & 3) * 2, x_v + (k >> 2) * 512 + (k & 3) * 2, id_dp,
                     k > 0);
         umma_commit(&dp_full);
@@ -855,7 +887,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[b]);
     }
-    TG* dqrow = static_cast<TG*>(p.dq) + ((int64_t)zh * p.s_q + row) * 128 + grp * 64;
+    TG* dqrow = static_cast<TG*>(p.dq) + ((int64_t)zh * p.s_q + row) * D + half * 128 + grp * 64;
     if (nstep > 0) {
       mbar_wait(&acc_done, 0, &err, 14);
       tc_fence_after();
@@ -940,7 +972,7 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
                             int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
                             int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
-  NVFP4_REQUIRE(d == 128, "nvfp4_bwd_hp: this build implements the backward for D = 128 only");
+  NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_bwd_hp: head dim must be 128 or 256");
   NVFP4_REQUIRE(z >= 1 && h >= 1 && hk >= 1 && h % hk == 0, "nvfp4_bwd_hp: bad head counts");
   NVFP4_REQUIRE(s_q >= 1 && s_kv >= 1 && s_q < (1LL << 30) && s_kv < (1LL << 30), "nvfp4_bwd_hp: bad sequence extents");
   NVFP4_REQUIRE(qnv && qsc && knv && ksc && q_bf16 && k_bf16 && v_bf16 && do_bf16 && lse && delta && dq && dk && dv,
@@ -955,16 +987,17 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
   const int64_t zh = z * h, zhk = z * hk;
   CUtensorMap t_qp64, t_qp128, t_kp64, t_kp128, t_v64, t_v128, t_do64, t_do128, t_q64, t_k64;
   int rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_qp64, qnv, 64, s_q, zh, 64, (uint64_t)s_q * 64, 64, "nvfp4_bwd_hp(Qp64)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_qp128, qnv, 64, s_q, zh, 64, (uint64_t)s_q * 64, 128, "nvfp4_bwd_hp(Qp128)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_kp64, knv, 64, s_kv, zhk, 64, (uint64_t)s_kv * 64, 64, "nvfp4_bwd_hp(Kp64)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_kp128, knv, 64, s_kv, zhk, 64, (uint64_t)s_kv * 64, 128, "nvfp4_bwd_hp(Kp128)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_v64, v_bf16, 128, s_kv, zhk, 256, (uint64_t)s_kv * 256, 64, "nvfp4_bwd_hp(V64)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_v128, v_bf16, 128, s_kv, zhk, 256, (uint64_t)s_kv * 256, 128, "nvfp4_bwd_hp(V128)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_do64, do_bf16, 128, s_q, zh, 256, (uint64_t)s_q * 256, 64, "nvfp4_bwd_hp(dO64)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_do128, do_bf16, 128, s_q, zh, 256, (uint64_t)s_q * 256, 128, "nvfp4_bwd_hp(dO128)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_q64, q_bf16, 128, s_q, zh, 256, (uint64_t)s_q * 256, 64, "nvfp4_bwd_hp(Q64)"))) return rc;
-  if ((rc = make_tmap_bf16_3d_sw128(&t_k64, k_bf16, 128, s_kv, zhk, 256, (uint64_t)s_kv * 256, 64, "nvfp4_bwd_hp(K64)"))) return rc;
+  const uint64_t pb = (uint64_t)d / 2, hb = (uint64_t)d * 2;   // bytes per pack row / bf16 row
+  if ((rc = make_tmap_u8_3d_sw64(&t_qp64, qnv, pb, s_q, zh, pb, (uint64_t)s_q * pb, 64, "nvfp4_bwd_hp(Qp64)"))) return rc;
+  if ((rc = make_tmap_u8_3d_sw64(&t_qp128, qnv, pb, s_q, zh, pb, (uint64_t)s_q * pb, 128, "nvfp4_bwd_hp(Qp128)"))) return rc;
+  if ((rc = make_tmap_u8_3d_sw64(&t_kp64, knv, pb, s_kv, zhk, pb, (uint64_t)s_kv * pb, 64, "nvfp4_bwd_hp(Kp64)"))) return rc;
+  if ((rc = make_tmap_u8_3d_sw64(&t_kp128, knv, pb, s_kv, zhk, pb, (uint64_t)s_kv * pb, 128, "nvfp4_bwd_hp(Kp128)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_v64, v_bf16, d, s_kv, zhk, hb, (uint64_t)s_kv * hb, 64, "nvfp4_bwd_hp(V64)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_v128, v_bf16, d, s_kv, zhk, hb, (uint64_t)s_kv * hb, 128, "nvfp4_bwd_hp(V128)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_do64, do_bf16, d, s_q, zh, hb, (uint64_t)s_q * hb, 64, "nvfp4_bwd_hp(dO64)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_do128, do_bf16, d, s_q, zh, hb, (uint64_t)s_q * hb, 128, "nvfp4_bwd_hp(dO128)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_q64, q_bf16, d, s_q, zh, hb, (uint64_t)s_q * hb, 64, "nvfp4_bwd_hp(Q64)"))) return rc;
+  if ((rc = make_tmap_bf16_3d_sw128(&t_k64, k_bf16, d, s_kv, zhk, hb, (uint64_t)s_kv * hb, 64, "nvfp4_bwd_hp(K64)"))) return rc;
   BwdParams p;
   p.qsc = qsc; p.ksc = ksc; p.lse = lse; p.delta = delta;
   p.seq_start = seq_start; p.seq_end = seq_end;
@@ -976,23 +1009,35 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
 #else
   p.timing = nullptr;
 #endif
-  auto launch = [&](auto kdkdv, auto kdq) -> int {
-    cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkdvSmem::TOTAL);
+  const unsigned halves = (unsigned)(d / 128);
+  auto launch = [&](auto kdkdv, auto kdq, int smem_dkdv, int smem_dq) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkdv);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_bwd_hp: smem attribute: %s", cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem::TOTAL);
+    e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_bwd_hp: smem attribute: %s", cudaGetErrorString(e));
-    dim3 g1((unsigned)zhk, (unsigned)((s_kv + 127) / 128));
-    kdkdv<<<g1, kBwdThreads, DkdvSmem::TOTAL, st>>>(t_kp128, t_qp64, t_v128, t_do64, t_q64, p);
+    dim3 g1((unsigned)zhk, (unsigned)((s_kv + 127) / 128), halves);
+    kdkdv<<<g1, kBwdThreads, smem_dkdv, st>>>(t_kp128, t_qp64, t_v128, t_do64, t_q64, p);
     int r1 = launch_result("nvfp4_bwd_hp(dkdv)");
     if (r1) return r1;
-    dim3 g2((unsigned)zh, (unsigned)((s_q + 127) / 128));
-    kdq<<<g2, kBwdThreads, DqSmem::TOTAL, st>>>(t_qp128, t_kp64, t_do128, t_v64, t_k64, p);
+    dim3 g2((unsigned)zh, (unsigned)((s_q + 127) / 128), halves);
+    kdq<<<g2, kBwdThreads, smem_dq, st>>>(t_qp128, t_kp64, t_do128, t_v64, t_k64, p);
     return launch_result("nvfp4_bwd_hp(dq)");
   };
+#define NVFP4_BWD_LAUNCH(DD, TT) \
+  launch(bwd_dkdv_kernel<DD, TT>, bwd_dq_kernel<DD, TT>, DkdvSmem<DD>::TOTAL, DqSmem<DD>::TOTAL)
+  if (d == 128) {
+    switch (grad_dtype) {
+      case NVFP4_DT_BF16: return NVFP4_BWD_LAUNCH(128, __nv_bfloat16);
+      case NVFP4_DT_FP16: return NVFP4_BWD_LAUNCH(128, __half);
+      case NVFP4_DT_FP32: return NVFP4_BWD_LAUNCH(128, float);
+      default: return fail(-1, "nvfp4_bwd_hp: unknown grad dtype %d", grad_dtype);
+    }
+  }
   switch (grad_dtype) {
-    case NVFP4_DT_BF16: return launch(bwd_dkdv_kernel<__nv_bfloat16>, bwd_dq_kernel<__nv_bfloat16>);
-    case NVFP4_DT_FP16: return launch(bwd_dkdv_kernel<__half>, bwd_dq_kernel<__half>);
-    case NVFP4_DT_FP32: return launch(bwd_dkdv_kernel<float>, bwd_dq_kernel<float>);
+    case NVFP4_DT_BF16: return NVFP4_BWD_LAUNCH(256, __nv_bfloat16);
+    case NVFP4_DT_FP16: return NVFP4_BWD_LAUNCH(256, __half);
+    case NVFP4_DT_FP32: return NVFP4_BWD_LAUNCH(256, float);
     default: return fail(-1, "nvfp4_bwd_hp: unknown grad dtype %d", grad_dtype);
   }
+#undef NVFP4_BWD_LAUNCH
 }

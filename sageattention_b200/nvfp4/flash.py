@@ -440,7 +440,7 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     """
     z, h, s_q, d = q.shape
     _, hk, s_kv, _ = k.shape
-    assert d == 128, "the B200 backward kernels of this build support head dim 128"
+    assert d in (128, 256), "D must be 128 or 256"
     dev = q.device
     if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
         out = out.transpose(1, 2)

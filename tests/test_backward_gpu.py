@@ -100,6 +100,46 @@ def test_backward_matches_reference_fixture(golden, name, floor):
         assert c >= floor, (nm, c)
 
 
+@pytest.mark.parametrize("z,h,hk,sq,skv,causal", [(1, 4, 2, 256, 256, True), (1, 2, 1, 200, 328, True),
+                                                  (2, 2, 2, 128, 192, False)])
+def test_backward_d256_matches_exact_gradients(z, h, hk, sq, skv, causal):
+    """Head dim 256: the kernels own a 128-wide half of each gradient tile per CTA."""
+    d = 256
+    q, qn = seeded_bf16((z, h, sq, d), 51)
+    k, kn = seeded_bf16((z, hk, skv, d), 52)
+    v, vn = seeded_bf16((z, hk, skv, d), 53)
+    do, don = seeded_bf16((z, h, sq, d), 54)
+    out, dq, dk, dv = _grads(q, k, v, do, causal, h // hk)
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, causal, h // hk)
+    for nm, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        a = a.float().cpu().numpy()
+        assert np.isfinite(a).all(), nm
+        c = cos(a, b)
+        print("d256", nm, "cos", c)
+        assert c >= (COS_HP if min(sq, skv) >= 256 else 0.985), (nm, c)
+
+
+def test_backward_d256_varlen_against_dense():
+    d, h, hk = 256, 2, 1
+    lens = [192, 70, 250]
+    s = sum(lens)
+    q, _ = seeded_bf16((1, h, s, d), 61)
+    k, _ = seeded_bf16((1, hk, s, d), 62)
+    v, _ = seeded_bf16((1, hk, s, d), 63)
+    do, _ = seeded_bf16((1, h, s, d), 64)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu)
+    a = 0
+    for n in lens:
+        sl = slice(a, a + n)
+        _, dq1, dk1, dv1 = _grads(q[:, :, sl].contiguous(), k[:, :, sl].contiguous(), v[:, :, sl].contiguous(),
+                                  do[:, :, sl].contiguous(), True, h // hk)
+        for nm, x, y in (("dq", dq[:, :, sl], dq1), ("dk", dk[:, :, sl], dk1), ("dv", dv[:, :, sl], dv1)):
+            c = cos(x.float().cpu().numpy(), y.float().cpu().numpy())
+            assert c >= 0.995, (nm, n, c)
+        a += n
+
+
 def test_backward_varlen_blocks_are_independent():
     """Packed varlen backward == per-sequence dense backward (reference: test_nvfp4_varlen.py)."""
     d, h, hk = 128, 2, 1

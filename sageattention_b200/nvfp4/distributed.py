@@ -15,7 +15,11 @@ The reference has no distributed code on this path.  Two schemes cover its confi
 
 ``ring_attention`` is written against two callables (block attention and merge) so the ring
 schedule and the message plumbing are testable with ``gloo`` on CPU; ``ring_flash_attention``
-binds them to the CUDA operators.
+binds them to the CUDA operators.  The backward (``ring_attention_backward`` /
+``ring_flash_attention_backward``) walks the same ring: a K/V block travels together with the
+fp32 accumulators of its dK/dV, every rank adds the contribution of its own queries (exact
+because the probabilities are recomputed against the merged LSE of the forward), and one last hop
+brings each accumulator home.  ``ring_flash_attn_func`` ties both into autograd.
 """
 
 from __future__ import annotations
@@ -118,6 +122,55 @@ def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
     return out, lse
 
 
+def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequence[torch.Tensor],
+                            block_backward: Callable, causal: bool, group=None):
+    """Gradients of ``ring_attention``.
+
+    ``kv_block``: the tensors that describe the local K/V block for the backward (fixed shapes
+    across ranks).  ``grad_like``: two tensors shaped like the local dK and dV (fp32 accumulators are
+    allocated like them).  ``block_backward(block, mode)`` returns ``(dq, dk, dv)`` of the local
+    queries against that block for mode "full" or "causal" (dq of the local queries, dk/dv of the
+    block's keys).  Returns ``(dq, dk, dv)`` for the local slices; dk/dv in fp32.
+
+    Step t works on the block that originated on rank ``rank - t``; the block's accumulators arrive
+    one step behind the block itself, so their transfer overlaps the next block computation.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    cur = list(kv_block)
+    acc = [torch.zeros_like(g, dtype=torch.float32) for g in grad_like]
+    acc_recv, acc_reqs = None, []
+    dq = None
+    for t, (src, mode) in enumerate(ring_steps(rank, world, causal)):
+        reqs, nxt_bufs = [], None
+        if t + 1 < world:
+            nxt_bufs = [torch.empty_like(x) for x in cur]
+            reqs = _exchange(cur, nxt_bufs, group, rank, world)
+        part = block_backward(cur, mode) if mode != "skip" else None
+        if t > 0:                       # accumulators of the block held now, sent after step t-1
+            for r in acc_reqs:
+                r.wait()
+            acc = acc_recv
+        if part is not None:
+            dq = part[0].float() if dq is None else dq + part[0].float()
+            acc[0] += part[1].float()
+            acc[1] += part[2].float()
+        for r in reqs:
+            r.wait()
+        if world > 1:                   # forward the accumulators (last step: the hop back home)
+            acc_recv = [torch.empty_like(a) for a in acc]
+            acc_reqs = _exchange(acc, acc_recv, group, rank, world)
+        if nxt_bufs is not None:
+            cur = nxt_bufs
+    if world > 1:
+        for r in acc_reqs:
+            r.wait()
+        acc = acc_recv
+    if dq is None:
+        dq = torch.zeros_like(grad_like[0][:0])
+    return dq, acc[0], acc[1]
+
+
 def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None):
     """NVFP4 ring attention on CUDA: ``query [Z,H,S_loc,D]``, ``key/value [Z,Hk,S_loc,D]`` are this
     rank's contiguous slice of the sequence (slice length a multiple of 128).  Returns
@@ -151,3 +204,65 @@ def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_
 
     out, lse = ring_attention(query, block, block_attention, merge, causal, group)
     return out.to(query.dtype), lse
+
+
+def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, causal=True,
+                                  num_key_value_groups=1, group=None):
+    """NVFP4 ring-attention backward on CUDA for the local sequence slices (bf16 tensors).
+
+    ``out`` / ``lse`` are the merged results of ``ring_flash_attention``; with them every block's
+    probabilities are the globally normalised ones, so the per-block backward kernels give exact
+    contributions.  Returns ``(dq, dk, dv)`` in ``dout.dtype``.
+    """
+    from .. import _lib
+    from . import flash
+
+    z, h, s_loc, d = query.shape
+    hk = key.shape[1]
+    dev = query.device
+    qc, kc, vc = flash._as_bf16_rows(query), flash._as_bf16_rows(key), flash._as_bf16_rows(value)
+    need_copy = not (dout.dtype == torch.bfloat16 and dout.is_contiguous())
+    doc, delta = flash._bwd_prep(dout, y=out.to(dout.dtype), want_copy=need_copy)
+    if doc is None:
+        doc = dout.view(z * h, s_loc, d)
+    qnv, qsc = flash._quant_nvfp4(query.reshape(z * h, s_loc, d))
+    knv, ksc = flash._quant_nvfp4(key.reshape(z * hk, s_loc, d))
+    lse = lse.contiguous()
+    block = [kc, vc, knv, ksc.view(torch.uint8)]
+
+    def block_backward(blk, mode):
+        dq = torch.empty(z, h, s_loc, d, dtype=torch.float32, device=dev)
+        dk = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+        dv = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+        _lib.check(_lib.lib().nvfp4_bwd_hp(
+            qnv.data_ptr(), qsc.data_ptr(), blk[2].data_ptr(), blk[3].data_ptr(), qc.data_ptr(),
+            blk[0].data_ptr(), blk[1].data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, None,
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.DT_FP32, z, h, hk, s_loc, s_loc, d, float(scaling),
+            1 if mode == "causal" else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+        return dq, dk, dv
+
+    like = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+    dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group)
+    gdt = dout.dtype
+    return dq.to(gdt), dk.to(gdt), dv.to(gdt)
+
+
+class _RingFlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, key, value, scaling, causal, g, group):
+        out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group)
+        ctx.save_for_backward(query, key, value, out, lse)
+        ctx.meta = (float(scaling), bool(causal), int(g), group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        query, key, value, out, lse = ctx.saved_tensors
+        scaling, causal, g, group = ctx.meta
+        dq, dk, dv = ring_flash_attention_backward(query, key, value, out, lse, grad_out, scaling, causal, g, group)
+        return dq, dk, dv, None, None, None, None
+
+
+def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None):
+    """Differentiable context-parallel NVFP4 attention over this rank's sequence slice."""
+    return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group)

@@ -102,3 +102,65 @@ def test_ring_attention_two_gloo_ranks_equals_single_process(causal):
         p.join(120)
         assert p.exitcode == 0
     assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)
+
+
+def _ring_bwd_worker(rank, world, port, causal, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        z, h, hk, s_loc, d = 1, 4, 2, 16, 8
+        g_ = h // hk
+        gen = torch.Generator().manual_seed(1)
+        q = torch.randn(z, h, s_loc * world, d, generator=gen)
+        k = torch.randn(z, hk, s_loc * world, d, generator=gen)
+        v = torch.randn(z, hk, s_loc * world, d, generator=gen)
+        do = torch.randn(z, h, s_loc * world, d, generator=gen)
+        sl = slice(rank * s_loc, (rank + 1) * s_loc)
+        ql, kl, vl, dol = (t[:, :, sl].contiguous() for t in (q, k, v, do))
+        rq, rk, rv = O.attention_grads(q.numpy(), k.numpy(), v.numpy(), do.numpy(), d ** -0.5, causal, g_)
+        out_full, p_full = O.attention_exact(q.numpy(), k.numpy(), v.numpy(), d ** -0.5, causal, g_)
+        out_l = torch.from_numpy(out_full[:, :, sl]).float()
+        # merged LSE of the forward for the local rows
+        sc = torch.matmul(q, k.repeat_interleave(g_, 1).transpose(-1, -2)) * d ** -0.5
+        if causal:
+            n = s_loc * world
+            sc = sc.masked_fill(~torch.ones(n, n, dtype=torch.bool).tril(), float("-inf"))
+        lse_l = torch.logsumexp(sc, dim=-1)[:, :, sl]
+        delta_l = (dol * out_l).sum(-1)
+
+        def block_backward(blk, mode):
+            kb, vb = blk
+            kk, vv = kb.repeat_interleave(g_, 1), vb.repeat_interleave(g_, 1)
+            s_ = torch.matmul(ql, kk.transpose(-1, -2)) * d ** -0.5
+            if mode == "causal":
+                s_ = s_.masked_fill(~torch.ones(s_loc, s_loc, dtype=torch.bool).tril(), float("-inf"))
+            p_ = torch.exp(s_ - lse_l[..., None])
+            dp = torch.matmul(dol, vv.transpose(-1, -2))
+            ds = p_ * (dp - delta_l[..., None]) * d ** -0.5
+            dq = torch.matmul(ds, kk)
+            dk = torch.matmul(ds.transpose(-1, -2), ql).reshape(z, hk, g_, s_loc, d).sum(2)
+            dv = torch.matmul(p_.transpose(-1, -2), dol).reshape(z, hk, g_, s_loc, d).sum(2)
+            return dq, dk, dv
+
+        dq, dk, dv = D.ring_attention_backward([kl, vl], [kl, vl], block_backward, causal)
+        err = max(float(np.abs(dq.numpy() - rq[:, :, sl]).max()), float(np.abs(dk.numpy() - rk[:, :, sl]).max()),
+                  float(np.abs(dv.numpy() - rv[:, :, sl]).max()))
+        ret[rank] = err
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal,world", [(True, 2), (False, 2), (True, 3)])
+def test_ring_backward_gloo_ranks_equal_single_process(causal, world):
+    """dK/dV accumulators travel with their block and come home after the last hop."""
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_ring_bwd_worker, args=(r, world, port, causal, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

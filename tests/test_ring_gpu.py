@@ -47,7 +47,20 @@ def _worker(rank, world, port, ret):
         gathered = [torch.empty_like(part) for _ in range(world)]
         dist.all_gather(gathered, part)
         shard_equal = bool(torch.equal(D.unshard_out(gathered, z, hk, world), full))
-        ret[rank] = (cos, lse_err, shard_equal)
+        # ring backward through autograd vs the single-GPU backward on the whole sequence
+        do = torch.randn(z, h, s, d, generator=g).to(torch.bfloat16).cuda()
+        ql = q[:, :, sl].contiguous().requires_grad_(True)
+        kl = k[:, :, sl].contiguous().requires_grad_(True)
+        vl = v[:, :, sl].contiguous().requires_grad_(True)
+        o_ring = D.ring_flash_attn_func(ql, kl, vl, d ** -0.5, causal=True, num_key_value_groups=h // hk)
+        o_ring.backward(do[:, :, sl].contiguous())
+        qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o_full = nv.nvfp4_flash_attn_func(qf, kf, vf, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                          backward_grad_dots="bf16")
+        o_full.backward(do)
+        cosf = lambda x, y: float(torch.nn.functional.cosine_similarity(x.float().flatten(), y.float().flatten(), dim=0))
+        gcos = (cosf(ql.grad, qf.grad[:, :, sl]), cosf(kl.grad, kf.grad[:, :, sl]), cosf(vl.grad, vf.grad[:, :, sl]))
+        ret[rank] = (cos, lse_err, shard_equal, gcos)
     finally:
         dist.destroy_process_group()
 
@@ -66,7 +79,8 @@ def test_ring_and_sharding_two_gpus_match_single_gpu():
         p.join(300)
         assert p.exitcode == 0
     for r in range(world):
-        cos, lse_err, shard_equal = ret[r]
+        cos, lse_err, shard_equal, gcos = ret[r]
+        assert min(gcos) >= 0.995, (r, gcos)   # ring gradients vs the single-GPU backward
         assert cos >= 0.995, (r, cos)          # same keys, different tile order: FP4-P rounding level
         assert lse_err <= 2e-3, (r, lse_err)   # the softmax statistics themselves are exact
         assert shard_equal                     # sharded units are bit-identical to the full run

@@ -413,6 +413,77 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_ring(args):
+    """BASELINE config 5: Z1 H16 Hk4 S131072 D256 causal forward + backward, the sequence split
+    over the ranks (context-parallel ring attention; one rank = the plain single-GPU operators)."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import sageattention_b200.nvfp4 as nv
+    from sageattention_b200 import _lib
+    from sageattention_b200.nvfp4 import distributed as RD
+    z, h, hk, d, s = 1, 16, 4, 256, args.ring_seq
+    s_loc = s // world
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
+    q, k, v, do = rn(z, h, s_loc, d), rn(z, hk, s_loc, d), rn(z, hk, s_loc, d), rn(z, h, s_loc, d)
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+
+    def step():
+        if world == 1:
+            o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                         backward_grad_dots="bf16")
+        else:
+            o = RD.ring_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk)
+        o.backward(do)
+        q.grad = k.grad = v.grad = None
+
+    def timed(n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            step()
+        b.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    ms = timed(steps)
+    RD.COMMUNICATE = False            # same kernels, same schedule, no messages
+    step()
+    ms_compute = timed(steps)
+    RD.COMMUNICATE = True
+    t = torch.tensor([ms, ms_compute], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_compute = (float(x) for x in t.tolist())
+    if rank == 0:
+        flops = 3.5 * 4.0 * z * h * float(s) * float(s) * d / 2.0
+        print(json.dumps({
+            "metric": "fp4_attn_fwd_bwd_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp4 S recompute + bf16 gradient GEMMs", "data": "synthetic",
+            "config": {"workload": f"BASELINE config 5: Z1 H16 Hk4 S{s} D256 causal fwd+bwd, ring attention over "
+                                   f"{world} rank(s), contiguous sequence slices"},
+            "compute_only_ms": ms_compute, "exposed_comm_ms": max(ms - ms_compute, 0.0),
+            "kernel_status": _lib.read_status(dev)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_profile_case(args):
     """Small single-kernel cases for `ncu` captures (a few launches, bounded memory)."""
     import torch
@@ -462,11 +533,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring"],
+                    help="prefill = BASELINE config 2 (the headline); ring = config 5 forward+backward")
+    ap.add_argument("--ring-seq", type=int, default=131072)
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "ring":
+        run_ring(args)
     else:
         run_gpu(args)
 

@@ -84,8 +84,17 @@ def ring_steps(rank: int, world: int, causal: bool) -> List[Tuple[int, str]]:
     return steps
 
 
+# Measurement switch: with False the ring schedule runs on the local block only (no messages), which
+# gives the pure compute time of a step; wall time minus that is the exposed communication.
+COMMUNICATE = True
+
+
 def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], group, rank: int, world: int):
     """Post sends of ``tensors`` to rank+1 and receives into ``recv`` from rank-1 (non-blocking)."""
+    if not COMMUNICATE:
+        for t, r in zip(tensors, recv):
+            r.copy_(t)
+        return []
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     ops = []
     for t, r in zip(tensors, recv):

@@ -89,6 +89,46 @@ def ring_steps(rank: int, world: int, causal: bool) -> List[Tuple[int, str]]:
 COMMUNICATE = True
 
 
+def ring_steps_zigzag(rank: int, world: int) -> List[Tuple[int, str]]:
+    """Causal schedule for the zigzag layout: the sequence is cut into ``2*world`` chunks and rank
+    r owns chunks r and ``2*world-1-r`` (concatenated in that order), which balances causal work.
+
+    With the block of rank ``src`` in hand: "causal" = the rank's own block (a plain causal mask
+    over the local concatenation is the global mask); "lo_kv" (src < rank) = every local query sees
+    the block's first chunk and nothing of its second; "hi_q" (src > rank) = only the local second
+    chunk sees the block, all of it.  Every step costs half a full block on every rank.
+    """
+    steps = []
+    for t in range(world):
+        src = (rank - t) % world
+        steps.append((src, "causal" if src == rank else ("lo_kv" if src < rank else "hi_q")))
+    return steps
+
+
+def zigzag_split(x: torch.Tensor, rank: int, world: int, dim: int = 2) -> torch.Tensor:
+    """This rank's slice of a full-sequence tensor in the zigzag layout (chunks r and 2W-1-r)."""
+    chunks = x.chunk(2 * world, dim=dim)
+    return torch.cat([chunks[rank], chunks[2 * world - 1 - rank]], dim=dim)
+
+
+def zigzag_merge(parts: Sequence[torch.Tensor], dim: int = 2) -> torch.Tensor:
+    """Inverse of ``zigzag_split`` over the per-rank slices (rank order)."""
+    world = len(parts)
+    chunks = [None] * (2 * world)
+    for r, p in enumerate(parts):
+        lo, hi = p.chunk(2, dim=dim)
+        chunks[r], chunks[2 * world - 1 - r] = lo, hi
+    return torch.cat(chunks, dim=dim)
+
+
+def _steps(rank: int, world: int, causal: bool, schedule: str):
+    if schedule not in ("contiguous", "zigzag"):
+        raise ValueError(f"schedule must be 'contiguous' or 'zigzag', got {schedule!r}")
+    if schedule == "zigzag" and causal:
+        return ring_steps_zigzag(rank, world)
+    return ring_steps(rank, world, causal)
+
+
 def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], group, rank: int, world: int):
     """Post sends of ``tensors`` to rank+1 and receives into ``recv`` from rank-1 (non-blocking)."""
     if not COMMUNICATE:
@@ -104,19 +144,22 @@ def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], gro
 
 
 def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
-                   block_attention: Callable, merge: Callable, causal: bool, group=None):
+                   block_attention: Callable, merge: Callable, causal: bool, group=None,
+                   schedule: str = "contiguous"):
     """Context-parallel attention of the local queries against every rank's K/V block.
 
     ``kv_block``: the tensors describing the local K/V block (anything with a fixed shape across
     ranks, e.g. the six pack tensors).  ``block_attention(q_local, block, mode)`` returns
-    ``(out, lse)`` for mode "full" or "causal"; ``merge(out_a, lse_a, out_b, lse_b)`` returns
-    the combined ``(out, lse)``.  Communication of step t+1 overlaps the compute of step t.
+    ``(out, lse)`` for mode "full" or "causal" (with ``schedule="zigzag"`` also "lo_kv" / "hi_q",
+    see ``ring_steps_zigzag``; rows a step does not touch carry lse = -inf);
+    ``merge(out_a, lse_a, out_b, lse_b)`` returns the combined ``(out, lse)``.  Communication of
+    step t+1 overlaps the compute of step t.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     cur = list(kv_block)
     out = lse = None
-    for t, (src, mode) in enumerate(ring_steps(rank, world, causal)):
+    for t, (src, mode) in enumerate(_steps(rank, world, causal, schedule)):
         reqs, nxt_bufs = [], None
         if t + 1 < world:
             nxt_bufs = [torch.empty_like(x) for x in cur]
@@ -132,7 +175,8 @@ def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
 
 
 def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequence[torch.Tensor],
-                            block_backward: Callable, causal: bool, group=None):
+                            block_backward: Callable, causal: bool, group=None,
+                            schedule: str = "contiguous"):
     """Gradients of ``ring_attention``.
 
     ``kv_block``: the tensors that describe the local K/V block for the backward (fixed shapes
@@ -150,7 +194,7 @@ def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequenc
     acc = [torch.zeros_like(g, dtype=torch.float32) for g in grad_like]
     acc_recv, acc_reqs = None, []
     dq = None
-    for t, (src, mode) in enumerate(ring_steps(rank, world, causal)):
+    for t, (src, mode) in enumerate(_steps(rank, world, causal, schedule)):
         reqs, nxt_bufs = [], None
         if t + 1 < world:
             nxt_bufs = [torch.empty_like(x) for x in cur]
@@ -180,25 +224,44 @@ def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequenc
     return dq, acc[0], acc[1]
 
 
-def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None):
+def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None,
+                         schedule="contiguous"):
     """NVFP4 ring attention on CUDA: ``query [Z,H,S_loc,D]``, ``key/value [Z,Hk,S_loc,D]`` are this
-    rank's contiguous slice of the sequence (slice length a multiple of 128).  Returns
-    ``(out [Z,H,S_loc,D], lse [Z*H, S_loc])``.
+    rank's slice of the sequence: one contiguous piece (``schedule="contiguous"``, length a multiple
+    of 128) or the two zigzag chunks (``schedule="zigzag"``, each a multiple of 128; see
+    ``zigzag_split``).  Returns ``(out [Z,H,S_loc,D], lse [Z*H, S_loc])``.
     """
     from .. import _lib
     from . import flash
 
     z, h, s_loc, d = query.shape
     hk = key.shape[1]
-    assert s_loc % 128 == 0, "ring attention needs slice lengths that are multiples of 128"
+    zig = schedule == "zigzag" and causal
+    c = s_loc // 2
+    assert s_loc % (256 if zig else 128) == 0, "ring attention needs 128-multiple slices (per chunk)"
     knv, ksc = flash._quant_nvfp4(key.reshape(z * hk, s_loc, d))
     vnv, vsc = flash._quant_nvfp4(value.reshape(z * hk, s_loc, d), transpose=True, k_pad=s_loc)
     qnv, qsc = flash._quant_nvfp4(query.reshape(z * h, s_loc, d))
     block = [knv, ksc.view(torch.uint8), vnv, vsc.view(torch.uint8)]
+    if zig:
+        qnv_hi, qsc_hi = qnv[:, c:].contiguous(), qsc[:, c:].contiguous()
+
+    def run(qn, qs, blk, sq, skv, is_causal):
+        return flash._run_flash_packed(qn, qs, blk[0], blk[1], blk[2], blk[3], z, h, hk, sq, skv, d,
+                                       scaling, torch.float32, causal=is_causal, return_lse=True)
 
     def block_attention(_q, blk, mode):
-        o, l = flash._run_flash_packed(qnv, qsc, blk[0], blk[1], blk[2], blk[3], z, h, hk, s_loc, s_loc, d,
-                                       scaling, torch.float32, causal=(mode == "causal"), return_lse=True)
+        if mode in ("full", "causal"):
+            return run(qnv, qsc, blk, s_loc, s_loc, mode == "causal")
+        if mode == "lo_kv":          # all local queries x the block's first chunk
+            lo = [blk[0][:, :c].contiguous(), blk[1][:, :c].contiguous(),
+                  blk[2][:, :, :c // 2].contiguous(), blk[3][:, :, :c // 16].contiguous()]
+            return run(qnv, qsc, lo, s_loc, c, False)
+        o_hi, l_hi = run(qnv_hi, qsc_hi, blk, c, s_loc, False)      # "hi_q": second local chunk x whole block
+        o = torch.zeros(z, h, s_loc, d, dtype=torch.float32, device=o_hi.device)
+        l = torch.full((z * h, s_loc), float("-inf"), dtype=torch.float32, device=o_hi.device)
+        o[:, :, c:] = o_hi
+        l[:, c:] = l_hi
         return o, l
 
     def merge(o1, l1, o2, l2):
@@ -211,12 +274,12 @@ def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_
         lse = m + torch.log(torch.exp(l1 - m) + torch.exp(l2 - m))
         return out, lse
 
-    out, lse = ring_attention(query, block, block_attention, merge, causal, group)
+    out, lse = ring_attention(query, block, block_attention, merge, causal, group, schedule)
     return out.to(query.dtype), lse
 
 
 def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, causal=True,
-                                  num_key_value_groups=1, group=None):
+                                  num_key_value_groups=1, group=None, schedule="contiguous"):
     """NVFP4 ring-attention backward on CUDA for the local sequence slices (bf16 tensors).
 
     ``out`` / ``lse`` are the merged results of ``ring_flash_attention``; with them every block's
@@ -229,6 +292,8 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
     z, h, s_loc, d = query.shape
     hk = key.shape[1]
     dev = query.device
+    zig = schedule == "zigzag" and causal
+    c = s_loc // 2
     qc, kc, vc = flash._as_bf16_rows(query), flash._as_bf16_rows(key), flash._as_bf16_rows(value)
     need_copy = not (dout.dtype == torch.bfloat16 and dout.is_contiguous())
     doc, delta = flash._bwd_prep(dout, y=out.to(dout.dtype), want_copy=need_copy)
@@ -238,40 +303,66 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
     knv, ksc = flash._quant_nvfp4(key.reshape(z * hk, s_loc, d))
     lse = lse.contiguous()
     block = [kc, vc, knv, ksc.view(torch.uint8)]
+    q_side = (qnv, qsc, qc, doc, lse, delta)
+    if zig:   # the second local chunk as contiguous tensors of its own
+        q_side_hi = tuple(t[:, c:].contiguous() for t in q_side)
+
+    def run(qs, blk, sq, skv, is_causal):
+        dq = torch.empty(z, h, sq, d, dtype=torch.float32, device=dev)
+        dk = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
+        dv = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
+        _lib.check(_lib.lib().nvfp4_bwd_hp(
+            qs[0].data_ptr(), qs[1].data_ptr(), blk[2].data_ptr(), blk[3].data_ptr(), qs[2].data_ptr(),
+            blk[0].data_ptr(), blk[1].data_ptr(), qs[3].data_ptr(), qs[4].data_ptr(), qs[5].data_ptr(), None, None,
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.DT_FP32, z, h, hk, sq, skv, d, float(scaling),
+            1 if is_causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+        return dq, dk, dv
 
     def block_backward(blk, mode):
-        dq = torch.empty(z, h, s_loc, d, dtype=torch.float32, device=dev)
-        dk = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
-        dv = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
-        _lib.check(_lib.lib().nvfp4_bwd_hp(
-            qnv.data_ptr(), qsc.data_ptr(), blk[2].data_ptr(), blk[3].data_ptr(), qc.data_ptr(),
-            blk[0].data_ptr(), blk[1].data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(), None, None,
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.DT_FP32, z, h, hk, s_loc, s_loc, d, float(scaling),
-            1 if mode == "causal" else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+        if mode in ("full", "causal"):
+            return run(q_side, blk, s_loc, s_loc, mode == "causal")
+        if mode == "lo_kv":
+            lo = [t[:, :c].contiguous() for t in blk]
+            dq, dk_lo, dv_lo = run(q_side, lo, s_loc, c, False)
+            dk = torch.zeros(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+            dv = torch.zeros(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+            dk[:, :, :c] = dk_lo
+            dv[:, :, :c] = dv_lo
+            return dq, dk, dv
+        dq_hi, dk, dv = run(q_side_hi, blk, c, s_loc, False)      # "hi_q"
+        dq = torch.zeros(z, h, s_loc, d, dtype=torch.float32, device=dev)
+        dq[:, :, c:] = dq_hi
         return dq, dk, dv
 
     like = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
-    dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group)
+    dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group, schedule)
     gdt = dout.dtype
     return dq.to(gdt), dk.to(gdt), dv.to(gdt)
 
 
 class _RingFlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, query, key, value, scaling, causal, g, group):
-        out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group)
+    def forward(ctx, query, key, value, scaling, causal, g, group, schedule):
+        out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group, schedule)
         ctx.save_for_backward(query, key, value, out, lse)
-        ctx.meta = (float(scaling), bool(causal), int(g), group)
+        ctx.meta = (float(scaling), bool(causal), int(g), group, schedule)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         query, key, value, out, lse = ctx.saved_tensors
-        scaling, causal, g, group = ctx.meta
-        dq, dk, dv = ring_flash_attention_backward(query, key, value, out, lse, grad_out, scaling, causal, g, group)
-        return dq, dk, dv, None, None, None, None
+        scaling, causal, g, group, schedule = ctx.meta
+        dq, dk, dv = ring_flash_attention_backward(query, key, value, out, lse, grad_out, scaling, causal, g,
+                                                   group, schedule)
+        return dq, dk, dv, None, None, None, None, None
 
 
-def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None):
-    """Differentiable context-parallel NVFP4 attention over this rank's sequence slice."""
-    return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group)
+def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None,
+                         schedule="zigzag"):
+    """Differentiable context-parallel NVFP4 attention over this rank's slice of the sequence.
+
+    ``schedule="zigzag"`` (default, causal only): the slice is chunks r and 2W-1-r of the sequence
+    (``zigzag_split``), every rank does the same work per ring step.  ``"contiguous"``: one piece per
+    rank; with a causal mask the last rank works on every step and the first on one.
+    """
+    return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group, schedule)

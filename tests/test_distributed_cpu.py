@@ -164,3 +164,106 @@ def test_ring_backward_gloo_ranks_equal_single_process(causal, world):
         p.join(120)
         assert p.exitcode == 0
     assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)
+
+
+def test_zigzag_split_merge_roundtrip_and_steps():
+    x = torch.arange(2 * 3 * 16 * 4, dtype=torch.float32).reshape(2, 3, 16, 4)
+    for world in (1, 2, 4):
+        parts = [D.zigzag_split(x, r, world) for r in range(world)]
+        assert torch.equal(D.zigzag_merge(parts), x)
+    assert D.ring_steps_zigzag(1, 4) == [(1, "causal"), (0, "lo_kv"), (3, "hi_q"), (2, "hi_q")]
+
+
+def _mode_mask(mode, n):
+    c = n // 2
+    m = torch.zeros(n, n, dtype=torch.bool)
+    if mode == "causal":
+        m = torch.ones(n, n, dtype=torch.bool).tril()
+    elif mode == "lo_kv":
+        m[:, :c] = True
+    elif mode == "hi_q":
+        m[c:, :] = True
+    elif mode == "full":
+        m[:] = True
+    return m
+
+
+def _zigzag_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        z, h, hk, c, d = 1, 2, 1, 8, 8
+        g_ = h // hk
+        s = 2 * c * world
+        n = 2 * c
+        gen = torch.Generator().manual_seed(2)
+        q = torch.randn(z, h, s, d, generator=gen)
+        k = torch.randn(z, hk, s, d, generator=gen)
+        v = torch.randn(z, hk, s, d, generator=gen)
+        do = torch.randn(z, h, s, d, generator=gen)
+        pos = torch.arange(s, dtype=torch.float32).reshape(1, 1, s, 1)
+        ql, kl, vl, dol, pl = (D.zigzag_split(t, rank, world) for t in (q, k, v, do, pos))
+        pos_q = pl.reshape(-1)
+
+        def scores(blk, mode):
+            kb, vb, pk = blk
+            # the mode's mask must be exactly the global causal mask between these positions
+            assert torch.equal(_mode_mask(mode, n), pk.reshape(1, -1) <= pos_q.reshape(-1, 1)), mode
+            sc = torch.matmul(ql, kb.repeat_interleave(g_, 1).transpose(-1, -2)) * d ** -0.5
+            return sc.masked_fill(~_mode_mask(mode, n), float("-inf")), vb.repeat_interleave(g_, 1)
+
+        def block_attention(q_loc, blk, mode):
+            sc, vv = scores(blk, mode)
+            m = sc.max(-1, keepdim=True).values
+            m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+            p = torch.exp(sc - m_safe)
+            l = p.sum(-1, keepdim=True)
+            o = torch.matmul(p, vv) / torch.where(l == 0, torch.ones_like(l), l)
+            return o, (m_safe + torch.log(l)).squeeze(-1)      # rows without keys: lse = -inf
+
+        def merge(o1, l1, o2, l2):
+            m = torch.maximum(l1, l2)
+            w1, w2 = torch.exp(l1 - m)[..., None], torch.exp(l2 - m)[..., None]
+            return (w1 * o1 + w2 * o2) / (w1 + w2), m + torch.log(torch.exp(l1 - m) + torch.exp(l2 - m))
+
+        out, lse = D.ring_attention(ql, [kl, vl, pl], block_attention, merge, True, schedule="zigzag")
+        ref, _ = O.attention_exact(q.numpy(), k.numpy(), v.numpy(), d ** -0.5, True, g_)
+        ref_l = D.zigzag_split(torch.from_numpy(ref).float(), rank, world)
+        err_f = float((out - ref_l).abs().max())
+        delta = (dol * out).sum(-1)
+
+        def block_backward(blk, mode):
+            sc, vv = scores(blk, mode)
+            kk = blk[0].repeat_interleave(g_, 1)
+            p_ = torch.exp(sc - lse[..., None])
+            dp = torch.matmul(dol, vv.transpose(-1, -2))
+            ds = p_ * (dp - delta[..., None]) * d ** -0.5
+            dq = torch.matmul(ds, kk)
+            dk = torch.matmul(ds.transpose(-1, -2), ql).reshape(z, hk, g_, n, d).sum(2)
+            dv = torch.matmul(p_.transpose(-1, -2), dol).reshape(z, hk, g_, n, d).sum(2)
+            return dq, dk, dv
+
+        dq, dk, dv = D.ring_attention_backward([kl, vl, pl], [kl, vl], block_backward, True, schedule="zigzag")
+        rq, rk, rv = O.attention_grads(q.numpy(), k.numpy(), v.numpy(), do.numpy(), d ** -0.5, True, g_)
+        errs = [float((a - D.zigzag_split(torch.from_numpy(b).float(), rank, world)).abs().max())
+                for a, b in ((dq, rq), (dk, rk), (dv, rv))]
+        ret[rank] = max([err_f] + errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_zigzag_ring_forward_backward_gloo(world):
+    """Zigzag layout: every step's mode mask equals the global causal mask, results equal the
+    single-process attention and its gradients."""
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_zigzag_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

@@ -26,7 +26,7 @@ def _worker(rank, world, port, ret):
     try:
         import sageattention_b200.nvfp4 as nv
         from sageattention_b200.nvfp4 import distributed as D
-        z, h, hk, d, s_loc = 1, 4, 2, 128, 256
+        z, h, hk, d, s_loc = 1, 4, 2, 128, 512
         s = s_loc * world
         g = torch.Generator().manual_seed(5)
         q = torch.randn(z, h, s, d, generator=g).to(torch.bfloat16).cuda()
@@ -52,7 +52,8 @@ def _worker(rank, world, port, ret):
         ql = q[:, :, sl].contiguous().requires_grad_(True)
         kl = k[:, :, sl].contiguous().requires_grad_(True)
         vl = v[:, :, sl].contiguous().requires_grad_(True)
-        o_ring = D.ring_flash_attn_func(ql, kl, vl, d ** -0.5, causal=True, num_key_value_groups=h // hk)
+        o_ring = D.ring_flash_attn_func(ql, kl, vl, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                        schedule="contiguous")
         o_ring.backward(do[:, :, sl].contiguous())
         qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
         o_full = nv.nvfp4_flash_attn_func(qf, kf, vf, d ** -0.5, causal=True, num_key_value_groups=h // hk,
@@ -60,7 +61,14 @@ def _worker(rank, world, port, ret):
         o_full.backward(do)
         cosf = lambda x, y: float(torch.nn.functional.cosine_similarity(x.float().flatten(), y.float().flatten(), dim=0))
         gcos = (cosf(ql.grad, qf.grad[:, :, sl]), cosf(kl.grad, kf.grad[:, :, sl]), cosf(vl.grad, vf.grad[:, :, sl]))
-        ret[rank] = (cos, lse_err, shard_equal, gcos)
+        # zigzag layout (balanced causal work): forward and backward vs the same single-GPU run
+        qz, kz, vz, dz = (D.zigzag_split(t, rank, world).contiguous() for t in (q, k, v, do))
+        qz.requires_grad_(True), kz.requires_grad_(True), vz.requires_grad_(True)
+        oz = D.ring_flash_attn_func(qz, kz, vz, d ** -0.5, causal=True, num_key_value_groups=h // hk)
+        oz.backward(dz)
+        zsp = lambda t: D.zigzag_split(t, rank, world)
+        zcos = (cosf(oz, zsp(full)), cosf(qz.grad, zsp(qf.grad)), cosf(kz.grad, zsp(kf.grad)), cosf(vz.grad, zsp(vf.grad)))
+        ret[rank] = (cos, lse_err, shard_equal, gcos, zcos)
     finally:
         dist.destroy_process_group()
 
@@ -79,7 +87,8 @@ def test_ring_and_sharding_two_gpus_match_single_gpu():
         p.join(300)
         assert p.exitcode == 0
     for r in range(world):
-        cos, lse_err, shard_equal, gcos = ret[r]
+        cos, lse_err, shard_equal, gcos, zcos = ret[r]
+        assert min(zcos) >= 0.995, (r, zcos)   # zigzag schedule: output and gradients
         assert min(gcos) >= 0.995, (r, gcos)   # ring gradients vs the single-GPU backward
         assert cos >= 0.995, (r, cos)          # same keys, different tile order: FP4-P rounding level
         assert lse_err <= 2e-3, (r, lse_err)   # the softmax statistics themselves are exact

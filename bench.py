@@ -477,7 +477,7 @@ def run_ring(args):
             "n_gpus": world, "steps": steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp4 S recompute + bf16 gradient GEMMs", "data": "synthetic",
             "config": {"workload": f"BASELINE config 5: Z1 H16 Hk4 S{s} D256 causal fwd+bwd, ring attention over "
-                                   f"{world} rank(s), contiguous sequence slices"},
+                                   f"{world} rank(s), zigzag sequence chunks (rank r owns chunks r and 2W-1-r)"},
             "compute_only_ms": ms_compute, "exposed_comm_ms": max(ms - ms_compute, 0.0),
             "kernel_status": _lib.read_status(dev)}))
     if world > 1:

@@ -85,31 +85,32 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// four consecutive elements, one vector load when the address allows it
+// eight consecutive elements, one 16-byte load (two for fp32) when the address allows it
 template <typename T>
-__device__ __forceinline__ void load4(const T* src, float (&v)[4]) {
+__device__ __forceinline__ void load8(const T* src, float (&v)[8]) {
   if constexpr (sizeof(T) == 2) {
-    if ((reinterpret_cast<uintptr_t>(src) & 7) == 0) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src);
       const T* t = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = to_f32<T>(t[e]);
+      for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(t[e]);
       return;
     }
   } else {
     if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-      const float4 raw = *reinterpret_cast<const float4*>(src);
-      v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+      const float4 a = *reinterpret_cast<const float4*>(src), c = *reinterpret_cast<const float4*>(src + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
       return;
     }
   }
 #pragma unroll
-  for (int e = 0; e < 4; ++e) v[e] = to_f32<T>(src[e]);
+  for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(src[e]);
 }
 
 // ------------------------------------------------------------------------------------------
 // Pre-pass over rows of x [B1, B2, S, D] (strided, unit stride along D): optional contiguous
-// bf16 copy xc [B1*B2, S, D] and optional delta [B1*B2, S] = rowsum(x o y).  One warp per row.
+// bf16 copy xc [B1*B2, S, D] and optional delta [B1*B2, S] = rowsum(x o y).  Half a warp per row,
+// 16 bytes per lane and load, two rows per warp in flight.
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, int64_t sxb1, int64_t sxb2,
@@ -117,35 +118,40 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
                                                        int64_t syb1, int64_t syb2, int64_t sys, int S, int D,
                                                        int64_t rows, __nv_bfloat16* __restrict__ xc,
                                                        float* __restrict__ delta) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int64_t nwarp = (int64_t)gridDim.x * 8;
-  for (int64_t row = warp0; row < rows; row += nwarp) {
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t base0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
+  const int64_t nhw = (int64_t)gridDim.x * 16;
+  for (int64_t base = base0; base < rows; base += nhw) {    // both half-warps take every trip (shuffles)
+    const int64_t row0 = base + (lane >> 4);
+    const bool live = row0 < rows;
+    const int64_t row = live ? row0 : rows - 1;
     const int64_t b = row / S;
     const int s = (int)(row - b * S);
     const int64_t b1 = b / nb2, b2 = b - b1 * nb2;
     const T* xr = x + b1 * sxb1 + b2 * sxb2 + (int64_t)s * sxs;
     const T* yr = y ? (y + b1 * syb1 + b2 * syb2 + (int64_t)s * sys) : nullptr;
     float acc = 0.0f;
-    for (int c = lane * 4; c < D; c += 128) {
-      float v[4], w4[4];
-      load4<T>(xr + c, v);
+    for (int c = l16 * 8; c < D; c += 128) {
+      float v[8], w8[8];
+      load8<T>(xr + c, v);
       if (yr) {
-        load4<T>(yr + c, w4);
+        load8<T>(yr + c, w8);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc = fmaf(v[e], w4[e], acc);
+        for (int e = 0; e < 8; ++e) acc = fmaf(v[e], w8[e], acc);
       }
-      if (xc) {
-        uint2 w;
+      if (xc && live) {
+        uint4 w;
         w.x = pack_bf16x2(v[0], v[1]);
         w.y = pack_bf16x2(v[2], v[3]);
-        *reinterpret_cast<uint2*>(xc + row * D + c) = w;
+        w.z = pack_bf16x2(v[4], v[5]);
+        w.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(xc + row * D + c) = w;
       }
     }
     if (delta) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) delta[row] = acc;
+      for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (l16 == 0 && live) delta[row] = acc;
     }
   }
 }
@@ -932,7 +938,7 @@ int prep_launch(const void* x, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t 
                 int64_t syb1, int64_t syb2, int64_t sys, int S, int D, __nv_bfloat16* xc, float* delta,
                 cudaStream_t st) {
   const int64_t rows = nb1 * nb2 * S;
-  const int64_t blocks = (rows + 7) / 8;
+  const int64_t blocks = (rows + 15) / 16;
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
   bwd_prep_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), sxb1, sxb2, sxs, (int)nb2,
                                            static_cast<const T*>(y), syb1, syb2, sys, S, D, rows, xc, delta);
@@ -947,7 +953,7 @@ extern "C" int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sx
                               nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(x != nullptr && (xc || delta), "nvfp4_bwd_prep: nothing to do");
-  NVFP4_REQUIRE(d >= 4 && d % 4 == 0 && s >= 1 && nb1 >= 1 && nb2 >= 1, "nvfp4_bwd_prep: bad extents");
+  NVFP4_REQUIRE(d >= 8 && d % 8 == 0 && s >= 1 && nb1 >= 1 && nb2 >= 1, "nvfp4_bwd_prep: bad extents");
   NVFP4_REQUIRE(s < (1LL << 31), "nvfp4_bwd_prep: sequence too long");
   NVFP4_REQUIRE(delta == nullptr || y != nullptr, "nvfp4_bwd_prep: delta needs the second operand");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -50,7 +50,7 @@ struct DecodeCfg {
   static constexpr int MERGE_BYTES = 16 * D * 4;   // one group's O^T partial at the item end
   static constexpr int PBUF_BYTES = 2 * STMAX * (P_BYTES + PSF_BYTES);
   // the merge buffer reuses the P tiles, which are idle once an item's last PV has completed
-  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + Q_BYTES + QSF_BYTES +
+  static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 2 * (Q_BYTES + QSF_BYTES) +
                                     (PBUF_BYTES > MERGE_BYTES ? PBUF_BYTES : MERGE_BYTES) + 1024;
   // TMEM columns: [buffer][tile of the super-tile][...]
   static constexpr int T_ST = 0;                              // 2 x STMAX x 16
@@ -58,8 +58,8 @@ struct DecodeCfg {
   static constexpr int T_SFK = T_OT + 2 * STMAX * MT * 16;    // 2 x STMAX x KB*4
   static constexpr int T_SFV = T_SFK + 2 * STMAX * KB * 4;    // 2 x STMAX x MT*8
   static constexpr int T_SFP = T_SFV + 2 * STMAX * MT * 8;    // 2 x STMAX x 8
-  static constexpr int T_SFQ = T_SFP + 2 * STMAX * 8;         // KB*4
-  static constexpr int T_END = T_SFQ + KB * 4;
+  static constexpr int T_SFQ = T_SFP + 2 * STMAX * 8;         // 2 x KB*4 (one per work-item parity)
+  static constexpr int T_END = T_SFQ + 2 * KB * 4;
   static constexpr int T_COLS = 512;
   static_assert(T_END <= T_COLS, "TMEM budget exceeded");
 };
@@ -108,14 +108,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* s_stage = smem;
-  uint8_t* s_q = s_stage + C::NSTAGE * C::STAGE_BYTES;
-  uint8_t* s_qsf = s_q + C::Q_BYTES;
-  uint8_t* s_p = s_qsf + C::QSF_BYTES;                    // [2][STMAX][P_BYTES]
+  // the quantised query rows are double buffered by work-item parity: item n+1's are prepared
+  // while item n runs, so the QK^T issuer walks into the next item without draining the pipeline
+  uint8_t* s_q = s_stage + C::NSTAGE * C::STAGE_BYTES;    // [2][Q_BYTES]
+  uint8_t* s_qsf = s_q + 2 * C::Q_BYTES;                  // [2][QSF_BYTES]
+  uint8_t* s_p = s_qsf + 2 * C::QSF_BYTES;                // [2][STMAX][P_BYTES]
   uint8_t* s_psf = s_p + 2 * C::STMAX * C::P_BYTES;       // [2][STMAX][PSF_BYTES]
   float* s_merge = reinterpret_cast<float*>(s_p);          // [16][D], only at the end of an item
 
   __shared__ uint64_t full_kv[C::NSTAGE], full_sf[C::NSTAGE], empty[C::NSTAGE];
-  __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], q_full;
+  __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], q_full[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
   __shared__ float xch[2][4][C::STMAX][16];
@@ -135,13 +137,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       mbar_init(&s_free[i], 256);
       mbar_init(&p_full[i], 8);
       mbar_init(&o_full[i], 1);
+      mbar_init(&q_full[i], 8);
     }
-    mbar_init(&q_full, 8);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, C::T_COLS);
   // zero the operand buffers that are only partly rewritten (rows >= G stay zero)
-  for (int i = tid; i < (C::Q_BYTES + C::QSF_BYTES + 2 * C::STMAX * (C::P_BYTES + C::PSF_BYTES)) / 4;
+  for (int i = tid; i < (2 * (C::Q_BYTES + C::QSF_BYTES) + 2 * C::STMAX * (C::P_BYTES + C::PSF_BYTES)) / 4;
        i += kDecodeThreads)
     reinterpret_cast<uint32_t*>(s_q)[i] = 0u;
   fence_proxy_async_smem();
@@ -166,13 +168,29 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         item_range(w, unit, t0, t1);
         for (int t = t0; t < t1; ++t, ++it) {
           // V^T rows are D separate strips in memory and a 128-key tile touches only 64 bytes of
-          // each; pull 1 KB per strip (16 tiles) into L2 one block ahead so DRAM sees long bursts
-          if (t == t0 || (t & 15) == 0) {
-            const int blk = (t >> 4) + ((t == t0) ? 0 : 1);
-            for (int bb = blk; bb <= (t >> 4) + 1; ++bb)
-              if (bb * 16 < t1 + 16 && bb * 16 < p.ntiles)
+          // each; 1 KB per strip (16 tiles) is pulled into L2 one 16-tile block ahead so DRAM sees
+          // long bursts.  The pull is spread over the tiles of the block before it (8 strips per
+          // tile): a whole block at once, from every CTA in step, stalls the demand loads behind it.
+          const int j = t - t0;
+          if (j == 0 && (w == (int64_t)blockIdx.x || t1 - t0 < 16)) {
+#pragma unroll 1
+            for (int r = 0; r < 16; ++r)
 #pragma unroll
-                for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, bb * 256, mt * 128, unit);
+              for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, t0 * 16, mt * 128 + r * 8, unit);
+          }
+          {
+            const int nb = t0 + ((j >> 4) + 1) * 16;      // first tile of the next block
+            if (nb < t1)
+#pragma unroll
+              for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, nb * 16, mt * 128 + (j & 15) * 8, unit);
+          }
+          // the first block of this CTA's NEXT work item, a whole item ahead: its first tiles would
+          // otherwise be 128 scattered 64-byte first touches each, ~15k clocks of DRAM latency
+          if (j < 16 && w + gridDim.x < p.nitems) {
+            int unit_n, t0n, t1n;
+            item_range(w + gridDim.x, unit_n, t0n, t1n);
+#pragma unroll
+            for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, t0n * 16, mt * 128 + j * 8, unit_n);
           }
           const int s = it % C::NSTAGE;
           if (it >= (uint32_t)C::NSTAGE) mbar_spin_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 1);
@@ -255,11 +273,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x, ++item_idx) {
         int unit, t0, t1;
         item_range(w, unit, t0, t1);
-        mbar_wait(&q_full, item_idx & 1, &err, 6);
+        const int qb = item_idx & 1;
+        mbar_wait(&q_full[qb], (item_idx >> 1) & 1, &err, 6);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < C::KB; ++k)
-          tmem_cp_32x128b_warpx4(tmem + C::T_SFQ + k * 4, smem_u32(s_qsf + k * 512));
+          tmem_cp_32x128b_warpx4(tmem + C::T_SFQ + qb * C::KB * 4 + k * 4,
+                                 smem_u32(s_qsf + qb * C::QSF_BYTES + k * 512));
         for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
           const int b = su & 1;
           const int nt = min(ST, t1 - ts0);
@@ -291,9 +311,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
             for (int k = 0; k < C::KB; ++k) {
               const uint64_t ad = make_smem_desc(smem_u32(st + (k >> 1) * 8192) + (k & 1) * 32, 16, 512, 4);
-              const uint64_t bd = make_smem_desc(smem_u32(s_q + (k >> 1) * 1024) + (k & 1) * 32, 16, 512, 4);
+              const uint64_t bd =
+                  make_smem_desc(smem_u32(s_q + qb * C::Q_BYTES + (k >> 1) * 1024) + (k & 1) * 32, 16, 512, 4);
               umma_nvfp4(tmem + C::T_ST + (b * C::STMAX + j) * 16, ad, bd, idesc, sfk + k * 4,
-                         tmem + C::T_SFQ + k * 4, k > 0);
+                         tmem + C::T_SFQ + qb * C::KB * 4 + k * 4, k > 0);
             }
           }
           umma_commit(&s_full[b]);
@@ -361,27 +382,37 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int tall = tid - 128;            // 0..255
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const TQ* qbase = static_cast<const TQ*>(p.q);
-    uint32_t su = 0;
-    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
-      int unit, t0, t1;
-      item_range(w, unit, t0, t1);
-      const int zi = unit / p.hk, kh = unit % p.hk;
-      // ---- quantise the G query rows of this kv head into the B operand of QK^T
+    // quantise the G query rows of item `wi`'s kv head into the B operand of QK^T, buffer `qb`
+    auto prep_q = [&](int64_t wi, int qb) {
+      int unit_q, t0q, t1q;
+      item_range(wi, unit_q, t0q, t1q);
+      const int zq = unit_q / p.hk, khq = unit_q % p.hk;
+      uint8_t* dq = s_q + qb * C::Q_BYTES;
+      uint8_t* dsf = s_qsf + qb * C::QSF_BYTES;
       for (int i = tall; i < p.g * (D / 16); i += 256) {
         const int qr = i / (D / 16), gi = i % (D / 16);
-        const TQ* src = qbase + zi * p.s_qz + (int64_t)(kh * p.g + qr) * p.s_qh + gi * 16;
+        const TQ* src = qbase + zq * p.s_qz + (int64_t)(khq * p.g + qr) * p.s_qh + gi * 16;
         float v[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = to_f32<TQ>(src[e]);
         uint32_t lo, hi;
         const uint8_t sb = pack_group16(v, lo, hi);
-        *reinterpret_cast<uint2*>(s_q + (gi >> 3) * 1024 + sw64_offset(qr, (gi & 7) * 8)) =
-            make_uint2(lo, hi);
-        s_qsf[(gi >> 2) * 512 + sf_atom_offset(qr, gi & 3)] = sb;
+        *reinterpret_cast<uint2*>(dq + (gi >> 3) * 1024 + sw64_offset(qr, (gi & 7) * 8)) = make_uint2(lo, hi);
+        dsf[(gi >> 2) * 512 + sf_atom_offset(qr, gi & 3)] = sb;
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&q_full);
+      if (lane == 0) mbar_arrive(&q_full[qb]);
+    };
+    uint32_t su = 0, item_idx = 0;
+    if ((int64_t)blockIdx.x < p.nitems) prep_q(blockIdx.x, 0);
+    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+      int unit, t0, t1;
+      item_range(w, unit, t0, t1);
+      // ---- the query rows of the NEXT item go into the other operand buffer now (its last reader,
+      //      the QK^T of the previous item, has completed: this warp consumed all of its rounds)
+      if (w + gridDim.x < p.nitems) prep_q(w + gridDim.x, (int)((item_idx + 1) & 1));
+      ++item_idx;
 
       float m_run[NQ], l_run[NQ];             // key-lane role: running max, partial row sum
       float o_run[C::MT][NQ], m_acc[NQ];      // d-row role: accumulated O^T, the max it refers to
@@ -743,7 +774,7 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
 
   rc = make_tmap_u32_3d_prefetch(&tm_vpf, vnv, (uint64_t)s_pad / 2, (uint64_t)d, (uint64_t)zhk,
                                  (uint64_t)vnv_row, (uint64_t)vnv_unit,
-                                 (uint32_t)std::min<uint64_t>(256, (uint64_t)s_pad / 8), 128,
+                                 (uint32_t)std::min<uint64_t>(256, (uint64_t)s_pad / 8), 8,
                                  "nvfp4_decode(V prefetch)");
   if (rc) return rc;
 

@@ -137,7 +137,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       mbar_init(&s_free[i], 256);
       mbar_init(&p_full[i], 8);
       mbar_init(&o_full[i], 1);
-      mbar_init(&q_full[i], 8);
+      mbar_init(&q_full[i], 1);
     }
     mbar_fence_init();
   }
@@ -157,6 +157,31 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int split = (int)(w % p.nsplit);
     t0 = split * p.chunk_tiles;
     t1 = min(t0 + p.chunk_tiles, p.ntiles);
+  };
+
+  // quantise the G query rows of item `wi`'s kv head into the B operand of QK^T, buffer `qb`
+  // (called by the 32 lanes of the QK^T issuer's warp, one work item ahead of the MMAs)
+  const TQ* qbase = static_cast<const TQ*>(p.q);
+  auto prep_q = [&](int64_t wi, int qb) {
+    int unit_q, t0q, t1q;
+    item_range(wi, unit_q, t0q, t1q);
+    const int zq = unit_q / p.hk, khq = unit_q % p.hk;
+    uint8_t* dq = s_q + qb * C::Q_BYTES;
+    uint8_t* dsf = s_qsf + qb * C::QSF_BYTES;
+    for (int i = lane; i < p.g * (D / 16); i += 32) {
+      const int qr = i / (D / 16), gi = i % (D / 16);
+      const TQ* src = qbase + zq * p.s_qz + (int64_t)(khq * p.g + qr) * p.s_qh + gi * 16;
+      float v[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) v[e] = to_f32<TQ>(src[e]);
+      uint32_t lo, hi;
+      const uint8_t sb = pack_group16(v, lo, hi);
+      *reinterpret_cast<uint2*>(dq + (gi >> 3) * 1024 + sw64_offset(qr, (gi & 7) * 8)) = make_uint2(lo, hi);
+      dsf[(gi >> 2) * 512 + sf_atom_offset(qr, gi & 3)] = sb;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_full[qb]);
   };
 
   if (warp == 0) {
@@ -266,13 +291,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     cp_async_wait<0>();
     for (; published < it; ++published) publish(published);
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ QK^T issuer
-    if (elect_one()) {
-      const uint32_t idesc = make_idesc_nvfp4(128, 16);
-      uint32_t it = 0, su = 0, item_idx = 0;
-      for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x, ++item_idx) {
-        int unit, t0, t1;
-        item_range(w, unit, t0, t1);
+    // ------------------------------------------------------------------ QK^T issuer (+ query prep)
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc_nvfp4(128, 16);
+    uint32_t it_w = 0, su_w = 0, item_idx = 0;   // warp-uniform: tiles and rounds issued before this item
+    if ((int64_t)blockIdx.x < p.nitems) prep_q(blockIdx.x, 0);
+    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x, ++item_idx) {
+      // the whole warp quantises the NEXT item's query rows into the other buffer; that buffer's
+      // last readers are the QK^T MMAs of the previous item, complete once its last s_full fired
+      if (w + gridDim.x < p.nitems) {
+        if (item_idx > 0) mbar_wait(&s_full[(su_w - 1) & 1], ((su_w - 1) >> 1) & 1, &err, 12);
+        prep_q(w + gridDim.x, (int)((item_idx + 1) & 1));
+      }
+      int unit, t0, t1;
+      item_range(w, unit, t0, t1);
+      if (leader) {
+        uint32_t it = it_w, su = su_w;      // the leader's running counters for this item
         const int qb = item_idx & 1;
         mbar_wait(&q_full[qb], (item_idx >> 1) & 1, &err, 6);
         tc_fence_after();
@@ -321,8 +355,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           DTRACE(3, su, 0);
         }
       }
+      it_w += (uint32_t)(t1 - t0);
+      su_w += (uint32_t)((t1 - t0 + ST - 1) / ST);
+      __syncwarp();
     }
-    __syncwarp();
   } else if (warp == 3) {
     // ------------------------------------------------------------------ PV issuer
     if (elect_one()) {
@@ -381,39 +417,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int ts = (tid - 128) & 127;      // key lane within a tile (softmax) / d row (accumulate)
     const int tall = tid - 128;            // 0..255
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const TQ* qbase = static_cast<const TQ*>(p.q);
-    // quantise the G query rows of item `wi`'s kv head into the B operand of QK^T, buffer `qb`
-    auto prep_q = [&](int64_t wi, int qb) {
-      int unit_q, t0q, t1q;
-      item_range(wi, unit_q, t0q, t1q);
-      const int zq = unit_q / p.hk, khq = unit_q % p.hk;
-      uint8_t* dq = s_q + qb * C::Q_BYTES;
-      uint8_t* dsf = s_qsf + qb * C::QSF_BYTES;
-      for (int i = tall; i < p.g * (D / 16); i += 256) {
-        const int qr = i / (D / 16), gi = i % (D / 16);
-        const TQ* src = qbase + zq * p.s_qz + (int64_t)(khq * p.g + qr) * p.s_qh + gi * 16;
-        float v[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = to_f32<TQ>(src[e]);
-        uint32_t lo, hi;
-        const uint8_t sb = pack_group16(v, lo, hi);
-        *reinterpret_cast<uint2*>(dq + (gi >> 3) * 1024 + sw64_offset(qr, (gi & 7) * 8)) = make_uint2(lo, hi);
-        dsf[(gi >> 2) * 512 + sf_atom_offset(qr, gi & 3)] = sb;
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&q_full[qb]);
-    };
-    uint32_t su = 0, item_idx = 0;
-    if ((int64_t)blockIdx.x < p.nitems) prep_q(blockIdx.x, 0);
+    uint32_t su = 0;
     for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
       int unit, t0, t1;
       item_range(w, unit, t0, t1);
-      // ---- the query rows of the NEXT item go into the other operand buffer now (its last reader,
-      //      the QK^T of the previous item, has completed: this warp consumed all of its rounds)
-      if (w + gridDim.x < p.nitems) prep_q(w + gridDim.x, (int)((item_idx + 1) & 1));
-      ++item_idx;
-
       float m_run[NQ], l_run[NQ];             // key-lane role: running max, partial row sum
       float o_run[C::MT][NQ], m_acc[NQ];      // d-row role: accumulated O^T, the max it refers to
       float w_prev[TPG][NQ], m_end_prev[NQ];  // weights of the round whose PV is still in flight

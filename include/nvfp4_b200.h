@@ -79,7 +79,11 @@ int nvfp4_kv_append(const void* k_new, const void* v_new, int dtype, int64_t s_n
  * Split-K decode plan for a cache of s_kv keys and zhk (batch x kv-head) units: how many
  * splits the decode kernel will use, keys per split (a multiple of 128) and the scratch bytes it
  * needs.  Replaces the heuristic of `_decode_compute` (flash.py:3255-3266), sized for the
- * device's SM count instead of a fixed 256 programs.
+ * device's SM count instead of a fixed 256 programs: the split count minimises
+ * waves x (tiles per item + per-item drain).  When it is cheaper still, the plan is the balanced
+ * decomposition, reported as *nsplit = 0, *split_kv = 0: every persistent CTA streams an equal
+ * share of the unit-major list of 128-key tiles, so a unit may be cut anywhere and its partials
+ * are the pieces of the CTAs that touch it (exact combine as for fixed splits).
  */
 int nvfp4_decode_plan(int64_t s_kv, int64_t zhk, int d, int sm_count, int* nsplit,
                       int64_t* split_kv, size_t* workspace_bytes);
@@ -96,6 +100,8 @@ int nvfp4_decode_plan(int64_t s_kv, int64_t zhk, int d, int sm_count, int* nspli
  *            up to 128.  Key groups beyond s_kv must hold zero nibbles (any scale byte).
  *   out      [Z, H, D] in `q_dtype`, contiguous.  lse: [Z, H] fp32 or NULL.
  *   workspace: >= workspace_bytes from nvfp4_decode_plan(nsplit as planned), 16-byte aligned.
+ *   nsplit / split_kv: as planned, or any explicit fixed split (nsplit * split_kv covering s_kv);
+ *            nsplit = 0 selects the balanced decomposition.
  *   status   device int, written non-zero if a bounded wait expired; may be NULL.
  */
 int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, const uint8_t* knv,

@@ -85,7 +85,12 @@ struct DecodeParams {
   int chunk_tiles;
   int ntiles;
   int64_t nitems;
-  float* ws_acc;  // [nitems][16][D]
+  // balanced mode: CTA b owns the global tiles [b*T/G, (b+1)*T/G) of the unit-major tile list
+  // (T = units * ntiles); its work items are the pieces of the units that range touches
+  int balanced;
+  int64_t total_tiles;
+  int maxseg;     // partial slots reserved per CTA
+  float* ws_acc;  // [slots][16][D]
   float* ws_m;    // [nitems][16]
   float* ws_l;    // [nitems][16]
   int* status;
@@ -152,19 +157,42 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
 
-  auto item_range = [&](int64_t w, int& unit, int& t0, int& t1) {
-    unit = (int)(w / p.nsplit);
-    const int split = (int)(w % p.nsplit);
-    t0 = split * p.chunk_tiles;
-    t1 = min(t0 + p.chunk_tiles, p.ntiles);
+  // work items of this CTA: i = 0 .. my_items-1
+  const int64_t nctas = gridDim.x;
+  int64_t bal_start = 0, bal_end = 0;
+  int bal_u0 = 0, my_items = 0;
+  if (p.balanced) {
+    bal_start = (int64_t)blockIdx.x * p.total_tiles / nctas;
+    bal_end = (int64_t)(blockIdx.x + 1) * p.total_tiles / nctas;
+    bal_u0 = (int)(bal_start / p.ntiles);
+    my_items = bal_end > bal_start ? (int)((bal_end - 1) / p.ntiles) - bal_u0 + 1 : 0;
+  } else if ((int64_t)blockIdx.x < p.nitems) {
+    my_items = (int)((p.nitems - blockIdx.x + nctas - 1) / nctas);
+  }
+  auto item_at = [&](int i, int& unit, int& t0, int& t1) {
+    if (p.balanced) {
+      unit = bal_u0 + i;
+      const int64_t base = (int64_t)unit * p.ntiles;
+      t0 = (int)(max(bal_start, base) - base);
+      t1 = (int)(min(bal_end, base + p.ntiles) - base);
+    } else {
+      const int64_t w = blockIdx.x + (int64_t)i * nctas;
+      unit = (int)(w / p.nsplit);
+      const int split = (int)(w % p.nsplit);
+      t0 = split * p.chunk_tiles;
+      t1 = min(t0 + p.chunk_tiles, p.ntiles);
+    }
+  };
+  auto slot_at = [&](int i) -> int64_t {
+    return p.balanced ? (int64_t)blockIdx.x * p.maxseg + i : blockIdx.x + (int64_t)i * nctas;
   };
 
   // quantise the G query rows of item `wi`'s kv head into the B operand of QK^T, buffer `qb`
   // (called by the 32 lanes of the QK^T issuer's warp, one work item ahead of the MMAs)
   const TQ* qbase = static_cast<const TQ*>(p.q);
-  auto prep_q = [&](int64_t wi, int qb) {
+  auto prep_q = [&](int wi, int qb) {
     int unit_q, t0q, t1q;
-    item_range(wi, unit_q, t0q, t1q);
+    item_at(wi, unit_q, t0q, t1q);
     const int zq = unit_q / p.hk, khq = unit_q % p.hk;
     uint8_t* dq = s_q + qb * C::Q_BYTES;
     uint8_t* dsf = s_qsf + qb * C::QSF_BYTES;
@@ -188,16 +216,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0;
-      for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+      for (int wi = 0; wi < my_items; ++wi) {
         int unit, t0, t1;
-        item_range(w, unit, t0, t1);
+        item_at(wi, unit, t0, t1);
         for (int t = t0; t < t1; ++t, ++it) {
           // V^T rows are D separate strips in memory and a 128-key tile touches only 64 bytes of
           // each; 1 KB per strip (16 tiles) is pulled into L2 one 16-tile block ahead so DRAM sees
           // long bursts.  The pull is spread over the tiles of the block before it (8 strips per
           // tile): a whole block at once, from every CTA in step, stalls the demand loads behind it.
           const int j = t - t0;
-          if (j == 0 && (w == (int64_t)blockIdx.x || t1 - t0 < 16)) {
+          if (j == 0 && (wi == 0 || t1 - t0 < 16)) {
 #pragma unroll 1
             for (int r = 0; r < 16; ++r)
 #pragma unroll
@@ -211,9 +239,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           }
           // the first block of this CTA's NEXT work item, a whole item ahead: its first tiles would
           // otherwise be 128 scattered 64-byte first touches each, ~15k clocks of DRAM latency
-          if (j < 16 && w + gridDim.x < p.nitems) {
+          if (j < 16 && wi + 1 < my_items) {
             int unit_n, t0n, t1n;
-            item_range(w + gridDim.x, unit_n, t0n, t1n);
+            item_at(wi + 1, unit_n, t0n, t1n);
 #pragma unroll
             for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, t0n * 16, mt * 128 + j * 8, unit_n);
           }
@@ -245,9 +273,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) { mbar_arrive(&full_sf[n % C::NSTAGE]); DTRACE(1, n, 0); }
     };
-    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+    for (int wi = 0; wi < my_items; ++wi) {
       int unit, t0, t1;
-      item_range(w, unit, t0, t1);
+      item_at(wi, unit, t0, t1);
       const uint8_t* ksrc = p.ksc + (int64_t)unit * p.ksc_unit;
       const uint8_t* vsrc = p.vsc + (int64_t)unit * p.vsc_unit;
       for (int t = t0; t < t1; ++t, ++it) {
@@ -295,16 +323,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const bool leader = elect_one();
     const uint32_t idesc = make_idesc_nvfp4(128, 16);
     uint32_t it_w = 0, su_w = 0, item_idx = 0;   // warp-uniform: tiles and rounds issued before this item
-    if ((int64_t)blockIdx.x < p.nitems) prep_q(blockIdx.x, 0);
-    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x, ++item_idx) {
+    if (my_items > 0) prep_q(0, 0);
+    for (int wi = 0; wi < my_items; ++wi, ++item_idx) {
       // the whole warp quantises the NEXT item's query rows into the other buffer; that buffer's
       // last readers are the QK^T MMAs of the previous item, complete once its last s_full fired
-      if (w + gridDim.x < p.nitems) {
+      if (wi + 1 < my_items) {
         if (item_idx > 0) mbar_wait(&s_full[(su_w - 1) & 1], ((su_w - 1) >> 1) & 1, &err, 12);
-        prep_q(w + gridDim.x, (int)((item_idx + 1) & 1));
+        prep_q(wi + 1, (int)((item_idx + 1) & 1));
       }
       int unit, t0, t1;
-      item_range(w, unit, t0, t1);
+      item_at(wi, unit, t0, t1);
       if (leader) {
         uint32_t it = it_w, su = su_w;      // the leader's running counters for this item
         const int qb = item_idx & 1;
@@ -364,9 +392,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (elect_one()) {
       const uint32_t idesc = make_idesc_nvfp4(128, 16);
       uint32_t it = 0, su = 0;
-      for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+      for (int wi = 0; wi < my_items; ++wi) {
         int unit, t0, t1;
-        item_range(w, unit, t0, t1);
+        item_at(wi, unit, t0, t1);
         for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
           const int b = su & 1;
           const int nt = min(ST, t1 - ts0);
@@ -418,9 +446,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int tall = tid - 128;            // 0..255
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     uint32_t su = 0;
-    for (int64_t w = blockIdx.x; w < p.nitems; w += gridDim.x) {
+    for (int wi = 0; wi < my_items; ++wi) {
       int unit, t0, t1;
-      item_range(w, unit, t0, t1);
+      item_at(wi, unit, t0, t1);
       float m_run[NQ], l_run[NQ];             // key-lane role: running max, partial row sum
       float o_run[C::MT][NQ], m_acc[NQ];      // d-row role: accumulated O^T, the max it refers to
       float w_prev[TPG][NQ], m_end_prev[NQ];  // weights of the round whose PV is still in flight
@@ -618,7 +646,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (tall == 0) DTRACE(4, su, 7);
       }
       // ---- item epilogue: fold the last round, merge the two groups, write un-normalised partials
+      const bool etr = lane == 0 && wi == 0;
+      if (etr) DTRACE(5, sw, 0);
       if (have_prev) accumulate(su - 1, nt_prev);
+      if (etr) DTRACE(5, sw, 1);
       {
         // bring this group's accumulator to the final running maximum
 #pragma unroll
@@ -642,8 +673,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           if (lane == 0) lred[sw][qi] = v;
         }
+        if (etr) DTRACE(5, sw, 2);
         named_bar_sync(1, 256);
+        if (etr) DTRACE(5, sw, 3);
         if (grp == 0) {
+          const int64_t w = slot_at(wi);
           float* acc = p.ws_acc + w * 16 * D;
 #pragma unroll
           for (int mt = 0; mt < C::MT; ++mt)
@@ -663,7 +697,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             p.ws_l[w * 16 + ts] = lsum;
           }
         }
-        named_bar_sync(1, 256);
+        if (etr) DTRACE(5, sw, 4);
+        // no barrier here: the merge buffer (= the P tiles) and lred are next written after the
+        // max-exchange barrier of the next item's first round, which these reads precede in
+        // program order; the kernel's final __syncthreads covers the last item
       }
     }
   }
@@ -698,12 +735,63 @@ __global__ void decode_combine_kernel(const float* __restrict__ ws_acc,
   if (lse != nullptr && t == 0) lse[row] = gm + logf(den);
 }
 
+// The same for the balanced decomposition: the partials of a unit are the pieces written by the
+// CTAs whose tile ranges reach into it.
+template <typename TQ>
+__global__ void decode_combine_balanced_kernel(const float* __restrict__ ws_acc,
+                                               const float* __restrict__ ws_m,
+                                               const float* __restrict__ ws_l, int64_t total_tiles,
+                                               int ntiles, int nctas, int maxseg, int hk, int g, int d,
+                                               TQ* __restrict__ out, float* __restrict__ lse) {
+  const int unit = blockIdx.x / g, qi = blockIdx.x % g;
+  const int t = threadIdx.x;
+  const int64_t x0 = (int64_t)unit * ntiles, x1 = x0 + ntiles;
+  int64_t b0 = x0 * nctas / total_tiles;      // the CTA whose range contains tile x0
+  while (b0 + 1 < nctas && (b0 + 1) * total_tiles / nctas <= x0) ++b0;
+  while (b0 > 0 && b0 * total_tiles / nctas > x0) --b0;
+  float gm = -INFINITY;
+  for (int64_t b = b0; b < nctas && b * total_tiles / nctas < x1; ++b) {
+    const int64_t st = b * total_tiles / nctas, en = (b + 1) * total_tiles / nctas;
+    if (en <= st || en <= x0) continue;
+    const int64_t w = b * maxseg + (unit - st / ntiles);
+    gm = fmaxf(gm, ws_m[w * 16 + qi]);
+  }
+  float acc = 0.0f, den = 0.0f;
+  for (int64_t b = b0; b < nctas && b * total_tiles / nctas < x1; ++b) {
+    const int64_t st = b * total_tiles / nctas, en = (b + 1) * total_tiles / nctas;
+    if (en <= st || en <= x0) continue;
+    const int64_t w = b * maxseg + (unit - st / ntiles);
+    const float ms = ws_m[w * 16 + qi];
+    const float f = (ms == -INFINITY) ? 0.0f : expf(ms - gm);
+    acc += f * ws_acc[(w * 16 + qi) * d + t];
+    den += f * ws_l[w * 16 + qi];
+  }
+  if (den == 0.0f) den = 1.0f;
+  const int zi = unit / hk, kh = unit % hk;
+  const int64_t row = (int64_t)zi * hk * g + kh * g + qi;
+  out[row * d + t] = from_f32<TQ>(acc / den);
+  if (lse != nullptr && t == 0) lse[row] = gm + logf(den);
+}
+
+// Balanced decomposition: CTAs and partial slots per CTA for `zhk` units of `ntiles` tiles.
+inline void decode_balanced_geometry(int64_t zhk, int64_t ntiles, int sm_count, int* nctas, int* maxseg) {
+  const int64_t total = zhk * ntiles;
+  const int64_t g = std::max<int64_t>(1, std::min<int64_t>(sm_count, total / 4 > 0 ? total / 4 : 1));
+  const int64_t per = (total + g - 1) / g;
+  *nctas = (int)g;
+  *maxseg = (int)((per + ntiles - 2) / ntiles + 1);
+}
+
 template <int D, typename TQ>
 int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_vpf,
                   const DecodeParams& p,
                   int64_t zhk, void* out, float* lse, int sm_count, cudaStream_t st) {
   using C = DecodeCfg<D>;
-  const int grid = (int)std::min<int64_t>(p.nitems, sm_count);
+  int grid = (int)std::min<int64_t>(p.nitems, sm_count);
+  if (p.balanced) {
+    int ms;
+    decode_balanced_geometry(zhk, p.ntiles, sm_count, &grid, &ms);
+  }
   auto launch = [&](auto kern) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
@@ -716,8 +804,13 @@ int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtens
   else if (p.g <= 8) rc = launch(decode_kernel<D, TQ, 8>);
   else rc = launch(decode_kernel<D, TQ, 16>);
   if (rc) return rc;
-  decode_combine_kernel<TQ><<<(unsigned)(zhk * p.g), D, 0, st>>>(
-      p.ws_acc, p.ws_m, p.ws_l, p.nsplit, p.hk, p.g, D, static_cast<TQ*>(out), lse);
+  if (p.balanced)
+    decode_combine_balanced_kernel<TQ><<<(unsigned)(zhk * p.g), D, 0, st>>>(
+        p.ws_acc, p.ws_m, p.ws_l, p.total_tiles, p.ntiles, grid, p.maxseg, p.hk, p.g, D,
+        static_cast<TQ*>(out), lse);
+  else
+    decode_combine_kernel<TQ><<<(unsigned)(zhk * p.g), D, 0, st>>>(
+        p.ws_acc, p.ws_m, p.ws_l, p.nsplit, p.hk, p.g, D, static_cast<TQ*>(out), lse);
   return launch_result("nvfp4_decode(combine)");
 }
 
@@ -730,14 +823,39 @@ extern "C" int nvfp4_decode_plan(int64_t s_kv, int64_t zhk, int d, int sm_count,
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_decode_plan: D must be 128 or 256");
   if (sm_count <= 0) sm_count = 148;
   const int64_t tiles = (s_kv + 127) / 128;
-  // about eight work items per SM keeps the persistent CTAs balanced; no item under 4 tiles
-  int64_t want = (8LL * sm_count + zhk - 1) / zhk;
-  want = std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(1, tiles / 4)));
-  const int64_t chunk = (tiles + want - 1) / want;
-  const int64_t ns = (tiles + chunk - 1) / chunk;
+  // Persistent CTAs take work items round-robin, so the step costs
+  //     waves * (tiles_per_item * t_tile + t_item),  waves = ceil(zhk * nsplit / sm_count):
+  // few splits leave SMs idle in the last wave, many splits pay the per-item pipeline drain
+  // (measured on B200: about 6 tile times per item).  Pick the split count that minimises it; no
+  // item under 4 tiles.
+  const int64_t max_split = std::max<int64_t>(1, std::min<int64_t>(tiles / 4, 64));
+  int64_t best_chunk = tiles;
+  double best_cost = 1e300;
+  for (int64_t want = 1; want <= max_split; ++want) {
+    const int64_t c = (tiles + want - 1) / want;
+    const int64_t n = (tiles + c - 1) / c;
+    const int64_t waves = (zhk * n + sm_count - 1) / sm_count;
+    const double cost = (double)waves * ((double)c + 6.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best_chunk = c; }
+  }
+  const int64_t chunk = best_chunk;
+  int64_t ns = (tiles + chunk - 1) / chunk;
+  size_t bytes = (size_t)(zhk * ns) * (size_t)(16 * d + 32) * sizeof(float);
+  // balanced decomposition (nsplit = 0): every CTA streams an equal share of the unit-major tile
+  // list and a unit's partials are the pieces of the CTAs that touch it
+  int bg, bm;
+  decode_balanced_geometry(zhk, tiles, sm_count, &bg, &bm);
+  const double per = (double)((zhk * tiles + bg - 1) / bg);
+  const double bal_cost = per + 6.0 * (1.0 + per / (double)tiles);
+  int64_t kv = chunk * 128;
+  if (bal_cost < best_cost) {
+    ns = 0;
+    kv = 0;
+    bytes = (size_t)bg * (size_t)bm * (size_t)(16 * d + 32) * sizeof(float);
+  }
   if (nsplit) *nsplit = (int)ns;
-  if (split_kv) *split_kv = chunk * 128;
-  if (workspace_bytes) *workspace_bytes = (size_t)(zhk * ns) * (size_t)(16 * d + 32) * sizeof(float);
+  if (split_kv) *split_kv = kv;
+  if (workspace_bytes) *workspace_bytes = bytes;
   return 0;
 }
 
@@ -753,12 +871,21 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   NVFP4_REQUIRE(g >= 1 && g <= 16, "nvfp4_decode: GQA group %d must be <= 16", g);
   NVFP4_REQUIRE(z >= 1 && hk >= 1 && s_kv >= 1, "nvfp4_decode: empty problem");
   NVFP4_REQUIRE(q && knv && ksc && vnv && vsc && out && workspace, "nvfp4_decode: null pointer");
-  NVFP4_REQUIRE(nsplit >= 1 && split_kv >= 128 && split_kv % 128 == 0,
+  const bool balanced = nsplit == 0;   // balanced decomposition chosen by nvfp4_decode_plan
+  NVFP4_REQUIRE(balanced || (nsplit >= 1 && split_kv >= 128 && split_kv % 128 == 0),
                 "nvfp4_decode: split_kv must be a positive multiple of 128");
-  NVFP4_REQUIRE((int64_t)nsplit * split_kv >= s_kv && (int64_t)(nsplit - 1) * split_kv < s_kv,
+  NVFP4_REQUIRE(balanced ||
+                    ((int64_t)nsplit * split_kv >= s_kv && (int64_t)(nsplit - 1) * split_kv < s_kv),
                 "nvfp4_decode: nsplit * split_kv does not cover s_kv exactly");
   const int64_t zhk = z * hk;
-  const size_t need = (size_t)(zhk * nsplit) * (size_t)(16 * d + 32) * sizeof(float);
+  int dev = 0, sm_count = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (sm_count <= 0) return fail(-1, "nvfp4_decode: no CUDA device");
+  int bal_ctas = 0, bal_maxseg = 0;
+  decode_balanced_geometry(zhk, (s_kv + 127) / 128, sm_count, &bal_ctas, &bal_maxseg);
+  const int64_t slots = balanced ? (int64_t)bal_ctas * bal_maxseg : zhk * nsplit;
+  const size_t need = (size_t)slots * (size_t)(16 * d + 32) * sizeof(float);
   NVFP4_REQUIRE(workspace_bytes >= need, "nvfp4_decode: workspace too small (%zu < %zu)",
                 workspace_bytes, need);
   NVFP4_REQUIRE(((uintptr_t)workspace & 15) == 0, "nvfp4_decode: workspace must be 16-byte aligned");
@@ -785,11 +912,6 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
                                  "nvfp4_decode(V prefetch)");
   if (rc) return rc;
 
-  int dev = 0, sm_count = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  if (sm_count <= 0) return fail(-1, "nvfp4_decode: no CUDA device");
-
   DecodeParams p;
   p.timing = nullptr;
 #ifdef NVFP4_DECODE_TIMING
@@ -800,12 +922,15 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   p.ksc = ksc; p.ksc_unit = ksc_unit;
   p.vsc = vsc; p.vsc_unit = vsc_unit; p.vsc_row = vsc_row;
   p.hk = (int)hk; p.g = g; p.s_kv = s_kv; p.scaling = scaling;
-  p.nsplit = nsplit; p.chunk_tiles = (int)(split_kv / 128); p.ntiles = (int)((s_kv + 127) / 128);
-  p.nitems = zhk * nsplit;
+  p.nsplit = balanced ? 1 : nsplit; p.chunk_tiles = (int)(split_kv / 128); p.ntiles = (int)((s_kv + 127) / 128);
+  p.nitems = balanced ? 0 : zhk * nsplit;
+  p.balanced = balanced ? 1 : 0;
+  p.total_tiles = zhk * p.ntiles;
+  p.maxseg = bal_maxseg;
   float* ws = static_cast<float*>(workspace);
   p.ws_acc = ws;
-  p.ws_m = ws + p.nitems * 16 * d;
-  p.ws_l = p.ws_m + p.nitems * 16;
+  p.ws_m = ws + slots * 16 * d;
+  p.ws_l = p.ws_m + slots * 16;
   p.status = status;
 
 #define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, tm_vpf, p, zhk, out, lse, sm_count, st)
@@ -876,8 +1001,16 @@ extern "C" int nvfp4_decode_static(const void* q, int q_dtype, int64_t s_qz, int
                                    int64_t split_kv, int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_decode_static: D must be 128 or 256");
-  NVFP4_REQUIRE(z >= 1 && hk >= 1 && nsplit >= 1, "nvfp4_decode_static: empty problem");
-  const size_t need = (size_t)(z * hk) * (size_t)nsplit * (size_t)(16 * d + 32) * sizeof(float);
+  NVFP4_REQUIRE(z >= 1 && hk >= 1 && nsplit >= 0 && s_kv >= 1, "nvfp4_decode_static: empty problem");
+  size_t slots = (size_t)(z * hk) * (size_t)nsplit;
+  if (nsplit == 0) {   // balanced decomposition
+    int dev = 0, sm_count = 0, bc = 0, bm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    decode_balanced_geometry(z * hk, (s_kv + 127) / 128, sm_count > 0 ? sm_count : 148, &bc, &bm);
+    slots = (size_t)bc * (size_t)bm;
+  }
+  const size_t need = slots * (size_t)(16 * d + 32) * sizeof(float);
   if (need > kStaticScratchBytes)
     return fail(-1,
                 "nvfp4_decode_static: this problem needs %zu bytes of split-K scratch but the static "

@@ -228,6 +228,14 @@ def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
         q3 = q3.contiguous()
     if split_kv is None:
         nsplit, split_kv, wbytes = _decode_plan(s_kv, zhk, d, dev)
+    elif split_kv == 0:
+        # balanced decomposition (every CTA streams an equal share of all key tiles), forced;
+        # slots as in `decode_balanced_geometry` of the C library
+        tiles = -(-s_kv // 128)
+        total = zhk * tiles
+        ctas = max(1, min(_sm_count(dev), total // 4 if total // 4 > 0 else 1))
+        per = -(-total // ctas)
+        nsplit, wbytes = 0, ctas * ((per + tiles - 2) // tiles + 1) * (16 * d + 32) * 4
     else:
         assert split_kv % 128 == 0
         nsplit = -(-s_kv // split_kv)

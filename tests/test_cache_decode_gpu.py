@@ -83,11 +83,37 @@ def test_decode_matches_oracle(z, h, hk, s, d):
     out, lse = flash._decode_prequant_with_lse(q.float(), packed, d ** -0.5, g)
     assert _status() == 0
     nsplit, split_kv, _ = flash._decode_plan(s, z * hk, d, "cuda")
+    if nsplit == 0:      # balanced decomposition: compare with the unsplit walk
+        split_kv = -(-s // 128) * 128
     ref, ref_lse = O.decode_prequant(qf, oracle_packed, d ** -0.5, g, split_kv=split_kv)
     o = out.cpu().numpy()
     assert cos(o, ref) >= 0.999, cos(o, ref)
     assert np.abs(o - ref).max() <= 2e-2
     assert np.abs(lse.cpu().numpy() - ref_lse).max() <= 2e-3
+
+
+@pytest.mark.parametrize("z,h,hk,s,d", [(3, 8, 2, 1100, 128), (37, 4, 4, 700, 128), (2, 16, 1, 5000, 128),
+                                         (5, 4, 2, 1300, 256), (1, 4, 1, 130, 128), (150, 2, 2, 100, 128)])
+def test_decode_balanced_decomposition(z, h, hk, s, d):
+    """Forced balanced decomposition: CTAs own equal shares of the unit-major tile list, so units
+    are cut at arbitrary tile boundaries and a CTA may hold pieces of several units."""
+    g = h // hk
+    q, qf = seeded_bf16((z, h, 1, d), 400 + s)
+    k, kf = seeded_bf16((z, hk, s, d), 500 + s)
+    v, vf = seeded_bf16((z, hk, s, d), 600 + s)
+    from sageattention_b200.nvfp4 import flash
+    packed = flash.nvfp4_quant_kv_decode(k, v)
+    out, lse = flash._decode_core(q.float(), packed, d ** -0.5, g, True, split_kv=0)
+    assert _status() == 0
+    fixed, fixed_lse = flash._decode_core(q.float(), packed, d ** -0.5, g, True, split_kv=-(-s // 128) * 128)
+    ref, ref_lse = O.decode_prequant(qf, O.quant_kv_decode(kf, vf), d ** -0.5, g, split_kv=-(-s // 128) * 128)
+    o = out.cpu().numpy()
+    assert np.isfinite(o).all()
+    print("balanced vs oracle cos", cos(o, ref), "maxabs", np.abs(o - ref).max(), "vs one split", cos(o, fixed.cpu().numpy()))
+    # another (equally valid) P-quantisation schedule than the unsplit walk: FP4-P rounding level
+    assert cos(o, ref) >= 0.997 and np.abs(o - ref).max() <= 2e-2, (cos(o, ref), np.abs(o - ref).max())
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() <= 2e-3      # the statistics themselves are exact
+    assert cos(o, fixed.cpu().numpy()) >= 0.997
 
 
 def test_decode_multi_split_explicit():

@@ -60,6 +60,22 @@ int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, i
                uint8_t* sc, int64_t ssb, int64_t ssr, nvfp4_stream_t stream);
 
 /*
+ * Rotary position embedding fused into the packer: y = rope(x) is rounded once to the input dtype
+ * and packed along D exactly as nvfp4_pack would pack it, without y ever reaching HBM.  The
+ * reference names this fused producer as the condition for an end-to-end win of its pre-packed
+ * entry points (`q_packs` / `k_packs`, flash.py:10-13, 2812-2821) and leaves it to the caller.
+ *   x [B, R, d]: element strides sxb, sxr, unit stride along d; d a power of two >= 32.
+ *   cos_tab / sin_tab [P, d/2] fp32; row r uses position positions[r] (int32, may be NULL) or
+ *   pos0 + r.  Half-split convention: y[i] = x[i] cos[i] - x[i + d/2] sin[i] (i < d/2),
+ *   y[i] = x[i] cos[i - d/2] + x[i - d/2] sin[i - d/2] (i >= d/2).
+ *   out_nib / out_sc as for nvfp4_pack (byte strides; nibble rows 8-byte aligned).
+ */
+int nvfp4_rope_pack(const void* x, int dtype, int64_t B, int64_t R, int d, int64_t sxb, int64_t sxr,
+                    const float* cos_tab, const float* sin_tab, const int32_t* positions,
+                    int64_t pos0, uint8_t* out_nib, int64_t snb, int64_t snr, uint8_t* out_sc,
+                    int64_t ssb, int64_t ssr, nvfp4_stream_t stream);
+
+/*
  * One decode-step append into an NVFP4 KV cache, one launch, no host synchronisation.
  * Replaces NVFP4KVCache.append (sageattention/nvfp4/kv_cache.py:228-257): packs the new K row
  * along D into position `pos`; stores the new V token into slot pos % 16 of the partial-group

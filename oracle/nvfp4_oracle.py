@@ -542,3 +542,29 @@ def attention_grads(q, k, v, do, scaling, causal=False, g=1, cu_seqlens=None):
 def cosine(a, b) -> float:
     a = np.asarray(a, np.float64).ravel(); b = np.asarray(b, np.float64).ravel()
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """fp32 -> bf16 (round to nearest even) -> fp32."""
+    u = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def rope_half_split(x, cos, sin, positions=None, pos0=0, round_to="bf16"):
+    """Rotary embedding, half-split ("rotate_half") convention, fp32 math, one rounding to the
+    storage dtype: the arithmetic of the fused rotary + pack producer (no reference counterpart:
+    flash.py:10-13 asks callers to fuse one).  x [B, R, D]; cos / sin [P, D/2]."""
+    x = np.asarray(x, np.float32)
+    b, r, d = x.shape
+    h = d // 2
+    pos = (np.arange(r) + pos0) if positions is None else np.asarray(positions)
+    c, s = np.asarray(cos, np.float32)[pos], np.asarray(sin, np.float32)[pos]
+    lo, hi = x[..., :h], x[..., h:]
+    # fused multiply-add of the kernel: fma(rot, sin, x * cos) with x * cos rounded to fp32 first
+    y_lo = (np.float64(np.float32(lo * c)) + np.float64(-hi) * np.float64(s)).astype(np.float32)
+    y_hi = (np.float64(np.float32(hi * c)) + np.float64(lo) * np.float64(s)).astype(np.float32)
+    y = np.concatenate([y_lo, y_hi], axis=-1)
+    if round_to == "bf16":
+        y = bf16_round(y)
+    return y

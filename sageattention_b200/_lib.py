@@ -42,6 +42,9 @@ SIGNATURES = {
     "nvfp4_window_attention": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                        c_int64, c_int64, c_int, c_int, c_int64, c_int64, c_int64,
                                        c_float, c_void_p, c_void_p, c_void_p]),
+    "nvfp4_rope_pack": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p,
+                                c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+                                c_void_p]),
     "nvfp4_bwd_prep": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_bwd_hp": (c_int, [c_void_p] * 15 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -73,6 +73,58 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(
   sc[b * ssb + r * ssr + g] = sb;
 }
 
+// ---------------------------------------------------------------- rotary embedding + pack
+// x [B, R, D] with the position of row r = pos0 + r (or positions[r]); cos / sin [P, D/2] fp32.
+// Half-split convention ("rotate_half"): y[i] = x[i] cos[i] - x[i + D/2] sin[i] for i < D/2,
+// y[i] = x[i] cos[i - D/2] + x[i - D/2] sin[i - D/2] otherwise; computed in fp32, rounded once to
+// the input dtype (what an unfused rotary kernel would have stored), then packed like pack_rows.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_pack_rows_kernel(
+    const T* __restrict__ x, int64_t R, int d, int ngroups_log2, int64_t per_batch, int64_t sxb,
+    int64_t sxr, const float* __restrict__ cs, const float* __restrict__ sn,
+    const int32_t* __restrict__ positions, int64_t pos0, uint8_t* __restrict__ nib, int64_t snb,
+    int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr, int vec_in) {
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= per_batch) return;
+  const int64_t b = blockIdx.y;
+  const int ngroups = d >> 4, half = d >> 1;
+  const int g = (int)(gid & (ngroups - 1));
+  const int64_t r = gid >> ngroups_log2;
+  const bool upper = g * 16 >= half;
+  const int gp = upper ? g - (ngroups >> 1) : g + (ngroups >> 1);      // partner group
+  const T* row = x + b * sxb + r * sxr;
+  const int64_t pos = positions ? (int64_t)positions[r] : pos0 + r;
+  const float* c = cs + pos * half + (upper ? gp : g) * 16;
+  const float* s_ = sn + pos * half + (upper ? gp : g) * 16;
+  float a[16], pa[16];
+  {
+    float t0[8], t1[8];
+    load8<T>(row + g * 16, vec_in, 16, t0);
+    load8<T>(row + g * 16 + 8, vec_in, 8, t1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = t0[i]; a[8 + i] = t1[i]; }
+    load8<T>(row + gp * 16, vec_in, 16, t0);
+    load8<T>(row + gp * 16 + 8, vec_in, 8, t1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { pa[i] = t0[i]; pa[8 + i] = t1[i]; }
+  }
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; i += 4) {
+    const float4 c4 = *reinterpret_cast<const float4*>(c + i), s4 = *reinterpret_cast<const float4*>(s_ + i);
+    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float rot = upper ? pa[i + e] : -pa[i + e];
+      v[i + e] = to_f32<T>(from_f32<T>(__fmaf_rn(rot, ss[e], a[i + e] * cc[e])));
+    }
+  }
+  uint32_t lo, hi;
+  const uint8_t sb = pack_group16(v, lo, hi);
+  *reinterpret_cast<uint2*>(nib + b * snb + r * snr + g * 8) = make_uint2(lo, hi);
+  sc[b * ssb + r * ssr + g] = sb;
+}
+
 // ---------------------------------------------------------------- rows contiguous (V^T)
 constexpr int kColsKeys = 128;  // contraction extent of a tile
 constexpr int kColsRows = 64;   // row (head-dim) extent of a tile
@@ -239,4 +291,42 @@ extern "C" int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_
     default:
       return fail(-1, "nvfp4_pack: unknown dtype %d", dtype);
   }
+}
+
+extern "C" int nvfp4_rope_pack(const void* x, int dtype, int64_t B, int64_t R, int d, int64_t sxb,
+                               int64_t sxr, const float* cos_tab, const float* sin_tab,
+                               const int32_t* positions, int64_t pos0, uint8_t* nib, int64_t snb,
+                               int64_t snr, uint8_t* sc, int64_t ssb, int64_t ssr,
+                               nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(x && cos_tab && sin_tab && nib && sc, "nvfp4_rope_pack: null pointer");
+  NVFP4_REQUIRE(d >= 32 && (d & (d - 1)) == 0, "nvfp4_rope_pack: head dim must be a power of two >= 32");
+  NVFP4_REQUIRE(B >= 0 && R >= 0 && B < 65536, "nvfp4_rope_pack: bad extents");
+  NVFP4_REQUIRE(((uintptr_t)nib & 7) == 0 && snb % 8 == 0 && snr % 8 == 0,
+                "nvfp4_rope_pack: nibble rows must be 8-byte aligned");
+  NVFP4_REQUIRE(((uintptr_t)cos_tab & 15) == 0 && ((uintptr_t)sin_tab & 15) == 0,
+                "nvfp4_rope_pack: cos / sin tables must be 16-byte aligned");
+  if (B == 0 || R == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int ngroups = d / 16;
+  int lg = 0;
+  while ((1 << lg) < ngroups) ++lg;
+  const int64_t per_batch = R * ngroups;
+  const int64_t blocks = (per_batch + 255) / 256;
+  NVFP4_REQUIRE(blocks < (1LL << 31), "nvfp4_rope_pack: tensor too large");
+  dim3 grid((unsigned)blocks, (unsigned)B);
+  const int es = dtype == NVFP4_DT_FP32 ? 4 : 2;
+  const int vec = ((uintptr_t)x % 16 == 0) && (sxb * es) % 16 == 0 && (sxr * es) % 16 == 0;
+#define NVFP4_ROPE(T)                                                                              \
+  rope_pack_rows_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), R, d, lg, per_batch, sxb, \
+                                                 sxr, cos_tab, sin_tab, positions, pos0, nib, snb,  \
+                                                 snr, sc, ssb, ssr, vec);                           \
+  return launch_result("nvfp4_rope_pack")
+  switch (dtype) {
+    case NVFP4_DT_BF16: NVFP4_ROPE(__nv_bfloat16);
+    case NVFP4_DT_FP16: NVFP4_ROPE(__half);
+    case NVFP4_DT_FP32: NVFP4_ROPE(float);
+    default: return fail(-1, "nvfp4_rope_pack: unknown dtype %d", dtype);
+  }
+#undef NVFP4_ROPE
 }

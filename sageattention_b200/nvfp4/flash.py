@@ -115,6 +115,33 @@ def _quant_nvfp4(x: torch.Tensor, transpose: bool = False, k_pad: int | None = N
     return nib, sc.view(torch.float8_e4m3fn)
 
 
+def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions=None, pos0: int = 0):
+    """Rotary embedding fused into the NVFP4 packer (the producer the reference asks callers to
+    fuse before `q_packs` / `k_packs`, flash.py:10-13, 2812-2821).
+
+    ``x`` ``[B, R, D]`` (row r at position ``positions[r]`` or ``pos0 + r``), ``cos`` / ``sin``
+    ``[P, D/2]`` fp32, half-split ("rotate_half") convention.  The rotated values are rounded once to
+    ``x.dtype`` and packed along D: bit-identical to ``_quant_nvfp4(rope(x).to(x.dtype))`` with the
+    rotation in fp32, without writing the rotated tensor.  Returns ``(uint8 [B,R,D/2],
+    float8_e4m3fn [B,R,D/16])``, directly usable as ``q_packs`` / ``k_packs``.
+    """
+    _lib.require_cuda(x, "x")
+    b, r, d = x.shape
+    assert x.stride(2) == 1, "rows must be contiguous along D"
+    assert cos.shape[-1] == d // 2 and sin.shape == cos.shape and cos.dtype == torch.float32
+    cos, sin = cos.contiguous(), sin.contiguous()
+    if positions is not None:
+        positions = positions.to(device=x.device, dtype=torch.int32).contiguous()
+        assert positions.numel() == r
+    nib = torch.empty(b, r, d // 2, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(b, r, d // 16, dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.lib().nvfp4_rope_pack(
+        x.data_ptr(), _lib.dtype_code(x.dtype), b, r, d, x.stride(0), x.stride(1), cos.data_ptr(), sin.data_ptr(),
+        positions.data_ptr() if positions is not None else None, int(pos0), nib.data_ptr(), nib.stride(0),
+        nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1), _lib.stream_ptr(x.device)), "nvfp4_rope_pack")
+    return nib, sc.view(torch.float8_e4m3fn)
+
+
 def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None):
     """Both layouts of ``x`` [B, S, D]: along D and along S (padded to ``s_pad``).
 

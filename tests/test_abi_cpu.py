@@ -38,9 +38,13 @@ def test_argument_validation_returns_error_text():
     rc = L.nvfp4_pack(None, 0, 1, 1, 24, 24, 0, 0, 1, None, 0, 0, None, 0, 0, None)
     assert rc < 0 and b"multiple of 16" in L.nvfp4_last_error()
     ns, sk, wb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_size_t()
+    # fixed splits: few units, long cache
+    assert L.nvfp4_decode_plan(131072, 4, 128, 148, ctypes.byref(ns), ctypes.byref(sk), ctypes.byref(wb)) == 0
+    assert ns.value >= 1 and sk.value % 128 == 0 and ns.value * sk.value >= 131072
+    assert wb.value == 4 * ns.value * (16 * 128 + 32) * 4
+    # many units: the balanced decomposition (nsplit = 0), two partial slots per CTA
     assert L.nvfp4_decode_plan(32768, 128, 128, 148, ctypes.byref(ns), ctypes.byref(sk), ctypes.byref(wb)) == 0
-    assert ns.value >= 1 and sk.value % 128 == 0 and ns.value * sk.value >= 32768
-    assert wb.value == 128 * ns.value * (16 * 128 + 32) * 4
+    assert ns.value == 0 and sk.value == 0 and wb.value == 148 * 2 * (16 * 128 + 32) * 4
     assert L.nvfp4_decode_plan(0, 1, 128, 148, None, None, None) < 0
     assert L.nvfp4_decode_plan(10, 1, 64, 148, None, None, None) < 0
 

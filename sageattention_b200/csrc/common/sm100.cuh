@@ -169,6 +169,13 @@ __device__ __forceinline__ void cp_async_4(uint32_t saddr, const void* gptr, uin
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(saddr), "l"(gptr), "r"(src_bytes)
                : "memory");
 }
+// The same with a hint that L2 should fetch the whole 128-byte line: for scattered small reads
+// whose neighbours in the line are wanted a few tiles later (strided scale bytes).
+__device__ __forceinline__ void cp_async_4_l2line(uint32_t saddr, const void* gptr, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global.L2::128B [%0], [%1], 4, %2;" ::"r"(saddr), "l"(gptr),
+               "r"(src_bytes)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -106,7 +106,8 @@ struct DecodeParams {
 template <int D, typename TQ, int NQ>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-              const __grid_constant__ CUtensorMap tm_vpf, const DecodeParams p) {
+              const __grid_constant__ CUtensorMap tm_vpf, const __grid_constant__ CUtensorMap tm_vpf4,
+              const DecodeParams p) {
   using C = DecodeCfg<D>;
   constexpr int ST = (NQ == 16 && C::STMAX > 2) ? 2 : C::STMAX;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -225,25 +226,32 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           // long bursts.  The pull is spread over the tiles of the block before it (8 strips per
           // tile): a whole block at once, from every CTA in step, stalls the demand loads behind it.
           const int j = t - t0;
+          // 8 strips (rows rows8 .. rows8+7 of every 128-row piece) of the block of <= 16 tiles that
+          // starts at tile tb and must not reach past tile te: 1 KB boxes for whole blocks, 256-byte
+          // boxes for a clipped tail, so nothing beyond the work item is read from DRAM
+          auto pull = [&](int un, int tb, int te, int rows8) {
+            const int nt = min(16, te - tb);
+            if (nt <= 0) return;
+#pragma unroll
+            for (int mt = 0; mt < C::MT; ++mt) {
+              if (nt == 16) {
+                tma_prefetch_3d(&tm_vpf, tb * 16, mt * 128 + rows8, un);
+              } else {
+                for (int q4 = 0; q4 * 4 < nt; ++q4) tma_prefetch_3d(&tm_vpf4, (tb + q4 * 4) * 16, mt * 128 + rows8, un);
+              }
+            }
+          };
           if (j == 0 && (wi == 0 || t1 - t0 < 16)) {
 #pragma unroll 1
-            for (int r = 0; r < 16; ++r)
-#pragma unroll
-              for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, t0 * 16, mt * 128 + r * 8, unit);
+            for (int r = 0; r < 16; ++r) pull(unit, t0, t1, r * 8);
           }
-          {
-            const int nb = t0 + ((j >> 4) + 1) * 16;      // first tile of the next block
-            if (nb < t1)
-#pragma unroll
-              for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, nb * 16, mt * 128 + (j & 15) * 8, unit);
-          }
+          pull(unit, t0 + ((j >> 4) + 1) * 16, t1, (j & 15) * 8);      // the next block of this item
           // the first block of this CTA's NEXT work item, a whole item ahead: its first tiles would
           // otherwise be 128 scattered 64-byte first touches each, ~15k clocks of DRAM latency
           if (j < 16 && wi + 1 < my_items) {
             int unit_n, t0n, t1n;
             item_at(wi + 1, unit_n, t0n, t1n);
-#pragma unroll
-            for (int mt = 0; mt < C::MT; ++mt) tma_prefetch_3d(&tm_vpf, t0n * 16, mt * 128 + j * 8, unit_n);
+            pull(unit_n, t0n, t1n, j * 8);
           }
           const int s = it % C::NSTAGE;
           if (it >= (uint32_t)C::NSTAGE) mbar_spin_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 1);
@@ -305,8 +313,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const int dr = lane + 32 * r8;
           const int mt = dr >> 7, r = dr & 127;
           const uint8_t* g = vsrc + (int64_t)dr * p.vsc_row + (int64_t)t * 8;
-          cp_async_4(st + C::KSF_BYTES + (mt * 2 + 0) * 512 + sf_atom_offset(r, 0), g, 4u);
-          cp_async_4(st + C::KSF_BYTES + (mt * 2 + 1) * 512 + sf_atom_offset(r, 0), g + 4, 4u);
+          cp_async_4_l2line(st + C::KSF_BYTES + (mt * 2 + 0) * 512 + sf_atom_offset(r, 0), g, 4u);
+          cp_async_4_l2line(st + C::KSF_BYTES + (mt * 2 + 1) * 512 + sf_atom_offset(r, 0), g + 4, 4u);
         }
         cp_async_commit();
         if (it + 1 - published > (uint32_t)kLag) {
@@ -784,6 +792,7 @@ inline void decode_balanced_geometry(int64_t zhk, int64_t ntiles, int sm_count, 
 
 template <int D, typename TQ>
 int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_vpf,
+                  const CUtensorMap& tm_vpf4,
                   const DecodeParams& p,
                   int64_t zhk, void* out, float* lse, int sm_count, cudaStream_t st) {
   using C = DecodeCfg<D>;
@@ -796,7 +805,7 @@ int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtens
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_decode: smem attribute: %s", cudaGetErrorString(e));
-    kern<<<grid, kDecodeThreads, C::SMEM_BYTES, st>>>(tm_k, tm_v, tm_vpf, p);
+    kern<<<grid, kDecodeThreads, C::SMEM_BYTES, st>>>(tm_k, tm_v, tm_vpf, tm_vpf4, p);
     return launch_result("nvfp4_decode");
   };
   int rc;
@@ -898,7 +907,7 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
                 "nvfp4_decode: V^T rows shorter than the padded key axis");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  CUtensorMap tm_k, tm_v, tm_vpf;
+  CUtensorMap tm_k, tm_v, tm_vpf, tm_vpf4;
   int rc = make_tmap_u8_3d_sw64(&tm_k, knv, (uint64_t)d / 2, (uint64_t)s_kv, (uint64_t)zhk,
                                 (uint64_t)d / 2, (uint64_t)knv_unit, 128, "nvfp4_decode(K)");
   if (rc) return rc;
@@ -910,6 +919,11 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
                                  (uint64_t)vnv_row, (uint64_t)vnv_unit,
                                  (uint32_t)std::min<uint64_t>(256, (uint64_t)s_pad / 8), 8,
                                  "nvfp4_decode(V prefetch)");
+  if (rc) return rc;
+  rc = make_tmap_u32_3d_prefetch(&tm_vpf4, vnv, (uint64_t)s_pad / 2, (uint64_t)d, (uint64_t)zhk,
+                                 (uint64_t)vnv_row, (uint64_t)vnv_unit,
+                                 (uint32_t)std::min<uint64_t>(64, (uint64_t)s_pad / 8), 8,
+                                 "nvfp4_decode(V prefetch, tail)");
   if (rc) return rc;
 
   DecodeParams p;
@@ -933,7 +947,7 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   p.ws_l = p.ws_m + slots * 16;
   p.status = status;
 
-#define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, tm_vpf, p, zhk, out, lse, sm_count, st)
+#define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, tm_vpf, tm_vpf4, p, zhk, out, lse, sm_count, st)
   if (d == 128) {
     switch (q_dtype) {
       case NVFP4_DT_BF16: NVFP4_DECODE(128, __nv_bfloat16);

@@ -185,9 +185,10 @@ def secondary_metrics(torch, nv, peaks):
                 "step_us": ms * 1e3, "append_us": ms_app * 1e3,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": gbs / peaks["hbm_gbs"],
-                             # ncu, S=8192 case: dram read 151.22 MB for 150.99 MB of packs (1.0015x);
-                             # traffic grows in proportion to the keys streamed
-                             "traffic": bytes_step * 1.0015 + 18.2e6, "algorithmic_bytes": bytes_step}})
+                             # ncu, S=8192 case (balanced decomposition): dram read 163.2 MB for 150.99 MB
+                             # of packs (1.081x: L2 prefetch granularity at segment ends, cold single
+                             # launch), 3.2 MB written (partials + output); reads grow with the keys streamed
+                             "traffic": bytes_step * 1.081 + 3.2e6, "algorithmic_bytes": bytes_step}})
     del cache, packed
     torch.cuda.empty_cache()
     x = torch.randn(Z * H, S, D, device=dev, dtype=torch.bfloat16)

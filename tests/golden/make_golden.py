@@ -20,7 +20,7 @@ Everything else -- scale computation, clamping, e4m3 casts, divisions, tile walk
 softmax, in-kernel P packing, split-K combine, the KV-cache state machine -- is the reference's
 code.  Run from the repository root, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to a checkout of the reference repository>
 
 It writes ``tests/golden/*.npz``.  Inputs are bf16-representable values stored as raw bf16 bit
 patterns (uint16) so the fixtures are exact; attention inputs are handed to the reference as
@@ -249,4 +249,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference repository>")
+    main(sys.argv[1])

@@ -394,10 +394,10 @@ def run_gpu(args):
                          "kernel": "fwd_kernel<128,bf16>", "kernel_ms": ms_kernel,
                          "peak_source": f"4 x bf16_tflops_sustained ({peak_src} MEASURED_PEAKS.json); "
                                         "no FP4 GEMM figure is in that file",
-                         "co_bound": {"what": "MUFU ex2 + cvt.e2m1x2 share a 16 lane/clk/SM pipe: 1.5 slots "
-                                              "per score element",
+                         "co_bound": {"what": "one MUFU ex2 per score element at 16 lanes/clk/SM (the e2m1x2 "
+                                              "converts run on a separate pipe)",
                                       "elements": exps,
-                                      "min_ms_at_1.9GHz": exps * 1.5 / (148 * 16 * 1.9e9) * 1e3}},
+                                      "min_ms_at_1.965GHz": exps / (148 * 16 * 1.965e9) * 1e3}},
             "e2e": {"value": world * FLOPS_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": int((qh.numel() + kh.numel() + vh.numel()) * 2),

@@ -324,7 +324,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   } else if (C::NSBUF == 2) {
     // ------------------------------------------------------------------ softmax / epilogue (D = 128)
     // Two groups of eight warps alternate key tiles (group g owns tiles g, g+2, ...), so while
-    // one group sits in its XU-bound exp/pack phase the other does its TMEM loads, row maxima,
+    // one group sits in its exp/pack phase the other does its TMEM loads, row maxima,
     // barrier and O rescale: the phases of consecutive tiles overlap instead of adding up.
     // Within a group two threads share a query row (64 key columns each, handled as two
     // 32-column chunks to stay inside the register budget of a 640-thread CTA).  The running

@@ -177,12 +177,29 @@ def secondary_metrics(torch, nv, peaks):
         step()
     ms = ev_ms(torch, step, 50)
     gbs = bytes_step / (ms * 1e-3) / 1e9
+    # the same step replayed from a CUDA graph (no launch overhead between its kernels)
+    graph_us = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+        for _ in range(3):
+            cg.replay()
+        graph_us = ev_ms(torch, cg.replay, 50) * 1e3
+        del cg
+    except Exception as exc:   # reported, not fatal: the eager figure above is the metric
+        graph_us = f"capture failed: {type(exc).__name__}"
     app = lambda: (cache.append(kn, kn), setattr(cache, "length", s), setattr(cache, "partial_len", 0))
     for _ in range(3):
         app()
     ms_app = ev_ms(torch, app, 50)
     out.append({"name": "decode_step Z16 H32 Hk8 D128 S32768 (BASELINE config 4)",
-                "step_us": ms * 1e3, "append_us": ms_app * 1e3,
+                "step_us": ms * 1e3, "step_us_cuda_graph": graph_us, "append_us": ms_app * 1e3,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": gbs / peaks["hbm_gbs"],
                              # ncu, S=8192 case (balanced decomposition): dram read 163.2 MB for 150.99 MB

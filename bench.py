@@ -206,7 +206,31 @@ def secondary_metrics(torch, nv, peaks):
                              # of packs (1.081x: L2 prefetch granularity at segment ends, cold single
                              # launch), 3.2 MB written (partials + output); reads grow with the keys streamed
                              "traffic": bytes_step * 1.081 + 3.2e6, "algorithmic_bytes": bytes_step}})
+    # config 4 as stated: 64 steps of (append one token, decode one query) on the live cache
+    def serve_step():
+        cache.append(kn, kn)
+        return nv.nvfp4_flash_decode_prequant(q, cache.get_packed(), d ** -0.5, h // hk)
+    cache.length, cache.partial_len = s, 0
+    serve_step()
+    cache.length, cache.partial_len = s, 0
+    torch.cuda.synchronize()
+    ms_serve = ev_ms(torch, serve_step, 64)
+    out[-1]["append_plus_decode_us_over_64_steps"] = ms_serve * 1e3
     del cache, packed
+    torch.cuda.empty_cache()
+    # the same with a 512-token bf16 recent window and hybrid_decode (FP4 prefix + bf16 window, exact LSE merge)
+    hc = nv.NVFP4KVCache(z, hk, d, s + 128, dev, recent_window=512)
+    kk = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
+    hc.prefill(kk, kk)
+    del kk
+    hyb = lambda: hc.hybrid_decode(q, d ** -0.5, h // hk)
+    for _ in range(3):
+        hyb()
+    ms_h = ev_ms(torch, hyb, 30)
+    window_bytes = 2 * z * hk * 512 * d * 2
+    out[-1]["hybrid_decode_us"] = ms_h * 1e3
+    out[-1]["hybrid_decode_gbs"] = (bytes_step + window_bytes) / (ms_h * 1e-3) / 1e9
+    del hc
     torch.cuda.empty_cache()
     x = torch.randn(Z * H, S, D, device=dev, dtype=torch.bfloat16)
     pk = lambda: nv._quant_nvfp4(x)

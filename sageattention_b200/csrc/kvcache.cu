@@ -61,58 +61,124 @@ __global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restric
   }
 }
 
-// Exact attention of one query row per head over `count` ring-resident keys.
-// One block (128 threads) per (z, h); scores live in shared memory.
+// Exact attention of the G query rows of one kv head over `count` ring-resident keys.
+// One block (512 threads) per (z, kv head): every K and V row of the window is read once and
+// serves all G heads; scores live in shared memory ([G][count] floats).
 template <typename T>
-__global__ void __launch_bounds__(128) window_attention_kernel(
+__global__ void __launch_bounds__(512) window_attention_kernel(
     const T* __restrict__ q, int64_t s_qz, int64_t s_qh, const T* __restrict__ rk,
     const T* __restrict__ rv, int hk, int g, int d, int64_t ring_cap, int64_t first_pos,
     int count, float scaling, float* __restrict__ out, float* __restrict__ lse) {
   extern __shared__ float sm[];
-  float* qs = sm;           // d
-  float* sc = sm + d;       // count
-  __shared__ float red[4];
-  const int h_all = hk * g;
-  const int zi = blockIdx.x / h_all, hi = blockIdx.x % h_all;
-  const int kh = hi / g;
+  float* qs = sm;                 // [g][d]
+  float* sc = sm + g * d;         // [g][count]
+  float* part = sc + g * count;   // [4][g][d] partial outputs of the four key quarters
+  __shared__ float row_m[16], row_l[16];
+  const int zi = blockIdx.x / hk, kh = blockIdx.x % hk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const T* qp = q + zi * s_qz + hi * s_qh;
-  for (int i = tid; i < d; i += 128) qs[i] = to_f32<T>(qp[i]);
+  for (int i = tid; i < g * d; i += 512) {
+    const int gq = i / d, e = i - gq * d;
+    qs[i] = to_f32<T>(q[zi * s_qz + (int64_t)(kh * g + gq) * s_qh + e]);
+  }
   __syncthreads();
   const T* kb = rk + ((int64_t)(zi * hk + kh) * ring_cap) * d;
   const T* vb = rv + ((int64_t)(zi * hk + kh) * ring_cap) * d;
-  float mloc = -INFINITY;
-  for (int j = warp; j < count; j += 4) {
-    const T* kr = kb + ((first_pos + j) % ring_cap) * d;
-    float s = 0.0f;
-    for (int i = lane; i < d; i += 32) s += qs[i] * to_f32<T>(kr[i]);
+  const int cap = (int)ring_cap, first = (int)(first_pos % ring_cap);   // slot of key j: first + j, wrapped once
+  auto slot = [&](int j) { const int sl = first + j; return sl >= cap ? sl - cap : sl; };
+  // scores: a warp takes four keys at a time (four independent row loads in flight), a lane owns
+  // four consecutive elements of every 128-element piece of the row; all heads per key
+  for (int j0 = warp * 4; j0 < count; j0 += 64) {
+    float acc[4][16];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    s *= scaling;
-    if (lane == 0) sc[j] = s;
-    mloc = fmaxf(mloc, s);
-  }
-  if (lane == 0) red[warp] = mloc;
-  __syncthreads();
-  const float m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  __syncthreads();
-  float lsum = 0.0f;
-  for (int j = tid; j < count; j += 128) {
-    const float e = expf(sc[j] - m);
-    sc[j] = e;
-    lsum += e;
-  }
+    for (int u = 0; u < 4; ++u)
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-  if (lane == 0) red[warp] = lsum;
-  __syncthreads();
-  const float l = red[0] + red[1] + red[2] + red[3];
-  for (int i = tid; i < d; i += 128) {
-    float acc = 0.0f;
-    for (int j = 0; j < count; ++j) acc += sc[j] * to_f32<T>(vb[((first_pos + j) % ring_cap) * d + i]);
-    out[(int64_t)blockIdx.x * d + i] = acc / l;
+      for (int gq = 0; gq < 16; ++gq) acc[u][gq] = 0.0f;
+    for (int c = 0; c < d; c += 128) {
+      float kv[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = min(j0 + u, count - 1);
+        const T* kr = kb + (int64_t)slot(j) * d + c + lane * 4;
+        if constexpr (sizeof(T) == 2) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(kr);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) kv[u][x] = to_f32<T>(e[x]);
+        } else {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) kv[u][x] = to_f32<T>(kr[x]);
+        }
+      }
+#pragma unroll
+      for (int gq = 0; gq < 16; ++gq)
+        if (gq < g) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + gq * d + c + lane * 4);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            acc[u][gq] += q4.x * kv[u][0] + q4.y * kv[u][1] + q4.z * kv[u][2] + q4.w * kv[u][3];
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int gq = 0; gq < 16; ++gq)
+        if (gq < g) {
+          float v = acc[u][gq];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0 && j0 + u < count) sc[gq * count + j0 + u] = v * scaling;
+        }
   }
-  if (tid == 0) lse[blockIdx.x] = m + logf(l);
+  __syncthreads();
+  // softmax statistics: one warp per head
+  for (int gq = warp; gq < g; gq += 16) {
+    float m = -INFINITY;
+    for (int j = lane; j < count; j += 32) m = fmaxf(m, sc[gq * count + j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.0f;
+    for (int j = lane; j < count; j += 32) {
+      const float e = expf(sc[gq * count + j] - m);
+      sc[gq * count + j] = e;
+      l += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) { row_m[gq] = m; row_l[gq] = l; }
+  }
+  __syncthreads();
+  // P.V: the block's four quarters of 128 threads split the keys, a thread owns output columns
+  const int half = tid >> 7, t = tid & 127;
+  const int per = (count + 3) / 4;
+  const int j0 = min(count, half * per), j1 = min(count, j0 + per);
+  for (int i = t; i < d; i += 128) {
+    float acc[16];
+#pragma unroll
+    for (int gq = 0; gq < 16; ++gq) acc[gq] = 0.0f;
+    for (int j = j0; j < j1; j += 4) {
+      float vv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        vv[u] = (j + u < j1) ? to_f32<T>(vb[(int64_t)slot(j + u) * d + i]) : 0.0f;
+#pragma unroll
+      for (int gq = 0; gq < 16; ++gq)
+        if (gq < g) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            acc[gq] = fmaf((j + u < j1) ? sc[gq * count + j + u] : 0.0f, vv[u], acc[gq]);
+        }
+    }
+#pragma unroll
+    for (int gq = 0; gq < 16; ++gq)
+      if (gq < g) part[(half * g + gq) * d + i] = acc[gq];
+  }
+  __syncthreads();
+  for (int i = tid; i < g * d; i += 512) {
+    const int gq = i / d;
+    out[((int64_t)(zi * hk + kh) * g) * d + i] =
+        (part[i] + part[g * d + i] + part[2 * g * d + i] + part[3 * g * d + i]) / row_l[gq];
+  }
+  if (tid < g) lse[(int64_t)(zi * hk + kh) * g + tid] = row_m[tid] + logf(row_l[tid]);
 }
 
 template <typename T>
@@ -182,12 +248,18 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
   NVFP4_REQUIRE(q && rk && rv && out && lse, "nvfp4_window_attention: null pointer");
   NVFP4_REQUIRE(count > 0 && count <= ring_cap, "nvfp4_window_attention: count must be in (0, ring_cap]");
   NVFP4_REQUIRE(z * hk * g < (1LL << 31), "nvfp4_window_attention: too many heads");
-  const size_t smem = (size_t)(d + count) * sizeof(float);
-  NVFP4_REQUIRE(smem <= 48 * 1024, "nvfp4_window_attention: window too long (%lld keys)", (long long)count);
+  const size_t smem = (size_t)(5 * g * d + g * count) * sizeof(float);
+  NVFP4_REQUIRE(g >= 1 && g <= 16, "nvfp4_window_attention: GQA group %d must be <= 16", g);
+  NVFP4_REQUIRE(smem <= 200 * 1024, "nvfp4_window_attention: window too long (%lld keys)", (long long)count);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned grid = (unsigned)(z * hk * g);
+  const unsigned grid = (unsigned)(z * hk);
 #define NVFP4_WIN(T)                                                                              \
-  window_attention_kernel<T><<<grid, 128, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh,       \
+  if (smem > 48 * 1024) {                                                                         \
+    cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T>,                              \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess) return fail((int)e, "nvfp4_window_attention: smem attribute: %s", cudaGetErrorString(e)); \
+  }                                                                                               \
+  window_attention_kernel<T><<<grid, 512, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh,       \
                                                       static_cast<const T*>(rk),                  \
                                                       static_cast<const T*>(rv), (int)hk, g, d,   \
                                                       ring_cap, first_pos, (int)count, scaling,   \

@@ -224,14 +224,16 @@ int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t
  * over the GQA group inside the kernel.  No atomics: results are run-to-run identical.
  *   qnv/qsc, knv/ksc   packs of Q [Z*H, s_q, .] and K [Z*Hk, s_kv, .] along D (as for nvfp4_fwd)
  *   q_bf16, do_bf16 [Z*H, s_q, D];  k_bf16, v_bf16 [Z*Hk, s_kv, D]      contiguous bf16
- *   lse, delta [Z*H, s_q] fp32;  seq_start / seq_end [s] int32 (packed varlen) or both NULL
+ *   lse, delta [Z*H, s_q] fp32;  key_bias [Z, s_kv] fp32 additive key bias of the forward or NULL
+ *   (flash.py:2098-2100; -inf masks a key);  seq_start / seq_end [s] int32 (packed varlen) or both NULL
  *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
  * flags: NVFP4_FWD_CAUSAL.  D is 128 or 256 (256: two 128-wide output halves per tile).
  */
 int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
                  const void* q_bf16, const void* k_bf16, const void* v_bf16, const void* do_bf16,
-                 const float* lse, const float* delta, const int32_t* seq_start,
-                 const int32_t* seq_end, void* dq, void* dk, void* dv, int grad_dtype, int64_t z,
+                 const float* lse, const float* delta, const float* key_bias,
+                 const int32_t* seq_start, const int32_t* seq_end, void* dq, void* dk, void* dv,
+                 int grad_dtype, int64_t z,
                  int64_t h, int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
                  int* status, nvfp4_stream_t stream);
 

@@ -497,7 +497,7 @@ class KVCacheOracle:
 
 
 # --------------------------------------------------------------------------- exact attention + grads
-def attention_exact(q, k, v, scaling, causal=False, g=1, cu_seqlens=None):
+def attention_exact(q, k, v, scaling, causal=False, g=1, cu_seqlens=None, key_pad_bias=None):
     """Plain fp32 attention on unquantised inputs with its gradients' building blocks.
 
     Returns (out, p) with p the softmax probabilities [Z,H,Sq,Skv]; used to derive reference
@@ -513,6 +513,8 @@ def attention_exact(q, k, v, scaling, causal=False, g=1, cu_seqlens=None):
     vis = _visible(sq, skv, causal, sid, sid)
     kk = np.repeat(k, g, axis=1); vv = np.repeat(v, g, axis=1)
     s = np.matmul(q, np.swapaxes(kk, -1, -2)) * scaling
+    if key_pad_bias is not None:       # [Z, Skv] additive, after the scaling (flash.py:2098-2100)
+        s = s + np.asarray(key_pad_bias, np.float64)[:, None, None, :]
     s = np.where(vis, s, -np.inf)
     m = s.max(axis=-1, keepdims=True)
     p = np.exp(s - m)
@@ -520,13 +522,13 @@ def attention_exact(q, k, v, scaling, causal=False, g=1, cu_seqlens=None):
     return np.matmul(p, vv), p
 
 
-def attention_grads(q, k, v, do, scaling, causal=False, g=1, cu_seqlens=None):
+def attention_grads(q, k, v, do, scaling, causal=False, g=1, cu_seqlens=None, key_pad_bias=None):
     """Analytic dQ, dK, dV of exact attention (fp64), GQA-reduced to [Z,Hk,Skv,D]."""
     q = np.asarray(q, np.float64); k = np.asarray(k, np.float64); v = np.asarray(v, np.float64)
     do = np.asarray(do, np.float64)
     z, h, sq, d = q.shape
     hk, skv = k.shape[1], k.shape[2]
-    out, p = attention_exact(q, k, v, scaling, causal, g, cu_seqlens)
+    out, p = attention_exact(q, k, v, scaling, causal, g, cu_seqlens, key_pad_bias)
     kk = np.repeat(k, g, axis=1); vv = np.repeat(v, g, axis=1)
     dv_h = np.matmul(np.swapaxes(p, -1, -2), do)
     dp = np.matmul(do, np.swapaxes(vv, -1, -2))

@@ -47,7 +47,7 @@ SIGNATURES = {
                                 c_void_p]),
     "nvfp4_bwd_prep": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
-    "nvfp4_bwd_hp": (c_int, [c_void_p] * 15 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+    "nvfp4_bwd_hp": (c_int, [c_void_p] * 16 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                              c_int, c_float, c_int, c_void_p, c_void_p]),
     "nvfp4_fwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "nvfp4_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,

@@ -170,6 +170,7 @@ struct BwdParams {
   const uint8_t* ksc;   // [ZHk, Skv, 8]
   const float* lse;     // [ZH, Sq] natural log
   const float* delta;   // [ZH, Sq]
+  const float* bias;    // [Z, Skv] additive key bias (after the scaling) or null
   const int32_t* seq_start;  // [S] or null (varlen)
   const int32_t* seq_end;    // [S] or null
   void* dq;             // [ZH, Sq, D]
@@ -211,29 +212,27 @@ __device__ __forceinline__ void zero_row(TG* dst, int n) {
   for (int e = 0; e < n; ++e) dst[e] = from_f32<TG>(0.0f);
 }
 
-// P for 32 columns of one accumulator row.  Per-column statistics (the dK/dV kernel): `nl` points
-// at the raw lse of the 32 columns in shared memory; per-row (the dQ kernel): `nl_row` is
-// -lse*log2e of the row.  Columns outside
-// [lo, hi) relative to the chunk's first column are masked when `masked`.
-template <bool kPerColumn>
+// P for 32 columns of one accumulator row: exp2(s * c2 + offsets).  Per-column statistics (the
+// dK/dV kernel): `nl` points at the raw lse of the 32 columns in shared memory and `nl_row` is a
+// per-thread offset (the key's bias * log2e, or 0).  Per-row (the dQ kernel): `nl_row` is
+// -lse*log2e of the row and `nl`, when not null, points at the raw key bias of the 32 columns.
+// Columns outside [lo, hi) relative to the chunk's first column are masked when `masked`.
+template <bool kPerColumn, bool kColumnBias = false>
 __device__ __forceinline__ void prob_chunk(const uint32_t (&sr)[32], float (&pf)[32], float c2, const float* nl,
                                            float nl_row, bool masked, int lo, int hi) {
   const float2 c22 = make_float2(c2, c2);
-  const float2 ml2 = make_float2(-kBwdLog2e, -kBwdLog2e);
+  const float2 row2 = make_float2(nl_row, nl_row);
+  const float2 ml2 = make_float2(kPerColumn ? -kBwdLog2e : kBwdLog2e, kPerColumn ? -kBwdLog2e : kBwdLog2e);
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
-    float4 n4;
-    if constexpr (kPerColumn) {
+    float2 n01 = row2, n23 = row2;
+    if constexpr (kPerColumn || kColumnBias) {
       const float4 l4 = *reinterpret_cast<const float4*>(nl + e);
-      const float2 a = __fmul2_rn(make_float2(l4.x, l4.y), ml2), b = __fmul2_rn(make_float2(l4.z, l4.w), ml2);
-      n4 = make_float4(a.x, a.y, b.x, b.y);
-    } else {
-      n4 = make_float4(nl_row, nl_row, nl_row, nl_row);
+      n01 = __ffma2_rn(make_float2(l4.x, l4.y), ml2, row2);
+      n23 = __ffma2_rn(make_float2(l4.z, l4.w), ml2, row2);
     }
-    const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c22,
-                                 make_float2(n4.x, n4.y));
-    const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])), c22,
-                                 make_float2(n4.z, n4.w));
+    const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), c22, n01);
+    const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])), c22, n23);
     pf[e] = ex2_bwd(t0.x);
     pf[e + 1] = ex2_bwd(t0.y);
     pf[e + 2] = ex2_bwd(t1.x);
@@ -542,6 +541,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
     const int key = n0 + row;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const float c2 = p.scaling * kBwdLog2e;
+    // additive bias of this key, in the exponent's base-2 units (-inf masks the key)
+    const float bk2 = (p.bias != nullptr && key < p.s_kv) ? p.bias[(int64_t)zi * p.s_kv + key] * kBwdLog2e : 0.0f;
     // visible queries of this key: [ql, qh)
     int ql = 0, qh = 0;
     if (key < p.s_kv) {
@@ -584,7 +585,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       {
         float pf[32];
         uint32_t w[16];
-        prob_chunk<true>(sr, pf, c2, aux, 0.0f, masked, ql - q0, qh - q0);
+        prob_chunk<true>(sr, pf, c2, aux, bk2, masked, ql - q0, qh - q0);
 #pragma unroll
         for (int e = 0; e < 16; ++e) w[e] = pack_bf16x2(pf[2 * e], pf[2 * e + 1]);
         tmem_st16(slot, w);
@@ -642,9 +643,9 @@ struct DqSmem {
   static constexpr int QSF = KB * 512;
   // per stage: V bf16 [64 keys x D] and the 128-wide half of K bf16 (8 KB sub-tiles), K pack
   // [64 keys x D/2 B], K scale atoms
-  static constexpr int V = DS * 8192, K = 16384, KP = KSUB * 4096, KSF = KB * 512;
-  static constexpr int O_V = 0, O_K = V, O_KP = V + K, O_KSF = O_KP + KP;
-  static constexpr int STAGE = V + K + KP + KSF;
+  static constexpr int V = DS * 8192, K = 16384, KP = KSUB * 4096, KSF = KB * 512, AUX = 1024;
+  static constexpr int O_V = 0, O_K = V, O_KP = V + K, O_KSF = O_KP + KP, O_AUX = O_KSF + KSF;   // AUX: key bias [64]
+  static constexpr int STAGE = V + K + KP + KSF + AUX;
   static constexpr int NSTAGE = D == 128 ? 4 : 2;
   static constexpr int TOTAL = DO + QP + NSTAGE * STAGE + QSF + 1024;
   static_assert(STAGE % 1024 == 0 && (DO + QP) % 1024 == 0, "128-byte-swizzled tiles need 1 KB alignment");
@@ -776,6 +777,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
           const uint8_t* g = ksrc + (int64_t)(ok ? key : 0) * (D / 16);
 #pragma unroll
           for (int c = 0; c < L::KB; ++c) cp_async_4(ksf + c * 512 + sf_atom_offset(r, 0), g + 4 * c, ok ? 4u : 0u);
+          if (p.bias != nullptr)
+            cp_async_4(smem_u32(s_stage + s * L::STAGE + L::O_AUX) + r * 4,
+                       p.bias + (int64_t)zi * p.s_kv + (ok ? key : 0), ok ? 4u : 0u);
         }
         cp_async_commit();
         cp_async_wait<0>();
@@ -870,6 +874,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       const int key0 = (j_lo + st) * 64 + grp * 32;
       const uint32_t slot = tmem + lane_addr + T_S + b * 64;
       const bool masked = !__all_sync(0xffffffffu, key0 >= kl && key0 + 32 <= kh);
+      const float* kbias = nullptr;
+      if (p.bias != nullptr) {      // the stage's key bias (landed with the scale atoms)
+        const int sg = st % L::NSTAGE;
+        mbar_wait(&full_sf[sg], (st / L::NSTAGE) & 1, &err, 10);
+        kbias = reinterpret_cast<const float*>(s_stage + sg * L::STAGE + L::O_AUX) + grp * 32;
+      }
       mbar_wait(&s_full[b], k2 & 1, &err, 11);
       mbar_wait(&dp_full, st & 1, &err, 13);
       tc_fence_after();
@@ -883,7 +893,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
       {
         float pf[32];
         uint32_t w[16];
-        prob_chunk<false>(sr, pf, c2, nullptr, nl, masked, kl - key0, kh - key0);
+        if (kbias != nullptr) prob_chunk<false, true>(sr, pf, c2, kbias, nl, masked, kl - key0, kh - key0);
+        else prob_chunk<false, false>(sr, pf, c2, nullptr, nl, masked, kl - key0, kh - key0);
         ds_chunk<false>(pf, dr, w, nullptr, nd);
         // dS of keys [32g, 32g+32) replaces the first 16 of the S columns this thread just read
         tmem_st16(slot + grp * 32, w);
@@ -973,8 +984,8 @@ extern "C" int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sx
 extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv,
                             const uint8_t* ksc, const void* q_bf16, const void* k_bf16,
                             const void* v_bf16, const void* do_bf16, const float* lse,
-                            const float* delta, const int32_t* seq_start, const int32_t* seq_end,
-                            void* dq, void* dk, void* dv, int grad_dtype, int64_t z, int64_t h,
+                            const float* delta, const float* key_bias, const int32_t* seq_start,
+                            const int32_t* seq_end, void* dq, void* dk, void* dv, int grad_dtype, int64_t z, int64_t h,
                             int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
                             int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
@@ -1005,7 +1016,7 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
   if ((rc = make_tmap_bf16_3d_sw128(&t_q64, q_bf16, d, s_q, zh, hb, (uint64_t)s_q * hb, 64, "nvfp4_bwd_hp(Q64)"))) return rc;
   if ((rc = make_tmap_bf16_3d_sw128(&t_k64, k_bf16, d, s_kv, zhk, hb, (uint64_t)s_kv * hb, 64, "nvfp4_bwd_hp(K64)"))) return rc;
   BwdParams p;
-  p.qsc = qsc; p.ksc = ksc; p.lse = lse; p.delta = delta;
+  p.qsc = qsc; p.ksc = ksc; p.lse = lse; p.delta = delta; p.bias = key_bias;
   p.seq_start = seq_start; p.seq_end = seq_end;
   p.dq = dq; p.dk = dk; p.dv = dv;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk); p.s_q = (int)s_q; p.s_kv = (int)s_kv;

@@ -313,7 +313,7 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
         dv = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
         _lib.check(_lib.lib().nvfp4_bwd_hp(
             qs[0].data_ptr(), qs[1].data_ptr(), blk[2].data_ptr(), blk[3].data_ptr(), qs[2].data_ptr(),
-            blk[0].data_ptr(), blk[1].data_ptr(), qs[3].data_ptr(), qs[4].data_ptr(), qs[5].data_ptr(), None, None,
+            blk[0].data_ptr(), blk[1].data_ptr(), qs[3].data_ptr(), qs[4].data_ptr(), qs[5].data_ptr(), None, None, None,
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.DT_FP32, z, h, hk, sq, skv, d, float(scaling),
             1 if is_causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
         return dq, dk, dv

@@ -465,7 +465,7 @@ def _as_bf16_rows(x):
 
 
 def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
-                q_packs=None, k_packs=None):
+                q_packs=None, k_packs=None, key_pad_bias=None):
     """High-precision-grad-dots backward (stands in for flash.py:3459-3805).
 
     ``q`` ``[Z,H,Sq,D]``, ``k``/``v`` ``[Z,Hk,Skv,D]`` (v may be a strided view), ``out``/``dout`` in
@@ -495,9 +495,14 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     if varlen_arrays is not None:
         _, sst, sen = varlen_arrays
     lse = lse.contiguous()
+    bias = None
+    if key_pad_bias is not None:
+        bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
+        assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
     _lib.check(_lib.lib().nvfp4_bwd_hp(
         qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), qc.data_ptr(), kc.data_ptr(),
         vc.data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+        bias.data_ptr() if bias is not None else None,
         sst.data_ptr() if sst is not None else None, sen.data_ptr() if sen is not None else None,
         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, d,
         float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)),
@@ -506,7 +511,7 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
 
 
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
-             mode="fp4_rownorm", q_packs=None, k_packs=None, **_unused):
+             mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, **_unused):
     """Backward for the ``fp4_rownorm`` / ``fp8_rownorm`` / ``fp4_legacy`` modes (flash.py:3811-4265).
 
     This build runs them on the high-precision gradient GEMM kernels: the probabilities still come
@@ -514,7 +519,7 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     mode (gradient cosine >= 0.93 against exact attention) with margin.
     """
     return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout,
-                       q_packs=q_packs, k_packs=k_packs)
+                       q_packs=q_packs, k_packs=k_packs, key_pad_bias=key_pad_bias)
 
 
 def _gqa_reduce_cast_dkdv(dk_planes: torch.Tensor, dv_planes: torch.Tensor, z: int, hk: int, g: int,
@@ -556,22 +561,24 @@ class _NVFP4FlashAttn(torch.autograd.Function):
             key_pad_bias=key_pad_bias, return_lse=True, return_packs=True, out_layout=out_layout,
             q_packs=(qnv_in, qsc_in) if qnv_in is not None else None,
             k_packs=(knv_in, ksc_in) if knv_in is not None else None, _varlen_arrays=varlen)
-        ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3])
+        bias = key_pad_bias if key_pad_bias is not None else torch.empty(0, device=query.device)
+        ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3], bias)
         ctx.meta = (float(scaling), bool(causal), int(num_key_value_groups), varlen, out_layout,
                     backward_grad_dots, key_pad_bias is not None)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        query, key, value, out, lse, qnv, qsc, knv, ksc = ctx.saved_tensors
+        query, key, value, out, lse, qnv, qsc, knv, ksc, bias = ctx.saved_tensors
         scaling, causal, g, varlen, out_layout, mode, has_bias = ctx.meta
-        assert not has_bias, "key_pad_bias is forward-only (as in the reference backward)"
+        bias = bias if has_bias else None
         if mode == "bf16":
             dq, dk, dv = _run_bwd_hp(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
-                                     out_layout, q_packs=(qnv, qsc), k_packs=(knv, ksc))
+                                     out_layout, q_packs=(qnv, qsc), k_packs=(knv, ksc), key_pad_bias=bias)
         else:
             dq, dk, dv = _run_bwd(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
-                                  out_layout, mode=mode, q_packs=(qnv, qsc), k_packs=(knv, ksc))
+                                  out_layout, mode=mode, q_packs=(qnv, qsc), k_packs=(knv, ksc),
+                                  key_pad_bias=bias)
         return (dq, dk, dv) + (None,) * 23
 
 

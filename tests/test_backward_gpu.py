@@ -190,6 +190,34 @@ def test_backward_zshd_layout_and_modes():
         _grads(q, k, v, do, True, h // hk, mode="fp16")
 
 
+@pytest.mark.parametrize("d", [128, 256])
+def test_backward_with_key_pad_bias(d):
+    """The additive key bias of the forward (flash.py:2098-2100) enters the recompute of P in both
+    backward kernels; -inf entries mask their keys (zero dK / dV rows)."""
+    z, h, hk, sq, skv = 2, 4, 2, 200, 333
+    q, qn = seeded_bf16((z, h, sq, d), 81)
+    k, kn = seeded_bf16((z, hk, skv, d), 82)
+    v, vn = seeded_bf16((z, hk, skv, d), 83)
+    do, don = seeded_bf16((z, h, sq, d), 84)
+    gen = torch.Generator().manual_seed(85)
+    bias = torch.randn(z, skv, generator=gen) * 0.7
+    bias[0, skv - 9:] = float("-inf")
+    bias[1, 40:57] = float("-inf")
+    qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = _n().nvfp4_flash_attn_func(qq, kk, vv, d ** -0.5, causal=False, num_key_value_groups=h // hk,
+                                     key_pad_bias=bias.cuda(), backward_grad_dots="bf16")
+    out.backward(do)
+    assert _status() == 0
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, False, h // hk, key_pad_bias=bias.numpy())
+    for nm, a, b in (("dq", qq.grad, rq), ("dk", kk.grad, rk), ("dv", vv.grad, rv)):
+        a = a.float().cpu().numpy()
+        assert np.isfinite(a).all(), nm
+        assert cos(a, b) >= 0.985, (nm, cos(a, b))
+    dkn, dvn = kk.grad.float().cpu().numpy(), vv.grad.float().cpu().numpy()
+    assert np.abs(dkn[0, :, skv - 9:]).max() == 0.0 and np.abs(dvn[0, :, skv - 9:]).max() == 0.0
+    assert np.abs(dkn[1, :, 40:57]).max() == 0.0 and np.abs(dvn[1, :, 40:57]).max() == 0.0
+
+
 def test_backward_is_deterministic_and_linear_in_dout():
     """Two runs agree bit for bit (no atomics on the gradient path) and grads scale with dO."""
     z, h, hk, s, d = 1, 4, 1, 512, 128

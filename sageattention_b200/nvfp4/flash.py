@@ -550,11 +550,20 @@ class _NVFP4FlashAttn(torch.autograd.Function):
                 save_backward_packs, backward_p_dv_sr, backward_dot_dv_sr, backward_ds_dq_sr,
                 dkdv_scratch_bf16, backward_grad_dots, out_zshd, block_m, block_n, num_warps, num_stages,
                 seq_id, seq_start, seq_end, qnv_in, qsc_in, knv_in, ksc_in):
+        varlen = (seq_id, seq_start, seq_end) if seq_id is not None else None
+        if varlen is not None:
+            assert not save_backward_packs, "varlen (cu_seqlens) is incompatible with save_backward_packs"
+        # direct callers of the Function may pass None (AUTO on s_kv) or a raw mode
+        backward_grad_dots = _resolve_backward_grad_dots(backward_grad_dots, key.shape[2], save_backward_packs,
+                                                         num_key_value_groups)
+        if backward_grad_dots == "fp8_rownorm":
+            assert not save_backward_packs, (
+                "backward_grad_dots='fp8_rownorm' is incompatible with the saved forward FP4 "
+                "transposed packs (save_backward_packs)")
         if qnv_in is not None or knv_in is not None:
             assert not save_backward_packs, (
                 "q_packs/k_packs are incompatible with save_backward_packs "
                 "(the saved pack set must come from the same fused HP read)")
-        varlen = (seq_id, seq_start, seq_end) if seq_id is not None else None
         out_layout = "zshd" if out_zshd else "zhsd"
         out, lse, packs = nvfp4_flash_attention(
             query, key, value, scaling, causal=causal, num_key_value_groups=num_key_value_groups,
@@ -596,32 +605,34 @@ def nvfp4_flash_attn_func(query, key, value, scaling, causal=False, num_key_valu
     spelling of "bf16" (not both).  The stochastic-rounding knobs and tile hints are accepted; the
     B200 backward always computes its gradient GEMMs in bf16 (see ``_run_bwd``).
     """
+    z, h, s_q, d = query.shape
+    hk, s_kv = key.shape[1], key.shape[2]
+    assert h % hk == 0 and h // hk == num_key_value_groups, "H must equal Hk * num_key_value_groups"
+    assert d in (128, 256), "head dim must be 128 or 256"
     if out_layout not in ("zhsd", "zshd"):
         raise ValueError(f"out_layout must be 'zhsd' or 'zshd', got {out_layout!r}")
-    assert not (backward_grad_dots is not None and backward_bf16_grad_dots is not None), (
-        "pass backward_grad_dots or the legacy backward_bf16_grad_dots, not both")
     if backward_bf16_grad_dots is not None:
+        assert backward_grad_dots is None, (
+            "pass either backward_grad_dots or the deprecated backward_bf16_grad_dots, not both")
         backward_grad_dots = "bf16" if backward_bf16_grad_dots else "fp4_legacy"
-    z, h, s_q, d = query.shape
-    s_kv = key.shape[2]
-    if cu_seqlens is not None:
-        assert z == 1, "cu_seqlens varlen requires Z must be 1 (one packed row)"
-        assert causal, "cu_seqlens varlen is block-diagonal causal: pass causal=True"
-        eff = s_q / max(1, cu_seqlens.numel() - 1)
-    else:
-        eff = s_kv
-    if save_backward_packs:
-        assert q_packs is None and k_packs is None, "save_backward_packs cannot be combined with external packs"
-    mode = _resolve_backward_grad_dots(backward_grad_dots, eff, save_backward_packs, num_key_value_groups)
-    if mode == "fp8_rownorm":
-        assert d in (128, 256), "fp8_rownorm needs head dim 128 or 256"
+    if backward_grad_dots is None:
+        # AUTO on the effective sequence: s_kv, or the mean sample length of a packed row
+        eff = s_kv if cu_seqlens is None else s_q / max(1, cu_seqlens.numel() - 1)
+        backward_grad_dots = _resolve_backward_grad_dots(None, eff, save_backward_packs, num_key_value_groups)
     seq_id = seq_start = seq_end = None
     if cu_seqlens is not None:
+        assert causal, "varlen (cu_seqlens) implements block-diagonal causal attention; pass causal=True"
+        assert z == 1, f"varlen packs all samples into one flattened row: Z must be 1, got Z={z}"
+        assert s_q == s_kv, f"varlen requires packed self-attention (Sq == Skv), got {s_q} vs {s_kv}"
         seq_id, seq_start, seq_end = _varlen_seq_arrays(cu_seqlens, s_q, query.device)
+    if q_packs is not None or k_packs is not None:
+        assert not save_backward_packs, (
+            "q_packs/k_packs are incompatible with save_backward_packs "
+            "(the saved pack set must come from the same fused HP read)")
     qnv_in, qsc_in = q_packs if q_packs is not None else (None, None)
     knv_in, ksc_in = k_packs if k_packs is not None else (None, None)
     return _NVFP4FlashAttn.apply(
         query, key, value, scaling, causal, num_key_value_groups, key_pad_bias, stochastic_rounding,
         save_backward_packs, backward_p_dv_stochastic_rounding, backward_dot_dv_stochastic_rounding,
-        backward_ds_dq_stochastic_rounding, dkdv_scratch_bf16, mode, out_layout == "zshd", block_m,
+        backward_ds_dq_stochastic_rounding, dkdv_scratch_bf16, backward_grad_dots, out_layout == "zshd", block_m,
         block_n, num_warps, num_stages, seq_id, seq_start, seq_end, qnv_in, qsc_in, knv_in, ksc_in)

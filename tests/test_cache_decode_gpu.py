@@ -229,3 +229,53 @@ def test_hybrid_decode_long_matches_oracle():
     assert _status() == 0
     ref = oc.hybrid_decode(qf, d ** -0.5, g)
     assert cos(out, ref) >= 0.999 and np.abs(out - ref).max() <= 2e-2
+
+
+def test_fp16_cache_cut_zero_hybrid_and_packed_prefix():
+    """fp16 operands (tests/test_nvfp4_kv_cache.py:501-524 of the reference), a sequence shorter
+    than the recent window (cut == 0: the whole answer comes from the unquantised window,
+    :339-364), and a 16-aligned packed prefix decoding like a one-shot pack of K/V[:cut] (:472-495)."""
+    n = _n()
+    z, hk, g, d, s = 1, 2, 4, 128, 200
+    gen = torch.Generator().manual_seed(9)
+    k = torch.randn(z, hk, s, d, generator=gen).to(torch.float16).cuda()
+    v = torch.randn(z, hk, s, d, generator=gen).to(torch.float16).cuda()
+    q = torch.randn(z, hk * g, 1, d, generator=gen).to(torch.float16).cuda()
+    c = n.NVFP4KVCache(z, hk, d, 256, "cuda", torch.float16)
+    c.prefill(k[:, :, :195], v[:, :, :195])
+    for t in range(195, s):
+        c.append(k[:, :, t:t + 1], v[:, :, t:t + 1])
+    out_c = n.nvfp4_flash_decode_prequant(q, c.get_packed(), d ** -0.5, g)
+    out_w = n.nvfp4_flash_decode_prequant(q, n.nvfp4_quant_kv_decode(k, v), d ** -0.5, g)
+    assert out_c.dtype == torch.float16
+    assert cos(out_c.float().cpu().numpy(), out_w.float().cpu().numpy()) > 0.9999   # same bytes on the valid region
+    sdpa = torch.nn.functional.scaled_dot_product_attention(
+        q.float(), k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1))
+    assert cos(out_c.float().cpu().numpy(), sdpa.cpu().numpy()) > 0.97
+
+    # cut == 0: pure unquantised-window path
+    z2, s2, win = 2, 40, 256
+    k2, _ = seeded_bf16((z2, hk, s2, d), 4)
+    v2, _ = seeded_bf16((z2, hk, s2, d), 5)
+    q2, _ = seeded_bf16((z2, hk * g, 1, d), 6)
+    ch = n.NVFP4KVCache(z2, hk, d, 512, "cuda", recent_window=win)
+    ch.prefill(k2[:, :, :35], v2[:, :, :35])
+    for t in range(35, s2):
+        ch.append(k2[:, :, t:t + 1], v2[:, :, t:t + 1])
+    oh = ch.hybrid_decode(q2, d ** -0.5, g)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q2.float(), k2.float().repeat_interleave(g, 1), v2.float().repeat_interleave(g, 1))
+    assert torch.isfinite(oh).all()
+    assert cos(oh.float().cpu().numpy(), ref.cpu().numpy()) > 0.999
+    assert ch.hybrid_bytes() > ch.fp4_bytes()
+
+    # packed prefix
+    s3, cut = 777, 512
+    k3, _ = seeded_bf16((z2, hk, s3, d), 7)
+    v3, _ = seeded_bf16((z2, hk, s3, d), 8)
+    c3 = n.NVFP4KVCache(z2, hk, d, 1024, "cuda")
+    c3.prefill(k3, v3)
+    a = n.nvfp4_flash_decode_prequant(q2, c3._packed_upto(cut), d ** -0.5, g)
+    b = n.nvfp4_flash_decode_prequant(q2, n.nvfp4_quant_kv_decode(k3[:, :, :cut], v3[:, :, :cut]), d ** -0.5, g)
+    assert cos(a.float().cpu().numpy(), b.float().cpu().numpy()) > 0.999
+    assert _status() == 0

@@ -291,13 +291,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const uint32_t idesc_pv = make_idesc_nvfp4(128, D);
       for (int i = 0; i < ntile; ++i) {
         const int s = i % C::NSTAGE, b = i % C::NSBUF;
-        mbar_spin_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
-        TRACE(3, i, 0);
         // the V tile and V scales of stage s landed before this tile's QK^T was issued, but this
-        // thread has to observe them itself
+        // thread has to observe them itself; it does so while P is still being written
         mbar_wait(&full_kv[s], (i / C::NSTAGE) & 1, &err, 15);
         mbar_wait(&full_sf[s], (i / C::NSTAGE) & 1, &err, 16);
+        mbar_spin_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
+        TRACE(3, i, 0);
         tc_fence_after();
+        TRACE(3, i, 2);
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
         const uint32_t sfp = tmem + C::T_SFP + (i & 1) * 8;
         const uint32_t sfv = tmem + C::T_SFV + (i & 1) * (2 * C::NT * 4);
@@ -308,6 +309,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int k = 0; k < 2 * C::NT; ++k)
           tmem_cp_32x128b_warpx4(sfv + k * 4,
                                  smem_u32(st + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + k * 512));
+        TRACE(3, i, 3);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint64_t ad = make_smem_desc(smem_u32(s_p + b * C::P_BYTES) + k * 32, 16, 512, 4);
@@ -315,6 +317,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           umma_nvfp4(tmem + C::T_O, ad, bd, idesc_pv, sfp + k * 4, sfv + k * C::NT * 4,
                      (i > 0 || k > 0) ? 1u : 0u);
         }
+        TRACE(3, i, 4);
         umma_commit(&pv_done[b]);
         umma_commit(&empty[s]);
         TRACE(3, i, 1);
@@ -373,49 +376,56 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
                                (p.bias != nullptr) || (p.seq_id != nullptr);
       const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
                            C::VSF_BYTES;
-      const float* aux_bias = reinterpret_cast<const float*>(aux) + half * 64;
-      const int32_t* aux_seq = reinterpret_cast<const int32_t*>(aux + 512) + half * 64;
-      // visible keys of this row inside the thread's 64 columns: [0, lim] (causal + tail)
-      const int lim = min(my_limit, p.s_kv - 1) - n0;
+      const float* aux_bias0 = reinterpret_cast<const float*>(aux);
+      const int32_t* aux_seq0 = reinterpret_cast<const int32_t*>(aux + 512);
+      // visible keys of this row inside the tile: columns [0, lim128] (causal + tail)
+      const int lim128 = min(my_limit, p.s_kv - 1) - t * 128;
+      auto mask_cols = [&](int col0, float (&sv)[32]) {   // col0: first key column inside the tile
+        if (tile_masked) {
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sv[e] += aux_bias0[col0 + e] * inv_scaling;
+          }
+          if (p.seq_id != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sv[e] = (aux_seq0[col0 + e] == my_seq) ? sv[e] : -INFINITY;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; ++e) sv[e] = (col0 + e <= lim128) ? sv[e] : -INFINITY;
+        }
+      };
+      auto mask_chunk = [&](int c, float (&sv)[32]) { mask_cols(half * 64 + c * 32, sv); };
       auto load_chunk = [&](int c, float (&sv)[32]) {
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r[e]);
-        if (tile_masked) {
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) sv[e] += aux_bias[c * 32 + e] * inv_scaling;
-          }
-          if (p.seq_id != nullptr) {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) sv[e] = (aux_seq[c * 32 + e] == my_seq) ? sv[e] : -INFINITY;
-          }
-#pragma unroll
-          for (int e = 0; e < 32; ++e) sv[e] = (c * 32 + e <= lim) ? sv[e] : -INFINITY;
-        }
+        mask_chunk(c, sv);
       };
       const bool trc = (wq == 0 && half == 0 && lane == 0);
       if (trc) TRACE(4 + grp, i, 0);
       mbar_wait(&s_full[b], (i >> 1) & 1, &err, 9);
       if (trc) TRACE(4 + grp, i, 1);
       tc_fence_after();
-      // ---- pass 1: row maximum of this thread's 64 columns
+      // ---- pass 1: maxima of the four 16-key groups of this thread's 64 columns, and their maximum
       float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float sv[32];
-        load_chunk(c, sv);
-        float m2[2];
+      float gm[4];
+      auto group_max = [&](int c, const float (&sv)[32]) {
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           float v = fmax3(sv[h2 * 16], sv[h2 * 16 + 1], sv[h2 * 16 + 2]);
 #pragma unroll
           for (int e = 3; e < 15; e += 2) v = fmax3(v, sv[h2 * 16 + e], sv[h2 * 16 + e + 1]);
-          m2[h2] = fmaxf(v, sv[h2 * 16 + 15]);
+          gm[c * 2 + h2] = fmaxf(v, sv[h2 * 16 + 15]);
         }
-        mx = fmax3(mx, m2[0], m2[1]);
+        mx = fmax3(mx, gm[c * 2], gm[c * 2 + 1]);
+      };
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float sv[32];
+        load_chunk(c, sv);
+        group_max(c, sv);
       }
       if (trc) TRACE(4 + grp, i, 2);
       const uint32_t xb = (uint32_t)(((i >> 1) & 1) * 4 + grp * 2);
@@ -440,6 +450,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       l_run *= ex2_approx(m_own - m_sf);
       m_own = m_new;
 
+      // Block scales of P ahead of the exponentials: ex2 is monotonic, so the largest probability
+      // of a 16-key group is ex2 of its largest score -- the same bits as the maximum over the
+      // sixteen results -- and the scale chain (e4m3 round, decode, reciprocal) leaves the
+      // dependent path of the pack.
+      uint32_t scw = 0u;
+      float inv_g[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const float am = ex2_approx(fmaf(gm[g], c2, -m_sf));
+        const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
+        uint16_t sb16;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
+        const uint32_t sb = sb16 & 0xFFu;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_g[g]) : "f"(e4m3_to_f32((uint8_t)sb)));
+        scw |= sb << (8 * g);
+      }
       // P buffer b must have been consumed by the PV of tile i - 2
       if (i >= 2) mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1, &err, 10);
       if (trc) TRACE(4 + grp, i, 4);
@@ -450,10 +476,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       float2 lsum4[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) lsum4[c] = make_float2(0.0f, 0.0f);
-      uint32_t scw = 0u;
       // ---- pass 2: exp, row sum, NVFP4 pack of P (two 32-column chunks = four 16-key groups)
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = cc;
         float sv[32];
         load_chunk(c, sv);
         if (c == 1) {
@@ -463,31 +489,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
         for (int g2 = 0; g2 < 2; ++g2) {
           const int g = c * 2 + g2;
-          float pe[16];
-#pragma unroll
-          for (int e = 0; e < 16; e += 2) {
-            const float2 t2 = __ffma2_rn(make_float2(sv[g2 * 16 + e], sv[g2 * 16 + e + 1]), c22, nm2);
-            pe[e] = ex2_approx(t2.x);
-            pe[e + 1] = ex2_approx(t2.y);
-            lsum4[g] = __fadd2_rn(lsum4[g], make_float2(pe[e], pe[e + 1]));
-          }
-          const float am = fmax3(fmax3(fmax3(pe[0], pe[1], pe[2]), pe[3], pe[4]),
-                                 fmax3(fmax3(pe[5], pe[6], pe[7]), pe[8], pe[9]),
-                                 fmax3(fmax3(pe[10], pe[11], pe[12]), fmaxf(pe[13], pe[14]), pe[15]));
-          const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
-          uint16_t sb16;
-          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
-          const uint32_t sb = sb16 & 0xFFu;
-          float inv;
-          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sb)));
-          const float2 inv2 = make_float2(inv, inv);
+          const float2 inv2 = make_float2(inv_g[g], inv_g[g]);
           float2 y[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(pe[2 * e], pe[2 * e + 1]), inv2);
+          for (int e = 0; e < 8; ++e) {
+            const float2 t2 = __ffma2_rn(make_float2(sv[g2 * 16 + 2 * e], sv[g2 * 16 + 2 * e + 1]), c22, nm2);
+            const float2 pe = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
+            lsum4[g] = __fadd2_rn(lsum4[g], pe);
+            y[e] = __fmul2_rn(pe, inv2);
+          }
           const uint32_t lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
           const uint32_t hi2 = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
           sts_v2(pt + sw64_offset(row_in, (half * 4 + g) * 8), lo, hi2);
-          scw |= sb << (8 * g);
         }
       }
       sts_b32(psf + half * 512 + sf_atom_offset(row_in, 0), scw);
@@ -503,18 +516,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tc_fence_after();
         const float a = changed ? alpha : 1.0f;
         const float2 a2 = make_float2(a, a);
+        {
 #pragma unroll
-        for (int c = 0; c < RC / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
-          tmem_ld_wait();
+          for (int c = 0; c < RC / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), a2);
-            r[e] = __float_as_uint(v.x);
-            r[e + 1] = __float_as_uint(v.y);
+            for (int e = 0; e < 32; e += 2) {
+              const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), a2);
+              r[e] = __float_as_uint(v.x);
+              r[e + 1] = __float_as_uint(v.y);
+            }
+            tmem_st32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
           }
-          tmem_st32(tmem + lane_addr + C::T_O + half * RC + c * 32, r);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -663,8 +678,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         }
       }
       float mx;
+      float m4[NG];                     // maxima of the thread's 16-key groups
       {
-        float m4[NG];
 #pragma unroll
         for (int c = 0; c < NG; ++c) {
           float v = fmax3(sv[c * 16], sv[c * 16 + 1], sv[c * 16 + 2]);
@@ -697,33 +712,33 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       uint32_t scw = 0u;
       const float2 c22 = make_float2(c2, c2);
       const float2 nm2 = make_float2(-m_sf, -m_sf);
+      // block scales of P ahead of the exponentials (ex2 is monotonic: the largest probability of a
+      // group is ex2 of its largest score), so the scale chain is off the dependent path of the pack
+      float inv_g[NG];
 #pragma unroll
       for (int g = 0; g < NG; ++g) {
-        float pe[16];
-#pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 t2 = __ffma2_rn(make_float2(sv[g * 16 + e], sv[g * 16 + e + 1]), c22, nm2);
-          pe[e] = ex2_approx(t2.x);
-          pe[e + 1] = ex2_approx(t2.y);
-          lsum4[g] = __fadd2_rn(lsum4[g], make_float2(pe[e], pe[e + 1]));
-        }
-        const float am = fmax3(fmax3(fmax3(pe[0], pe[1], pe[2]), pe[3], pe[4]),
-                               fmax3(fmax3(pe[5], pe[6], pe[7]), pe[8], pe[9]),
-                               fmax3(fmax3(pe[10], pe[11], pe[12]), fmaxf(pe[13], pe[14]), pe[15]));
+        const float am = ex2_approx(fmaf(m4[g], c2, -m_sf));
         const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
         uint16_t sb16;
         asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
         const uint32_t sb = sb16 & 0xFFu;
-        float inv;
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sb)));
-        const float2 inv2 = make_float2(inv, inv);
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv_g[g]) : "f"(e4m3_to_f32((uint8_t)sb)));
+        scw |= sb << (8 * g);
+      }
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const float2 inv2 = make_float2(inv_g[g], inv_g[g]);
         float2 y[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(pe[2 * e], pe[2 * e + 1]), inv2);
+        for (int e = 0; e < 8; ++e) {
+          const float2 t2 = __ffma2_rn(make_float2(sv[g * 16 + 2 * e], sv[g * 16 + 2 * e + 1]), c22, nm2);
+          const float2 pe = make_float2(ex2_approx(t2.x), ex2_approx(t2.y));
+          lsum4[g] = __fadd2_rn(lsum4[g], pe);
+          y[e] = __fmul2_rn(pe, inv2);
+        }
         const uint32_t lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
         const uint32_t hi2 = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
         sts_v2(pt + sw64_offset(row_in, (half * NG + g) * 8), lo, hi2);
-        scw |= sb << (8 * g);
       }
       // this thread's NG scale bytes: groups half*NG .. of the row's 8 (4 per K=64 atom)
       if constexpr (NG == 4) {

@@ -175,6 +175,52 @@ class NVFP4KVCache:
             _lib.stream_ptr(query.device)), "nvfp4_lse_merge")
         return merged.reshape(z, h, 1, d).to(query.dtype)
 
+    # ------------------------------------------------------------------ checkpoint / resume
+    def state_dict(self) -> dict:
+        """Everything needed to resume decoding: the packed prefix (only the ``length`` valid
+        tokens, so a long-capacity cache checkpoints at its fill level), the bf16 stash of the open
+        16-key V group, the recent-window ring and the geometry.  Tensors are clones on the
+        cache's device; ``torch.save`` moves them like any other state dict.  (No counterpart in
+        the reference; the cache there is rebuilt by re-running the prompt.)"""
+        s = self.length
+        s_grp = _next_mult(s, self.GROUP)
+        sd = {
+            "geometry": (self.z, self.hk, self.d, self.max_seq_len, self.block_n, self.recent_window,
+                         str(self.dtype)),
+            "length": s, "partial_len": self.partial_len,
+            "knv": self.knv[:, :s].clone(), "ksc": self.ksc[:, :s].view(torch.uint8).clone(),
+            "vnv": self.vnv[:, :, : s_grp // 2].clone(),
+            "vsc": self.vsc[:, :, : s_grp // 16].view(torch.uint8).clone(),
+            "v_partial": self.v_partial_bf16.clone(),
+        }
+        if self.recent_window > 0:
+            sd["rk"], sd["rv"] = self.rk.clone(), self.rv.clone()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        """Restore a cache saved by ``state_dict`` into this (same-geometry) cache; the capacity
+        may differ as long as it holds ``length`` tokens."""
+        z, hk, d, _cap, block_n, window, dt = sd["geometry"]
+        assert (z, hk, d, block_n, window, dt) == (self.z, self.hk, self.d, self.block_n,
+                                                   self.recent_window, str(self.dtype)), "geometry mismatch"
+        s = int(sd["length"])
+        assert s <= self.max_seq_len, "saved cache exceeds capacity"
+        s_grp = _next_mult(s, self.GROUP)
+        dev = self.device
+        for buf in (self.knv, self.vnv):
+            buf.zero_()
+        self.ksc.view(torch.uint8).zero_()
+        self.vsc.view(torch.uint8).zero_()
+        self.knv[:, :s] = sd["knv"].to(dev)
+        self.ksc.view(torch.uint8)[:, :s] = sd["ksc"].to(dev)
+        self.vnv[:, :, : s_grp // 2] = sd["vnv"].to(dev)
+        self.vsc.view(torch.uint8)[:, :, : s_grp // 16] = sd["vsc"].to(dev)
+        self.v_partial_bf16.copy_(sd["v_partial"].to(dev))
+        if self.recent_window > 0:
+            self.rk.copy_(sd["rk"].to(dev))
+            self.rv.copy_(sd["rv"].to(dev))
+        self.length, self.partial_len = s, int(sd["partial_len"])
+
     # ------------------------------------------------------------------ accounting
     def fp4_bytes(self) -> int:
         s = self.length

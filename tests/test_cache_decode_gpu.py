@@ -279,3 +279,46 @@ def test_fp16_cache_cut_zero_hybrid_and_packed_prefix():
     b = n.nvfp4_flash_decode_prequant(q2, n.nvfp4_quant_kv_decode(k3[:, :, :cut], v3[:, :, :cut]), d ** -0.5, g)
     assert cos(a.float().cpu().numpy(), b.float().cpu().numpy()) > 0.999
     assert _status() == 0
+
+
+def test_state_dict_roundtrip_resumes_decoding(tmp_path):
+    """A cache restored from its state dict (through torch.save / torch.load, into a cache of a
+    different capacity) holds the same bytes and keeps appending and decoding bit-identically."""
+    n = _n()
+    z, hk, g, d, win = 2, 2, 4, 128, 64
+    k, _ = seeded_bf16((z, hk, 300, d), 71)
+    v, _ = seeded_bf16((z, hk, 300, d), 72)
+    q, _ = seeded_bf16((z, hk * g, 1, d), 73)
+    a = n.NVFP4KVCache(z, hk, d, 512, "cuda", recent_window=win)
+    a.prefill(k[:, :, :250], v[:, :, :250])
+    for t in range(250, 275):                               # stops inside a 16-key V group
+        a.append(k[:, :, t:t + 1], v[:, :, t:t + 1])
+    path = tmp_path / "cache.pt"
+    torch.save(a.state_dict(), path)
+    b = n.NVFP4KVCache(z, hk, d, 1024, "cuda", recent_window=win)
+    b.load_state_dict(torch.load(path))
+    assert (b.length, b.partial_len) == (a.length, a.partial_len)
+    for t in range(275, 300):
+        a.append(k[:, :, t:t + 1], v[:, :, t:t + 1])
+        b.append(k[:, :, t:t + 1], v[:, :, t:t + 1])
+    pa, pb = a.get_packed(), b.get_packed()
+    assert torch.equal(pa[0], pb[0]) and torch.equal(pa[1].view(torch.uint8), pb[1].view(torch.uint8))
+    ng = -(-300 // 16)
+    assert torch.equal(pa[2][:, :, : ng * 8], pb[2][:, :, : ng * 8])
+    assert torch.equal(pa[3].view(torch.uint8)[:, :, :ng], pb[3].view(torch.uint8)[:, :, :ng])
+    assert torch.equal(n.nvfp4_flash_decode_prequant(q, pa, d ** -0.5, g),
+                       n.nvfp4_flash_decode_prequant(q, pb, d ** -0.5, g))
+    assert torch.equal(a.hybrid_decode(q, d ** -0.5, g), b.hybrid_decode(q, d ** -0.5, g))
+    with pytest.raises(AssertionError, match="geometry"):
+        n.NVFP4KVCache(z, hk, 256, 512, "cuda", recent_window=win).load_state_dict(a.state_dict())
+    assert _status() == 0
+
+
+def test_decode_demo_small_model():
+    """The decode demo (random-weight GQA decoder, per-layer caches) tracks its bf16-cache run."""
+    from sageattention_b200.nvfp4 import demo_decode
+    rep = demo_decode.main(["--layers", "2", "--hidden", "512", "--heads", "4", "--kv-heads", "2",
+                            "--vocab", "512", "--batch", "1", "--prompt", "300", "--new", "8", "--window", "64"])
+    assert rep["fp4"]["logit_cos"] > 0.97 and rep["hybrid"]["logit_cos"] > 0.97
+    assert rep["fp4"]["bf16_bytes"] / rep["fp4"]["bytes"] > 2.5
+    assert _status() == 0

@@ -95,7 +95,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int D, typename TO>
+// kVarlen: packed rows with per-token sample ids (a separate instantiation keeps the dense kernel
+// free of the sample tests).
+// sample-id test: a compile-time yes in the varlen instantiation, the run-time test otherwise
+#define FWD_HAS_SEQ (kVarlen || p.seq_id != nullptr)
+template <int D, typename TO, bool kVarlen>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
            const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -154,7 +158,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
     mbar_init(&qsf_full, 4);
     mbar_fence_init();
     int lo = 0;
-    if (p.seq_start != nullptr) lo = (p.seq_start[min(m0, p.s_q - 1)] / 128) * 128;
+    if (FWD_HAS_SEQ) lo = (p.seq_start[min(m0, p.s_q - 1)] / 128) * 128;
     s_lo_tile = lo / 128;
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, 512);
@@ -212,7 +216,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
           for (int k = 0; k < C::KB; ++k) kx[j][k] = __ldg(gsrc + k);
           if (p.bias != nullptr) nb[j] = __ldg(p.bias + (int64_t)zi * p.s_kv + key);
-          if (p.seq_id != nullptr) ns[j] = __ldg(p.seq_id + key);
+          if (FWD_HAS_SEQ) ns[j] = __ldg(p.seq_id + key);
         }
       }
 #pragma unroll
@@ -360,7 +364,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&qsf_full);
     }
-    const int my_seq = (p.seq_id != nullptr) ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    const int my_seq = FWD_HAS_SEQ ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    // packed rows: when all 128 rows of this tile belong to one sample, key tiles that lie wholly
+    // inside that sample need no per-element sample test
+    const bool q_one_sample =
+        FWD_HAS_SEQ && (p.seq_id[min(m0, p.s_q - 1)] == p.seq_id[min(m0 + 127, p.s_q - 1)]);
     const int my_limit = p.causal ? (row + shift) : (p.s_kv - 1);
     const float c2 = p.scaling * kFwdLog2e;
     const float inv_scaling = 1.0f / p.scaling;
@@ -372,8 +380,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       const int b = i & 1, s = i % C::NSTAGE, t = t_lo + i;
       const int n0 = t * 128 + half * 64;
       const uint32_t s_addr = tmem + lane_addr + C::T_S + b * 128 + half * 64;
-      const bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
-                               (p.bias != nullptr) || (p.seq_id != nullptr);
+      bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
+                         (p.bias != nullptr) || (!kVarlen && p.seq_id != nullptr);   // varlen: completed below
       const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
                            C::VSF_BYTES;
       const float* aux_bias0 = reinterpret_cast<const float*>(aux);
@@ -386,7 +394,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
 #pragma unroll
             for (int e = 0; e < 32; ++e) sv[e] += aux_bias0[col0 + e] * inv_scaling;
           }
-          if (p.seq_id != nullptr) {
+          if (FWD_HAS_SEQ) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) sv[e] = (aux_seq0[col0 + e] == my_seq) ? sv[e] : -INFINITY;
           }
@@ -408,6 +416,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       mbar_wait(&s_full[b], (i >> 1) & 1, &err, 9);
       if (trc) TRACE(4 + grp, i, 1);
       tc_fence_after();
+      if constexpr (kVarlen)   // keys are sorted by sample: first and last id equal => all equal
+        tile_masked = tile_masked || !(q_one_sample && aux_seq0[0] == my_seq && aux_seq0[127] == my_seq);
       // ---- pass 1: maxima of the four 16-key groups of this thread's 64 columns, and their maximum
       float mx = -INFINITY;
       float gm[4];
@@ -634,7 +644,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&qsf_full);
     }
-    const int my_seq = (p.seq_id != nullptr) ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    const int my_seq = FWD_HAS_SEQ ? p.seq_id[min(row, p.s_q - 1)] : 0;
+    const bool q_one_sample =
+        FWD_HAS_SEQ && (p.seq_id[min(m0, p.s_q - 1)] == p.seq_id[min(m0 + 127, p.s_q - 1)]);
     const int my_limit = p.causal ? (row + shift) : (p.s_kv - 1);  // last visible key index
     const float c2 = p.scaling * kFwdLog2e;
     const float inv_scaling = 1.0f / p.scaling;
@@ -660,8 +672,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       tc_fence_before();
       mbar_arrive(&s_free[b]);
 
-      const bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
-                               (p.bias != nullptr) || (p.seq_id != nullptr);
+      bool tile_masked = (t * 128 + 127 > m0 + shift && p.causal) || (t * 128 + 128 > p.s_kv) ||
+                         (p.bias != nullptr) || (!kVarlen && p.seq_id != nullptr);
+      {
+        const int32_t* aux_seq0 = reinterpret_cast<const int32_t*>(
+            s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + C::VSF_BYTES + 512);
+        if constexpr (kVarlen)   // keys are sorted by sample: first and last id equal => all equal
+          tile_masked = tile_masked || !(q_one_sample && aux_seq0[0] == my_seq && aux_seq0[127] == my_seq);
+      }
       if (tile_masked) {
         const uint8_t* aux = s_stage + s * C::STAGE_BYTES + C::K_BYTES + C::V_BYTES + C::KSF_BYTES +
                              C::VSF_BYTES;
@@ -673,7 +691,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           if (p.bias != nullptr) v += aux_bias[e] * inv_scaling;
           const int key = n0 + e;
           bool ok = key <= my_limit && key < p.s_kv;
-          if (p.seq_id != nullptr) ok = ok && (aux_seq[e] == my_seq);
+          if (FWD_HAS_SEQ) ok = ok && (aux_seq[e] == my_seq);
           sv[e] = ok ? v : -INFINITY;
         }
       }
@@ -843,11 +861,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   if (tid == 32) TRACE(5, 70, 6);
 }
 
+#undef FWD_HAS_SEQ
 template <int D, typename TO>
 int fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                const FwdParams& p, int64_t zh, cudaStream_t st) {
   using C = FwdCfg<D>;
-  auto kern = fwd_kernel<D, TO>;
+  auto kern = (p.seq_id != nullptr) ? fwd_kernel<D, TO, true> : fwd_kernel<D, TO, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return fail((int)e, "nvfp4_fwd: smem attribute: %s", cudaGetErrorString(e));
   dim3 grid((unsigned)zh, (unsigned)((p.s_q + 127) / 128));

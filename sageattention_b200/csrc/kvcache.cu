@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
   extern __shared__ float sm[];
   float* qs = sm;                 // [g][d]
   float* sc = sm + g * d;         // [g][count]
-  float* part = sc + g * count;   // [4][g][d] partial outputs of the four key quarters
+  float* part = sc + ((g * count + 3) & ~3);   // [4][g][d] partial outputs (four slots shared by the sixteen warps), 16-byte aligned
   __shared__ float row_m[16], row_l[16];
   const int zi = blockIdx.x / hk, kh = blockIdx.x % hk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -147,32 +147,59 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
     if (lane == 0) { row_m[gq] = m; row_l[gq] = l; }
   }
   __syncthreads();
-  // P.V: the block's four quarters of 128 threads split the keys, a thread owns output columns
-  const int half = tid >> 7, t = tid & 127;
-  const int per = (count + 3) / 4;
-  const int j0 = min(count, half * per), j1 = min(count, j0 + per);
-  for (int i = t; i < d; i += 128) {
-    float acc[16];
+  // P.V: warp w takes keys w, w + 16, ... (four row loads in flight), a lane owns four consecutive
+  // columns of each 128-column piece; the sixteen warps' partial sums meet in four shared slots
+  // (warps w, w + 4, w + 8, w + 12 add into slot w & 3 in turn)
+  for (int c = 0; c < d; c += 128) {
+    float acc[16][4];
 #pragma unroll
-    for (int gq = 0; gq < 16; ++gq) acc[gq] = 0.0f;
-    for (int j = j0; j < j1; j += 4) {
-      float vv[4];
+    for (int gq = 0; gq < 16; ++gq)
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        vv[u] = (j + u < j1) ? to_f32<T>(vb[(int64_t)slot(j + u) * d + i]) : 0.0f;
+      for (int x = 0; x < 4; ++x) acc[gq][x] = 0.0f;
+    for (int j0 = warp; j0 < count; j0 += 64) {
+      float vv[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = min(j0 + 16 * u, count - 1);
+        const T* vr = vb + (int64_t)slot(j) * d + c + lane * 4;
+        if constexpr (sizeof(T) == 2) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(vr);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) vv[u][x] = to_f32<T>(e[x]);
+        } else {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) vv[u][x] = to_f32<T>(vr[x]);
+        }
+      }
 #pragma unroll
       for (int gq = 0; gq < 16; ++gq)
         if (gq < g) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            acc[gq] = fmaf((j + u < j1) ? sc[gq * count + j + u] : 0.0f, vv[u], acc[gq]);
+          for (int u = 0; u < 4; ++u) {
+            const float pr = (j0 + 16 * u < count) ? sc[gq * count + j0 + 16 * u] : 0.0f;
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[gq][x] = fmaf(pr, vv[u][x], acc[gq][x]);
+          }
         }
     }
+    for (int r = 0; r < 4; ++r) {
+      if ((warp >> 2) == r) {
 #pragma unroll
-    for (int gq = 0; gq < 16; ++gq)
-      if (gq < g) part[(half * g + gq) * d + i] = acc[gq];
+        for (int gq = 0; gq < 16; ++gq)
+          if (gq < g) {
+            float4* dst = reinterpret_cast<float4*>(part + ((warp & 3) * g + gq) * d + c + lane * 4);
+            float4 v = make_float4(acc[gq][0], acc[gq][1], acc[gq][2], acc[gq][3]);
+            if (r > 0) {
+              const float4 o = *dst;
+              v = make_float4(v.x + o.x, v.y + o.y, v.z + o.z, v.w + o.w);
+            }
+            *dst = v;
+          }
+      }
+      __syncthreads();
+    }
   }
-  __syncthreads();
   for (int i = tid; i < g * d; i += 512) {
     const int gq = i / d;
     out[((int64_t)(zi * hk + kh) * g) * d + i] =
@@ -248,7 +275,7 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
   NVFP4_REQUIRE(q && rk && rv && out && lse, "nvfp4_window_attention: null pointer");
   NVFP4_REQUIRE(count > 0 && count <= ring_cap, "nvfp4_window_attention: count must be in (0, ring_cap]");
   NVFP4_REQUIRE(z * hk * g < (1LL << 31), "nvfp4_window_attention: too many heads");
-  const size_t smem = (size_t)(5 * g * d + g * count) * sizeof(float);
+  const size_t smem = (size_t)(5 * g * d + g * count + 4) * sizeof(float);
   NVFP4_REQUIRE(g >= 1 && g <= 16, "nvfp4_window_attention: GQA group %d must be <= 16", g);
   NVFP4_REQUIRE(smem <= 200 * 1024, "nvfp4_window_attention: window too long (%lld keys)", (long long)count);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -4,27 +4,35 @@
 
 Headline workload (BASELINE config 2, "prefill forward"): Z=4, H=32, Hk=8, S=8192, D=128, causal,
 bf16 Q/K/V ~ N(0,1) with a constant offset ~ N(0, sigma=2) on 8 random K channels, scaling
-1/sqrt(128).  One step = one `nvfp4_flash_attention` call = NVFP4 pack of Q, K (along D) and V
-(along keys) + the tcgen05 forward kernel.  FLOPs per step = 4*Z*H*S^2*D/2 = 2.199e12 (the pack
-is counted in time, not in FLOPs).
+1/sqrt(128).  One step = one `nvfp4_flash_attention` call = one NVFP4 pre-pack launch (Q, K along
+D, V along keys) + the tcgen05 forward kernel.  FLOPs per step = 4*Z*H*S^2*D/2 = 2.199e12 (the
+pack is counted in time, not in FLOPs).
 
 Printed JSON (one line, rank 0):
-  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks
-  e2e        same metric through the public API with pinned HOST buffers: H2D of q,k,v and D2H
-             of the output inside the timed region
-  roofline   the forward kernel alone (CUDA events around it on its stream) against the tensor
-             peak; also the MUFU co-bound that actually limits a D=128 FP4 forward
-  secondary  HBM rooflines of the decode step (config 4) and of the packer; the training step
-             (config 3: packed varlen forward + backward) against the bf16 tensor peak
+  value      TFLOP/s of the whole job, inputs resident in HBM, CUDA-event timed, max over ranks;
+             with N > 1 every rank runs its own full-size copy ("weak", no data-path collective)
+  e2e        the same metric through the public API with pinned HOST buffers: H2D of q, k, v and
+             D2H of the output inside the timed region; `host_copy` gives the plain pinned-copy
+             rates of the same ranks, which is the ceiling of that figure
+  roofline   the forward kernel alone against the FP4 tensor peak MEASURED in the same run
+             (`nvfp4_peak_probe`) and against 4 x the bf16 figure of MEASURED_PEAKS.json; also the
+             MUFU co-bound that actually limits a D=128 FP4 forward
+  parity     kernel vs the numpy oracle on one (batch, KV-group) unit of THIS run's inputs
+  secondary  at every N, each with its own clock sample: config 2 strong-scaled over (batch,
+             KV-group) shards with a bit-for-bit check against the unsharded run; config 3 (packed
+             varlen training step, KV groups sharded) for both backward modes; config 4 (decode
+             from the NVFP4 cache, cache units sharded, plus hybrid decode); config 5 (D=256,
+             S=131072 forward + backward, ring attention over the ranks) with compute-only time
+             and exposed communication; at N = 1 also the packer
   cpu_baseline  the CPU oracle (a port of the reference arithmetic) on a bounded sample
 
-With N > 1 (torchrun) every rank owns its own (batch, KV-group) shard of the same size: no
-collective on the data path, "weak" scaling.  `--impl reference` times the CPU oracle port.
+`--impl reference` times the CPU oracle port (the reference has no CPU implementation).
 """
 
 from __future__ import annotations
 
 import argparse
+import itertools
 import json
 import os
 import subprocess
@@ -51,32 +59,37 @@ def _measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.rows, self.proc, self.gpu = [], None, gpu_index
+    def __init__(self, gpu_index: int, enabled: bool = True):
+        self.rows, self.proc, self.gpu, self.enabled = [], None, gpu_index, enabled
 
     def start(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if not self.enabled:
+            return None
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         sm, mx, reasons = [], None, set()
         for r in self.rows:
@@ -93,22 +106,76 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bind_near_gpu(torch, local: int):
+    """Bind this process (and so its pinned allocations, first-touch) to the CPUs that sit on the
+    GPU's PCIe root: the `local_cpulist` of the device in sysfs.  Returns what was done."""
+    try:
+        q = subprocess.run(["nvidia-smi", "--query-gpu=uuid,pci.bus_id", "--format=csv,noheader"],
+                           capture_output=True, text=True, timeout=20).stdout.strip().splitlines()
+        uuid = str(getattr(torch.cuda.get_device_properties(local), "uuid", ""))
+        bus = None
+        for i, line in enumerate(q):
+            u, b = [x.strip() for x in line.split(",")]
+            if (uuid and uuid.replace("GPU-", "") in u) or (not uuid and i == local):
+                bus = b
+        if bus is None and local < len(q):
+            bus = q[local].split(",")[1].strip()
+        dom, rest = bus.split(":", 1)
+        path = f"/sys/bus/pci/devices/{dom[-4:].lower()}:{rest.lower()}"
+        cpulist = open(path + "/local_cpulist").read().strip()
+        node = open(path + "/numa_node").read().strip()
+        cpus = set()
+        for part in cpulist.split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        return {"pci": bus, "numa_node": node, "cpus": cpulist, "bound": bool(cpus)}
+    except Exception as exc:          # reported, not fatal
+        return {"bound": False, "why": f"{type(exc).__name__}: {exc}"}
+
+
+# ------------------------------------------------------------------------------ inputs
+def make_inputs(torch, seed, device=None):
+    """bf16 Q/K/V of config 2 from a CPU generator (every caller of a seed sees the same bits)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(Z, H, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32)
+    ch = torch.randperm(D, generator=g)[:8]
+    k[..., ch] += torch.randn(8, generator=g) * 2.0   # "N(0,4)" read as variance 4, sigma 2
+    k = k.to(torch.bfloat16)
+    v = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return q, k, v
+
+
+def varlen_lengths(total=16384, lo=256, hi=4096, seed=3):
+    """Segment lengths uniform[lo, hi] from the seed until they cover `total`, last one truncated."""
+    rng = np.random.default_rng(seed)
+    lens = []
+    while sum(lens) < total:
+        lens.append(int(rng.integers(lo, hi + 1)))
+    lens[-1] -= sum(lens) - total
+    return [n for n in lens if n > 0]
+
+
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_sample(heads: int = 4, s: int = S):
-    """The oracle (mode B: the reference's arithmetic, numpy on the host cores) on a bounded
-    sample of the workload: `heads` query heads sharing one KV head, causal, D=128.  The default
-    (4 heads, S=8192) is exactly one (batch, KV-group) unit of the 32 units in a step."""
-    from oracle import nvfp4_oracle as O
-    rng = np.random.default_rng(0)
-    bf = lambda a: (a.astype(np.float32).view(np.uint32) & 0xFFFF0000).view(np.float32)
-    q = bf(rng.standard_normal((1, heads, s, D))); k = bf(rng.standard_normal((1, 1, s, D)))
-    v = bf(rng.standard_normal((1, 1, s, D)))
-    t0 = time.perf_counter()
-    O.attention_mode_b(q, k, v, D ** -0.5, True, heads)
-    dt = time.perf_counter() - t0
-    flops = heads * 4.0 * s * s * D / 2.0
-    return flops / dt / 1e12, dt, (f"oracle mode B (numpy), {heads} query head(s) on 1 KV head, S={s}, "
-                                   f"D={D}, causal ({flops / 1e9:.1f} GFLOP)")
+def cpu_sample(q_unit, k_unit, v_unit, out_unit=None):
+    """The oracle (mode B: the reference's arithmetic, numpy on the host cores) on ONE (batch,
+    KV-group) unit of the workload: G query heads sharing one KV head, causal, D=128.  Returns
+    (TFLOP/s, seconds, description, parity-or-None); with `out_unit` the kernel's output of the
+    same unit is compared with what the oracle just computed."""
+    from oracle import parity_checks as PC
+    g, s, d = q_unit.shape
+    res = PC.forward_unit(out_unit if out_unit is not None else np.zeros_like(q_unit), q_unit, k_unit, v_unit,
+                          d ** -0.5)
+    dt = res["oracle_seconds"]
+    desc = (f"oracle mode B (numpy), {g} query head(s) on 1 KV head, S={s}, D={d}, causal "
+            f"({res['flops'] / 1e9:.1f} GFLOP)")
+    parity = None
+    if out_unit is not None:
+        parity = {"cosine_vs_oracle_mode_b": res["cosine"], "max_abs_vs_oracle_mode_b": res["max_abs"]}
+    return res["flops"] / dt / 1e12, dt, desc, parity
 
 
 def run_reference(args):
@@ -116,12 +183,16 @@ def run_reference(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    bf = lambda a: (a.astype(np.float32).view(np.uint32) & 0xFFFF0000).view(np.float32)
+    s = 4096
+    q, k, v = bf(rng.standard_normal((1, s, D))), bf(rng.standard_normal((s, D))), bf(rng.standard_normal((s, D)))
     vals = []
     for i in range(args.warmup + args.steps):
-        v, dt, sample = cpu_sample(heads=1, s=4096)
+        val, dt, sample, _ = cpu_sample(q, k, v)
         if i >= args.warmup:
-            vals.append((v, dt))
-    val = float(np.mean([v for v, _ in vals]))
+            vals.append((val, dt))
+    val = float(np.mean([x for x, _ in vals]))
     ms = float(np.mean([dt for _, dt in vals])) * 1e3
     line = {
         "impl": "reference", "metric": "fp4_attn_fwd_tflops", "value": val, "unit": "TFLOP/s",
@@ -135,16 +206,56 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-# ------------------------------------------------------------------------------ GPU arm
-def make_inputs(torch, seed, device):
-    g = torch.Generator().manual_seed(seed)
-    q = torch.randn(Z, H, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    k = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32)
-    ch = torch.randperm(D, generator=g)[:8]
-    k[..., ch] += torch.randn(8, generator=g) * 2.0   # "N(0,4)" read as variance 4, sigma 2
-    k = k.to(torch.bfloat16)
-    v = torch.randn(Z, HK, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
-    return q, k, v
+# ------------------------------------------------------------------------------ GPU arm helpers
+class Ctx:
+    """Rank context: timing with barriers on both sides and the maximum over ranks."""
+
+    def __init__(self, torch, dist, rank, world, local, dev):
+        self.torch, self.dist, self.rank, self.world, self.local, self.dev = torch, dist, rank, world, local, dev
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, *vals):
+        t = self.torch.tensor(list(vals), device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    def sum_over_ranks(self, *vals):
+        t = self.torch.tensor(list(vals), device=self.dev, dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return [float(x) for x in t.tolist()]
+
+    def timed(self, fn, iters, warm=3, min_seconds=0.0):
+        """ms per call of `fn`: `warm` untimed calls, then >= `iters` timed ones (more until the
+        region lasts `min_seconds`, so that the clock sampler sees it), barrier + synchronize on
+        both sides, CUDA events on the launching stream, maximum over ranks.  Returns (ms, clocks)."""
+        torch = self.torch
+        for _ in range(warm):
+            fn()
+        self.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        one = max(a.elapsed_time(b) * 1e-3, 1e-6)
+        n = max(iters, int(min_seconds / one) + 1) if min_seconds > 0 else iters
+        n = int(self.max_over_ranks(float(n))[0])
+        sampler = ClockSampler(self.local, enabled=self.rank == 0).start()
+        self.barrier()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        self.barrier()
+        ms = a.elapsed_time(b) / n
+        clocks = sampler.stop()
+        return self.max_over_ranks(ms)[0], clocks, n
 
 
 def ev_ms(torch, fn, iters):
@@ -157,29 +268,191 @@ def ev_ms(torch, fn, iters):
     return a.elapsed_time(b) / iters
 
 
-def secondary_metrics(torch, nv, peaks):
-    """Decode step (BASELINE config 4) and packer, both HBM-bound, timed with CUDA events."""
-    out = []
-    dev = "cuda"
-    z, h, hk, s, d = 16, 32, 8, 32768, 128
+def measure_peaks(cx, _lib):
+    """Pipe rates of this device from the library's own resident-operand micro-kernels."""
+    import ctypes
+    torch = cx.torch
+    sink = torch.zeros(4, dtype=torch.float32, device=cx.dev)
+    names = {0: "fp4_mma_tflops", 1: "bf16_mma_tflops", 2: "ex2_per_sm_per_clk", 3: "cvt_e2m1x2_per_sm_per_clk",
+             4: "fma_per_sm_per_clk"}
+    out = {}
+    sms = torch.cuda.get_device_properties(cx.dev).multi_processor_count
+    for what, key in names.items():
+        iters = 8192 if what <= 1 else 4096
+        work = ctypes.c_double()
+        call = lambda: _lib.call("nvfp4_peak_probe", cx.dev, what, iters, ctypes.byref(work), sink.data_ptr(),
+                                 _lib.status_word(cx.dev).data_ptr(), _lib.stream_ptr(cx.dev))
+        for _ in range(2):
+            call()
+        torch.cuda.synchronize()
+        best = min(ev_ms(torch, call, 1) for _ in range(5))
+        if what <= 1:
+            out[key] = work.value / (best * 1e-3) / 1e12
+        else:
+            out[key] = work.value / (best * 1e-3) / sms          # thread-instructions per SM per second
+    return out
+
+
+def host_copy_rates(cx):
+    """Plain pinned-memory copy rates of every rank at once: H2D, D2H, and both together."""
+    torch = cx.torch
+    n = 256 << 20
+    hb = torch.empty(n, dtype=torch.uint8).pin_memory()
+    hb2 = torch.empty(n, dtype=torch.uint8).pin_memory()
+    db = torch.empty(n, dtype=torch.uint8, device=cx.dev)
+    db2 = torch.empty(n, dtype=torch.uint8, device=cx.dev)
+    s2 = torch.cuda.Stream()
+    h2d = lambda: db.copy_(hb, non_blocking=True)
+    d2h = lambda: hb2.copy_(db2, non_blocking=True)
+
+    def both():
+        db.copy_(hb, non_blocking=True)
+        with torch.cuda.stream(s2):
+            hb2.copy_(db2, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s2)
+
+    res = {}
+    for name, fn, nbytes in (("h2d", h2d, n), ("d2h", d2h, n), ("h2d_and_d2h", both, 2 * n)):
+        ms, _, _ = cx.timed(fn, 5, warm=1)
+        mine = nbytes / (ms * 1e-3) / 1e9            # every rank moved nbytes in the slowest rank's time
+        res[name + "_gbs_per_rank"] = mine
+        res[name + "_gbs_all_ranks"] = mine * cx.world
+    return res
+
+
+# ------------------------------------------------------------------------------ secondary entries
+def sharded_prefill(cx, nv, RD, q, k, v, out_full, steps):
+    """Config 2 strong-scaled: the 32 (batch, KV-group) units of rank 0's inputs are dealt round-robin
+    to the ranks (no data-path collective); the first unit of every rank is compared bit for bit with
+    the unsharded run of rank 0."""
+    torch, dist = cx.torch, cx.dist
+    if cx.world > 1:
+        if cx.rank != 0:
+            q, k, v = (torch.empty(sh, dtype=torch.bfloat16, device=cx.dev)
+                       for sh in ((Z, H, S, D), (Z, HK, S, D), (Z, HK, S, D)))
+        for t in (q, k, v):
+            dist.broadcast(t, 0)
+    qs, ks, vs, mine = RD.shard_qkv(q, k, v, cx.rank, cx.world)
+    g = H // HK
+    fn = lambda: nv.nvfp4_flash_attention(qs, ks, vs, D ** -0.5, causal=True, num_key_value_groups=g)
+    ms, clocks, n = cx.timed(fn, steps, min_seconds=0.4)
+    part = fn()
+    equal = None
+    if cx.world > 1:
+        first = part[0].contiguous()
+        got = [torch.empty_like(first) for _ in range(cx.world)] if cx.rank == 0 else None
+        dist.gather(first, got, dst=0)
+        if cx.rank == 0:
+            assign = RD.unit_partition(Z, HK, cx.world)
+            equal = all(bool(torch.equal(got[r], out_full[assign[r][0][0], assign[r][0][1] * g:(assign[r][0][1] + 1) * g]))
+                        for r in range(cx.world))
+    else:
+        equal = bool(torch.equal(part.reshape(Z, HK, g, S, D).reshape(Z, H, S, D), out_full))
+    tf = FLOPS_PER_STEP / (ms * 1e-3) / 1e12
+    return {"name": "config 2 sharded by (batch, KV-group): 32 units over the ranks, strong scaling",
+            "units_per_rank": len(mine), "ms_per_step": ms, "tflops_all_gpus": tf, "steps": n, "scaling": "strong",
+            "sharded_first_units_bit_identical_to_unsharded": equal, "clocks": clocks}
+
+
+def train_metrics(cx, nv, RD, peaks, steps):
+    """Config 3: packed varlen forward + backward, both backward modes; the 8 KV groups are dealt
+    to the ranks (1 per GPU at 8).  FLOPs: forward 4*H*D*sum(s_i^2)/2, backward 2.5x."""
+    torch = cx.torch
+    from sageattention_b200.nvfp4 import flash
+    dev = cx.dev
+    h, hk, d, total = 32, 8, 128, 16384
+    g = h // hk
+    lens = varlen_lengths(total)
+    cu = torch.tensor([0] + list(itertools.accumulate(lens)), dtype=torch.int32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=gen)
+    qf, kf, vf, dof = rn(1, h, total, d), rn(1, hk, total, d), rn(1, hk, total, d), rn(1, h, total, d)
+    kv_heads = list(range(cx.rank, hk, cx.world))
+    q_heads = [kh * g + i for kh in kv_heads for i in range(g)]
+    if not kv_heads:
+        kv_heads, q_heads = [0], list(range(g))           # more ranks than KV groups: idle ranks repeat group 0
+    q, k, v, do = (qf[:, q_heads].contiguous(), kf[:, kv_heads].contiguous(), vf[:, kv_heads].contiguous(),
+                   dof[:, q_heads].contiguous())
+    del qf, kf, vf, dof
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    sum_sq = float(sum(n * n for n in lens))
+    fwd_flops = 4.0 * h * d * sum_sq / 2.0
+    res, clocks, grads = {}, {}, {}
+    for mode in ("bf16", "fp4_rownorm"):
+        def step():
+            o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=g,
+                                         cu_seqlens=cu, backward_grad_dots=mode)
+            o.backward(do)
+            gr = (q.grad, k.grad, v.grad)
+            q.grad = k.grad = v.grad = None
+            return gr
+        res[mode], clocks[mode], _ = cx.timed(step, steps, min_seconds=0.4)
+        grads[mode] = step()
+    # backward alone (pre-pass + gradient kernels), operands from one forward
+    bwd_ms = {}
+    with torch.no_grad():
+        arrays = flash._varlen_seq_arrays(cu, total, q.device)
+        o, lse, packs = nv.nvfp4_flash_attention(q, k, v, d ** -0.5, causal=True, num_key_value_groups=g,
+                                                 cu_seqlens=cu, return_lse=True, return_packs=True)
+        hp = lambda: flash._run_bwd_hp(q, k, v, o, lse, do, d ** -0.5, True, g, arrays,
+                                       q_packs=packs[0:2], k_packs=packs[2:4])
+        f4 = lambda: flash._run_bwd(q, k, v, o, lse, do, d ** -0.5, True, g, arrays, mode="fp4_rownorm",
+                                    q_packs=packs[0:2], k_packs=packs[2:4])
+        bwd_ms["bf16"], _, _ = cx.timed(hp, steps, min_seconds=0.2)
+        bwd_ms["fp4_rownorm"], _, _ = cx.timed(f4, steps, min_seconds=0.2)
+    # gradient cosine against bf16 attention on the first sample of this rank's first KV group
+    n0 = lens[0]
+    qs = q.detach()[:, :g, :n0].clone().requires_grad_(True)
+    ks = k.detach()[:, :1, :n0].clone().requires_grad_(True)
+    vs = v.detach()[:, :1, :n0].clone().requires_grad_(True)
+    ref = torch.nn.functional.scaled_dot_product_attention(qs, ks.expand(-1, g, -1, -1), vs.expand(-1, g, -1, -1),
+                                                           is_causal=True)
+    ref.backward(do[:, :g, :n0])
+    cosf = lambda a, b: float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
+    cos = {m: {"dq": cosf(grads[m][0][:, :g, :n0], qs.grad), "dk": cosf(grads[m][1][:, :1, :n0], ks.grad),
+               "dv": cosf(grads[m][2][:, :1, :n0], vs.grad)} for m in grads}
+    peak = peaks["bf16_tflops_sustained"]
+    bwd_tf = {m: 2.5 * fwd_flops / (bwd_ms[m] * 1e-3) / 1e12 for m in bwd_ms}
+    return {"name": "config 3: train fwd+bwd, packed varlen 16384 tokens H32 Hk8 D128, KV groups sharded over the ranks",
+            "segments": lens, "sum_len_sq": sum_sq, "kv_groups_per_rank": len(kv_heads), "scaling": "strong",
+            "fwd_bwd_ms": {"hp_grad_dots(bf16)": res["bf16"], "fp4_rownorm": res["fp4_rownorm"]},
+            "fwd_bwd_tflops_all_gpus": {"hp_grad_dots(bf16)": 3.5 * fwd_flops / (res["bf16"] * 1e-3) / 1e12,
+                                        "fp4_rownorm": 3.5 * fwd_flops / (res["fp4_rownorm"] * 1e-3) / 1e12},
+            "bwd_only_ms": bwd_ms, "grad_cosine_vs_bf16_sdpa": cos,
+            "clocks": clocks["bf16"], "clocks_fp4_rownorm": clocks["fp4_rownorm"],
+            "roofline": {"bound": "tensor", "achieved": bwd_tf["bf16"], "peak": peak * cx.world, "unit": "TFLOP/s",
+                         "frac": bwd_tf["bf16"] / (peak * cx.world), "traffic": None,
+                         "kernel": "bwd_dkdv_kernel + bwd_dq_kernel (+ delta pre-pass), hp_grad_dots mode",
+                         "achieved_fp4_rownorm": bwd_tf["fp4_rownorm"],
+                         "note": "2.5 x forward FLOPs (5 GEMMs; the S and dP recompute of the second kernel "
+                                 "is not counted) over the bf16 sustained GEMM peak of all ranks"}}
+
+
+def decode_metrics(cx, nv, peaks, steps):
+    """Config 4: batch 16 x 8 KV heads = 128 cache units of 32768 tokens, dealt to the ranks by batch
+    entry; one decode step streams every unit's packs once.  Plus append, the 64-step serve loop,
+    and hybrid decode with a 512-token high-precision window."""
+    torch = cx.torch
+    dev = cx.dev
+    zt, h, hk, s, d = 16, 32, 8, 32768, 128
+    z = max(1, zt // cx.world)
+    g = h // hk
     cache = nv.NVFP4KVCache(z, hk, d, s + 128, dev)
-    g = torch.Generator(device=dev).manual_seed(4)
-    k = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
-    v = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
+    gen = torch.Generator(device=dev).manual_seed(4 + cx.rank)
+    k = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=gen)
+    v = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=gen)
     cache.prefill(k, v)
     del k, v
-    q = torch.randn(z, h, 1, d, device=dev, dtype=torch.bfloat16, generator=g)
-    kn = torch.randn(z, hk, 1, d, device=dev, dtype=torch.bfloat16, generator=g)
+    q = torch.randn(z, h, 1, d, device=dev, dtype=torch.bfloat16, generator=gen)
+    kn = torch.randn(z, hk, 1, d, device=dev, dtype=torch.bfloat16, generator=gen)
     packed = cache.get_packed()
-    bytes_step = z * hk * (s * (d // 2 + d // 16) + d * (s // 2 + s // 16))
-    step = lambda: nv.nvfp4_flash_decode_prequant(q, packed, d ** -0.5, h // hk)
-    for _ in range(5):
-        step()
-    ms = ev_ms(torch, step, 50)
-    gbs = bytes_step / (ms * 1e-3) / 1e9
-    # the same step replayed from a CUDA graph (no launch overhead between its kernels)
+    bytes_rank = z * hk * (s * (d // 2 + d // 16) + d * (s // 2 + s // 16))
+    bytes_all = bytes_rank * cx.world
+    step = lambda: nv.nvfp4_flash_decode_prequant(q, packed, d ** -0.5, g)
+    ms, clocks, n = cx.timed(step, steps, warm=5, min_seconds=0.3)
+    gbs = bytes_all / (ms * 1e-3) / 1e9
     graph_us = None
-    try:
+    try:      # the same step replayed from a CUDA graph (no launch overhead between its kernels)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -195,130 +468,111 @@ def secondary_metrics(torch, nv, peaks):
     except Exception as exc:   # reported, not fatal: the eager figure above is the metric
         graph_us = f"capture failed: {type(exc).__name__}"
     app = lambda: (cache.append(kn, kn), setattr(cache, "length", s), setattr(cache, "partial_len", 0))
-    for _ in range(3):
-        app()
-    ms_app = ev_ms(torch, app, 50)
-    out.append({"name": "decode_step Z16 H32 Hk8 D128 S32768 (BASELINE config 4)",
-                "step_us": ms * 1e3, "step_us_cuda_graph": graph_us, "append_us": ms_app * 1e3,
-                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": gbs / peaks["hbm_gbs"],
-                             # ncu, S=8192 case (balanced decomposition): dram read 163.2 MB for 150.99 MB
-                             # of packs (1.081x: L2 prefetch granularity at segment ends, cold single
-                             # launch), 3.2 MB written (partials + output); reads grow with the keys streamed
-                             "traffic": bytes_step * 1.081 + 3.2e6, "algorithmic_bytes": bytes_step}})
+    ms_app, _, _ = cx.timed(app, 30)
+    entry = {"name": "config 4: decode step Z16 H32 Hk8 D128 S32768, cache units sharded over the ranks by batch entry",
+             "cache_units_per_rank": z * hk, "scaling": "strong", "step_us": ms * 1e3, "step_us_cuda_graph": graph_us,
+             "append_us": ms_app * 1e3, "steps": n, "clocks": clocks,
+             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"] * cx.world, "unit": "GB/s",
+                          "frac": gbs / (peaks["hbm_gbs"] * cx.world),
+                          # ncu, S=8192 case (balanced decomposition): dram read 163.2 MB for 150.99 MB of
+                          # packs (1.081x: L2 prefetch granularity at segment ends, cold single launch), 3.2 MB
+                          # written (partials + output); reads grow with the keys streamed
+                          "traffic": bytes_rank * 1.081 + 3.2e6, "algorithmic_bytes": bytes_all,
+                          "note": "achieved and peak are sums over the ranks; traffic is per launch (one rank)"}}
+
     # config 4 as stated: 64 steps of (append one token, decode one query) on the live cache
     def serve_step():
         cache.append(kn, kn)
-        return nv.nvfp4_flash_decode_prequant(q, cache.get_packed(), d ** -0.5, h // hk)
+        return nv.nvfp4_flash_decode_prequant(q, cache.get_packed(), d ** -0.5, g)
     cache.length, cache.partial_len = s, 0
     serve_step()
     cache.length, cache.partial_len = s, 0
-    torch.cuda.synchronize()
-    ms_serve = ev_ms(torch, serve_step, 64)
-    out[-1]["append_plus_decode_us_over_64_steps"] = ms_serve * 1e3
+    cx.barrier()
+    ms_serve = cx.max_over_ranks(ev_ms(torch, serve_step, 64))[0]
+    entry["append_plus_decode_us_over_64_steps"] = ms_serve * 1e3
     del cache, packed
     torch.cuda.empty_cache()
-    # the same with a 512-token bf16 recent window and hybrid_decode (FP4 prefix + bf16 window, exact LSE merge)
+    # the same with a 512-token high-precision recent window and hybrid_decode
     hc = nv.NVFP4KVCache(z, hk, d, s + 128, dev, recent_window=512)
-    kk = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=g)
+    kk = torch.randn(z, hk, s, d, device=dev, dtype=torch.bfloat16, generator=gen)
     hc.prefill(kk, kk)
     del kk
-    hyb = lambda: hc.hybrid_decode(q, d ** -0.5, h // hk)
-    for _ in range(3):
-        hyb()
-    ms_h = ev_ms(torch, hyb, 30)
-    window_bytes = 2 * z * hk * 512 * d * 2
-    out[-1]["hybrid_decode_us"] = ms_h * 1e3
-    out[-1]["hybrid_decode_gbs"] = (bytes_step + window_bytes) / (ms_h * 1e-3) / 1e9
+    hyb = lambda: hc.hybrid_decode(q, d ** -0.5, g)
+    ms_h, _, _ = cx.timed(hyb, 30)
+    window_bytes = 2 * z * hk * 512 * d * 2 * cx.world
+    entry["hybrid_decode_us"] = ms_h * 1e3
+    entry["hybrid_decode_gbs"] = (bytes_all + window_bytes) / (ms_h * 1e-3) / 1e9
     del hc
     torch.cuda.empty_cache()
-    x = torch.randn(Z * H, S, D, device=dev, dtype=torch.bfloat16)
+    # a GQA group of 8 (the wider query tile of the decode kernel), same cache bytes per unit
+    c8 = nv.NVFP4KVCache(z, 4, d, s, dev)
+    kk = torch.randn(z, 4, s, d, device=dev, dtype=torch.bfloat16, generator=gen)
+    c8.prefill(kk, kk)
+    del kk
+    q8 = torch.randn(z, 32, 1, d, device=dev, dtype=torch.bfloat16, generator=gen)
+    p8 = c8.get_packed()
+    st8 = lambda: nv.nvfp4_flash_decode_prequant(q8, p8, d ** -0.5, 8)
+    ms8, _, _ = cx.timed(st8, 30)
+    b8 = z * 4 * (s * (d // 2 + d // 16) + d * (s // 2 + s // 16)) * cx.world
+    entry["g8_step_us"] = ms8 * 1e3
+    entry["g8_gbs"] = b8 / (ms8 * 1e-3) / 1e9
+    del c8, p8
+    torch.cuda.empty_cache()
+    return entry
+
+
+def pack_metrics(cx, nv, peaks):
+    torch = cx.torch
+    x = torch.randn(Z * H, S, D, device=cx.dev, dtype=torch.bfloat16)
     pk = lambda: nv._quant_nvfp4(x)
-    for _ in range(3):
-        pk()
-    ms = ev_ms(torch, pk, 20)
+    ms, clocks, _ = cx.timed(pk, 20, min_seconds=0.2)
     b = x.numel() * (2 + 0.5625)
     gbs = b / (ms * 1e-3) / 1e9
-    out.append({"name": "pack Q [128, 8192, 128] bf16 along D", "ms": ms,
-                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": b}})
-    del x
-    torch.cuda.empty_cache()
-    out.append(train_metrics(torch, nv, peaks))
-    return out
+    return {"name": "pack Q [128, 8192, 128] bf16 along D", "ms": ms, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes": b}}
 
 
-def varlen_lengths(total=16384, lo=256, hi=4096, seed=3):
-    """Segment lengths uniform[lo, hi] from the seed until they cover `total`, last one truncated."""
-    import numpy as np
-    rng = np.random.default_rng(seed)
-    lens = []
-    while sum(lens) < total:
-        lens.append(int(rng.integers(lo, hi + 1)))
-    lens[-1] -= sum(lens) - total
-    return [n for n in lens if n > 0]
-
-
-def train_metrics(torch, nv, peaks):
-    """Training step of BASELINE config 3: packed varlen forward + backward (HP gradient GEMMs)."""
-    from sageattention_b200.nvfp4 import flash
-    dev = "cuda"
-    h, hk, d, total = 32, 8, 128, 16384
-    lens = varlen_lengths(total)
-    cu = torch.tensor([0] + list(__import__("itertools").accumulate(lens)), dtype=torch.int32, device=dev)
-    g = torch.Generator(device=dev).manual_seed(3)
-    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
-    q, k, v, do = rn(1, h, total, d), rn(1, hk, total, d), rn(1, hk, total, d), rn(1, h, total, d)
+def ring_metrics(cx, nv, RD, _lib, steps, seq):
+    """Config 5: Z1 H16 Hk4 D256 causal forward + backward at S = `seq`, the sequence split over
+    the ranks in zigzag chunks (context-parallel ring attention); one rank = the single-GPU
+    operators.  `compute_only_ms` is the same schedule with the messages replaced by local copies."""
+    torch = cx.torch
+    dev = cx.dev
+    z, h, hk, d = 1, 16, 4, 256
+    s_loc = seq // cx.world
+    gen = torch.Generator(device=dev).manual_seed(50 + cx.rank)
+    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=gen)
+    q, k, v, do = rn(z, h, s_loc, d), rn(z, hk, s_loc, d), rn(z, hk, s_loc, d), rn(z, h, s_loc, d)
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-    sum_sq = float(sum(n * n for n in lens))
-    fwd_flops = 4.0 * h * d * sum_sq / 2.0
-    res = {}
-    for mode in ("bf16", "fp4_rownorm"):
+
+    def make(comm):
         def step():
-            o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
-                                         cu_seqlens=cu, backward_grad_dots=mode)
+            if cx.world == 1:
+                o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                             backward_grad_dots="bf16")
+            else:
+                o = RD.ring_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                            _communicate=comm)
             o.backward(do)
-            gr = (q.grad, k.grad, v.grad)
             q.grad = k.grad = v.grad = None
-            return gr
-        for _ in range(3):
-            grads = step()
-        res[mode] = ev_ms(torch, step, 10)
-    # backward alone (delta pre-pass + dK/dV kernel + dQ kernel), operands from one forward
-    with torch.no_grad():
-        arrays = flash._varlen_seq_arrays(cu, total, q.device)
-        o, lse, packs = nv.nvfp4_flash_attention(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
-                                                 cu_seqlens=cu, return_lse=True, return_packs=True)
-        bwd = lambda: flash._run_bwd_hp(q, k, v, o, lse, do, d ** -0.5, True, h // hk, arrays,
-                                        q_packs=packs[0:2], k_packs=packs[2:4])
-        for _ in range(3):
-            bwd()
-        ms_bwd = ev_ms(torch, bwd, 10)
-    # gradient cosine against bf16 attention on the first sample, first KV group
-    n0 = lens[0]
-    qs = q.detach()[:, :h // hk, :n0].clone().requires_grad_(True)
-    ks = k.detach()[:, :1, :n0].clone().requires_grad_(True)
-    vs = v.detach()[:, :1, :n0].clone().requires_grad_(True)
-    ref = torch.nn.functional.scaled_dot_product_attention(qs, ks.expand(-1, h // hk, -1, -1),
-                                                           vs.expand(-1, h // hk, -1, -1), is_causal=True)
-    ref.backward(do[:, :h // hk, :n0])
-    cosf = lambda a, b: float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
-    cos = {"dq": cosf(grads[0][:, :h // hk, :n0], qs.grad), "dk": cosf(grads[1][:, :1, :n0], ks.grad),
-           "dv": cosf(grads[2][:, :1, :n0], vs.grad)}
-    bwd_tf = 2.5 * fwd_flops / (ms_bwd * 1e-3) / 1e12
-    peak = peaks["bf16_tflops_sustained"]
-    return {"name": "train fwd+bwd, packed varlen 16384 tokens H32 Hk8 D128 (BASELINE config 3)",
-            "segments": lens, "sum_len_sq": sum_sq,
-            "fwd_bwd_ms": {"hp_grad_dots(bf16)": res["bf16"], "fp4_rownorm(request)": res["fp4_rownorm"]},
-            "fwd_bwd_tflops": 3.5 * fwd_flops / (res["bf16"] * 1e-3) / 1e12,
-            "bwd_only_ms": ms_bwd, "grad_cosine_vs_bf16_sdpa": cos,
-            "roofline": {"bound": "tensor", "achieved": bwd_tf, "peak": peak, "unit": "TFLOP/s",
-                         "frac": bwd_tf / peak, "traffic": None,
-                         "kernel": "bwd_dkdv_kernel + bwd_dq_kernel (+ delta pre-pass)",
-                         "note": "2.5 x forward FLOPs (5 GEMMs; the S and dP recompute of the second kernel "
-                                 "is not counted) over the bf16 sustained GEMM peak"}}
+        return step
+
+    n = max(1, min(steps, 3))
+    ms, clocks, n = cx.timed(make(True), n, warm=1)
+    ms_c = ms
+    if cx.world > 1:
+        ms_c, _, _ = cx.timed(make(False), n, warm=1)
+    flops = 3.5 * 4.0 * z * h * float(seq) * float(seq) * d / 2.0
+    return {"name": f"config 5: Z1 H16 Hk4 S{seq} D256 causal fwd+bwd, ring attention over {cx.world} rank(s), "
+                    "zigzag chunks (rank r owns chunks r and 2W-1-r)",
+            "scaling": "strong", "ms_per_step": ms, "tflops_all_gpus": flops / (ms * 1e-3) / 1e12, "steps": n,
+            "compute_only_ms": ms_c, "exposed_comm_ms": max(ms - ms_c, 0.0), "clocks": clocks,
+            "kernel_status": _lib.read_status(dev),
+            "dtype": "fp4 forward + fp4 S recompute, bf16 gradient GEMMs"}
 
 
+# ------------------------------------------------------------------------------ GPU arm
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -329,53 +583,49 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    affinity = bind_near_gpu(torch, local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     import sageattention_b200.nvfp4 as nv
     from sageattention_b200 import _lib
+    from sageattention_b200.nvfp4 import distributed as RD
     from sageattention_b200.nvfp4 import flash
     _lib.lib()   # fails loudly if the CUDA library is missing
     peaks, peak_src = _measured_peaks()
+    cx = Ctx(torch, dist, rank, world, local, dev)
 
-    # each rank owns its own (batch, KV-group) shard of the full size: no data-path collective
-    qh, kh, vh = make_inputs(torch, 1234 + rank, dev)
+    # each rank owns its own full-size copy of the workload: no data-path collective ("weak")
+    qh, kh, vh = make_inputs(torch, 1234 + rank)
     qh, kh, vh = qh.pin_memory(), kh.pin_memory(), vh.pin_memory()
     q, k, v = qh.to(dev), kh.to(dev), vh.to(dev)
     scaling = D ** -0.5
     step = lambda: nv.nvfp4_flash_attention(q, k, v, scaling, causal=True, num_key_value_groups=H // HK)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local, enabled=rank == 0).start()
     for _ in range(max(args.warmup, 3)):
         out = step()
-    barrier()
+    cx.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    cx.barrier()
     a.record()
     for _ in range(args.steps):
         out = step()
     b.record()
-    barrier()
+    cx.barrier()
     ms = a.elapsed_time(b) / args.steps
     status = _lib.read_status(dev)
 
     # forward kernel alone (operands packed once): the roofline kernel
-    s_pad = S
-    qnv, qsc = nv._quant_nvfp4(q.reshape(Z * H, S, D))
-    knv, ksc = nv._quant_nvfp4(k.reshape(Z * HK, S, D))
-    vnv, vsc = nv._quant_nvfp4(v.reshape(Z * HK, S, D), transpose=True, k_pad=s_pad)
+    qnv, qsc, knv, ksc, vnv, vsc = flash._quant_qkv_fwd(q.reshape(Z * H, S, D), k.reshape(Z * HK, S, D),
+                                                        v.reshape(Z * HK, S, D), S)
     kern = lambda: flash._run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, Z, H, HK, S, S, D, scaling,
                                            torch.bfloat16, causal=True)
     for _ in range(3):
         kern()
     torch.cuda.synchronize()
     ms_kernel = ev_ms(torch, kern, args.steps)
+    del qnv, qsc, knv, ksc, vnv, vsc
 
     # end to end: pinned host buffers in, output back to pinned host memory, every step.  Measured
     # twice: serially (copy in, compute, copy out, one after the other) and as a user would run a
@@ -390,13 +640,13 @@ def run_gpu(args):
 
     for _ in range(2):
         e2e_step()
-    barrier()
+    cx.barrier()
     e2e_steps = max(3, min(args.steps, 10))
     a.record()
     for _ in range(e2e_steps):
         e2e_step()
     b.record()
-    barrier()
+    cx.barrier()
     ms_e2e_serial = a.elapsed_time(b) / e2e_steps
 
     cur = torch.cuda.current_stream()
@@ -429,143 +679,101 @@ def run_gpu(args):
         cur.wait_stream(s_out)
 
     e2e_pipelined(2)
-    barrier()
+    cx.barrier()
     a.record()
     e2e_pipelined(e2e_steps)
     b.record()
-    barrier()
+    cx.barrier()
     ms_e2e = a.elapsed_time(b) / e2e_steps
-    # keep the GPU busy long enough for a few 100 ms clock samples, then stop the sampler
-    t_end = time.time() + 1.0
+    # keep the GPU busy long enough for a few clock samples, then stop the sampler
+    t_end = time.time() + 0.6
     while rank == 0 and time.time() < t_end:
-        kern()
+        kern_out = step()
     torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
+    del slots
+    ms, ms_kernel, ms_e2e, ms_e2e_serial = cx.max_over_ranks(ms, ms_kernel, ms_e2e, ms_e2e_serial)
+    copies = host_copy_rates(cx)
 
-    t = torch.tensor([ms, ms_kernel, ms_e2e, ms_e2e_serial], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_kernel, ms_e2e, ms_e2e_serial = (float(x) for x in t.tolist())
+    secondary = []
+    probe = measure_peaks(cx, _lib)
+    secondary.append(sharded_prefill(cx, nv, RD, q, k, v, out, args.steps))
+    out_unit = out[0, :H // HK].float().cpu().numpy() if rank == 0 else None
+    del q, k, v, out
+    torch.cuda.empty_cache()
+    secondary.append(train_metrics(cx, nv, RD, peaks, min(args.steps, 10)))
+    torch.cuda.empty_cache()
+    secondary.append(decode_metrics(cx, nv, peaks, 50))
+    torch.cuda.empty_cache()
+    if world == 1:
+        secondary.append(pack_metrics(cx, nv, peaks))
+        torch.cuda.empty_cache()
+    secondary.append(ring_metrics(cx, nv, RD, _lib, args.steps, args.ring_seq))
+    torch.cuda.empty_cache()
 
     if rank == 0:
-        # correctness spot check against fp32 attention on one head (not timed)
-        ref = torch.nn.functional.scaled_dot_product_attention(
-            q[:1, :1].float(), k[:1, :1].float(), v[:1, :1].float(), is_causal=True)
-        cosv = float(torch.nn.functional.cosine_similarity(out[:1, :1].float().flatten(), ref.flatten(), dim=0))
-        secondary = secondary_metrics(torch, nv, peaks) if world == 1 else []
-        cpu_v, cpu_dt, cpu_sample_desc = cpu_sample() if world == 1 else (None, None, None)
+        # CPU leg (rank 0, N = 1 only): the oracle on unit (z=0, kv-head 0) of THIS run's inputs --
+        # its time is the CPU baseline, its result is the parity check of the headline kernel
+        cpu = None
+        parity = None
+        if world == 1:
+            g = H // HK
+            f = lambda t: t.float().numpy()
+            cpu_v, cpu_dt, cpu_desc, parity = cpu_sample(f(qh[0, :g]), f(kh[0, 0]), f(vh[0, 0]), out_unit)
+            cpu = {"value": cpu_v, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                   "sample": cpu_desc, "seconds": cpu_dt}
         tflops = world * FLOPS_PER_STEP / (ms * 1e-3) / 1e12
         k_tflops = FLOPS_PER_STEP / (ms_kernel * 1e-3) / 1e12
-        fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+        fp4_peak = probe["fp4_mma_tflops"]
+        fp4_inferred = 4.0 * peaks["bf16_tflops"]
         exps = Z * H * S * S / 2.0
+        sm_hz = (clocks or {}).get("sm_mhz") or 1965.0
         line = {
             "metric": "fp4_attn_fwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp4(e2m1, e4m3 scale per 16) x fp4, fp32 accumulate", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu_shard": f"Z{Z} H{H} Hk{HK} S{S} D{D}",
-                       "parallelism": f"(batch,kv-group) shards x{world}, no collective",
+                       "parallelism": f"one full-size copy per rank x{world}, no collective",
                        "l2": "inputs (402 MB bf16 + 101 MB packs) larger than the 126 MB L2",
                        "k_outliers": "8 channels, offset sigma=2 (variance 4)"},
             "roofline": {"bound": "tensor", "achieved": k_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
                          "frac": k_tflops / fp4_peak,
+                         "peak_fp4_measured": fp4_peak,
+                         "peak_source": "nvfp4_peak_probe: back-to-back kind::mxf4nvf4 M128 N128 K64 MMAs on every SM, "
+                                        "resident operands, CUDA-event timed in this run (burst: the kernel is timed alone)",
+                         "peak_4x_bf16_burst": fp4_inferred, "frac_of_4x_bf16_burst": k_tflops / fp4_inferred,
+                         "peak_4x_bf16_source": f"4 x bf16_tflops ({peak_src} MEASURED_PEAKS.json)",
                          # ncu, Z1 S4096 case: dram read 14.34 MB for 14.16 MB of packed operands (1.01x),
                          # the output is written once: scaled to this launch = packs + bf16 output
                          "traffic": 1.01 * (Z * H * S * D * 0.5625 + 2 * Z * HK * S * D * 0.5625) + Z * H * S * D * 2,
                          "kernel": "fwd_kernel<128,bf16>", "kernel_ms": ms_kernel,
-                         "peak_source": f"4 x bf16_tflops_sustained ({peak_src} MEASURED_PEAKS.json); "
-                                        "no FP4 GEMM figure is in that file",
                          "co_bound": {"what": "one MUFU ex2 per score element at 16 lanes/clk/SM (the e2m1x2 "
                                               "converts run on a separate pipe)",
                                       "elements": exps,
-                                      "min_ms_at_1.965GHz": exps / (148 * 16 * 1.965e9) * 1e3}},
+                                      "min_ms_at_sampled_clock": exps / (148 * 16 * sm_hz * 1e6) * 1e3,
+                                      "frac_of_co_bound": exps / (148 * 16 * sm_hz * 1e6) * 1e3 / ms_kernel},
+                         "measured_pipe_rates": probe},
             "e2e": {"value": world * FLOPS_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": ms_e2e,
                     "how": "requests pipelined over three streams (H2D of step i+1 and D2H of step i-1 "
                            "overlap the kernels of step i); every step copies its own inputs and result",
                     "serial_ms_per_step": ms_e2e_serial,
                     "h2d_bytes_per_step": int((qh.numel() + kh.numel() + vh.numel()) * 2),
-                    "d2h_bytes_per_step": int(out_h[0].numel() * 2)},
-            "gpu_launches": 4 * args.steps,
-            "clocks": clocks, "kernel_status": status, "cosine_vs_fp32_sdpa_head0": cosv,
+                    "d2h_bytes_per_step": int(out_h[0].numel() * 2),
+                    "host_copy": copies, "cpu_affinity": affinity,
+                    # what the plain copies of one step cost at the rates just measured on these ranks
+                    "copy_bound_ms_per_step": max((qh.numel() + kh.numel() + vh.numel()) * 2 / copies["h2d_gbs_per_rank"],
+                                                  out_h[0].numel() * 2 / copies["d2h_gbs_per_rank"]) * 1e-6},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks, "kernel_status": status, "parity": parity,
             "secondary": secondary,
         }
-        if cpu_v is not None:
-            line["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": os.cpu_count(),
-                                    "kind": "port", "sample": cpu_sample_desc, "seconds": cpu_dt}
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
-
-
-def run_ring(args):
-    """BASELINE config 5: Z1 H16 Hk4 S131072 D256 causal forward + backward, the sequence split
-    over the ranks (context-parallel ring attention; one rank = the plain single-GPU operators)."""
-    import torch
-    import torch.distributed as dist
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    import sageattention_b200.nvfp4 as nv
-    from sageattention_b200 import _lib
-    from sageattention_b200.nvfp4 import distributed as RD
-    z, h, hk, d, s = 1, 16, 4, 256, args.ring_seq
-    s_loc = s // world
-    g = torch.Generator(device=dev).manual_seed(50 + rank)
-    rn = lambda *sh: torch.randn(*sh, device=dev, dtype=torch.bfloat16, generator=g)
-    q, k, v, do = rn(z, h, s_loc, d), rn(z, hk, s_loc, d), rn(z, hk, s_loc, d), rn(z, h, s_loc, d)
-    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-
-    def step():
-        if world == 1:
-            o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
-                                         backward_grad_dots="bf16")
-        else:
-            o = RD.ring_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk)
-        o.backward(do)
-        q.grad = k.grad = v.grad = None
-
-    def timed(n):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n):
-            step()
-        b.record()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / n
-
-    for _ in range(max(1, min(args.warmup, 2))):
-        step()
-    steps = max(1, min(args.steps, 5))
-    ms = timed(steps)
-    RD.COMMUNICATE = False            # same kernels, same schedule, no messages
-    step()
-    ms_compute = timed(steps)
-    RD.COMMUNICATE = True
-    t = torch.tensor([ms, ms_compute], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_compute = (float(x) for x in t.tolist())
-    if rank == 0:
-        flops = 3.5 * 4.0 * z * h * float(s) * float(s) * d / 2.0
-        print(json.dumps({
-            "metric": "fp4_attn_fwd_bwd_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": steps, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp4 S recompute + bf16 gradient GEMMs", "data": "synthetic",
-            "config": {"workload": f"BASELINE config 5: Z1 H16 Hk4 S{s} D256 causal fwd+bwd, ring attention over "
-                                   f"{world} rank(s), zigzag sequence chunks (rank r owns chunks r and 2W-1-r)"},
-            "compute_only_ms": ms_compute, "exposed_comm_ms": max(ms - ms_compute, 0.0),
-            "kernel_status": _lib.read_status(dev)}))
-    if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -590,18 +798,32 @@ def run_profile_case(args):
         q = rn(16, 32, 1, 128)
         packed = cache.get_packed()
         fn = lambda: nv.nvfp4_flash_decode_prequant(q, packed, 128 ** -0.5, 4)
-    elif case == "bwd":        # Z1 H32 Hk8 S4096 D128 causal fwd+bwd: 0.48 TFLOP per step
+    elif case in ("bwd", "bwd_fp4"):   # Z1 H32 Hk8 S4096 D128 causal fwd+bwd: 0.48 TFLOP per step
         q, k, v, do = rn(1, 32, 4096, 128), rn(1, 8, 4096, 128), rn(1, 8, 4096, 128), rn(1, 32, 4096, 128)
         q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+        mode = "bf16" if case == "bwd" else "fp4_rownorm"
 
         def fn():
             o = nv.nvfp4_flash_attn_func(q, k, v, 128 ** -0.5, causal=True, num_key_value_groups=4,
-                                         backward_grad_dots="bf16")
+                                         backward_grad_dots=mode)
             o.backward(do)
             q.grad = k.grad = v.grad = None
     elif case == "pack":       # 64 x 8192 x 128 bf16: 172 MB read+written per launch
         x = rn(64, 8192, 128)
         fn = lambda: (nv._quant_nvfp4(x), nv._quant_nvfp4(x, transpose=True))
+    elif case == "umma_peak":  # the FP4 / bf16 tensor-pipe and ALU-pipe rates of this device
+        import torch.distributed as dist
+        cx = Ctx(torch, dist, 0, 1, 0, torch.device("cuda", 0))
+        sampler = ClockSampler(0).start()
+        rates = measure_peaks(cx, _lib)
+        for _ in range(20):
+            measure_peaks(cx, _lib)
+        clocks = sampler.stop()
+        mhz = (clocks or {}).get("sm_mhz") or 1965.0
+        per_clk = {k_: v_ / (mhz * 1e6) for k_, v_ in rates.items() if k_.endswith("per_clk")}
+        print(json.dumps({"profile_case": case, "rates": rates, "per_sm_per_clk_at_sampled_clock": per_clk,
+                          "clocks": clocks, "status": _lib.read_status(dev)}))
+        return
     else:
         raise SystemExit(f"unknown profile case {case}")
     for _ in range(args.steps):
@@ -612,22 +834,20 @@ def run_profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "fwd_d256", "decode", "pack", "bwd"],
+    ap.add_argument("--profile-case", default=None,
+                    choices=["fwd", "fwd_d256", "decode", "pack", "bwd", "bwd_fp4", "umma_peak"],
                     help="run one small kernel case --steps times (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring"],
-                    help="prefill = BASELINE config 2 (the headline); ring = config 5 forward+backward")
-    ap.add_argument("--ring-seq", type=int, default=131072)
+    ap.add_argument("--ring-seq", type=int, default=131072,
+                    help="sequence length of the config-5 entry (131072 as stated; smaller for quick runs)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)
     elif args.impl == "reference":
         run_reference(args)
-    elif args.workload == "ring":
-        run_ring(args)
     else:
         run_gpu(args)
 

@@ -60,6 +60,28 @@ int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, i
                uint8_t* sc, int64_t ssb, int64_t ssr, nvfp4_stream_t stream);
 
 /*
+ * Both packs of x [B, S, d] (element strides sxb, sxs; unit stride along d) from ONE read: along d
+ * (dnib [B, S, d/2], dsc [B, S, d/16]) and along S as the transposed layout (tnib [B, d, s_pad/2],
+ * tsc [B, d, s_pad/16], tokens >= S read as +0.0).  All four outputs contiguous.  Replaces
+ * `_quant_nvfp4_dual` / `_quant_nvfp4_dual_kernel` (flash.py:434-561); bytes equal two nvfp4_pack
+ * calls.  d % 16 == 0, s_pad % 16 == 0, s_pad >= S.
+ */
+int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
+                    int64_t sxb, int64_t sxs, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib,
+                    uint8_t* tsc, nvfp4_stream_t stream);
+
+/*
+ * Forward pre-pack in ONE launch: Q [bq, s_q, d] and K [bk, s_kv, d] along d, V [bk, s_kv, d] along
+ * the keys as V^T padded to s_pad.  Replaces `_quant_qkv_fwd` / `_quant_qkv_fwd_kernel`
+ * (flash.py:579-732).  Inputs have unit stride along d and element strides (batch, row) as given;
+ * outputs are contiguous in the layouts of nvfp4_pack.  Bytes equal three nvfp4_pack calls.
+ */
+int nvfp4_pack_qkv(const void* q, const void* k, const void* v, int dtype, int64_t bq, int64_t bk,
+                   int64_t s_q, int64_t s_kv, int64_t s_pad, int d, int64_t sqb, int64_t sqr,
+                   int64_t skb, int64_t skr, int64_t svb, int64_t svk, uint8_t* qnv, uint8_t* qsc,
+                   uint8_t* knv, uint8_t* ksc, uint8_t* vnv, uint8_t* vsc, nvfp4_stream_t stream);
+
+/*
  * Rotary position embedding fused into the packer: y = rope(x) is rounded once to the input dtype
  * and packed along D exactly as nvfp4_pack would pack it, without y ever reaching HBM.  The
  * reference names this fused producer as the condition for an end-to-end win of its pre-packed
@@ -160,10 +182,13 @@ int nvfp4_decode_static(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, 
  * Exact merge of two attention results over disjoint key sets from their log-sum-exps:
  * out = (e^{lse1-m} o1 + e^{lse2-m} o2) / (e^{lse1-m} + e^{lse2-m}).  Replaces the torch
  * expressions of NVFP4KVCache.hybrid_decode (kv_cache.py:346-351).  o1,o2,out: [rows, d] in
- * `dtype`; lse1,lse2: [rows] fp32.
+ * `dtype`; lse1,lse2: [rows] fp32; lse_out [rows] fp32 receives the merged log-sum-exp
+ * m + log(e^{lse1-m} + e^{lse2-m}) (rows where both inputs are -inf stay -inf and get a zero
+ * output row) or is NULL.
  */
 int nvfp4_lse_merge(const void* o1, const float* lse1, const void* o2, const float* lse2,
-                    void* out, int dtype, int64_t rows, int d, nvfp4_stream_t stream);
+                    void* out, float* lse_out, int dtype, int64_t rows, int d,
+                    nvfp4_stream_t stream);
 
 /*
  * Exact attention of one query token per head over a short high-precision window held in ring
@@ -236,6 +261,26 @@ int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, con
                  int grad_dtype, int64_t z,
                  int64_t h, int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
                  int* status, nvfp4_stream_t stream);
+
+/*
+ * Measured pipe rates (no counterpart in the reference): launches a resident-operand micro-kernel
+ * on every SM -- what = 0: tcgen05.mma kind::mxf4nvf4 M128 N128 K64; 1: kind::f16 (bf16) M128 N128
+ * K16; 2: ex2.approx.f32; 3: cvt e2m1x2; 4: fma.f32 -- `iters` operations per issuing thread, and
+ * stores the work of one launch in *work_per_launch (FLOP for 0/1, thread-instructions for 2-4).
+ * The caller times the launch with CUDA events; the result is the roofline denominator benchmarks
+ * of this library quote.  `sink` is one device float (never written in practice).
+ */
+int nvfp4_peak_probe(int what, int iters, double* work_per_launch, float* sink, int* status,
+                     nvfp4_stream_t stream);
+
+/*
+ * Self-test of the failure-detection path (no counterpart in the reference, whose kernels have no
+ * device-side waits): one small kernel waits on a barrier that is never completed, with a budget of
+ * `spins` probes, gives up, and writes KSTAT_WAIT_TIMEOUT (0x100) | site to *status exactly as a
+ * production kernel would.  Nothing asynchronous is in flight and nothing traps: the kernel ends
+ * by itself in well under a millisecond and the context stays usable.
+ */
+int nvfp4_selftest_wait_timeout(int site, unsigned spins, int* status, nvfp4_stream_t stream);
 
 #ifdef __cplusplus
 }

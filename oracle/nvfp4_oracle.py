@@ -329,12 +329,15 @@ def decode_split_plan(s_kv: int, zhk: int, block_n: int = 128, target_programs: 
 
 
 def decode_prequant(query, kv_packed, scaling, g=1, block_n=128, split_kv=None,
-                    target_programs=256):
+                    target_programs=256, pieces=None):
     """Split-K decode over packs with exact combine; flash.py:3031-3208 and kv_cache.py:83-97.
 
     query [Z,H,1,D] fp32; kv_packed as returned by ``quant_kv_decode``.  ``split_kv`` (keys per
     split, multiple of block_n) overrides the reference heuristic so a kernel with a different
-    split policy can be checked tile-for-tile.  Returns (out fp32 [Z,H,1,D], lse fp32 [Z,H]).
+    split policy can be checked tile-for-tile.  ``pieces`` (unit index -> list of (lo, hi) key
+    ranges, multiples of block_n except the last hi) replaces the equal splits altogether, for
+    decompositions that cut units at arbitrary tile boundaries.
+    Returns (out fp32 [Z,H,1,D], lse fp32 [Z,H]).
     """
     query = np.asarray(query, np.float32)
     z, h, one, d = query.shape
@@ -353,8 +356,9 @@ def decode_prequant(query, kv_packed, scaling, g=1, block_n=128, split_kv=None,
     vis = np.ones((g, s_kv), dtype=bool)
     for u in range(zhk):
         parts = []
-        for start in range(0, s_kv, split_kv):
-            hi = min(s_kv, start + split_kv)
+        ranges = pieces[u] if pieces is not None else [(st, min(s_kv, st + split_kv))
+                                                       for st in range(0, s_kv, split_kv)]
+        for start, hi in ranges:
             parts.append(_walk_tiles(qd[u], kd[u], vdT[u], scaling, vis, None, block_n, start, hi))
         ms = np.stack([p[1] for p in parts])                # [nsplit, g]
         gm = ms.max(axis=0)

@@ -22,6 +22,11 @@ SIGNATURES = {
     "nvfp4_last_error": (c_char_p, []),
     "nvfp4_pack": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                            c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
+    "nvfp4_pack_dual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int64, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvfp4_pack_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
+                               c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvfp4_kv_append": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int64,
                                 c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                 c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
@@ -37,7 +42,7 @@ SIGNATURES = {
                                     c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
                                     c_int64, c_int64, c_int, c_int, c_int64, c_float, c_void_p,
                                     c_void_p, c_int, c_int64, c_void_p, c_void_p]),
-    "nvfp4_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+    "nvfp4_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
                                 c_int, c_void_p]),
     "nvfp4_window_attention": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p,
                                        c_int64, c_int64, c_int, c_int, c_int64, c_int64, c_int64,
@@ -49,6 +54,8 @@ SIGNATURES = {
                                c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_bwd_hp": (c_int, [c_void_p] * 16 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                              c_int, c_float, c_int, c_void_p, c_void_p]),
+    "nvfp4_peak_probe": (c_int, [c_int, c_int, POINTER(ctypes.c_double), c_void_p, c_void_p, c_void_p]),
+    "nvfp4_selftest_wait_timeout": (c_int, [c_int, ctypes.c_uint, c_void_p, c_void_p]),
     "nvfp4_fwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "nvfp4_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,
                           c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_int,
@@ -79,6 +86,46 @@ def check(rc: int, what: str = "nvfp4") -> None:
     if rc != 0:
         msg = lib().nvfp4_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def call(name: str, device, *args) -> None:
+    """Run the C entry ``name`` with ``device`` current and raise on a non-zero return.
+
+    The C entries launch on the calling thread's current device (tensor maps, SM counts and the
+    static scratch address are all per device), so every launch goes through this guard: a tensor
+    on ``cuda:1`` is served correctly while ``cuda:0`` is current.  With ``NVFP4_CHECK_STATUS=1`` in
+    the environment the device status word is read back (a synchronising read) after the call and
+    an expired in-kernel wait raises instead of returning undefined tensors.
+    """
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"{name}: operands must live on a CUDA device (got {dev})")
+    with torch.cuda.device(dev):
+        rc = getattr(lib(), name)(*args)
+    check(rc, name)
+    if os.environ.get("NVFP4_CHECK_STATUS", "0") == "1":
+        st = read_status(dev)
+        if st:
+            raise RuntimeError(f"{name}: a bounded in-kernel wait expired (status 0x{st:x}: "
+                               f"site {st & 0xFF}); outputs of this call are undefined")
+
+
+def same_device(*tensors) -> torch.device:
+    """The one CUDA device all given tensors (None entries skipped) live on."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                f"operands must be CUDA tensors: sageattention_b200 has no CPU path (got device {t.device})")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"operands live on different devices: {dev} and {t.device}")
+    if dev is None:
+        raise RuntimeError("no tensor operand")
+    return dev
 
 
 def dtype_code(dt: torch.dtype) -> int:

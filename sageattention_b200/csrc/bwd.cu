@@ -156,15 +156,6 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
   }
 }
 
-#ifdef NVFP4_BWD_TIMING
-#ifndef BTRACE_Y
-#define BTRACE_Y 0
-#endif
-#define BTRACE(role, step, slot) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == BTRACE_Y && (step) < 80) p.timing[((role) * 80 + (step)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define BTRACE(role, step, slot) do { } while (0)
-#endif
-
 struct BwdParams {
   const uint8_t* qsc;   // [ZH, Sq, 8]
   const uint8_t* ksc;   // [ZHk, Skv, 8]
@@ -181,7 +172,6 @@ struct BwdParams {
   float scaling;
   int causal;
   int* status;
-  long long* timing;    // debug only (NVFP4_BWD_TIMING builds)
 };
 
 // 32 fp32 accumulator columns -> 32 contiguous gradient elements
@@ -389,7 +379,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         if (st + kBwdPrefetch < nstep) prefetch(st + kBwdPrefetch);
         if (st >= L::NSTAGE) mbar_wait(&empty[s], ((st / L::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * L::STAGE;
-        BTRACE(0, st, 0);
         mbar_expect_tx(&full_tma[s], L::QP + L::DO + L::Q);
 #pragma unroll
         for (int c = 0; c < L::KSUB; ++c)
@@ -445,18 +434,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         cp_async_wait<0>();
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&full_aux[s]); BTRACE(1, st, 0); }
+        if (lane == 0) mbar_arrive(&full_aux[s]);
       }
     }
-#ifdef NVFP4_BWD_TIMING
-  } else if (warp == 3) {
-    if (lane == 0 && p.timing && blockIdx.x == 0 && blockIdx.y == BTRACE_Y) {
-      for (int st = 0; st < min(nstep, 80); ++st) {
-        mbar_spin_wait(&full_tma[st % L::NSTAGE], (st / L::NSTAGE) & 1, &err, 20);
-        BTRACE(3, st, 0);
-      }
-    }
-#endif
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one() && nstep > 0) {
@@ -494,7 +474,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
         mbar_wait(&full_tma[s], ph, &err, 5);
         mbar_wait(&full_aux[s], ph, &err, 6);
         tc_fence_after();
-        BTRACE(2, st, 0);
         // S^T slot b: its P^T / dS^T were consumed by the gradient GEMMs of step st-2, issued
         // earlier on this in-order pipe
 #pragma unroll
@@ -507,22 +486,18 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
           umma_nvfp4(tmem + T_ST + b * 64, b_kp + (k >> 1) * 512 + (k & 1) * 2, x_qp + (k >> 1) * 256 + (k & 1) * 2,
                      id_s, tmem + T_SFK + k * 4, tmem + T_SFQ + b * SFQ_SLOT + k * 4, k > 0);
         umma_commit(&s_full[b]);
-        BTRACE(2, st, 1);
         if (st > 0) {
           mbar_wait(&dp_free, (st - 1) & 1, &err, 7);
           tc_fence_after();
         }
-        BTRACE(2, st, 2);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
           umma_bf16(tmem + T_DPT, b_v + (k >> 2) * 1024 + (k & 3) * 2, x_do + (k >> 2) * 512 + (k & 3) * 2, id_dp,
                     k > 0);
         umma_commit(&dp_full);
-        BTRACE(2, st, 3);
         if (st > 0) {
           mbar_wait(&pds_full[b ^ 1], ((st - 1) >> 1) & 1, &err, 8);
           tc_fence_after();
-          BTRACE(2, st, 4);
           grad_gemms(st - 1);
           umma_commit(&empty[(st - 1) % L::NSTAGE]);
         }
@@ -562,16 +537,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       const float* aux = reinterpret_cast<const float*>(sb + L::O_AUX) + grp * 32;
       const uint32_t slot = tmem + lane_addr + T_ST + b * 64 + grp * 32;
       const bool masked = !__all_sync(0xffffffffu, q0 >= ql && q0 + 32 <= qh);
-      [[maybe_unused]] const int trole = 4 + grp + 2 * (warp & 3);
-      [[maybe_unused]] const bool trc_any = lane == 0;
-      if (trc_any) BTRACE(trole, st, 0);
       mbar_wait(&full_aux[s], (st / L::NSTAGE) & 1, &err, 10);
-      if (trc_any) BTRACE(trole, st, 1);
       mbar_wait(&s_full[b], k2 & 1, &err, 11);
-      if (trc_any) BTRACE(trole, st, 2);
       mbar_wait(&dp_full, st & 1, &err, 13);
       tc_fence_after();
-      if (trc_any) BTRACE(trole, st, 3);
       // dP^T first: the single dP^T slot goes back to the issuer before any arithmetic
       uint32_t dr[32], sr[32];
       tmem_ld32(tmem + lane_addr + T_DPT + grp * 32, dr);
@@ -580,7 +549,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dp_free);
-      if (trc_any) BTRACE(trole, st, 4);
       // P^T -> 16 columns, dS^T -> the next 16, over the S^T columns just read
       {
         float pf[32];
@@ -589,16 +557,13 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_kp, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 16; ++e) w[e] = pack_bf16x2(pf[2 * e], pf[2 * e + 1]);
         tmem_st16(slot, w);
-        if (trc_any) BTRACE(trole, st, 5);
         ds_chunk<true>(pf, dr, w, aux + 64, 0.0f);
         tmem_st16(slot + 16, w);
       }
-      if (trc_any) BTRACE(trole, st, 6);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_full[b]);
-      if (trc_any) BTRACE(trole, st, 7);
     }
     // ---- epilogue: group g writes gradient columns [64g, 64g+64)
     TG* dkrow = static_cast<TG*>(p.dk) + ((int64_t)unit * p.s_kv + key) * D + half * 128 + grp * 64;
@@ -1021,11 +986,6 @@ extern "C" int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_
   p.dq = dq; p.dk = dk; p.dv = dv;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk); p.s_q = (int)s_q; p.s_kv = (int)s_kv;
   p.scaling = scaling; p.causal = (flags & NVFP4_FWD_CAUSAL) ? 1 : 0; p.status = status;
-#ifdef NVFP4_BWD_TIMING
-  p.timing = reinterpret_cast<long long*>(status) + 8;   // timing builds: the status buffer carries the trace
-#else
-  p.timing = nullptr;
-#endif
   const unsigned halves = (unsigned)(d / 128);
   auto launch = [&](auto kdkdv, auto kdq, int smem_dkdv, int smem_dq) -> int {
     cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkdv);

@@ -80,18 +80,23 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. `err` is a CTA-shared int (0 = healthy). Returns false on timeout.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err,
-                                          int site) {
+// Bounded wait with an explicit probe budget. `err` is a CTA-shared int (0 = healthy). Returns
+// false on timeout, after recording KSTAT_WAIT_TIMEOUT | site in `err`.
+__device__ __forceinline__ bool mbar_wait_n(uint64_t* bar, uint32_t parity, volatile int* err,
+                                            int site, uint32_t spins) {
   if (mbar_test_wait(bar, parity)) return true;
   if (mbar_try_wait(bar, parity)) return true;
   if (*err) return false;
-  for (uint32_t i = 0; i < NVFP4_WAIT_SPINS; ++i) {
+  for (uint32_t i = 0; i < spins; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*err) return false;
   }
   *err = KSTAT_WAIT_TIMEOUT | site;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err,
+                                          int site) {
+  return mbar_wait_n(bar, parity, err, site, NVFP4_WAIT_SPINS);
 }
 
 // Bounded wait that polls without parking the thread: lowest wake-up latency, meant for a lone

@@ -64,14 +64,8 @@ struct DecodeCfg {
   static_assert(T_END <= T_COLS, "TMEM budget exceeded");
 };
 
-#ifdef NVFP4_DECODE_TIMING
-#define DTRACE(role, idx, slot) do { if (p.timing && blockIdx.x == 0 && (idx) < 64) p.timing[((role) * 64 + (idx)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define DTRACE(role, idx, slot) do { } while (0)
-#endif
 
 struct DecodeParams {
-  long long* timing;  // debug only (NVFP4_DECODE_TIMING builds)
   const void* q;
   int64_t s_qz, s_qh;
   const uint8_t* ksc;
@@ -256,7 +250,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const int s = it % C::NSTAGE;
           if (it >= (uint32_t)C::NSTAGE) mbar_spin_wait(&empty[s], ((it / C::NSTAGE) & 1) ^ 1, &err, 1);
           uint8_t* st = s_stage + s * C::STAGE_BYTES;
-          DTRACE(0, it, 0);
           mbar_expect_tx(&full_kv[s], C::K_BYTES + C::V_BYTES);
 #pragma unroll
           for (int ks = 0; ks < C::KSUB; ++ks)
@@ -279,7 +272,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     auto publish = [&](uint32_t n) {
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&full_sf[n % C::NSTAGE]); DTRACE(1, n, 0); }
+      if (lane == 0) mbar_arrive(&full_sf[n % C::NSTAGE]);
     };
     for (int wi = 0; wi < my_items; ++wi) {
       int unit, t0, t1;
@@ -362,9 +355,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             const int s = it % C::NSTAGE;
             const uint32_t ph = (it / C::NSTAGE) & 1;
             mbar_spin_wait(&full_kv[s], ph, &err, 3);
-            DTRACE(2, it, 0);
             mbar_spin_wait(&full_sf[s], ph, &err, 4);
-            DTRACE(2, it, 1);
             tc_fence_after();
             uint8_t* st = s_stage + s * C::STAGE_BYTES;
             const uint32_t sfk = tmem + C::T_SFK + (b * C::STMAX + j) * C::KB * 4;
@@ -388,7 +379,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
           }
           umma_commit(&s_full[b]);
-          DTRACE(3, su, 0);
         }
       }
       it_w += (uint32_t)(t1 - t0);
@@ -407,7 +397,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           const int b = su & 1;
           const int nt = min(ST, t1 - ts0);
           mbar_spin_wait(&p_full[b], (su >> 1) & 1, &err, 7);
-          DTRACE(3, su, 1);
           tc_fence_after();
           for (int j = 0; j < nt; ++j, ++it) {
             // V^T tile and scales of stage s were observed by the QK^T issuer before S^T of this
@@ -435,7 +424,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             umma_commit(&empty[s]);
           }
           umma_commit(&o_full[b]);
-          DTRACE(3, su, 2);
         }
       }
     }
@@ -507,9 +495,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       for (int ts0 = t0; ts0 < t1; ts0 += ST, ++su) {
         const int b = su & 1;
         const int nt = min(ST, t1 - ts0);
-        if (tall == 0) DTRACE(4, su, 0);
         mbar_wait(&s_full[b], (su >> 1) & 1, &err, 8);
-        if (tall == 0) DTRACE(4, su, 1);
         tc_fence_after();
         float sv[TPG][NQ];
         {
@@ -558,9 +544,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
               for (int qi = 0; qi < NQ; ++qi) xch[b][wq][grp * TPG + jj][qi] = wmx[jj][qi];
           }
         }
-        if (tall == 0) DTRACE(4, su, 2);
         named_bar_sync(1, 256);
-        if (tall == 0) DTRACE(4, su, 3);
         // running maximum advances tile by tile; weights bring each tile to the round's end
         float m_mine[TPG][NQ];
 #pragma unroll
@@ -579,9 +563,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
         // the previous round's PV has had a whole round to finish: fold it into registers now,
         // which also frees its P buffers for rewriting
-        if (tall == 0) DTRACE(4, su, 4);
         if (have_prev) accumulate(su - 1, nt_prev);
-        if (tall == 0) DTRACE(4, su, 5);
         float w_cur[TPG][NQ], pv[TPG][NQ], am[TPG][NQ];
 #pragma unroll
         for (int jj = 0; jj < TPG; ++jj)
@@ -647,17 +629,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int qi = 0; qi < NQ; ++qi) m_end_prev[qi] = m_run[qi];
         nt_prev = nt;
         have_prev = true;
-        if (tall == 0) DTRACE(4, su, 6);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[b]);
-        if (tall == 0) DTRACE(4, su, 7);
       }
       // ---- item epilogue: fold the last round, merge the two groups, write un-normalised partials
-      const bool etr = lane == 0 && wi == 0;
-      if (etr) DTRACE(5, sw, 0);
       if (have_prev) accumulate(su - 1, nt_prev);
-      if (etr) DTRACE(5, sw, 1);
       {
         // bring this group's accumulator to the final running maximum
 #pragma unroll
@@ -681,9 +658,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
           if (lane == 0) lred[sw][qi] = v;
         }
-        if (etr) DTRACE(5, sw, 2);
         named_bar_sync(1, 256);
-        if (etr) DTRACE(5, sw, 3);
         if (grp == 0) {
           const int64_t w = slot_at(wi);
           float* acc = p.ws_acc + w * 16 * D;
@@ -705,7 +680,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             p.ws_l[w * 16 + ts] = lsum;
           }
         }
-        if (etr) DTRACE(5, sw, 4);
         // no barrier here: the merge buffer (= the P tiles) and lred are next written after the
         // max-exchange barrier of the next item's first round, which these reads precede in
         // program order; the kernel's final __syncthreads covers the last item
@@ -927,11 +901,6 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   if (rc) return rc;
 
   DecodeParams p;
-  p.timing = nullptr;
-#ifdef NVFP4_DECODE_TIMING
-  p.timing = reinterpret_cast<long long*>(lse);  // debug builds smuggle the trace buffer in `lse`
-  lse = nullptr;
-#endif
   p.q = q; p.s_qz = s_qz; p.s_qh = s_qh;
   p.ksc = ksc; p.ksc_unit = ksc_unit;
   p.vsc = vsc; p.vsc_unit = vsc_unit; p.vsc_row = vsc_row;

@@ -58,15 +58,7 @@ struct FwdCfg {
   static_assert(T_END <= 512, "TMEM budget exceeded");
 };
 
-#ifdef NVFP4_FWD_TIMING
-// debug trace: trace[role][tile][slot] = clock64, recorded by CTA (0,0) only
-#define TRACE(role, tile, slot) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 80) p.timing[((role) * 80 + (tile)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(role, tile, slot) do { } while (0)
-#endif
-
 struct FwdParams {
-  long long* timing;   // debug only (NVFP4_FWD_TIMING builds)
   const uint8_t* qsc;  // [ZH, Sq, D/16]
   const uint8_t* ksc;  // [ZHk, Skv, D/16]
   const uint8_t* vsc;  // [ZHk, D, s_pad/16]
@@ -124,7 +116,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __shared__ uint64_t m_ready[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) TRACE(5, 70, 0);
   // grid = (heads, query tiles): all heads of the heaviest (last) query tile are scheduled first,
   // so the kernel ends on the cheapest tiles instead of on a long straggler
   const int mblk = gridDim.y - 1 - blockIdx.y;
@@ -166,7 +157,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  if (tid == 0) TRACE(5, 70, 1);
   // varlen: rows of a tile are sorted by sample, so the first row has the earliest start
   const int t_lo = s_lo_tile;
   const int ntile = max(t_hi - t_lo, 0);
@@ -181,7 +171,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int s = i % C::NSTAGE, t = t_lo + i;
         if (i >= C::NSTAGE) mbar_wait(&empty[s], ((i / C::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
-        TRACE(0, i, 0);
         mbar_expect_tx(&full_kv[s], C::K_BYTES + C::V_BYTES);
 #pragma unroll
         for (int ks = 0; ks < C::KSUB; ++ks)
@@ -250,7 +239,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       if (i + 1 < ntile) fetch(t_lo + i + 1);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&full_sf[s]); TRACE(1, i, 0); }
+      if (lane == 0) mbar_arrive(&full_sf[s]);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ QK^T issuer
@@ -266,11 +255,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const int s = j % C::NSTAGE, b = j % C::NSBUF;
         const uint32_t ph = (j / C::NSTAGE) & 1;
         mbar_wait(&full_kv[s], ph, &err, 5);
-        TRACE(2, j, 0);
         mbar_wait(&full_sf[s], ph, &err, 6);
-        TRACE(2, j, 1);
         if (j >= C::NSBUF) mbar_spin_wait(&s_free[b], ((j / C::NSBUF) & 1) ^ 1, &err, 7);
-        TRACE(2, j, 2);
         tc_fence_after();
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
         const uint32_t sfk = tmem + C::T_SFK + (j & 1) * C::KB * 4;
@@ -300,9 +286,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mbar_wait(&full_kv[s], (i / C::NSTAGE) & 1, &err, 15);
         mbar_wait(&full_sf[s], (i / C::NSTAGE) & 1, &err, 16);
         mbar_spin_wait(&p_full[b], (i / C::NSBUF) & 1, &err, 8);
-        TRACE(3, i, 0);
         tc_fence_after();
-        TRACE(3, i, 2);
         uint8_t* st = s_stage + s * C::STAGE_BYTES;
         const uint32_t sfp = tmem + C::T_SFP + (i & 1) * 8;
         const uint32_t sfv = tmem + C::T_SFV + (i & 1) * (2 * C::NT * 4);
@@ -313,7 +297,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int k = 0; k < 2 * C::NT; ++k)
           tmem_cp_32x128b_warpx4(sfv + k * 4,
                                  smem_u32(st + C::K_BYTES + C::V_BYTES + C::KSF_BYTES + k * 512));
-        TRACE(3, i, 3);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const uint64_t ad = make_smem_desc(smem_u32(s_p + b * C::P_BYTES) + k * 32, 16, 512, 4);
@@ -321,10 +304,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
           umma_nvfp4(tmem + C::T_O, ad, bd, idesc_pv, sfp + k * 4, sfv + k * C::NT * 4,
                      (i > 0 || k > 0) ? 1u : 0u);
         }
-        TRACE(3, i, 4);
         umma_commit(&pv_done[b]);
         umma_commit(&empty[s]);
-        TRACE(3, i, 1);
       }
     }
     __syncwarp();
@@ -411,10 +392,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r[e]);
         mask_chunk(c, sv);
       };
-      const bool trc = (wq == 0 && half == 0 && lane == 0);
-      if (trc) TRACE(4 + grp, i, 0);
       mbar_wait(&s_full[b], (i >> 1) & 1, &err, 9);
-      if (trc) TRACE(4 + grp, i, 1);
       tc_fence_after();
       if constexpr (kVarlen)   // keys are sorted by sample: first and last id equal => all equal
         tile_masked = tile_masked || !(q_one_sample && aux_seq0[0] == my_seq && aux_seq0[127] == my_seq);
@@ -437,7 +415,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         load_chunk(c, sv);
         group_max(c, sv);
       }
-      if (trc) TRACE(4 + grp, i, 2);
       const uint32_t xb = (uint32_t)(((i >> 1) & 1) * 4 + grp * 2);
       sts_f32(xmax_s + ((xb + half) * 128 + row_in) * 4u, mx);
       named_bar_sync(1 + grp, 256);
@@ -448,7 +425,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         mbar_wait(&m_ready[b ^ 1], ((i - 1) >> 1) & 1, &err, 13);
         m_prev = lds_f32(mrow_s + (uint32_t)((b ^ 1) * 128 + row_in) * 4u);
       }
-      if (trc) TRACE(4 + grp, i, 3);
       const float m_new = fmaxf(m_prev, mx * c2);
       if (half == 0) {
         sts_f32(mrow_s + (uint32_t)(b * 128 + row_in) * 4u, m_new);
@@ -478,7 +454,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       }
       // P buffer b must have been consumed by the PV of tile i - 2
       if (i >= 2) mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1, &err, 10);
-      if (trc) TRACE(4 + grp, i, 4);
       const uint32_t pt = smem_u32(s_p + b * C::P_BYTES);
       const uint32_t psf = smem_u32(s_psf + b * C::PSF_BYTES);
       const float2 c22 = make_float2(c2, c2);
@@ -519,7 +494,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         const float2 tt = __fadd2_rn(t01, t23);
         l_run += tt.x + tt.y;
       }
-      if (trc) TRACE(4 + grp, i, 5);
       if (__any_sync(0xffffffffu, changed)) {
         // O is rescaled (this thread: half of its row) once the PV of tile i - 1 has landed
         mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1, &err, 11);
@@ -544,14 +518,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
         tmem_st_wait();
         tc_fence_before();
       }
-      if (trc) TRACE(4 + grp, i, 6);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[b]);
-      if (trc) TRACE(4 + grp, i, 7);
     }
 
-    if (tid == 128) TRACE(5, 70, 3);
     // ---- epilogue: bring the four partial row sums to the final maximum, O / l -> out, LSE
     float m_fin = -INFINITY;
     if (ntile > 0) {
@@ -852,13 +823,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUt
       p.lse[(int64_t)zh * p.s_q + row] = m_fin * 0.6931471805599453f + logf(l_safe);
     }
   }
-  if (tid == 128) TRACE(5, 70, 4);
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) TRACE(5, 70, 5);
   if (tid == 0 && err != 0 && p.status != nullptr) atomicExch(p.status, err);
   if (warp == 1) tmem_dealloc(tmem, 512);
-  if (tid == 32) TRACE(5, 70, 6);
 }
 
 #undef FWD_HAS_SEQ
@@ -914,10 +882,6 @@ extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* 
   rc = make_tmap_u8_3d_sw64(&tv, vnv, s_pad / 2, d, zhk, s_pad / 2, (uint64_t)d * (s_pad / 2), 128, "nvfp4_fwd(V)");
   if (rc) return rc;
   FwdParams p;
-  p.timing = nullptr;
-#ifdef NVFP4_FWD_TIMING
-  p.timing = static_cast<long long*>(workspace);
-#endif
   p.qsc = qsc; p.ksc = ksc; p.vsc = vsc; p.bias = bias; p.seq_id = seq_id; p.seq_start = seq_start;
   p.out = out; p.so_z = so_z; p.so_h = so_h; p.so_s = so_s; p.lse = lse;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk);

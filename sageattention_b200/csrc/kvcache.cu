@@ -211,14 +211,23 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
 template <typename T>
 __global__ void lse_merge_kernel(const T* __restrict__ o1, const float* __restrict__ l1,
                                  const T* __restrict__ o2, const float* __restrict__ l2,
-                                 T* __restrict__ out, int64_t rows, int d) {
+                                 T* __restrict__ out, float* __restrict__ lse_out, int64_t rows, int d) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * d) return;
   const int64_t r = i / d;
   const float a1 = l1[r], a2 = l2[r];
   const float m = fmaxf(a1, a2);
+  if (m == -INFINITY) {   // a row neither side touched
+    out[i] = from_f32<T>(0.0f);
+    if (lse_out != nullptr && i == r * d) lse_out[r] = -INFINITY;
+    return;
+  }
   const float w1 = expf(a1 - m), w2 = expf(a2 - m);
-  out[i] = from_f32<T>((w1 * to_f32<T>(o1[i]) + w2 * to_f32<T>(o2[i])) / (w1 + w2));
+  // a side with weight 0 may hold anything (an untouched row of an empty buffer)
+  const float v1 = w1 > 0.0f ? w1 * to_f32<T>(o1[i]) : 0.0f;
+  const float v2 = w2 > 0.0f ? w2 * to_f32<T>(o2[i]) : 0.0f;
+  out[i] = from_f32<T>((v1 + v2) / (w1 + w2));
+  if (lse_out != nullptr && i == r * d) lse_out[r] = m + logf(w1 + w2);
 }
 
 template <typename T>
@@ -302,7 +311,8 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
 }
 
 extern "C" int nvfp4_lse_merge(const void* o1, const float* lse1, const void* o2, const float* lse2,
-                               void* out, int dtype, int64_t rows, int d, nvfp4_stream_t stream) {
+                               void* out, float* lse_out, int dtype, int64_t rows, int d,
+                               nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(o1 && o2 && lse1 && lse2 && out, "nvfp4_lse_merge: null pointer");
   if (rows * d == 0) return 0;
@@ -311,7 +321,7 @@ extern "C" int nvfp4_lse_merge(const void* o1, const float* lse1, const void* o2
 #define NVFP4_MERGE(T)                                                                           \
   lse_merge_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(o1), lse1,                     \
                                             static_cast<const T*>(o2), lse2, static_cast<T*>(out), \
-                                            rows, d);                                            \
+                                            lse_out, rows, d);                                   \
   return launch_result("nvfp4_lse_merge")
   switch (dtype) {
     case NVFP4_DT_BF16: NVFP4_MERGE(__nv_bfloat16);

@@ -34,14 +34,22 @@ __device__ __forceinline__ void load8(const T* p, bool vec_ok, int valid, float 
 // grid = (blocks over the R * ngroups groups of one batch entry, B); ngroups_log2 >= 0 when the
 // group count per row is a power of two (the usual D/16), which keeps 64-bit divisions out of
 // a kernel that is otherwise a few dozen instructions per thread.
+struct RowsArgs {
+  const void* x;
+  int64_t R, k_read, ngroups, per_batch, sxb, sxr;
+  int ngroups_log2, vec_in;
+  uint8_t* nib;
+  int64_t snb, snr;
+  uint8_t* sc;
+  int64_t ssb, ssr;
+};
+
+// group `gid` of batch entry `b`
 template <typename T>
-__global__ void __launch_bounds__(256) pack_rows_kernel(
-    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t ngroups, int ngroups_log2,
-    int64_t per_batch, int64_t sxb, int64_t sxr, uint8_t* __restrict__ nib, int64_t snb,
-    int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr, int vec_in) {
-  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gid >= per_batch) return;
-  const int64_t b = blockIdx.y;
+__device__ __forceinline__ void pack_rows_group(
+    const T* __restrict__ x, int64_t k_read, int64_t ngroups, int ngroups_log2,
+    int64_t sxb, int64_t sxr, uint8_t* __restrict__ nib, int64_t snb,
+    int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr, int vec_in, int64_t gid, int64_t b) {
   int64_t g, r;
   if (ngroups_log2 >= 0) {
     g = gid & (ngroups - 1);
@@ -71,6 +79,17 @@ __global__ void __launch_bounds__(256) pack_rows_kernel(
     for (int i = 0; i < 4; ++i) { pn[i] = (lo >> (8 * i)) & 0xFF; pn[4 + i] = (hi >> (8 * i)) & 0xFF; }
   }
   sc[b * ssb + r * ssr + g] = sb;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pack_rows_kernel(
+    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t ngroups, int ngroups_log2,
+    int64_t per_batch, int64_t sxb, int64_t sxr, uint8_t* __restrict__ nib, int64_t snb,
+    int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr, int vec_in) {
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= per_batch) return;
+  pack_rows_group<T>(x, k_read, ngroups, ngroups_log2, sxb, sxr, nib, snb, snr, sc, ssb, ssr, vec_in, gid,
+                     blockIdx.y);
 }
 
 // ---------------------------------------------------------------- rotary embedding + pack
@@ -129,18 +148,27 @@ __global__ void __launch_bounds__(256) rope_pack_rows_kernel(
 constexpr int kColsKeys = 128;  // contraction extent of a tile
 constexpr int kColsRows = 64;   // row (head-dim) extent of a tile
 
-template <typename T>
-__global__ void __launch_bounds__(256) pack_cols_kernel(
-    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
+struct ColsSmem {
+  float tile[kColsKeys][kColsRows + 1];
+  __align__(16) uint8_t onib[kColsRows][kColsKeys / 2];
+  __align__(8) uint8_t osc[kColsRows][kColsKeys / 16];
+};
+
+// One 128-key x 64-row tile (tile coordinates bx, by of batch entry b).  With kDual the same tile
+// also yields the pack along the contiguous axis (rows of 16 consecutive elements of each key):
+// dnib [B, keys, R/2], dsc [B, keys, R/16], from the one read of x.
+template <typename T, bool kDual>
+__device__ __forceinline__ void pack_cols_tile(
+    ColsSmem& sm, const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
-    int64_t ssr, int vec_in) {
-  __shared__ float tile[kColsKeys][kColsRows + 1];
-  __shared__ __align__(16) uint8_t onib[kColsRows][kColsKeys / 2];
-  __shared__ __align__(8) uint8_t osc[kColsRows][kColsKeys / 16];
+    int64_t ssr, int vec_in, int64_t bx, int64_t by, int64_t b, uint8_t* __restrict__ dnib, int64_t dnb,
+    int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr) {
+  auto& tile = sm.tile;
+  auto& onib = sm.onib;
+  auto& osc = sm.osc;
   const int tid = threadIdx.x;
-  const int64_t k0 = (int64_t)blockIdx.x * kColsKeys;
-  const int64_t r0 = (int64_t)blockIdx.y * kColsRows;
-  const int64_t b = blockIdx.z;
+  const int64_t k0 = bx * kColsKeys;
+  const int64_t r0 = by * kColsRows;
   const T* xb = x + b * sxb;
   // load: 8 threads x 8 elements cover 64 rows of one key; 32 keys per pass
 #pragma unroll
@@ -164,6 +192,23 @@ __global__ void __launch_bounds__(256) pack_cols_kernel(
     for (int i = 0; i < 8; ++i) tile[key][rc + i] = v[i];
   }
   __syncthreads();
+  if constexpr (kDual) {
+    // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2)
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int key = tid & 127;
+      const int g = (tid >> 7) + it * 2;
+      if (k0 + key < k_read && r0 + g * 16 < R) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = tile[key][g * 16 + j];
+        uint32_t lo, hi;
+        const uint8_t sb = pack_group16(v, lo, hi);
+        *reinterpret_cast<uint2*>(dnib + b * dnb + (k0 + key) * dnr + (r0 + g * 16) / 2) = make_uint2(lo, hi);
+        dsc[b * dsb + (k0 + key) * dsr + (r0 + g * 16) / 16] = sb;
+      }
+    }
+  }
   // quantise: thread -> (row = tid % 64, groups tid / 64 and tid / 64 + 4)
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
@@ -202,6 +247,64 @@ __global__ void __launch_bounds__(256) pack_cols_kernel(
       for (int i = 0; i < ng; ++i) ps[i] = osc[tid][i];
     }
   }
+}
+
+template <typename T, bool kDual>
+__global__ void __launch_bounds__(256) pack_cols_kernel(
+    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
+    uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
+    int64_t ssr, int vec_in, uint8_t* __restrict__ dnib, int64_t dnb, int64_t dnr,
+    uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr) {
+  __shared__ ColsSmem sm;
+  pack_cols_tile<T, kDual>(sm, x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc, ssb, ssr, vec_in, blockIdx.x,
+                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr);
+}
+
+// ---------------------------------------------------------------- Q, K along D and V^T in one launch
+// A flat grid: the first nbq blocks pack Q's 16-groups, the next nbk blocks K's, the rest are the
+// 128-key x 64-row tiles of V -> V^T.  Below a few thousand tokens three launches cost more than
+// the packing itself; this is one.
+struct QkvArgs {
+  const void *q, *k, *v;
+  int64_t rq, rk;            // rows of Q / K per batch entry
+  int64_t bq, bk;            // batch entries of Q / K (= V)
+  int d, ngroups_log2, vec_q, vec_k, vec_v;
+  int64_t sqb, sqr, skb, skr, svb, svk;   // element strides
+  int64_t bpq, bpk;          // 256-thread blocks per batch entry
+  int64_t nbq, nbk;          // blocks of the Q and K parts
+  int64_t s_kv, s_pad, tx, ty;            // V: keys, padded keys, tiles along keys / along D
+  uint8_t *qnv, *qsc, *knv, *ksc, *vnv, *vsc;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) pack_qkv_kernel(const QkvArgs a) {
+  __shared__ ColsSmem sm;
+  const int64_t v = blockIdx.x;
+  const int ngroups = a.d >> 4;
+  if (v < a.nbq + a.nbk) {
+    const bool is_q = v < a.nbq;
+    const int64_t w = is_q ? v : v - a.nbq;
+    const int64_t bp = is_q ? a.bpq : a.bpk;
+    const int64_t b = w / bp;
+    const int64_t gid = (w - b * bp) * 256 + threadIdx.x;
+    const int64_t rows = is_q ? a.rq : a.rk;
+    if (gid >= rows * ngroups) return;
+    if (is_q)
+      pack_rows_group<T>(static_cast<const T*>(a.q), a.d, ngroups, a.ngroups_log2, a.sqb, a.sqr, a.qnv,
+                         rows * (a.d / 2), a.d / 2, a.qsc, rows * ngroups, ngroups, a.vec_q, gid, b);
+    else
+      pack_rows_group<T>(static_cast<const T*>(a.k), a.d, ngroups, a.ngroups_log2, a.skb, a.skr, a.knv,
+                         rows * (a.d / 2), a.d / 2, a.ksc, rows * ngroups, ngroups, a.vec_k, gid, b);
+    return;
+  }
+  const int64_t w = v - a.nbq - a.nbk;
+  const int64_t per = a.tx * a.ty;
+  const int64_t b = w / per;
+  const int64_t rem = w - b * per;
+  const int64_t by = rem / a.tx, bx = rem - by * a.tx;
+  pack_cols_tile<T, false>(sm, static_cast<const T*>(a.v), a.d, a.s_kv, a.s_pad, a.svb, a.svk, a.vnv,
+                           (int64_t)a.d * (a.s_pad / 2), a.s_pad / 2, a.vsc, (int64_t)a.d * (a.s_pad / 16),
+                           a.s_pad / 16, a.vec_v, bx, by, b, nullptr, 0, 0, nullptr, 0, 0);
 }
 
 // ---------------------------------------------------------------- any strides (scalar)
@@ -254,8 +357,8 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
     const int vec = base_ok && sxb % kVecElems == 0 && sxk % kVecElems == 0;
     dim3 grid((unsigned)((k_pad + kColsKeys - 1) / kColsKeys),
               (unsigned)((R + kColsRows - 1) / kColsRows), (unsigned)B);
-    pack_cols_kernel<T><<<grid, 256, 0, st>>>(x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc,
-                                              ssb, ssr, vec);
+    pack_cols_kernel<T, false><<<grid, 256, 0, st>>>(x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc,
+                                                     ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0);
     return launch_result("nvfp4_pack(cols)");
   }
   const int64_t blocks = (total + 255) / 256;
@@ -290,6 +393,91 @@ extern "C" int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_
                                   nib, snb, snr, sc, ssb, ssr, st);
     default:
       return fail(-1, "nvfp4_pack: unknown dtype %d", dtype);
+  }
+}
+
+namespace nvfp4 {
+
+template <typename T>
+int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, int64_t sxb, int64_t sxs,
+                     uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, cudaStream_t st) {
+  constexpr int64_t kVecElems = 16 / sizeof(T);
+  const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && sxb % kVecElems == 0 && sxs % kVecElems == 0;
+  dim3 grid((unsigned)((s_pad + kColsKeys - 1) / kColsKeys), (unsigned)((d + kColsRows - 1) / kColsRows),
+            (unsigned)B);
+  pack_cols_kernel<T, true><<<grid, 256, 0, st>>>(
+      static_cast<const T*>(x), d, S, s_pad, sxb, sxs, tnib, (int64_t)d * (s_pad / 2), s_pad / 2, tsc,
+      (int64_t)d * (s_pad / 16), s_pad / 16, vec, dnib, S * (int64_t)(d / 2), d / 2, dsc, S * (int64_t)(d / 16),
+      d / 16);
+  return launch_result("nvfp4_pack_dual");
+}
+
+template <typename T>
+int pack_qkv_launch(QkvArgs a, cudaStream_t st) {
+  constexpr int64_t kVecElems = 16 / sizeof(T);
+  auto vec_ok = [&](const void* p, int64_t s0, int64_t s1) {
+    return (int)((reinterpret_cast<uintptr_t>(p) & 15) == 0 && s0 % kVecElems == 0 && s1 % kVecElems == 0);
+  };
+  a.vec_q = vec_ok(a.q, a.sqb, a.sqr);
+  a.vec_k = vec_ok(a.k, a.skb, a.skr);
+  a.vec_v = vec_ok(a.v, a.svb, a.svk);
+  const int64_t total = a.nbq + a.nbk + a.bk * a.tx * a.ty;
+  NVFP4_REQUIRE(total < (1LL << 31), "nvfp4_pack_qkv: tensors too large");
+  pack_qkv_kernel<T><<<(unsigned)total, 256, 0, st>>>(a);
+  return launch_result("nvfp4_pack_qkv");
+}
+
+}  // namespace nvfp4
+
+extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
+                               int64_t sxb, int64_t sxs, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib,
+                               uint8_t* tsc, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(B >= 0 && S >= 0 && d >= 16 && d % 16 == 0, "nvfp4_pack_dual: head dim must be a positive multiple of 16");
+  NVFP4_REQUIRE(s_pad % 16 == 0 && s_pad >= S, "nvfp4_pack_dual: s_pad must be a multiple of 16 >= S");
+  if (B == 0 || s_pad == 0) return 0;
+  NVFP4_REQUIRE(x && dnib && dsc && tnib && tsc, "nvfp4_pack_dual: null pointer");
+  NVFP4_REQUIRE(B < 65536, "nvfp4_pack_dual: too many batch entries");
+  NVFP4_REQUIRE(((uintptr_t)dnib & 7) == 0, "nvfp4_pack_dual: nibble buffers must be 8-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case NVFP4_DT_BF16: return pack_dual_launch<__nv_bfloat16>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP16: return pack_dual_launch<__half>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
+    default: return fail(-1, "nvfp4_pack_dual: unknown dtype %d", dtype);
+  }
+}
+
+extern "C" int nvfp4_pack_qkv(const void* q, const void* k, const void* v, int dtype, int64_t bq,
+                              int64_t bk, int64_t s_q, int64_t s_kv, int64_t s_pad, int d,
+                              int64_t sqb, int64_t sqr, int64_t skb, int64_t skr, int64_t svb,
+                              int64_t svk, uint8_t* qnv, uint8_t* qsc, uint8_t* knv, uint8_t* ksc,
+                              uint8_t* vnv, uint8_t* vsc, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(d >= 16 && (d & (d - 1)) == 0, "nvfp4_pack_qkv: head dim must be a power of two >= 16");
+  NVFP4_REQUIRE(bq >= 1 && bk >= 1 && s_q >= 1 && s_kv >= 1, "nvfp4_pack_qkv: empty problem");
+  NVFP4_REQUIRE(s_pad % 16 == 0 && s_pad >= s_kv, "nvfp4_pack_qkv: s_pad must be a multiple of 16 >= s_kv");
+  NVFP4_REQUIRE(q && k && v && qnv && qsc && knv && ksc && vnv && vsc, "nvfp4_pack_qkv: null pointer");
+  NVFP4_REQUIRE((((uintptr_t)qnv | (uintptr_t)knv | (uintptr_t)vnv) & 15) == 0 && (((uintptr_t)vsc) & 7) == 0,
+                "nvfp4_pack_qkv: outputs must be 16-byte aligned");
+  QkvArgs a;
+  a.q = q; a.k = k; a.v = v; a.rq = s_q; a.rk = s_kv; a.bq = bq; a.bk = bk; a.d = d;
+  int lg = 0;
+  while ((1 << lg) < d / 16) ++lg;
+  a.ngroups_log2 = lg;
+  a.sqb = sqb; a.sqr = sqr; a.skb = skb; a.skr = skr; a.svb = svb; a.svk = svk;
+  a.bpq = (s_q * (d / 16) + 255) / 256; a.bpk = (s_kv * (d / 16) + 255) / 256;
+  a.nbq = a.bpq * bq; a.nbk = a.bpk * bk;
+  a.s_kv = s_kv; a.s_pad = s_pad;
+  a.tx = (s_pad + kColsKeys - 1) / kColsKeys; a.ty = (d + kColsRows - 1) / kColsRows;
+  a.qnv = qnv; a.qsc = qsc; a.knv = knv; a.ksc = ksc; a.vnv = vnv; a.vsc = vsc;
+  a.vec_q = a.vec_k = a.vec_v = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case NVFP4_DT_BF16: return pack_qkv_launch<__nv_bfloat16>(a, st);
+    case NVFP4_DT_FP16: return pack_qkv_launch<__half>(a, st);
+    case NVFP4_DT_FP32: return pack_qkv_launch<float>(a, st);
+    default: return fail(-1, "nvfp4_pack_qkv: unknown dtype %d", dtype);
   }
 }
 

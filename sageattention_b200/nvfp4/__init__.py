@@ -33,4 +33,5 @@ __all__ = [
     "nvfp4_flash_decode_prequant",
     "nvfp4_quant_kv_decode",
     "NVFP4KVCache",
+    "convert_fp32_to_fp4_packed",
 ]

@@ -84,11 +84,6 @@ def ring_steps(rank: int, world: int, causal: bool) -> List[Tuple[int, str]]:
     return steps
 
 
-# Measurement switch: with False the ring schedule runs on the local block only (no messages), which
-# gives the pure compute time of a step; wall time minus that is the exposed communication.
-COMMUNICATE = True
-
-
 def ring_steps_zigzag(rank: int, world: int) -> List[Tuple[int, str]]:
     """Causal schedule for the zigzag layout: the sequence is cut into ``2*world`` chunks and rank
     r owns chunks r and ``2*world-1-r`` (concatenated in that order), which balances causal work.
@@ -129,9 +124,13 @@ def _steps(rank: int, world: int, causal: bool, schedule: str):
     return ring_steps(rank, world, causal)
 
 
-def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], group, rank: int, world: int):
-    """Post sends of ``tensors`` to rank+1 and receives into ``recv`` from rank-1 (non-blocking)."""
-    if not COMMUNICATE:
+def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], group, rank: int, world: int,
+              communicate: bool = True):
+    """Post sends of ``tensors`` to rank+1 and receives into ``recv`` from rank-1 (non-blocking).
+
+    ``communicate=False`` (a measurement aid) copies the local tensors instead of exchanging
+    messages: the same kernels run on the same schedule without any communication."""
+    if not communicate:
         for t, r in zip(tensors, recv):
             r.copy_(t)
         return []
@@ -143,10 +142,37 @@ def _exchange(tensors: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], gro
     return dist.batch_isend_irecv(ops)
 
 
+class RingPeerTimeout(RuntimeError):
+    """A neighbour of the ring did not deliver (or accept) a block within the allowed time."""
+
+
+def _wait_all(reqs, timeout_s, what: str):
+    """Wait for posted sends / receives.  With ``timeout_s`` the wait is bounded on the host: a
+    peer that died, never joined the step or never posted its send surfaces here as
+    ``RingPeerTimeout`` instead of blocking this rank forever (the backends report an expired wait
+    as an exception or a False return)."""
+    if timeout_s is None:
+        for r in reqs:
+            r.wait()
+        return
+    import datetime
+    limit = datetime.timedelta(seconds=float(timeout_s))
+    for r in reqs:
+        try:
+            ok = r.wait(limit)
+        except Exception as exc:        # gloo: RuntimeError "Timed out waiting ..."; nccl: DistBackendError
+            raise RingPeerTimeout(f"ring attention: {what} not completed within {timeout_s} s ({exc})") from exc
+        if ok is False:
+            raise RingPeerTimeout(f"ring attention: {what} not completed within {timeout_s} s")
+
+
 def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
                    block_attention: Callable, merge: Callable, causal: bool, group=None,
-                   schedule: str = "contiguous"):
+                   schedule: str = "contiguous", _communicate: bool = True, timeout_s=None):
     """Context-parallel attention of the local queries against every rank's K/V block.
+
+    ``timeout_s`` bounds every wait on a neighbour (``RingPeerTimeout`` on expiry); None waits as
+    long as the process group allows.
 
     ``kv_block``: the tensors describing the local K/V block (anything with a fixed shape across
     ranks, e.g. the six pack tensors).  ``block_attention(q_local, block, mode)`` returns
@@ -163,12 +189,11 @@ def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
         reqs, nxt_bufs = [], None
         if t + 1 < world:
             nxt_bufs = [torch.empty_like(x) for x in cur]
-            reqs = _exchange(cur, nxt_bufs, group, rank, world)
+            reqs = _exchange(cur, nxt_bufs, group, rank, world, _communicate)
         if mode != "skip":
             o, l = block_attention(q_local, cur, mode)
             out, lse = (o, l) if out is None else merge(out, lse, o, l)
-        for r in reqs:
-            r.wait()
+        _wait_all(reqs, timeout_s, f"K/V block exchange of step {t}")
         if nxt_bufs is not None:
             cur = nxt_bufs
     return out, lse
@@ -176,8 +201,8 @@ def ring_attention(q_local, kv_block: Sequence[torch.Tensor],
 
 def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequence[torch.Tensor],
                             block_backward: Callable, causal: bool, group=None,
-                            schedule: str = "contiguous"):
-    """Gradients of ``ring_attention``.
+                            schedule: str = "contiguous", _communicate: bool = True, timeout_s=None):
+    """Gradients of ``ring_attention``.  ``timeout_s`` as in ``ring_attention``.
 
     ``kv_block``: the tensors that describe the local K/V block for the backward (fixed shapes
     across ranks).  ``grad_like``: two tensors shaped like the local dK and dV (fp32 accumulators are
@@ -198,26 +223,23 @@ def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequenc
         reqs, nxt_bufs = [], None
         if t + 1 < world:
             nxt_bufs = [torch.empty_like(x) for x in cur]
-            reqs = _exchange(cur, nxt_bufs, group, rank, world)
+            reqs = _exchange(cur, nxt_bufs, group, rank, world, _communicate)
         part = block_backward(cur, mode) if mode != "skip" else None
         if t > 0:                       # accumulators of the block held now, sent after step t-1
-            for r in acc_reqs:
-                r.wait()
+            _wait_all(acc_reqs, timeout_s, f"dK/dV accumulator hop before step {t}")
             acc = acc_recv
         if part is not None:
             dq = part[0].float() if dq is None else dq + part[0].float()
             acc[0] += part[1].float()
             acc[1] += part[2].float()
-        for r in reqs:
-            r.wait()
+        _wait_all(reqs, timeout_s, f"K/V block exchange of step {t}")
         if world > 1:                   # forward the accumulators (last step: the hop back home)
             acc_recv = [torch.empty_like(a) for a in acc]
-            acc_reqs = _exchange(acc, acc_recv, group, rank, world)
+            acc_reqs = _exchange(acc, acc_recv, group, rank, world, _communicate)
         if nxt_bufs is not None:
             cur = nxt_bufs
     if world > 1:
-        for r in acc_reqs:
-            r.wait()
+        _wait_all(acc_reqs, timeout_s, "last dK/dV accumulator hop")
         acc = acc_recv
     if dq is None:
         dq = torch.zeros_like(grad_like[0][:0])
@@ -225,7 +247,7 @@ def ring_attention_backward(kv_block: Sequence[torch.Tensor], grad_like: Sequenc
 
 
 def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None,
-                         schedule="contiguous"):
+                         schedule="contiguous", _communicate=True):
     """NVFP4 ring attention on CUDA: ``query [Z,H,S_loc,D]``, ``key/value [Z,Hk,S_loc,D]`` are this
     rank's slice of the sequence: one contiguous piece (``schedule="contiguous"``, length a multiple
     of 128) or the two zigzag chunks (``schedule="zigzag"``, each a multiple of 128; see
@@ -266,20 +288,19 @@ def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_
 
     def merge(o1, l1, o2, l2):
         rows = z * h * s_loc
-        out = torch.empty_like(o1)
-        _lib.check(_lib.lib().nvfp4_lse_merge(o1.data_ptr(), l1.data_ptr(), o2.data_ptr(), l2.data_ptr(),
-                                              out.data_ptr(), _lib.DT_FP32, rows, d,
-                                              _lib.stream_ptr(o1.device)), "nvfp4_lse_merge")
-        m = torch.maximum(l1, l2)
-        lse = m + torch.log(torch.exp(l1 - m) + torch.exp(l2 - m))
+        out, lse = torch.empty_like(o1), torch.empty_like(l1)
+        _lib.call("nvfp4_lse_merge", _lib.same_device(o1, l1, o2, l2),
+                  o1.data_ptr(), l1.data_ptr(), o2.data_ptr(), l2.data_ptr(),
+                  out.data_ptr(), lse.data_ptr(), _lib.DT_FP32, rows, d, _lib.stream_ptr(o1.device))
         return out, lse
 
-    out, lse = ring_attention(query, block, block_attention, merge, causal, group, schedule)
+    out, lse = ring_attention(query, block, block_attention, merge, causal, group, schedule, _communicate)
     return out.to(query.dtype), lse
 
 
 def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, causal=True,
-                                  num_key_value_groups=1, group=None, schedule="contiguous"):
+                                  num_key_value_groups=1, group=None, schedule="contiguous",
+                                  _communicate=True):
     """NVFP4 ring-attention backward on CUDA for the local sequence slices (bf16 tensors).
 
     ``out`` / ``lse`` are the merged results of ``ring_flash_attention``; with them every block's
@@ -311,11 +332,11 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
         dq = torch.empty(z, h, sq, d, dtype=torch.float32, device=dev)
         dk = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
         dv = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
-        _lib.check(_lib.lib().nvfp4_bwd_hp(
+        _lib.call("nvfp4_bwd_hp", _lib.same_device(*qs, *blk),
             qs[0].data_ptr(), qs[1].data_ptr(), blk[2].data_ptr(), blk[3].data_ptr(), qs[2].data_ptr(),
             blk[0].data_ptr(), blk[1].data_ptr(), qs[3].data_ptr(), qs[4].data_ptr(), qs[5].data_ptr(), None, None, None,
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.DT_FP32, z, h, hk, sq, skv, d, float(scaling),
-            1 if is_causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_bwd_hp")
+            1 if is_causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
         return dq, dk, dv
 
     def block_backward(blk, mode):
@@ -335,34 +356,36 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
         return dq, dk, dv
 
     like = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
-    dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group, schedule)
+    dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group, schedule,
+                                         _communicate)
     gdt = dout.dtype
     return dq.to(gdt), dk.to(gdt), dv.to(gdt)
 
 
 class _RingFlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, query, key, value, scaling, causal, g, group, schedule):
-        out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group, schedule)
+    def forward(ctx, query, key, value, scaling, causal, g, group, schedule, communicate):
+        out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group, schedule, communicate)
         ctx.save_for_backward(query, key, value, out, lse)
-        ctx.meta = (float(scaling), bool(causal), int(g), group, schedule)
+        ctx.meta = (float(scaling), bool(causal), int(g), group, schedule, communicate)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         query, key, value, out, lse = ctx.saved_tensors
-        scaling, causal, g, group, schedule = ctx.meta
+        scaling, causal, g, group, schedule, communicate = ctx.meta
         dq, dk, dv = ring_flash_attention_backward(query, key, value, out, lse, grad_out, scaling, causal, g,
-                                                   group, schedule)
-        return dq, dk, dv, None, None, None, None, None
+                                                   group, schedule, communicate)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None,
-                         schedule="zigzag"):
+                         schedule="zigzag", _communicate=True):
     """Differentiable context-parallel NVFP4 attention over this rank's slice of the sequence.
 
     ``schedule="zigzag"`` (default, causal only): the slice is chunks r and 2W-1-r of the sequence
     (``zigzag_split``), every rank does the same work per ring step.  ``"contiguous"``: one piece per
     rank; with a causal mask the last rank works on every step and the first on one.
     """
-    return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group, schedule)
+    return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group, schedule,
+                                _communicate)

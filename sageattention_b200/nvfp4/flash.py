@@ -89,10 +89,10 @@ def _pack_into(x, nib, sc, transpose=False, k_pad=None):
     assert nib.stride(2) == 1 and sc.stride(2) == 1
     if b * r * kp == 0:
         return
-    _lib.check(_lib.lib().nvfp4_pack(
-        x.data_ptr(), _lib.dtype_code(x.dtype), b, r, k_read, kp, sxb, sxr, sxk,
-        nib.data_ptr(), nib.stride(0), nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1),
-        _lib.stream_ptr(x.device)), "nvfp4_pack")
+    _lib.call("nvfp4_pack", _lib.same_device(x, nib, sc),
+              x.data_ptr(), _lib.dtype_code(x.dtype), b, r, k_read, kp, sxb, sxr, sxk,
+              nib.data_ptr(), nib.stride(0), nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1),
+              _lib.stream_ptr(x.device))
 
 
 def _quant_nvfp4(x: torch.Tensor, transpose: bool = False, k_pad: int | None = None):
@@ -135,32 +135,61 @@ def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
         assert positions.numel() == r
     nib = torch.empty(b, r, d // 2, dtype=torch.uint8, device=x.device)
     sc = torch.empty(b, r, d // 16, dtype=torch.uint8, device=x.device)
-    _lib.check(_lib.lib().nvfp4_rope_pack(
-        x.data_ptr(), _lib.dtype_code(x.dtype), b, r, d, x.stride(0), x.stride(1), cos.data_ptr(), sin.data_ptr(),
-        positions.data_ptr() if positions is not None else None, int(pos0), nib.data_ptr(), nib.stride(0),
-        nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1), _lib.stream_ptr(x.device)), "nvfp4_rope_pack")
+    _lib.call("nvfp4_rope_pack", _lib.same_device(x, cos, sin, positions),
+              x.data_ptr(), _lib.dtype_code(x.dtype), b, r, d, x.stride(0), x.stride(1), cos.data_ptr(), sin.data_ptr(),
+              positions.data_ptr() if positions is not None else None, int(pos0), nib.data_ptr(), nib.stride(0),
+              nib.stride(1), sc.data_ptr(), sc.stride(0), sc.stride(1), _lib.stream_ptr(x.device))
     return nib, sc.view(torch.float8_e4m3fn)
 
 
 def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None):
-    """Both layouts of ``x`` [B, S, D]: along D and along S (padded to ``s_pad``).
+    """Both layouts of ``x`` [B, S, D] from one read: along D and along S (padded to ``s_pad``).
 
-    Stands in for flash.py:514-561; bit-identical to two ``_quant_nvfp4`` calls by construction.
-    Returns ``(nib_d, sc_d, nib_s, sc_s)``.
+    Stands in for flash.py:514-561 (one kernel, one pass over ``x``); bytes equal two
+    ``_quant_nvfp4`` calls.  Returns ``(nib_d, sc_d, nib_s, sc_s)``.
     """
+    _lib.require_cuda(x, "x")
     b, s, d = x.shape
-    sp = _next_mult(s, 16) if s_pad is None else s_pad
-    nd, sd = _quant_nvfp4(x)
-    ns, ss = _quant_nvfp4(x, transpose=True, k_pad=sp)
-    return nd, sd, ns, ss
+    sp = _next_mult(s, 16) if s_pad is None else int(s_pad)
+    assert sp % 16 == 0 and sp >= s, "s_pad must be a multiple of 16 covering S"
+    assert d % 16 == 0, "D must be a multiple of 16"
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    dev = x.device
+    nd = torch.empty(b, s, d // 2, dtype=torch.uint8, device=dev)
+    sd = torch.empty(b, s, d // 16, dtype=torch.uint8, device=dev)
+    ns = torch.empty(b, d, sp // 2, dtype=torch.uint8, device=dev)
+    ss = torch.empty(b, d, sp // 16, dtype=torch.uint8, device=dev)
+    if b * sp > 0:
+        _lib.call("nvfp4_pack_dual", dev, x.data_ptr(), _lib.dtype_code(x.dtype), b, s, d, sp, x.stride(0),
+                  x.stride(1), nd.data_ptr(), sd.data_ptr(), ns.data_ptr(), ss.data_ptr(), _lib.stream_ptr(dev))
+    return nd, sd.view(torch.float8_e4m3fn), ns, ss.view(torch.float8_e4m3fn)
 
 
 def _quant_qkv_fwd(q2, k2, v2, s_kv_pad):
-    """Q, K along D and V along keys (padded); stands in for flash.py:682-732."""
-    qnv, qsc = _quant_nvfp4(q2)
-    knv, ksc = _quant_nvfp4(k2)
-    vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_kv_pad)
-    return qnv, qsc, knv, ksc, vnv, vsc
+    """Q, K along D and V along keys (padded to ``s_kv_pad``) in one launch; stands in for
+    flash.py:682-732.  ``q2`` [ZH, Sq, D], ``k2`` / ``v2`` [ZHk, Skv, D].  Operands that are not
+    unit-stride along D (or differ in dtype) fall back to one ``_quant_nvfp4`` launch each."""
+    bq, s_q, d = q2.shape
+    bk, s_kv, _ = k2.shape
+    fused = (q2.dtype == k2.dtype == v2.dtype and q2.stride(2) == 1 and k2.stride(2) == 1 and v2.stride(2) == 1
+             and v2.shape == k2.shape and d in (64, 128, 256) and s_kv_pad % 16 == 0 and bq * s_q * bk * s_kv > 0)
+    if not fused:
+        qnv, qsc = _quant_nvfp4(q2)
+        knv, ksc = _quant_nvfp4(k2)
+        vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_kv_pad)
+        return qnv, qsc, knv, ksc, vnv, vsc
+    dev = _lib.same_device(q2, k2, v2)
+    u8 = lambda *sh: torch.empty(*sh, dtype=torch.uint8, device=dev)
+    qnv, qsc = u8(bq, s_q, d // 2), u8(bq, s_q, d // 16)
+    knv, ksc = u8(bk, s_kv, d // 2), u8(bk, s_kv, d // 16)
+    vnv, vsc = u8(bk, d, s_kv_pad // 2), u8(bk, d, s_kv_pad // 16)
+    _lib.call("nvfp4_pack_qkv", dev, q2.data_ptr(), k2.data_ptr(), v2.data_ptr(), _lib.dtype_code(q2.dtype),
+              bq, bk, s_q, s_kv, s_kv_pad, d, q2.stride(0), q2.stride(1), k2.stride(0), k2.stride(1),
+              v2.stride(0), v2.stride(1), qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(),
+              vnv.data_ptr(), vsc.data_ptr(), _lib.stream_ptr(dev))
+    f8 = torch.float8_e4m3fn
+    return qnv, qsc.view(f8), knv, ksc.view(f8), vnv, vsc.view(f8)
 
 
 def convert_fp32_to_fp4_packed(x_pairs):
@@ -232,7 +261,7 @@ def _sm_count(device) -> int:
 def _decode_plan(s_kv: int, zhk: int, d: int, device):
     ns, sk, wb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_size_t()
     _lib.check(_lib.lib().nvfp4_decode_plan(s_kv, zhk, d, _sm_count(device), ctypes.byref(ns),
-                                            ctypes.byref(sk), ctypes.byref(wb)), "nvfp4_decode_plan")
+                                            ctypes.byref(sk), ctypes.byref(wb)), "nvfp4_decode_plan")   # host only
     return ns.value, sk.value, wb.value
 
 
@@ -273,13 +302,13 @@ def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
     for t in (knv, ksc, vnv, vsc):
         assert t.stride(-1) == 1, "packed cache rows must be contiguous"
     assert knv.stride(1) == d // 2 and ksc.stride(1) == d // 16, "K rows must be dense"
-    _lib.check(_lib.lib().nvfp4_decode(
-        q3.data_ptr(), _lib.dtype_code(q3.dtype), q3.stride(0), q3.stride(1),
-        knv.data_ptr(), knv.stride(0), ksc.data_ptr(), ksc.stride(0),
-        vnv.data_ptr(), vnv.stride(0), vnv.stride(1), vsc.data_ptr(), vsc.stride(0), vsc.stride(1),
-        z, hk, g, d, s_kv, float(scaling), out.data_ptr(),
-        lse.data_ptr() if lse is not None else None, ws.data_ptr(), wbytes, nsplit, split_kv,
-        _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)), "nvfp4_decode")
+    _lib.call("nvfp4_decode", _lib.same_device(q3, knv, ksc, vnv, vsc),
+              q3.data_ptr(), _lib.dtype_code(q3.dtype), q3.stride(0), q3.stride(1),
+              knv.data_ptr(), knv.stride(0), ksc.data_ptr(), ksc.stride(0),
+              vnv.data_ptr(), vnv.stride(0), vnv.stride(1), vsc.data_ptr(), vsc.stride(0), vsc.stride(1),
+              z, hk, g, d, s_kv, float(scaling), out.data_ptr(),
+              lse.data_ptr() if lse is not None else None, ws.data_ptr(), wbytes, nsplit, split_kv,
+              _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return out.reshape(z, h, 1, d), lse
 
 
@@ -347,19 +376,18 @@ def _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scal
     if key_pad_bias is not None:
         bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
         assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
-    L = _lib.lib()
-    wbytes = L.nvfp4_fwd_workspace_bytes(z, h, hk, s_q, s_kv, d)
-    ws = torch.empty(max(wbytes, 16), dtype=torch.uint8, device=dev)
+    wbytes = _lib.lib().nvfp4_fwd_workspace_bytes(z, h, hk, s_q, s_kv, d)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=dev) if wbytes else None
     tensors = [t.contiguous() for t in (qnv, qsc, knv, ksc, vnv, vsc)]
-    _lib.check(L.nvfp4_fwd(
-        *(t.data_ptr() for t in tensors),
-        bias.data_ptr() if bias is not None else None,
-        seq_id.data_ptr() if seq_id is not None else None,
-        seq_start.data_ptr() if seq_start is not None else None,
-        out.data_ptr(), _lib.dtype_code(out_dtype), so_z, so_h, so_s,
-        lse.data_ptr() if lse is not None else None, z, h, hk, s_q, s_kv, s_pad, d, float(scaling),
-        1 if causal else 0, ws.data_ptr(), wbytes, _lib.status_word(dev).data_ptr(),
-        _lib.stream_ptr(dev)), "nvfp4_fwd")
+    _lib.call("nvfp4_fwd", _lib.same_device(*tensors, bias, seq_id, seq_start),
+              *(t.data_ptr() for t in tensors),
+              bias.data_ptr() if bias is not None else None,
+              seq_id.data_ptr() if seq_id is not None else None,
+              seq_start.data_ptr() if seq_start is not None else None,
+              out.data_ptr(), _lib.dtype_code(out_dtype), so_z, so_h, so_s,
+              lse.data_ptr() if lse is not None else None, z, h, hk, s_q, s_kv, s_pad, d, float(scaling),
+              1 if causal else 0, ws.data_ptr() if ws is not None else None, wbytes,
+              _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return (out, lse) if return_lse else out
 
 
@@ -411,15 +439,18 @@ def nvfp4_flash_attention(query, key, value, scaling, causal=False, num_key_valu
     q2 = query.reshape(z * h, s_q, d)
     k2 = key.reshape(z * hk, s_kv, d)
     v2 = value.reshape(z * hk, s_kv, d) if value.dim() == 4 else value
-    if q_packs is not None:
-        qnv, qsc = _check_packs(q_packs, (z * h, s_q, d), "q_packs layout")
+    if q_packs is None and k_packs is None and v2.dim() == 3:
+        qnv, qsc, knv, ksc, vnv, vsc = _quant_qkv_fwd(q2, k2, v2, s_pad)     # one launch
     else:
-        qnv, qsc = _quant_nvfp4(q2)
-    if k_packs is not None:
-        knv, ksc = _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout")
-    else:
-        knv, ksc = _quant_nvfp4(k2)
-    vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_pad)
+        if q_packs is not None:
+            qnv, qsc = _check_packs(q_packs, (z * h, s_q, d), "q_packs layout")
+        else:
+            qnv, qsc = _quant_nvfp4(q2)
+        if k_packs is not None:
+            knv, ksc = _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout")
+        else:
+            knv, ksc = _quant_nvfp4(k2)
+        vnv, vsc = _quant_nvfp4(v2, transpose=True, k_pad=s_pad)
     res = _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scaling,
                             query.dtype, causal, key_pad_bias, cu_seqlens, block_m, block_n,
                             num_warps, num_stages, out_layout, return_lse, _varlen_arrays)
@@ -446,13 +477,13 @@ def _bwd_prep(x, y=None, want_copy=False):
             y = y.to(x.dtype)
         if y.stride(3) != 1:
             y = y.contiguous()
-    _lib.check(_lib.lib().nvfp4_bwd_prep(
-        x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), x.stride(2), b1, b2,
-        y.data_ptr() if y is not None else None,
-        y.stride(0) if y is not None else 0, y.stride(1) if y is not None else 0,
-        y.stride(2) if y is not None else 0, s, d,
-        xc.data_ptr() if xc is not None else None,
-        delta.data_ptr() if delta is not None else None, _lib.stream_ptr(dev)), "nvfp4_bwd_prep")
+    _lib.call("nvfp4_bwd_prep", _lib.same_device(x, y),
+              x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), x.stride(1), x.stride(2), b1, b2,
+              y.data_ptr() if y is not None else None,
+              y.stride(0) if y is not None else 0, y.stride(1) if y is not None else 0,
+              y.stride(2) if y is not None else 0, s, d,
+              xc.data_ptr() if xc is not None else None,
+              delta.data_ptr() if delta is not None else None, _lib.stream_ptr(dev))
     return xc, delta
 
 
@@ -485,8 +516,16 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     if doc is None:
         doc = dout.view(z * h, s_q, d)
     qc, kc, vc = _as_bf16_rows(q), _as_bf16_rows(k), _as_bf16_rows(v)
-    qnv, qsc = q_packs if q_packs is not None else _quant_nvfp4(q.reshape(z * h, s_q, d))
-    knv, ksc = k_packs if k_packs is not None else _quant_nvfp4(k.reshape(z * hk, s_kv, d))
+    # packs handed in by the caller may be strided views (a slice of a fused producer's buffer):
+    # the kernels' tensor maps assume dense [rows, D/2] / [rows, D/16] rows
+    if q_packs is not None:
+        qnv, qsc = (t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
+    else:
+        qnv, qsc = _quant_nvfp4(q.reshape(z * h, s_q, d))
+    if k_packs is not None:
+        knv, ksc = (t.contiguous() for t in _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout"))
+    else:
+        knv, ksc = _quant_nvfp4(k.reshape(z * hk, s_kv, d))
     gdt = dout.dtype
     dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
     dk = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
@@ -499,14 +538,13 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     if key_pad_bias is not None:
         bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
         assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
-    _lib.check(_lib.lib().nvfp4_bwd_hp(
-        qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), qc.data_ptr(), kc.data_ptr(),
-        vc.data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-        bias.data_ptr() if bias is not None else None,
-        sst.data_ptr() if sst is not None else None, sen.data_ptr() if sen is not None else None,
-        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, d,
-        float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev)),
-        "nvfp4_bwd_hp")
+    _lib.call("nvfp4_bwd_hp", _lib.same_device(qnv, qsc, knv, ksc, qc, kc, vc, doc, lse, delta, bias, sst, sen),
+              qnv.data_ptr(), qsc.data_ptr(), knv.data_ptr(), ksc.data_ptr(), qc.data_ptr(), kc.data_ptr(),
+              vc.data_ptr(), doc.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+              bias.data_ptr() if bias is not None else None,
+              sst.data_ptr() if sst is not None else None, sen.data_ptr() if sen is not None else None,
+              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, d,
+              float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return dq, dk, dv
 
 

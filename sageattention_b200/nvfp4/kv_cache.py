@@ -111,14 +111,14 @@ class NVFP4KVCache:
         if kn.stride(0) != vn.stride(0):
             kn, vn = kn.contiguous(), vn.contiguous()
         ring = self.recent_window > 0
-        _lib.check(_lib.lib().nvfp4_kv_append(
+        _lib.call("nvfp4_kv_append", _lib.same_device(kn, vn, self.knv),
             kn.data_ptr(), vn.data_ptr(), _lib.dtype_code(self.dtype), kn.stride(0), self.zhk, d, t,
             self.knv.data_ptr(), self.knv.stride(0), self.ksc.data_ptr(), self.ksc.stride(0),
             self.vnv.data_ptr(), self.vnv.stride(0), self.vnv.stride(1),
             self.vsc.data_ptr(), self.vsc.stride(0), self.vsc.stride(1),
             self.v_partial_bf16.data_ptr(),
             self.rk.data_ptr() if ring else None, self.rv.data_ptr() if ring else None,
-            self.ring_cap, _lib.stream_ptr(self.device)), "nvfp4_kv_append")
+            self.ring_cap, _lib.stream_ptr(self.device))
         self.length = t + 1
         self.partial_len = (t % self.GROUP) + 1
         if self.partial_len == self.GROUP:
@@ -159,20 +159,19 @@ class NVFP4KVCache:
             qv = qv.to(self.dtype)
         out_rec = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
         lse_rec = torch.empty(z, h, dtype=torch.float32, device=query.device)
-        _lib.check(_lib.lib().nvfp4_window_attention(
+        _lib.call("nvfp4_window_attention", _lib.same_device(qv, self.rk),
             qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
             self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling),
-            out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(query.device)),
-            "nvfp4_window_attention")
+            out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(query.device))
         if cut == 0:
             return out_rec.reshape(z, h, 1, d).to(query.dtype)
         out_old, lse_old = _flash._decode_prequant_with_lse(
             query.float(), self._packed_upto(cut), scaling, g, block_n=self.block_n)
         merged = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
-        _lib.check(_lib.lib().nvfp4_lse_merge(
+        _lib.call("nvfp4_lse_merge", _lib.same_device(out_old, out_rec),
             out_old.reshape(z * h, d).data_ptr(), lse_old.data_ptr(), out_rec.data_ptr(),
-            lse_rec.data_ptr(), merged.data_ptr(), _lib.DT_FP32, z * h, d,
-            _lib.stream_ptr(query.device)), "nvfp4_lse_merge")
+            lse_rec.data_ptr(), merged.data_ptr(), None, _lib.DT_FP32, z * h, d,
+            _lib.stream_ptr(query.device))
         return merged.reshape(z, h, 1, d).to(query.dtype)
 
     # ------------------------------------------------------------------ checkpoint / resume

@@ -128,3 +128,89 @@ def test_large_pack_roundtrip_property():
     assert float(err.max()) <= 1.0 + 1e-3      # widest e2m1 gap is 2 (4 -> 6): half of it
     nib2, sc2 = n._quant_nvfp4(deq.to(torch.bfloat16))
     assert torch.equal(nib2, nib) and torch.equal(sc2.view(torch.uint8), sc.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("b,s,d,pad", [(2, 300, 128, 384), (1, 16, 128, 16), (3, 77, 256, 128), (1, 1000, 64, 1008),
+                                       (2, 129, 48, None)])
+def test_dual_pack_equals_two_single_packs(dtype, b, s, d, pad):
+    """One-read dual pack (reference property, tests/test_nvfp4_attention.py:423-447): bytes equal
+    the along-D pack and the along-S pack taken separately, and both equal the oracle."""
+    g = torch.Generator().manual_seed(s * 13 + d)
+    x = (torch.randn(b, s, d, generator=g) * 1.3).to(dtype)
+    n = _nvfp4()
+    nd, sd, ns, ss = n._quant_nvfp4_dual(x.cuda(), pad)
+    sp = pad if pad is not None else ((s + 15) // 16) * 16
+    assert ns.shape == (b, d, sp // 2) and ss.shape == (b, d, sp // 16) and sd.dtype == torch.float8_e4m3fn
+    od, osd = n._quant_nvfp4(x.cuda())
+    ot, ost = n._quant_nvfp4(x.cuda(), transpose=True, k_pad=sp)
+    assert torch.equal(nd, od) and torch.equal(sd.view(torch.uint8), osd.view(torch.uint8))
+    assert torch.equal(ns, ot) and torch.equal(ss.view(torch.uint8), ost.view(torch.uint8))
+    cn, cs = O.pack(x.float().numpy())
+    tn, ts = O.pack(x.float().numpy(), transpose=True, k_pad=sp)
+    assert np.array_equal(np_u8(nd), cn) and np.array_equal(np_u8(sd), cs)
+    assert np.array_equal(np_u8(ns), tn) and np.array_equal(np_u8(ss), ts)
+
+
+def test_dual_pack_strided_rows():
+    z, s, h, d = 2, 70, 3, 128
+    x, xf = seeded_bf16((z, s, h, d), seed=21)
+    view = x.permute(0, 2, 1, 3)[1]          # [H, S, D] with row stride H*D
+    nd, sd, ns, ss = _nvfp4()._quant_nvfp4_dual(view, 128)
+    ref = np.transpose(xf, (0, 2, 1, 3))[1]
+    cn, cs = O.pack(ref)
+    tn, ts = O.pack(ref, transpose=True, k_pad=128)
+    assert np.array_equal(np_u8(nd), cn) and np.array_equal(np_u8(sd), cs)
+    assert np.array_equal(np_u8(ns), tn) and np.array_equal(np_u8(ss), ts)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("zh,zhk,sq,skv,d", [(4, 2, 200, 200, 128), (2, 2, 1, 300, 128), (6, 3, 130, 257, 256),
+                                             (32, 8, 1024, 1024, 128)])
+def test_fused_qkv_prepack_equals_three_packs(dtype, zh, zhk, sq, skv, d):
+    """One-launch Q/K/V pre-pack (flash.py:579-732): bytes equal three separate packs."""
+    g = torch.Generator().manual_seed(zh * 1000 + skv)
+    q = torch.randn(zh, sq, d, generator=g).to(dtype).cuda()
+    k = (torch.randn(zhk, skv, d, generator=g) * 2.0).to(dtype).cuda()
+    v = torch.randn(zhk, skv, d, generator=g).to(dtype).cuda()
+    n = _nvfp4()
+    sp = ((skv + 127) // 128) * 128
+    from sageattention_b200.nvfp4 import flash
+    got = flash._quant_qkv_fwd(q, k, v, sp)
+    want = (*n._quant_nvfp4(q), *n._quant_nvfp4(k), *n._quant_nvfp4(v, transpose=True, k_pad=sp))
+    for a, b in zip(got, want):
+        assert a.shape == b.shape and a.dtype == b.dtype
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    # strided operands (a [Z, S, H, D] projection output viewed per head) take the same path
+    big = torch.randn(2, skv, zhk, d, generator=g).to(dtype).cuda()
+    kv = big.permute(0, 2, 1, 3)[0]          # [zhk, skv, d], unit stride along d only
+    got = flash._quant_qkv_fwd(q, kv, kv, sp)
+    want = (*n._quant_nvfp4(q), *n._quant_nvfp4(kv), *n._quant_nvfp4(kv, transpose=True, k_pad=sp))
+    for a, b in zip(got, want):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+
+
+def test_convert_fp32_to_fp4_packed_pairs():
+    """Host-callable stand-in for the reference's device function (_fp4_pack.py:15-56): first
+    element of a pair in the low nibble, RTNE to the e2m1 grid, saturating, sign kept on -0."""
+    vals = torch.tensor([0.0, -0.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.3, -6.5, 0.5, 1.0, 1.5, 6.0],
+                        dtype=torch.float32).cuda()
+    lo, hi = vals, vals.flip(0)
+    got = _nvfp4().convert_fp32_to_fp4_packed((lo, hi)).cpu().numpy()
+    c_lo = O.e2m1_codes(lo.cpu().numpy())
+    c_hi = O.e2m1_codes(hi.cpu().numpy())
+    assert np.array_equal(got, (c_lo | (c_hi << 4)).astype(np.uint8))
+    assert "convert_fp32_to_fp4_packed" in _nvfp4().__all__
+
+
+def test_gqa_reduce_cast_dkdv():
+    """`_gqa_reduce_cast_dkdv` (flash.py:2525-2557): per-query-head planes summed over each group."""
+    z, hk, g, s, d = 2, 3, 4, 10, 16
+    gen = torch.Generator().manual_seed(3)
+    a = torch.randn(z * hk * g, s, d, generator=gen).cuda()
+    b = torch.randn(z * hk * g, s, d, generator=gen).cuda()
+    dk, dv = _nvfp4()._gqa_reduce_cast_dkdv(a, b, z, hk, g, torch.bfloat16)
+    assert dk.shape == (z, hk, s, d) and dk.dtype == torch.bfloat16
+    ref = a.reshape(z, hk, g, s, d).double().sum(2)
+    assert torch.allclose(dk.double(), ref, atol=2e-2, rtol=1e-2)
+    assert torch.allclose(dv.double(), b.reshape(z, hk, g, s, d).double().sum(2), atol=2e-2, rtol=1e-2)

@@ -16,17 +16,19 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, d, s_loc):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import datetime
     import torch.distributed as dist
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         import sageattention_b200.nvfp4 as nv
         from sageattention_b200.nvfp4 import distributed as D
-        z, h, hk, d, s_loc = 1, 4, 2, 128, 512
+        z, h, hk = 1, 4, 2
         s = s_loc * world
         g = torch.Generator().manual_seed(5)
         q = torch.randn(z, h, s, d, generator=g).to(torch.bfloat16).cuda()
@@ -73,18 +75,30 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_ring_and_sharding_two_gpus_match_single_gpu():
+@pytest.mark.parametrize("d,s_loc", [(128, 512), (256, 2048)])
+def test_ring_and_sharding_two_gpus_match_single_gpu(d, s_loc):
+    """D=256 with 2048 local tokens (two zigzag chunks of 1024) is the shape class of the
+    long-context configuration the ring exists for."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     world, port = 2, _free_port()
     ctx = mp.get_context("spawn")
     ret = ctx.Manager().dict()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret, d, s_loc)) for r in range(world)]
     for p in procs:
         p.start()
+    try:
+        for p in procs:
+            p.join(300)
+    finally:               # a rank that stalled must not keep holding a GPU after the test
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
     for p in procs:
-        p.join(300)
         assert p.exitcode == 0
     for r in range(world):
         cos, lse_err, shard_equal, gcos, zcos = ret[r]

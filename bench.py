@@ -273,8 +273,8 @@ def measure_peaks(cx, _lib):
     import ctypes
     torch = cx.torch
     sink = torch.zeros(4, dtype=torch.float32, device=cx.dev)
-    names = {0: "fp4_mma_tflops", 1: "bf16_mma_tflops", 2: "ex2_per_sm_per_clk", 3: "cvt_e2m1x2_per_sm_per_clk",
-             4: "fma_per_sm_per_clk"}
+    names = {0: "fp4_mma_tflops", 1: "bf16_mma_tflops", 2: "ex2_per_sm_per_s", 3: "cvt_e2m1x2_per_sm_per_s",
+             4: "fma_per_sm_per_s"}
     out = {}
     sms = torch.cuda.get_device_properties(cx.dev).multi_processor_count
     for what, key in names.items():
@@ -820,7 +820,7 @@ def run_profile_case(args):
             measure_peaks(cx, _lib)
         clocks = sampler.stop()
         mhz = (clocks or {}).get("sm_mhz") or 1965.0
-        per_clk = {k_: v_ / (mhz * 1e6) for k_, v_ in rates.items() if k_.endswith("per_clk")}
+        per_clk = {k_.replace("_per_s", "_per_clk"): v_ / (mhz * 1e6) for k_, v_ in rates.items() if k_.endswith("per_sm_per_s")}
         print(json.dumps({"profile_case": case, "rates": rates, "per_sm_per_clk_at_sampled_clock": per_clk,
                           "clocks": clocks, "status": _lib.read_status(dev)}))
         return

@@ -64,11 +64,14 @@ int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, i
  * (dnib [B, S, d/2], dsc [B, S, d/16]) and along S as the transposed layout (tnib [B, d, s_pad/2],
  * tsc [B, d, s_pad/16], tokens >= S read as +0.0).  All four outputs contiguous.  Replaces
  * `_quant_nvfp4_dual` / `_quant_nvfp4_dual_kernel` (flash.py:434-561); bytes equal two nvfp4_pack
- * calls.  d % 16 == 0, s_pad % 16 == 0, s_pad >= S.
+ * calls.  d % 16 == 0, s_pad % 16 == 0, s_pad >= S.  With `prescale_amax` (a device float holding
+ * max|x|, e.g. from nvfp4_bwd_prep) every element is first divided by the smallest power of two
+ * >= that value (exact), so the packed tensor is x / 2^e with 0.5 < max|.| <= 1 -- the global
+ * normalisation of dO in the all-FP4 backward; NULL packs x itself.
  */
 int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
-                    int64_t sxb, int64_t sxs, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib,
-                    uint8_t* tsc, nvfp4_stream_t stream);
+                    int64_t sxb, int64_t sxs, const float* prescale_amax, uint8_t* dnib,
+                    uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, nvfp4_stream_t stream);
 
 /*
  * Forward pre-pack in ONE launch: Q [bq, s_q, d] and K [bk, s_kv, d] along d, V [bk, s_kv, d] along
@@ -233,13 +236,14 @@ int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const 
 /*
  * Backward pre-pass over x [nb1, nb2, s, d] (element strides sxb1, sxb2, sxs; unit stride along
  * d): writes either or both of xc [nb1*nb2, s, d] (contiguous bf16 copy) and delta [nb1*nb2, s] =
- * rowsum(x o y) (y has its own strides, same dtype as x).  Replaces the delta part of
- * `_flash_bwd_packprep_kernel` (flash.py:1175-1403); the reference's transposed packs have no
- * counterpart here because the gradient GEMMs read row-major bf16 tiles in either orientation.
+ * rowsum(x o y) (y has its own strides, same dtype as x); with `amax` (one device float the
+ * caller zeroed) also max|x| over the whole tensor by atomic maximum, which the all-FP4 backward
+ * turns into its global power-of-two pre-scale of dO.  Replaces the delta part of
+ * `_flash_bwd_packprep_kernel` (flash.py:1175-1403).
  */
 int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t nb1,
                    int64_t nb2, const void* y, int64_t syb1, int64_t syb2, int64_t sys, int64_t s,
-                   int d, void* xc, float* delta, nvfp4_stream_t stream);
+                   int d, void* xc, float* delta, float* amax, nvfp4_stream_t stream);
 
 /*
  * Backward with high-precision gradient GEMMs: dQ, dK, dV of the forward above.  Replaces
@@ -261,6 +265,36 @@ int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, con
                  int grad_dtype, int64_t z,
                  int64_t h, int64_t hk, int64_t s_q, int64_t s_kv, int d, float scaling, int flags,
                  int* status, nvfp4_stream_t stream);
+
+/*
+ * Backward with ALL GEMMs in NVFP4 (the "fp4_rownorm" mode).  Replaces `_run_bwd` and its kernels
+ * `_flash_bwd_dkdv_kernel` / `_flash_bwd_dq_kernel` (flash.py:1559-1995, 3811-4265); the pre-pass
+ * packs (`_flash_bwd_packprep_kernel`, `_flash_bwd_kprep_kernel`, flash.py:1175-1538) are made with
+ * nvfp4_bwd_prep (delta, max|dO|), nvfp4_pack_dual (dO with the power-of-two pre-scale) and
+ * nvfp4_pack.  S and dP are block-scaled FP4 products of along-D packs; P and dS are packed along
+ * the contraction axis inside the kernels and multiplied with the transposed packs.  The
+ * reference keeps operand scales in range with a per-row rms factor recomputed every tile
+ * (flash.py:184-228); here the factors are constant while a tile accumulates (dO / 2^e globally,
+ * P * 2^11, dS * 2^9), so dK / dV / dQ accumulate in tensor memory and dK / dV are reduced over
+ * the GQA group in the kernel.  No atomics.
+ *   qnv/qsc, knv/ksc     packs of Q [Z*H, s_q, .] and K [Z*Hk, s_kv, .] along D (the forward's)
+ *   vdnv/vdsc            V [Z*Hk, s_kv, .] packed along D
+ *   donv/dosc            dO / 2^e [Z*H, s_q, .] along D;  dotnv/dotsc its transpose [Z*H, D, sq_pad/2 | /16]
+ *   qtnv/qtsc            Q^T [Z*H, D, sq_pad/2 | /16];  ktnv/ktsc  K^T [Z*Hk, D, skv_pad/2 | /16]
+ *   lse, delta [Z*H, s_q] fp32 (delta in units of dO);  do_amax: device float, max|dO| (2^e is the
+ *   smallest power of two >= it);  key_bias [Z, s_kv] or NULL;  seq_start / seq_end [s] or NULL
+ *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
+ * sq_pad / skv_pad: multiples of 128.  flags: NVFP4_FWD_CAUSAL.  D is 128 or 256.
+ */
+int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
+                  const uint8_t* vdnv, const uint8_t* vdsc, const uint8_t* donv, const uint8_t* dosc,
+                  const uint8_t* dotnv, const uint8_t* dotsc, const uint8_t* qtnv,
+                  const uint8_t* qtsc, const uint8_t* ktnv, const uint8_t* ktsc, const float* lse,
+                  const float* delta, const float* do_amax, const float* key_bias,
+                  const int32_t* seq_start, const int32_t* seq_end, void* dq, void* dk, void* dv,
+                  int grad_dtype, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
+                  int64_t sq_pad, int64_t skv_pad, int d, float scaling, int flags, int* status,
+                  nvfp4_stream_t stream);
 
 /*
  * Measured pipe rates (no counterpart in the reference): launches a resident-operand micro-kernel

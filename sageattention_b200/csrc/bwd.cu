@@ -28,6 +28,7 @@
 #include "common/fp4.cuh"
 #include "common/sm100.cuh"
 #include "common/tma_host.cuh"
+#include "common/bwd_util.cuh"
 
 namespace nvfp4 {
 
@@ -62,51 +63,6 @@ __device__ __forceinline__ void umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, u
       "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ float ex2_bwd(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// K-major bf16 tile, rows of 128 bytes (64 elements), 128-byte swizzle: the MMA that consumes the
-// 16 elements starting at element k16*16 of every row.
-__device__ __forceinline__ uint64_t desc_sw128(const void* tile, int k16) {
-  return make_smem_desc(smem_u32(tile) + (k16 & 3) * 32, 16, 1024, 2);
-}
-// The same kind of tile read as an MN-major operand: the contraction runs over the rows (16 rows
-// = 2 KB per MMA), the 128 output columns are two 64-element sub-tiles `sub_bytes` apart.
-__device__ __forceinline__ uint64_t desc_sw128_mn(const void* tile, int k16, uint32_t sub_bytes) {
-  return make_smem_desc(smem_u32(tile) + k16 * 2048, sub_bytes, 1024, 2);
-}
-__device__ __forceinline__ uint64_t desc_sw64(const void* tile, int k64) {
-  return make_smem_desc(smem_u32(tile) + (k64 & 1) * 32, 16, 512, 4);
-}
-__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-// eight consecutive elements, one 16-byte load (two for fp32) when the address allows it
-template <typename T>
-__device__ __forceinline__ void load8(const T* src, float (&v)[8]) {
-  if constexpr (sizeof(T) == 2) {
-    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(src);
-      const T* t = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(t[e]);
-      return;
-    }
-  } else {
-    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-      const float4 a = *reinterpret_cast<const float4*>(src), c = *reinterpret_cast<const float4*>(src + 4);
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
-      return;
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(src[e]);
-}
-
 // ------------------------------------------------------------------------------------------
 // Pre-pass over rows of x [B1, B2, S, D] (strided, unit stride along D): optional contiguous
 // bf16 copy xc [B1*B2, S, D] and optional delta [B1*B2, S] = rowsum(x o y).  Half a warp per row,
@@ -117,10 +73,11 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
                                                        int64_t sxs, int nb2, const T* __restrict__ y,
                                                        int64_t syb1, int64_t syb2, int64_t sys, int S, int D,
                                                        int64_t rows, __nv_bfloat16* __restrict__ xc,
-                                                       float* __restrict__ delta) {
+                                                       float* __restrict__ delta, float* __restrict__ amax) {
   const int lane = threadIdx.x & 31, l16 = lane & 15;
   const int64_t base0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
   const int64_t nhw = (int64_t)gridDim.x * 16;
+  float vmax = 0.0f;   // largest |x| this thread has seen (non-negative floats order like their bit patterns)
   for (int64_t base = base0; base < rows; base += nhw) {    // both half-warps take every trip (shuffles)
     const int64_t row0 = base + (lane >> 4);
     const bool live = row0 < rows;
@@ -134,6 +91,10 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
     for (int c = l16 * 8; c < D; c += 128) {
       float v[8], w8[8];
       load8<T>(xr + c, v);
+      if (amax != nullptr && live) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
+      }
       if (yr) {
         load8<T>(yr + c, w8);
 #pragma unroll
@@ -154,6 +115,12 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, 
       if (l16 == 0 && live) delta[row] = acc;
     }
   }
+  if (amax != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    if (lane == 0 && vmax > 0.0f && vmax < INFINITY)
+      atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(vmax));
+  }
 }
 
 struct BwdParams {
@@ -173,34 +140,6 @@ struct BwdParams {
   int causal;
   int* status;
 };
-
-// 32 fp32 accumulator columns -> 32 contiguous gradient elements
-template <typename TG>
-__device__ __forceinline__ void store_row32(TG* dst, const uint32_t (&r)[32], float mul) {
-  if constexpr (sizeof(TG) == 2) {
-    uint32_t w[16];
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const TG a0 = from_f32<TG>(__uint_as_float(r[2 * e]) * mul);
-      const TG a1 = from_f32<TG>(__uint_as_float(r[2 * e + 1]) * mul);
-      w[e] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&a0)) |
-             ((uint32_t)(*reinterpret_cast<const uint16_t*>(&a1)) << 16);
-    }
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) d4[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
-  } else {
-    float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-    for (int e = 0; e < 8; ++e)
-      d4[e] = make_float4(__uint_as_float(r[4 * e]) * mul, __uint_as_float(r[4 * e + 1]) * mul,
-                          __uint_as_float(r[4 * e + 2]) * mul, __uint_as_float(r[4 * e + 3]) * mul);
-  }
-}
-template <typename TG>
-__device__ __forceinline__ void zero_row(TG* dst, int n) {
-  for (int e = 0; e < n; ++e) dst[e] = from_f32<TG>(0.0f);
-}
 
 // P for 32 columns of one accumulator row: exp2(s * c2 + offsets).  Per-column statistics (the
 // dK/dV kernel): `nl` points at the raw lse of the 32 columns in shared memory and `nl_row` is a
@@ -912,12 +851,12 @@ inline int make_tmap_bf16_3d_sw128(CUtensorMap* m, const void* base, uint64_t n0
 template <typename T>
 int prep_launch(const void* x, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t nb1, int64_t nb2, const void* y,
                 int64_t syb1, int64_t syb2, int64_t sys, int S, int D, __nv_bfloat16* xc, float* delta,
-                cudaStream_t st) {
+                float* amax, cudaStream_t st) {
   const int64_t rows = nb1 * nb2 * S;
   const int64_t blocks = (rows + 15) / 16;
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
   bwd_prep_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), sxb1, sxb2, sxs, (int)nb2,
-                                           static_cast<const T*>(y), syb1, syb2, sys, S, D, rows, xc, delta);
+                                           static_cast<const T*>(y), syb1, syb2, sys, S, D, rows, xc, delta, amax);
   return launch_result("nvfp4_bwd_prep");
 }
 
@@ -925,10 +864,10 @@ int prep_launch(const void* x, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t 
 
 extern "C" int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t sxs,
                               int64_t nb1, int64_t nb2, const void* y, int64_t syb1, int64_t syb2,
-                              int64_t sys, int64_t s, int d, void* xc, float* delta,
+                              int64_t sys, int64_t s, int d, void* xc, float* delta, float* amax,
                               nvfp4_stream_t stream) {
   using namespace nvfp4;
-  NVFP4_REQUIRE(x != nullptr && (xc || delta), "nvfp4_bwd_prep: nothing to do");
+  NVFP4_REQUIRE(x != nullptr && (xc || delta || amax), "nvfp4_bwd_prep: nothing to do");
   NVFP4_REQUIRE(d >= 8 && d % 8 == 0 && s >= 1 && nb1 >= 1 && nb2 >= 1, "nvfp4_bwd_prep: bad extents");
   NVFP4_REQUIRE(s < (1LL << 31), "nvfp4_bwd_prep: sequence too long");
   NVFP4_REQUIRE(delta == nullptr || y != nullptr, "nvfp4_bwd_prep: delta needs the second operand");
@@ -936,11 +875,11 @@ extern "C" int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sx
   auto* c = static_cast<__nv_bfloat16*>(xc);
   switch (dtype) {
     case NVFP4_DT_BF16:
-      return prep_launch<__nv_bfloat16>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, st);
+      return prep_launch<__nv_bfloat16>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, amax, st);
     case NVFP4_DT_FP16:
-      return prep_launch<__half>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, st);
+      return prep_launch<__half>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, amax, st);
     case NVFP4_DT_FP32:
-      return prep_launch<float>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, st);
+      return prep_launch<float>(x, sxb1, sxb2, sxs, nb1, nb2, y, syb1, syb2, sys, (int)s, d, c, delta, amax, st);
     default:
       return fail(-1, "nvfp4_bwd_prep: unknown dtype %d", dtype);
   }

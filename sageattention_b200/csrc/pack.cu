@@ -9,6 +9,7 @@
 // A scalar kernel covers any other stride combination.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
+#include "common/bwd_util.cuh"
 
 namespace nvfp4 {
 
@@ -162,7 +163,9 @@ __device__ __forceinline__ void pack_cols_tile(
     ColsSmem& sm, const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
     int64_t ssr, int vec_in, int64_t bx, int64_t by, int64_t b, uint8_t* __restrict__ dnib, int64_t dnb,
-    int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr) {
+    int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax) {
+  // exact division by a power of two (1 when no pre-scale is asked for)
+  const float pre = (kDual && prescale_amax != nullptr) ? __frcp_rn(pow2_ceil(*prescale_amax)) : 1.0f;
   auto& tile = sm.tile;
   auto& onib = sm.onib;
   auto& osc = sm.osc;
@@ -189,7 +192,7 @@ __device__ __forceinline__ void pack_cols_tile(
       for (int i = 0; i < 8; ++i) v[i] = 0.0f;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) tile[key][rc + i] = v[i];
+    for (int i = 0; i < 8; ++i) tile[key][rc + i] = kDual ? v[i] * pre : v[i];
   }
   __syncthreads();
   if constexpr (kDual) {
@@ -254,10 +257,10 @@ __global__ void __launch_bounds__(256) pack_cols_kernel(
     const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
     int64_t ssr, int vec_in, uint8_t* __restrict__ dnib, int64_t dnb, int64_t dnr,
-    uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr) {
+    uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax) {
   __shared__ ColsSmem sm;
   pack_cols_tile<T, kDual>(sm, x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc, ssb, ssr, vec_in, blockIdx.x,
-                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr);
+                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr, prescale_amax);
 }
 
 // ---------------------------------------------------------------- Q, K along D and V^T in one launch
@@ -304,7 +307,7 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const QkvArgs a) {
   const int64_t by = rem / a.tx, bx = rem - by * a.tx;
   pack_cols_tile<T, false>(sm, static_cast<const T*>(a.v), a.d, a.s_kv, a.s_pad, a.svb, a.svk, a.vnv,
                            (int64_t)a.d * (a.s_pad / 2), a.s_pad / 2, a.vsc, (int64_t)a.d * (a.s_pad / 16),
-                           a.s_pad / 16, a.vec_v, bx, by, b, nullptr, 0, 0, nullptr, 0, 0);
+                           a.s_pad / 16, a.vec_v, bx, by, b, nullptr, 0, 0, nullptr, 0, 0, nullptr);
 }
 
 // ---------------------------------------------------------------- any strides (scalar)
@@ -358,7 +361,7 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
     dim3 grid((unsigned)((k_pad + kColsKeys - 1) / kColsKeys),
               (unsigned)((R + kColsRows - 1) / kColsRows), (unsigned)B);
     pack_cols_kernel<T, false><<<grid, 256, 0, st>>>(x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc,
-                                                     ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0);
+                                                     ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0, nullptr);
     return launch_result("nvfp4_pack(cols)");
   }
   const int64_t blocks = (total + 255) / 256;
@@ -400,7 +403,8 @@ namespace nvfp4 {
 
 template <typename T>
 int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, int64_t sxb, int64_t sxs,
-                     uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, cudaStream_t st) {
+                     const float* prescale_amax, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc,
+                     cudaStream_t st) {
   constexpr int64_t kVecElems = 16 / sizeof(T);
   const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && sxb % kVecElems == 0 && sxs % kVecElems == 0;
   dim3 grid((unsigned)((s_pad + kColsKeys - 1) / kColsKeys), (unsigned)((d + kColsRows - 1) / kColsRows),
@@ -408,7 +412,7 @@ int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, 
   pack_cols_kernel<T, true><<<grid, 256, 0, st>>>(
       static_cast<const T*>(x), d, S, s_pad, sxb, sxs, tnib, (int64_t)d * (s_pad / 2), s_pad / 2, tsc,
       (int64_t)d * (s_pad / 16), s_pad / 16, vec, dnib, S * (int64_t)(d / 2), d / 2, dsc, S * (int64_t)(d / 16),
-      d / 16);
+      d / 16, prescale_amax);
   return launch_result("nvfp4_pack_dual");
 }
 
@@ -430,8 +434,8 @@ int pack_qkv_launch(QkvArgs a, cudaStream_t st) {
 }  // namespace nvfp4
 
 extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
-                               int64_t sxb, int64_t sxs, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib,
-                               uint8_t* tsc, nvfp4_stream_t stream) {
+                               int64_t sxb, int64_t sxs, const float* prescale_amax, uint8_t* dnib,
+                               uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(B >= 0 && S >= 0 && d >= 16 && d % 16 == 0, "nvfp4_pack_dual: head dim must be a positive multiple of 16");
   NVFP4_REQUIRE(s_pad % 16 == 0 && s_pad >= S, "nvfp4_pack_dual: s_pad must be a multiple of 16 >= S");
@@ -441,9 +445,9 @@ extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, i
   NVFP4_REQUIRE(((uintptr_t)dnib & 7) == 0, "nvfp4_pack_dual: nibble buffers must be 8-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case NVFP4_DT_BF16: return pack_dual_launch<__nv_bfloat16>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
-    case NVFP4_DT_FP16: return pack_dual_launch<__half>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
-    case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_BF16: return pack_dual_launch<__nv_bfloat16>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP16: return pack_dual_launch<__half>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
     default: return fail(-1, "nvfp4_pack_dual: unknown dtype %d", dtype);
   }
 }

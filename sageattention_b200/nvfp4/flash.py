@@ -142,11 +142,13 @@ def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     return nib, sc.view(torch.float8_e4m3fn)
 
 
-def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None):
+def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None, _prescale_amax: torch.Tensor | None = None):
     """Both layouts of ``x`` [B, S, D] from one read: along D and along S (padded to ``s_pad``).
 
     Stands in for flash.py:514-561 (one kernel, one pass over ``x``); bytes equal two
-    ``_quant_nvfp4`` calls.  Returns ``(nib_d, sc_d, nib_s, sc_s)``.
+    ``_quant_nvfp4`` calls.  Returns ``(nib_d, sc_d, nib_s, sc_s)``.  ``_prescale_amax`` (a device
+    float holding max|x|) first divides ``x`` by the smallest power of two >= that value (the global
+    normalisation of dO in the all-FP4 backward).
     """
     _lib.require_cuda(x, "x")
     b, s, d = x.shape
@@ -162,7 +164,8 @@ def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None):
     ss = torch.empty(b, d, sp // 16, dtype=torch.uint8, device=dev)
     if b * sp > 0:
         _lib.call("nvfp4_pack_dual", dev, x.data_ptr(), _lib.dtype_code(x.dtype), b, s, d, sp, x.stride(0),
-                  x.stride(1), nd.data_ptr(), sd.data_ptr(), ns.data_ptr(), ss.data_ptr(), _lib.stream_ptr(dev))
+                  x.stride(1), _prescale_amax.data_ptr() if _prescale_amax is not None else None,
+                  nd.data_ptr(), sd.data_ptr(), ns.data_ptr(), ss.data_ptr(), _lib.stream_ptr(dev))
     return nd, sd.view(torch.float8_e4m3fn), ns, ss.view(torch.float8_e4m3fn)
 
 
@@ -463,15 +466,17 @@ def nvfp4_flash_attention(query, key, value, scaling, causal=False, num_key_valu
 
 
 # --------------------------------------------------------------------------- backward
-def _bwd_prep(x, y=None, want_copy=False):
+def _bwd_prep(x, y=None, want_copy=False, want_amax=False):
     """C-ABI pre-pass on a ``[B1, B2, S, D]`` tensor with unit stride along D (any other strides):
-    returns ``(xc [B1*B2, S, D] bf16 | None, delta [B1*B2, S] = rowsum(x*y) | None)``."""
+    returns ``(xc [B1*B2, S, D] bf16 | None, delta [B1*B2, S] = rowsum(x*y) | None)``, and with
+    ``want_amax`` a third element: a device float holding max|x|."""
     b1, b2, s, d = x.shape
     if x.stride(3) != 1:
         x = x.contiguous()
     dev = x.device
     xc = torch.empty(b1 * b2, s, d, dtype=torch.bfloat16, device=dev) if want_copy else None
     delta = torch.empty(b1 * b2, s, dtype=torch.float32, device=dev) if y is not None else None
+    amax = torch.zeros(1, dtype=torch.float32, device=dev) if want_amax else None
     if y is not None:
         if y.dtype != x.dtype:
             y = y.to(x.dtype)
@@ -483,7 +488,10 @@ def _bwd_prep(x, y=None, want_copy=False):
               y.stride(0) if y is not None else 0, y.stride(1) if y is not None else 0,
               y.stride(2) if y is not None else 0, s, d,
               xc.data_ptr() if xc is not None else None,
-              delta.data_ptr() if delta is not None else None, _lib.stream_ptr(dev))
+              delta.data_ptr() if delta is not None else None,
+              amax.data_ptr() if amax is not None else None, _lib.stream_ptr(dev))
+    if want_amax:
+        return xc, delta, amax
     return xc, delta
 
 
@@ -548,16 +556,72 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     return dq, dk, dv
 
 
+_FP8_NOTE_SHOWN = False
+
+
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
              mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, **_unused):
-    """Backward for the ``fp4_rownorm`` / ``fp8_rownorm`` / ``fp4_legacy`` modes (flash.py:3811-4265).
+    """All-FP4 backward for the ``fp4_rownorm`` / ``fp4_legacy`` modes (stands in for
+    flash.py:3811-4265): every GEMM of the backward is a block-scaled NVFP4 tensor-core product.
 
-    This build runs them on the high-precision gradient GEMM kernels: the probabilities still come
-    from the FP4 recompute, the gradient GEMMs are bf16, which meets the accuracy floor of every
-    mode (gradient cosine >= 0.93 against exact attention) with margin.
+    Pre-pass (four small launches): delta = rowsum(dO o O) and max|dO|; dO / 2^e packed along D and
+    along the tokens from one read; Q^T and K^T packed along the tokens; V packed along D.  Then the
+    dK/dV kernel (GQA reduced in tensor memory) and the dQ kernel.  ``fp8_rownorm`` (MXFP8 gradient
+    operands in the reference) has no kernel of its own here: it runs the high-precision
+    gradient-GEMM kernels, which are strictly more accurate; a note is printed once.
     """
-    return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout,
-                       q_packs=q_packs, k_packs=k_packs, key_pad_bias=key_pad_bias)
+    if mode == "fp8_rownorm":
+        global _FP8_NOTE_SHOWN
+        if not _FP8_NOTE_SHOWN:
+            import warnings
+            warnings.warn("backward_grad_dots='fp8_rownorm': no MXFP8 gradient kernels in this build; "
+                          "running the bf16 gradient-GEMM kernels instead", stacklevel=2)
+            _FP8_NOTE_SHOWN = True
+        return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout,
+                           q_packs=q_packs, k_packs=k_packs, key_pad_bias=key_pad_bias)
+    z, h, s_q, d = q.shape
+    _, hk, s_kv, _ = k.shape
+    assert d in (128, 256), "D must be 128 or 256"
+    dev = q.device
+    if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
+        out = out.transpose(1, 2)
+        dout = dout.transpose(1, 2)
+    need_copy = not dout.is_contiguous()
+    doc, delta, amax = _bwd_prep(dout, y=out, want_copy=need_copy, want_amax=True)
+    do3 = doc if doc is not None else dout.reshape(z * h, s_q, d)
+    sq_pad, skv_pad = _next_mult(s_q, _KEY_TILE), _next_mult(s_kv, _KEY_TILE)
+    donv, dosc, dotnv, dotsc = _quant_nvfp4_dual(do3, sq_pad, _prescale_amax=amax)
+    q3, k3, v3 = q.reshape(z * h, s_q, d), k.reshape(z * hk, s_kv, d), v.reshape(z * hk, s_kv, d)
+    if q_packs is not None:
+        qnv, qsc = (t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
+        qtnv, qtsc = _quant_nvfp4(q3, transpose=True, k_pad=sq_pad)
+    else:
+        qnv, qsc, qtnv, qtsc = _quant_nvfp4_dual(q3, sq_pad)
+    if k_packs is not None:
+        knv, ksc = (t.contiguous() for t in _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout"))
+        ktnv, ktsc = _quant_nvfp4(k3, transpose=True, k_pad=skv_pad)
+    else:
+        knv, ksc, ktnv, ktsc = _quant_nvfp4_dual(k3, skv_pad)
+    vdnv, vdsc = _quant_nvfp4(v3)
+    gdt = dout.dtype
+    dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
+    dk = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
+    dv = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
+    sst = sen = None
+    if varlen_arrays is not None:
+        _, sst, sen = varlen_arrays
+    lse = lse.contiguous()
+    bias = None
+    if key_pad_bias is not None:
+        bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
+        assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _lib.call("nvfp4_bwd_fp4", _lib.same_device(qnv, knv, vdnv, donv, dotnv, qtnv, ktnv, lse, delta, bias, sst, sen),
+              ptr(qnv), ptr(qsc), ptr(knv), ptr(ksc), ptr(vdnv), ptr(vdsc), ptr(donv), ptr(dosc), ptr(dotnv),
+              ptr(dotsc), ptr(qtnv), ptr(qtsc), ptr(ktnv), ptr(ktsc), ptr(lse), ptr(delta), ptr(amax), ptr(bias),
+              ptr(sst), ptr(sen), ptr(dq), ptr(dk), ptr(dv), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, sq_pad,
+              skv_pad, d, float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    return dq, dk, dv
 
 
 def _gqa_reduce_cast_dkdv(dk_planes: torch.Tensor, dv_planes: torch.Tensor, z: int, hk: int, g: int,

@@ -80,17 +80,19 @@ def test_backward_matches_exact_gradients(z, h, hk, sq, skv, causal):
         assert c >= floor, (nm, c)
 
 
-@pytest.mark.parametrize("name,floor", [("hp_d128", 0.995), ("hp_varlen_d128", 0.995), ("rownorm_d128", 0.95)])
-def test_backward_matches_reference_fixture(golden, name, floor):
+@pytest.mark.parametrize("name,mode,floor", [("hp_d128", "bf16", 0.995), ("hp_varlen_d128", "bf16", 0.995),
+                                             ("rownorm_d128", "bf16", 0.95), ("rownorm_d128", "fp4_rownorm", 0.97)])
+def test_backward_matches_reference_fixture(golden, name, mode, floor):
     """Gradients of the reference's own backward kernels on the same inputs (fp32 tensors holding
     bf16 values, so gradients come back in fp32).  The high-precision mode shares this build's
-    algorithm (FP4 recompute of P, bf16 gradient GEMMs); the all-FP4 mode of the reference carries
-    its own quantisation noise, so the floor against it is lower."""
+    algorithm (FP4 recompute of P, bf16 gradient GEMMs).  The reference's all-FP4 gradients carry
+    their own quantisation noise: this build's all-FP4 kernels (other normalisation factors, same
+    operand precision) must agree with them to 0.97, its bf16 kernels to 0.95."""
     g = golden("backward")
     z, h, hk, s, d = g[name + "_meta"].tolist()
     q, k, v, do = (_bits_to_cuda(g[f"{name}_{t}"]).float() for t in ("q", "k", "v", "do"))
     cu = torch.from_numpy(g[name + "_cu"]).cuda() if name + "_cu" in g.files else None
-    out, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu)
+    out, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu, mode=mode)
     assert dq.dtype == torch.float32
     co = cos(out.cpu().numpy(), g[name + "_out"])
     assert co >= 0.995, co
@@ -117,6 +119,107 @@ def test_backward_d256_matches_exact_gradients(z, h, hk, sq, skv, causal):
         c = cos(a, b)
         print("d256", nm, "cos", c)
         assert c >= (COS_HP if min(sq, skv) >= 256 else 0.985), (nm, c)
+
+
+FP4_CASES = CASES + [
+    (1, 4, 2, 1024, 1024, True),     # several 128-column stages per tile, GQA reduction
+    (2, 2, 1, 333, 777, False),      # ragged stages on both sides
+    (1, 2, 2, 300, 300, True),
+]
+
+
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("z,h,hk,sq,skv,causal", FP4_CASES)
+def test_all_fp4_backward_matches_exact_gradients(z, h, hk, sq, skv, causal, d):
+    """`backward_grad_dots="fp4_rownorm"`: every GEMM of the backward in NVFP4 (its own kernels, not
+    the bf16 ones): gradient cosine >= 0.93 against exact attention, and not the bf16 result."""
+    q, qn = seeded_bf16((z, h, sq, d), 111)
+    k, kn = seeded_bf16((z, hk, skv, d), 112)
+    v, vn = seeded_bf16((z, hk, skv, d), 113)
+    do, don = seeded_bf16((z, h, sq, d), 114)
+    out, dq, dk, dv = _grads(q, k, v, do, causal, h // hk, mode="fp4_rownorm")
+    _, hq, hk_, hv = _grads(q, k, v, do, causal, h // hk, mode="bf16")
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, causal, h // hk)
+    for nm, a, b, hp in (("dq", dq, rq, hq), ("dk", dk, rk, hk_), ("dv", dv, rv, hv)):
+        an = a.float().cpu().numpy()
+        assert np.isfinite(an).all(), nm
+        c = cos(an, b)
+        print("fp4", d, nm, "cos vs exact", c, "vs bf16 kernels", cos(an, hp.float().cpu().numpy()))
+        if sq == 1 and nm != "dv":
+            continue            # one query row over few keys: dQ / dK are dominated by the P noise
+        assert c >= COS_FP4, (nm, c)
+        assert not torch.equal(a, hp), f"{nm}: the all-FP4 mode returned the bf16 kernels' result"
+
+
+@pytest.mark.parametrize("d", [128, 256])
+def test_all_fp4_backward_varlen_bias_and_scale_invariance(d):
+    h, hk = 4, 2
+    lens = [130, 1, 255, 64, 190]
+    s = sum(lens)
+    q, qn = seeded_bf16((1, h, s, d), 121)
+    k, kn = seeded_bf16((1, hk, s, d), 122)
+    v, vn = seeded_bf16((1, hk, s, d), 123)
+    do, don = seeded_bf16((1, h, s, d), 124)
+    cu_np = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cu = torch.tensor(cu_np, dtype=torch.int32, device="cuda")
+    _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu, mode="fp4_rownorm")
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, True, h // hk, cu_seqlens=cu_np)
+    for nm, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        c = cos(a.float().cpu().numpy(), b)
+        print("fp4 varlen", d, nm, c)
+        assert c >= COS_FP4, (nm, c)
+    # the global power-of-two pre-scale of dO makes the result exactly linear in powers of two
+    _, dq2, dk2, dv2 = _grads(q, k, v, do * 2.0 ** -20, True, h // hk, cu=cu, mode="fp4_rownorm")
+    for a, b in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        assert torch.equal((a.float() * 2.0 ** -20).to(torch.bfloat16), b)
+    # deterministic (no atomics on the gradient path)
+    _, dq3, dk3, dv3 = _grads(q, k, v, do, True, h // hk, cu=cu, mode="fp4_rownorm")
+    assert torch.equal(dq, dq3) and torch.equal(dk, dk3) and torch.equal(dv, dv3)
+    # key bias with masked keys, cross attention
+    z, sq, skv = 2, 200, 333
+    q, qn = seeded_bf16((z, h, sq, d), 131)
+    k, kn = seeded_bf16((z, hk, skv, d), 132)
+    v, vn = seeded_bf16((z, hk, skv, d), 133)
+    do, don = seeded_bf16((z, h, sq, d), 134)
+    gen = torch.Generator().manual_seed(135)
+    bias = torch.randn(z, skv, generator=gen) * 0.7
+    bias[0, skv - 9:] = float("-inf")
+    bias[1, 40:57] = float("-inf")
+    qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = _n().nvfp4_flash_attn_func(qq, kk, vv, d ** -0.5, causal=False, num_key_value_groups=h // hk,
+                                     key_pad_bias=bias.cuda(), backward_grad_dots="fp4_rownorm")
+    out.backward(do)
+    assert _status() == 0
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, False, h // hk, key_pad_bias=bias.numpy())
+    for nm, a, b in (("dq", qq.grad, rq), ("dk", kk.grad, rk), ("dv", vv.grad, rv)):
+        a = a.float().cpu().numpy()
+        assert np.isfinite(a).all(), nm
+        assert cos(a, b) >= COS_FP4, (nm, cos(a, b))
+    dkn, dvn = kk.grad.float().cpu().numpy(), vv.grad.float().cpu().numpy()
+    assert np.abs(dkn[0, :, skv - 9:]).max() == 0.0 and np.abs(dvn[0, :, skv - 9:]).max() == 0.0
+    assert np.abs(dkn[1, :, 40:57]).max() == 0.0 and np.abs(dvn[1, :, 40:57]).max() == 0.0
+
+
+def test_all_fp4_backward_zshd_fp16_and_external_packs():
+    """fp16 tensors, `out_layout="zshd"` (a strided [Z,S,H,D] gradient) and caller-supplied packs."""
+    z, h, hk, s, d = 1, 4, 2, 384, 128
+    gen = torch.Generator().manual_seed(141)
+    q, k, v, do = (torch.randn(*sh, generator=gen).to(torch.float16).cuda()
+                   for sh in ((z, h, s, d), (z, hk, s, d), (z, hk, s, d), (z, h, s, d)))
+    ref = _grads(q, k, v, do, True, h // hk, mode="fp4_rownorm")
+    got = _grads(q, k, v, do.transpose(1, 2).contiguous(), True, h // hk, mode="fp4_rownorm", out_layout="zshd")
+    assert got[1].dtype == torch.float16
+    for a, b in zip(got[1:], ref[1:]):
+        assert torch.equal(a, b)
+    n = _n()
+    qp = n._quant_nvfp4(q.reshape(z * h, s, d))
+    kp = n._quant_nvfp4(k.reshape(z * hk, s, d))
+    qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+    n.nvfp4_flash_attn_func(qq, kk, vv, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                            backward_grad_dots="fp4_rownorm", q_packs=qp, k_packs=kp).backward(do)
+    assert _status() == 0
+    for a, b in zip((qq.grad, kk.grad, vv.grad), ref[1:]):
+        assert torch.equal(a, b)
 
 
 def test_backward_d256_varlen_against_dense():

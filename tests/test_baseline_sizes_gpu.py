@@ -32,7 +32,7 @@ def _status():
 
 
 def _f(t):
-    return t.float().cpu().numpy()
+    return t.detach().float().cpu().numpy()
 
 
 def test_config2_prefill_unit_matches_oracle_at_full_size():

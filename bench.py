@@ -274,7 +274,8 @@ def measure_peaks(cx, _lib):
     torch = cx.torch
     sink = torch.zeros(4, dtype=torch.float32, device=cx.dev)
     names = {0: "fp4_mma_tflops", 1: "bf16_mma_tflops", 2: "ex2_per_sm_per_s", 3: "cvt_e2m1x2_per_sm_per_s",
-             4: "fma_per_sm_per_s"}
+             4: "fma_per_sm_per_s", 5: "ex2_plus_cvt_e2m1x2_pairs_per_sm_per_s", 6: "cvt_e4m3x2_per_sm_per_s",
+             7: "cvt_f16x2_from_e4m3x2_per_sm_per_s", 8: "cvt_bf16x2_per_sm_per_s"}
     out = {}
     sms = torch.cuda.get_device_properties(cx.dev).multi_processor_count
     for what, key in names.items():

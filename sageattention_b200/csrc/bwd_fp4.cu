@@ -14,10 +14,11 @@
 //               group in turn (dK / dV are reduced over the group in TMEM and written once);
 //   dQ pass     rows = queries of a head, columns = keys.
 // Per step the issuer thread queues S (or S^T) and dP as two N=64 block-scaled MMAs each; a
-// softmax thread owns one row and 32 columns, so the per-16 packs of P and dS along the columns are
-// thread-local: nibbles and scale bytes go to shared memory in the operand layout and feed one
-// M128 N128 K64 MMA per gradient.  Six FP4 MMAs per step replace the twenty bf16 MMAs of the
-// high-precision kernels.
+// softmax thread owns one row and the step's 64 columns, so the per-16 packs of P and dS along the
+// columns are thread-local: nibbles and scale bytes go to shared memory in the operand layout and
+// feed one M128 N128 K64 MMA per gradient.  Six FP4 MMAs per step replace the twenty bf16 MMAs of
+// the high-precision kernels.  Two teams of four softmax warps alternate steps, so the TMEM loads
+// and barrier waits of one step hide behind the arithmetic of the other.
 //
 // Keeping the packed operands inside the e4m3 scale range (2^-9 .. 448) -- the job of the
 // reference's per-row rms normalisation, flash.py:184-228 -- is done with factors that never change
@@ -41,8 +42,8 @@ namespace nvfp4 {
 constexpr int kB4Threads = 384;
 constexpr float kB4Log2e = 1.4426950408889634f;
 constexpr float kB4PShift = 11.0f;   // P is packed as P * 2^11
-constexpr float kB4DsShift = 9.0f;   // dS is packed as dS * 2^9
 constexpr int kB4Prefetch = 2;       // stages prefetched into L2 ahead of the ring
+
 
 template <int D>
 struct B4Cfg {
@@ -91,29 +92,50 @@ struct B4Params {
   int* status;
 };
 
-// 16 values -> 8 nibble bytes (two words) + the e4m3 scale byte, with the packer's scale rule; the
+__device__ __forceinline__ float b4_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float b4_absmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+  return d;
+}
+
+// 16 values -> 8 nibble bytes (two words) and the e4m3 scale byte, with the packer's scale rule; the
 // divisions are reciprocal multiplies here (these operands exist only inside the kernel).
 template <bool kSigned>
-__device__ __forceinline__ uint32_t b4_pack16(const float* v, uint32_t& lo, uint32_t& hi) {
-  float am;
+__device__ __forceinline__ uint32_t b4_pack16(const float* x, uint32_t& lo, uint32_t& hi) {
+  float m;
   if constexpr (kSigned) {
-    am = fmaxf(fabsf(v[0]), fabsf(v[1]));
+    m = fabsf(x[0]);
 #pragma unroll
-    for (int e = 2; e < 16; ++e) am = fmaxf(am, fabsf(v[e]));
+    for (int e = 1; e < 15; e += 2) m = b4_absmax3(m, x[e], x[e + 1]);
+    m = fmaxf(m, fabsf(x[15]));
   } else {
-    am = fmaxf(v[0], v[1]);
+    m = x[0];
 #pragma unroll
-    for (int e = 2; e < 16; ++e) am = fmaxf(am, v[e]);
+    for (int e = 1; e < 15; e += 2) m = b4_max3(m, x[e], x[e + 1]);
+    m = fmaxf(m, x[15]);
   }
-  const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
-  uint16_t sb16;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
-  const uint32_t sb = sb16 & 0xFFu;
+  uint32_t sb;
   float inv;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sb)));
-  lo = e2m1x8(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv, v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-  hi = e2m1x8(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv, v[12] * inv, v[13] * inv, v[14] * inv,
-              v[15] * inv);
+  {
+    const float s32 = fminf(fmaxf(m * 0.16666667f, kScaleFloor), kScaleMax);
+    uint16_t sb16;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(sb16));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(__half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFF)))));
+    sb = sb16 & 0xFFu;
+  }
+  const float2 i2 = make_float2(inv, inv);
+  float2 y[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(x[2 * e], x[2 * e + 1]), i2);
+  lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
+  hi = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
   return sb;
 }
 
@@ -192,12 +214,12 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
     mbar_init(&x_full, 1);
     mbar_init(&xsf_full, 1);
     mbar_init(&g_full, 1);
-    mbar_init(&g_free, 8);
+    mbar_init(&g_free, 4);
     mbar_init(&acc_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_free[b], 8);
-      mbar_init(&a_full[b], 8);
+      mbar_init(&s_free[b], 4);
+      mbar_init(&a_full[b], 4);
       mbar_init(&a_free[b], 1);
     }
     mbar_fence_init();
@@ -395,15 +417,25 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           umma_nvfp4(tmem + C::T_G, d_x2 + (k >> 1) * 512 + (k & 1) * 2, d_y2 + so + (k >> 1) * 512 + (k & 1) * 2,
                      id_n64, tmem + C::T_SFX2 + k * 4, tmem + C::T_SFY + k * 4, k > 0);
         umma_commit(&g_full);
-        if (st > 0) grad_gemms(st - 1);
+        // The gradient GEMMs trail by two steps: S and dP of step st are queued while the team that
+        // will consume them is still finishing step st - 2, so it finds them ready when it is done;
+        // waiting here for step st - 1 instead would put the whole MMA round trip between two steps
+        // of a team.
+        if (st > 1) grad_gemms(st - 2);
       }
+      grad_gemms(nstep - 2);
       grad_gemms(nstep - 1);
       umma_commit(&acc_done);
     }
     __syncwarp();
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ softmax groups, epilogue
-    const int grp = (warp - 4) >> 2;     // which 32 columns of a 64-column step
+    // ------------------------------------------------------------------ softmax teams, epilogue
+    // Two teams of four warps alternate steps (team t owns the steps of parity t, hence S slot t and
+    // half t of the operand tiles' rows), so one team's TMEM loads and barrier waits overlap the
+    // other team's arithmetic.  A thread owns one row and the 64 columns of its step, handled as
+    // two chunks of 32 (four 16-column groups packed thread-locally).
+    const int team = (warp - 4) >> 2;
+    const int grp = team;                 // epilogue: which 64 accumulator columns this thread stores
     const int wq = warp & 3;
     const int row_in = wq * 32 + lane;
     const int row = row0 + row_in;
@@ -411,6 +443,7 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
     const float c2 = p.scaling * kB4Log2e;
     const float cds = p.scaling * 0.25f;           // dS * 2^9 = (P * 2^11) * (dP - delta') * scaling / 4
     const bool row_ok = row < R;
+    const bool has_bias = p.bias != nullptr;
     // visible columns of this row: [lo, hi); per-row terms of the exponent and of dS
     int lo = 0, hi = 0;
     float row_e = 0.0f, row_nd = 0.0f;
@@ -423,7 +456,7 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           hi = min(hi, (int)p.seq_end[row]);
         }
         hi = max(hi, lo);
-        if (p.bias != nullptr) row_e = p.bias[(int64_t)zi * p.s_kv + row] * kB4Log2e;
+        if (has_bias) row_e = p.bias[(int64_t)zi * p.s_kv + row] * kB4Log2e;
       }
     } else {
       if (row_ok) {
@@ -439,70 +472,96 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
     }
     const uint32_t a1_s = smem_u32(s_res + C::O_A1), a2_s = smem_u32(s_res + C::O_A2);
     const uint32_t asf_s = smem_u32(s_res + C::O_ASF);
-    for (int st = 0; st < nstep; ++st) {
-      const int pp = st & 1, sg = st >> 1, s = sg % C::NSTAGE;
+    const float2 c22 = make_float2(c2, c2), cds2 = make_float2(cds, cds);
+    // dQ pass: the per-row exponent offset and -delta' term; dK/dV pass: these come per column from aux
+    const float2 re2 = kDkdv ? make_float2(0.0f, 0.0f) : make_float2(row_e, row_e);
+    const float2 rnd2 = make_float2(row_nd, row_nd);
+    for (int st = team; st < nstep; st += 2) {
+      const int pp = team, sg = st >> 1, s = sg % C::NSTAGE;
       int cb, col0;
       stage_cols(sg, cb, col0);
-      const int c0 = col0 + 64 * pp + 32 * grp;      // first column of this thread's chunk
-      const float* aux = reinterpret_cast<const float*>(s_stage + s * C::STAGE + C::S_AUX) + 64 * pp + 32 * grp;
-      const bool masked = !__all_sync(0xffffffffu, c0 >= lo && c0 + 32 <= hi);
-      if (pp == 0) mbar_wait(&full_aux[s], (sg / C::NSTAGE) & 1, &err, 10);
+      const float* aux0 = reinterpret_cast<const float*>(s_stage + s * C::STAGE + C::S_AUX) + 64 * pp;
+      const int cs0 = col0 + 64 * pp;                // first column of the step
+      const bool masked = !__all_sync(0xffffffffu, cs0 >= lo && cs0 + 64 <= hi);
+      mbar_wait(&full_aux[s], (sg / C::NSTAGE) & 1, &err, 10);
       mbar_wait(&s_full[pp], (st >> 1) & 1, &err, 11);
       mbar_wait(&g_full, st & 1, &err, 12);
       tc_fence_after();
-      uint32_t gr[32], sr[32];
-      tmem_ld32(tmem + lane_addr + C::T_G + grp * 32, gr);
-      tmem_ld32(tmem + lane_addr + C::T_S + pp * 64 + grp * 32, sr);
+      // dP (or dP^T): all 64 columns at once, so the single slot goes back to the issuer right away;
+      // S in 16-column chunks, the next one in flight while the current one is worked on
+      uint32_t g0[32], g1[32], sa[16], sb[16];
+      tmem_ld32(tmem + lane_addr + C::T_G, g0);
+      tmem_ld32(tmem + lane_addr + C::T_G + 32, g1);
+      tmem_ld16(tmem + lane_addr + C::T_S + pp * 64, sa);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&g_free);
-        mbar_arrive(&s_free[pp]);
-      }
-      // P * 2^11 and dS * 2^9 for the 32 columns
-      float pf[32], ds[32];
+      if (lane == 0) mbar_arrive(&g_free);
+      uint32_t wp[4], wd[4], scp = 0u, scd = 0u;
 #pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        float4 eo, nd4;
-        if constexpr (kDkdv) {
-          const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
-          eo = make_float4(a4.x + row_e, a4.y + row_e, a4.z + row_e, a4.w + row_e);
-          nd4 = *reinterpret_cast<const float4*>(aux + 128 + e);
-        } else {
-          const float4 a4 = *reinterpret_cast<const float4*>(aux + e);      // key bias (0 without one)
-          eo = make_float4(a4.x + row_e, a4.y + row_e, a4.z + row_e, a4.w + row_e);
-          nd4 = make_float4(row_nd, row_nd, row_nd, row_nd);
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t* cur = (ch & 1) ? sb : sa;
+        if (ch < 3) {
+          if (ch & 1) tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sa);
+          else tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sb);
         }
-        pf[e] = ex2_bwd(fmaf(__uint_as_float(sr[e]), c2, eo.x));
-        pf[e + 1] = ex2_bwd(fmaf(__uint_as_float(sr[e + 1]), c2, eo.y));
-        pf[e + 2] = ex2_bwd(fmaf(__uint_as_float(sr[e + 2]), c2, eo.z));
-        pf[e + 3] = ex2_bwd(fmaf(__uint_as_float(sr[e + 3]), c2, eo.w));
-        ds[e] = fmaf(__uint_as_float(gr[e]), cds, nd4.x);
-        ds[e + 1] = fmaf(__uint_as_float(gr[e + 1]), cds, nd4.y);
-        ds[e + 2] = fmaf(__uint_as_float(gr[e + 2]), cds, nd4.z);
-        ds[e + 3] = fmaf(__uint_as_float(gr[e + 3]), cds, nd4.w);
-      }
-      if (masked) {
+        const uint32_t* gsrc = ch < 2 ? g0 + 16 * ch : g1 + 16 * (ch - 2);
+        const float* aux = aux0 + 16 * ch;
+        float pf[16], ds[16];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) pf[e] = (c0 + e >= lo && c0 + e < hi) ? pf[e] : 0.0f;
-      }
+        for (int e = 0; e < 16; e += 4) {
+          float2 eo01 = re2, eo23 = re2, nd01 = rnd2, nd23 = rnd2;
+          if constexpr (kDkdv) {
+            const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
+            const float4 n4 = *reinterpret_cast<const float4*>(aux + 128 + e);
+            eo01 = make_float2(a4.x, a4.y); eo23 = make_float2(a4.z, a4.w);
+            nd01 = make_float2(n4.x, n4.y); nd23 = make_float2(n4.z, n4.w);
+          }
+          const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(cur[e]), __uint_as_float(cur[e + 1])), c22, eo01);
+          const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3])), c22, eo23);
+          const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e]), __uint_as_float(gsrc[e + 1])), cds2, nd01);
+          const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e + 2]), __uint_as_float(gsrc[e + 3])), cds2, nd23);
+          pf[e] = t01.x; pf[e + 1] = t01.y; pf[e + 2] = t23.x; pf[e + 3] = t23.y;
+          ds[e] = a01.x; ds[e + 1] = a01.y; ds[e + 2] = a23.x; ds[e + 3] = a23.y;
+        }
+        if (has_bias) {           // row bias (dK/dV pass) or column bias (dQ pass), base-2 units
 #pragma unroll
-      for (int e = 0; e < 32; ++e) ds[e] *= pf[e];
-      // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
-      if (st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
-      uint32_t w[4];
-      if constexpr (kDkdv) {
-        const uint32_t sb0 = b4_pack16<false>(pf, w[0], w[1]);
-        const uint32_t sb1 = b4_pack16<false>(pf + 16, w[2], w[3]);
-        sts_v4(a1_s + sw64_offset(row_in, pp * 32 + grp * 16), w[0], w[1], w[2], w[3]);
-        sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, grp * 2), sb0 | (sb1 << 8));
-      }
-      {
-        const uint32_t sb0 = b4_pack16<true>(ds, w[0], w[1]);
-        const uint32_t sb1 = b4_pack16<true>(ds + 16, w[2], w[3]);
-        sts_v4(a2_s + sw64_offset(row_in, pp * 32 + grp * 16), w[0], w[1], w[2], w[3]);
-        sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, grp * 2), sb0 | (sb1 << 8));
+          for (int e = 0; e < 16; ++e) pf[e] += kDkdv ? row_e : aux[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) pf[e] = ex2_bwd(pf[e]);
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pf[e] = (cs0 + 16 * ch + e >= lo && cs0 + 16 * ch + e < hi) ? pf[e] : 0.0f;
+        }
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
+          ds[e] = d2.x; ds[e + 1] = d2.y;
+        }
+        if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+        scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+        if (ch & 1) {
+          // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
+          if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
+          const int c2i = ch >> 1;      // which 32 columns of the step
+          if constexpr (kDkdv) {
+            sts_v4(a1_s + sw64_offset(row_in, pp * 32 + c2i * 16), wp[0], wp[1], wp[2], wp[3]);
+            sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, c2i * 2), scp);
+            scp = 0u;
+          }
+          sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
+          sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
+          scd = 0u;
+        }
+        if (ch < 3) {
+          tmem_ld_wait();
+          if (ch == 2) {          // the last chunk of S is in registers: the slot goes back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[pp]);
+          }
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();

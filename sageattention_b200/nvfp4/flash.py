@@ -586,9 +586,9 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
         out = out.transpose(1, 2)
         dout = dout.transpose(1, 2)
-    need_copy = not dout.is_contiguous()
-    doc, delta, amax = _bwd_prep(dout, y=out, want_copy=need_copy, want_amax=True)
-    do3 = doc if doc is not None else dout.reshape(z * h, s_q, d)
+    _, delta, amax = _bwd_prep(dout, y=out, want_amax=True)       # strided reads: no copy for the pre-pass
+    # the dual pack wants one batch stride: a [Z,S,H,D] gradient viewed per head has two (Z > 1)
+    do3 = dout.reshape(z * h, s_q, d) if (dout.is_contiguous() or z == 1) else dout.contiguous().view(z * h, s_q, d)
     sq_pad, skv_pad = _next_mult(s_q, _KEY_TILE), _next_mult(s_kv, _KEY_TILE)
     donv, dosc, dotnv, dotsc = _quant_nvfp4_dual(do3, sq_pad, _prescale_amax=amax)
     q3, k3, v3 = q.reshape(z * h, s_q, d), k.reshape(z * hk, s_kv, d), v.reshape(z * hk, s_kv, d)

@@ -111,16 +111,6 @@ __device__ __forceinline__ bool mbar_spin_wait(uint64_t* bar, uint32_t parity, v
   return false;
 }
 
-// Bounded wait that polls a few hundred times before parking: for waits that are usually short
-// and sit on a critical path, without the issue-slot cost of polling through a long wait.
-__device__ __forceinline__ bool mbar_poll_wait(uint64_t* bar, uint32_t parity, volatile int* err,
-                                               int site) {
-#pragma unroll 1
-  for (int i = 0; i < 512; ++i)
-    if (mbar_test_wait(bar, parity)) return true;
-  return mbar_wait(bar, parity, err, site);
-}
-
 // barrier among a subset of warps (id 1..15, nthreads multiple of 32)
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -182,6 +182,34 @@ int nvfp4_decode_static(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, 
                         int* status, nvfp4_stream_t stream);
 
 /*
+ * Hybrid decode in two calls, replacing the torch code of `NVFP4KVCache.hybrid_decode`
+ * (kv_cache.py:293-351: FP4 prefix decode, bf16 window attention, log-sum-exp merge).
+ *
+ * nvfp4_window_partials: exact attention of one query token per head over `count` high-precision
+ * ring keys (layout as nvfp4_window_attention), cut into `pieces` key ranges; block (unit, piece)
+ * writes its UN-normalised result (sum exp(s - m) v, m, sum exp(s - m)) as split-K partial slot
+ * extra_base + unit * pieces + piece of `workspace`, whose layout is that of nvfp4_decode with
+ * `total_slots` slots: acc [total_slots][16][d], then m [total_slots][16], then l.
+ *
+ * nvfp4_decode_hybrid: nvfp4_decode over the FP4 prefix whose final combine also merges `n_extra`
+ * such partials per unit (they follow the kernel's own slots: extra_base = own slots, total_slots =
+ * own slots + Z*Hk*n_extra; workspace_bytes must cover them).  out / lse are the attention over
+ * prefix and window together, written once in the query dtype.
+ */
+int nvfp4_window_partials(const void* q, int dtype, int64_t s_qz, int64_t s_qh, const void* rk,
+                          const void* rv, int64_t z, int64_t hk, int g, int d, int64_t ring_cap,
+                          int64_t first_pos, int64_t count, float scaling, int pieces,
+                          void* workspace, int64_t total_slots, int64_t extra_base,
+                          nvfp4_stream_t stream);
+int nvfp4_decode_hybrid(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh, const uint8_t* knv,
+                        int64_t knv_unit, const uint8_t* ksc, int64_t ksc_unit, const uint8_t* vnv,
+                        int64_t vnv_unit, int64_t vnv_row, const uint8_t* vsc, int64_t vsc_unit,
+                        int64_t vsc_row, int64_t z, int64_t hk, int g, int d, int64_t s_kv,
+                        float scaling, void* out, float* lse, void* workspace,
+                        size_t workspace_bytes, int nsplit, int64_t split_kv, int n_extra,
+                        int* status, nvfp4_stream_t stream);
+
+/*
  * Exact merge of two attention results over disjoint key sets from their log-sum-exps:
  * out = (e^{lse1-m} o1 + e^{lse2-m} o2) / (e^{lse1-m} + e^{lse2-m}).  Replaces the torch
  * expressions of NVFP4KVCache.hybrid_decode (kv_cache.py:346-351).  o1,o2,out: [rows, d] in

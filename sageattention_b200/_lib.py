@@ -37,6 +37,13 @@ SIGNATURES = {
                              c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
                              c_int, c_int, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_size_t,
                              c_int, c_int64, c_void_p, c_void_p]),
+    "nvfp4_decode_hybrid": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                    c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                    c_int, c_int, c_int64, c_float, c_void_p, c_void_p, c_void_p, c_size_t,
+                                    c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "nvfp4_window_partials": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+                                      c_int, c_int, c_int64, c_int64, c_int64, c_float, c_int, c_void_p,
+                                      c_int64, c_int64, c_void_p]),
     "nvfp4_decode_static_capacity": (c_size_t, []),
     "nvfp4_decode_static": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int64, c_void_p,
                                     c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,

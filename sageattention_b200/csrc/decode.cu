@@ -87,6 +87,8 @@ struct DecodeParams {
   float* ws_acc;  // [slots][16][D]
   float* ws_m;    // [nitems][16]
   float* ws_l;    // [nitems][16]
+  int64_t extra_base;   // first of the partial slots appended by another kernel (n_extra per unit)
+  int n_extra;
   int* status;
 };
 
@@ -125,33 +127,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (tid == 0) {
-    err = 0;
-    for (int i = 0; i < C::NSTAGE; ++i) {
-      mbar_init(&full_kv[i], 1);
-      mbar_init(&full_sf[i], 1);
-      mbar_init(&empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 256);
-      mbar_init(&p_full[i], 8);
-      mbar_init(&o_full[i], 1);
-      mbar_init(&q_full[i], 1);
-    }
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc(&tmem_base_s, C::T_COLS);
-  // zero the operand buffers that are only partly rewritten (rows >= G stay zero)
-  for (int i = tid; i < (2 * (C::Q_BYTES + C::QSF_BYTES) + 2 * C::STMAX * (C::P_BYTES + C::PSF_BYTES)) / 4;
-       i += kDecodeThreads)
-    reinterpret_cast<uint32_t*>(s_q)[i] = 0u;
-  fence_proxy_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_base_s;
-
   // work items of this CTA: i = 0 .. my_items-1
   const int64_t nctas = gridDim.x;
   int64_t bal_start = 0, bal_end = 0;
@@ -181,6 +156,57 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   auto slot_at = [&](int i) -> int64_t {
     return p.balanced ? (int64_t)blockIdx.x * p.maxseg + i : blockIdx.x + (int64_t)i * nctas;
   };
+
+  // Before anything else: ask L2 for the scale bytes of this CTA's first tiles.  They are the
+  // scattered first touches of the kernel (one 128-byte line per V^T row, a few KB of K scales), and
+  // their DRAM latency otherwise sits in front of the very first MMA.
+  if (my_items > 0) {
+    int unit, t0, t1;
+    item_at(0, unit, t0, t1);
+    if (tid < D) {                      // V^T scale row `tid`: the line holding tiles t0 .. t0 + 15
+      prefetch_l2(p.vsc + (int64_t)unit * p.vsc_unit + (int64_t)tid * p.vsc_row + (int64_t)t0 * 8);
+    } else {                            // K scales: contiguous, 128 * D/16 bytes per tile
+      const int64_t line = tid - D;
+      const int64_t off = (int64_t)t0 * 128 * (D / 16) + line * 128;
+      const int64_t end = min((int64_t)min(t1, t0 + 8) * 128, p.s_kv) * (D / 16);
+      if (off < end) prefetch_l2(p.ksc + (int64_t)unit * p.ksc_unit + off);
+    }
+  }
+
+  if (tid == 0) {
+    err = 0;
+    for (int i = 0; i < C::NSTAGE; ++i) {
+      mbar_init(&full_kv[i], 1);
+      mbar_init(&full_sf[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 256);
+      mbar_init(&p_full[i], 8);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&q_full[i], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  // The TMA producer (warp 0) and the scale loader (warp 2) need nothing but the barriers and the
+  // stage buffers: they start streaming now, while the other warps allocate TMEM and clear the
+  // operand buffers behind a barrier of their own.
+  uint32_t tmem = 0;
+  if (warp != 0 && warp != 2) {
+    if (warp == 1) tmem_alloc(&tmem_base_s, C::T_COLS);
+    // zero the operand buffers that are only partly rewritten (rows >= G stay zero)
+    const int zt = warp == 1 ? lane : (warp == 3 ? 32 + lane : tid - 64);     // 0 .. 319
+    for (int i = zt; i < (2 * (C::Q_BYTES + C::QSF_BYTES) + 2 * C::STMAX * (C::P_BYTES + C::PSF_BYTES)) / 4;
+         i += kDecodeThreads - 64)
+      reinterpret_cast<uint32_t*>(s_q)[i] = 0u;
+    fence_proxy_async_smem();
+    tc_fence_before();
+    named_bar_sync(5, kDecodeThreads - 64);
+    tc_fence_after();
+    tmem = tmem_base_s;
+  }
 
   // quantise the G query rows of item `wi`'s kv head into the B operand of QK^T, buffer `qb`
   // (called by the 32 lanes of the QK^T issuer's warp, one work item ahead of the MMAs)
@@ -696,15 +722,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 template <typename TQ>
 __global__ void decode_combine_kernel(const float* __restrict__ ws_acc,
                                       const float* __restrict__ ws_m,
-                                      const float* __restrict__ ws_l, int nsplit, int hk, int g, int d,
+                                      const float* __restrict__ ws_l, int nsplit, int64_t extra_base,
+                                      int n_extra, int hk, int g, int d,
                                       TQ* __restrict__ out, float* __restrict__ lse) {
   const int unit = blockIdx.x / g, qi = blockIdx.x % g;
   const int t = threadIdx.x;
   float gm = -INFINITY;
   for (int s = 0; s < nsplit; ++s) gm = fmaxf(gm, ws_m[((int64_t)unit * nsplit + s) * 16 + qi]);
+  // partials appended by another kernel over further keys of the unit (a high-precision window)
+  for (int e = 0; e < n_extra; ++e) gm = fmaxf(gm, ws_m[(extra_base + (int64_t)unit * n_extra + e) * 16 + qi]);
   float acc = 0.0f, den = 0.0f;
-  for (int s = 0; s < nsplit; ++s) {
-    const int64_t w = (int64_t)unit * nsplit + s;
+  for (int s = 0; s < nsplit + n_extra; ++s) {
+    const int64_t w = s < nsplit ? (int64_t)unit * nsplit + s : extra_base + (int64_t)unit * n_extra + (s - nsplit);
     const float ms = ws_m[w * 16 + qi];
     const float f = (ms == -INFINITY) ? 0.0f : expf(ms - gm);
     acc += f * ws_acc[(w * 16 + qi) * d + t];
@@ -723,7 +752,8 @@ template <typename TQ>
 __global__ void decode_combine_balanced_kernel(const float* __restrict__ ws_acc,
                                                const float* __restrict__ ws_m,
                                                const float* __restrict__ ws_l, int64_t total_tiles,
-                                               int ntiles, int nctas, int maxseg, int hk, int g, int d,
+                                               int ntiles, int nctas, int maxseg, int64_t extra_base,
+                                               int n_extra, int hk, int g, int d,
                                                TQ* __restrict__ out, float* __restrict__ lse) {
   const int unit = blockIdx.x / g, qi = blockIdx.x % g;
   const int t = threadIdx.x;
@@ -738,7 +768,15 @@ __global__ void decode_combine_balanced_kernel(const float* __restrict__ ws_acc,
     const int64_t w = b * maxseg + (unit - st / ntiles);
     gm = fmaxf(gm, ws_m[w * 16 + qi]);
   }
+  for (int e = 0; e < n_extra; ++e) gm = fmaxf(gm, ws_m[(extra_base + (int64_t)unit * n_extra + e) * 16 + qi]);
   float acc = 0.0f, den = 0.0f;
+  for (int e = 0; e < n_extra; ++e) {
+    const int64_t w = extra_base + (int64_t)unit * n_extra + e;
+    const float ms = ws_m[w * 16 + qi];
+    const float f = (ms == -INFINITY) ? 0.0f : expf(ms - gm);
+    acc += f * ws_acc[(w * 16 + qi) * d + t];
+    den += f * ws_l[w * 16 + qi];
+  }
   for (int64_t b = b0; b < nctas && b * total_tiles / nctas < x1; ++b) {
     const int64_t st = b * total_tiles / nctas, en = (b + 1) * total_tiles / nctas;
     if (en <= st || en <= x0) continue;
@@ -789,11 +827,11 @@ int decode_launch(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtens
   if (rc) return rc;
   if (p.balanced)
     decode_combine_balanced_kernel<TQ><<<(unsigned)(zhk * p.g), D, 0, st>>>(
-        p.ws_acc, p.ws_m, p.ws_l, p.total_tiles, p.ntiles, grid, p.maxseg, p.hk, p.g, D,
+        p.ws_acc, p.ws_m, p.ws_l, p.total_tiles, p.ntiles, grid, p.maxseg, p.extra_base, p.n_extra, p.hk, p.g, D,
         static_cast<TQ*>(out), lse);
   else
     decode_combine_kernel<TQ><<<(unsigned)(zhk * p.g), D, 0, st>>>(
-        p.ws_acc, p.ws_m, p.ws_l, p.nsplit, p.hk, p.g, D, static_cast<TQ*>(out), lse);
+        p.ws_acc, p.ws_m, p.ws_l, p.nsplit, p.extra_base, p.n_extra, p.hk, p.g, D, static_cast<TQ*>(out), lse);
   return launch_result("nvfp4_decode(combine)");
 }
 
@@ -849,7 +887,21 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
                             int64_t hk, int g, int d, int64_t s_kv, float scaling, void* out,
                             float* lse, void* workspace, size_t workspace_bytes, int nsplit,
                             int64_t split_kv, int* status, nvfp4_stream_t stream) {
+  return nvfp4_decode_hybrid(q, q_dtype, s_qz, s_qh, knv, knv_unit, ksc, ksc_unit, vnv, vnv_unit, vnv_row, vsc,
+                             vsc_unit, vsc_row, z, hk, g, d, s_kv, scaling, out, lse, workspace, workspace_bytes,
+                             nsplit, split_kv, 0, status, stream);
+}
+
+extern "C" int nvfp4_decode_hybrid(const void* q, int q_dtype, int64_t s_qz, int64_t s_qh,
+                                   const uint8_t* knv, int64_t knv_unit, const uint8_t* ksc,
+                                   int64_t ksc_unit, const uint8_t* vnv, int64_t vnv_unit,
+                                   int64_t vnv_row, const uint8_t* vsc, int64_t vsc_unit,
+                                   int64_t vsc_row, int64_t z, int64_t hk, int g, int d, int64_t s_kv,
+                                   float scaling, void* out, float* lse, void* workspace,
+                                   size_t workspace_bytes, int nsplit, int64_t split_kv, int n_extra,
+                                   int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
+  NVFP4_REQUIRE(n_extra >= 0 && n_extra <= 64, "nvfp4_decode: extra partials per unit must be in [0, 64]");
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_decode: D must be 128 or 256");
   NVFP4_REQUIRE(g >= 1 && g <= 16, "nvfp4_decode: GQA group %d must be <= 16", g);
   NVFP4_REQUIRE(z >= 1 && hk >= 1 && s_kv >= 1, "nvfp4_decode: empty problem");
@@ -867,7 +919,8 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   if (sm_count <= 0) return fail(-1, "nvfp4_decode: no CUDA device");
   int bal_ctas = 0, bal_maxseg = 0;
   decode_balanced_geometry(zhk, (s_kv + 127) / 128, sm_count, &bal_ctas, &bal_maxseg);
-  const int64_t slots = balanced ? (int64_t)bal_ctas * bal_maxseg : zhk * nsplit;
+  const int64_t own_slots = balanced ? (int64_t)bal_ctas * bal_maxseg : zhk * nsplit;
+  const int64_t slots = own_slots + zhk * n_extra;      // the caller's extra partials follow the kernel's own
   const size_t need = (size_t)slots * (size_t)(16 * d + 32) * sizeof(float);
   NVFP4_REQUIRE(workspace_bytes >= need, "nvfp4_decode: workspace too small (%zu < %zu)",
                 workspace_bytes, need);
@@ -914,6 +967,8 @@ extern "C" int nvfp4_decode(const void* q, int q_dtype, int64_t s_qz, int64_t s_
   p.ws_acc = ws;
   p.ws_m = ws + slots * 16 * d;
   p.ws_l = p.ws_m + slots * 16;
+  p.extra_base = own_slots;
+  p.n_extra = n_extra;
   p.status = status;
 
 #define NVFP4_DECODE(DD, T) return decode_launch<DD, T>(tm_k, tm_v, tm_vpf, tm_vpf4, p, zhk, out, lse, sm_count, st)

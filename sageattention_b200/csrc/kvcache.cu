@@ -64,15 +64,39 @@ __global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restric
 // Exact attention of the G query rows of one kv head over `count` ring-resident keys.
 // One block (512 threads) per (z, kv head): every K and V row of the window is read once and
 // serves all G heads; scores live in shared memory ([G][count] floats).
-template <typename T>
+// With `ws_acc` (partial mode) the window is cut into gridDim.y pieces of `chunk` keys and block
+// (unit, j) writes the UN-normalised result of its piece -- sum exp(s - m) v, m, sum exp(s - m) -- as
+// one more split-K partial of the unit (slot extra_base + unit * gridDim.y + j, the layout of the
+// FP4 decode's partials), so the decode's combine merges prefix and window in one pass.
+// kStaged (partial mode only): the K and V rows of the piece are first copied to shared memory with
+// one burst of 16-byte cp.async (every byte of the piece in flight at once), because walking them
+// straight from global memory is a chain of dependent DRAM round trips -- 0.7 TB/s on a window that
+// should stream at HBM rate.
+template <typename T, bool kStaged>
 __global__ void __launch_bounds__(512) window_attention_kernel(
     const T* __restrict__ q, int64_t s_qz, int64_t s_qh, const T* __restrict__ rk,
-    const T* __restrict__ rv, int hk, int g, int d, int64_t ring_cap, int64_t first_pos,
-    int count, float scaling, float* __restrict__ out, float* __restrict__ lse) {
-  extern __shared__ float sm[];
+    const T* __restrict__ rv, int hk, int g, int d, int64_t ring_cap, int64_t first_pos_all,
+    int count_all, int chunk, float scaling, float* __restrict__ out, float* __restrict__ lse,
+    float* __restrict__ ws_acc, float* __restrict__ ws_m, float* __restrict__ ws_l, int64_t extra_base) {
+  extern __shared__ __align__(16) float sm[];
+  const bool partial = ws_acc != nullptr;
+  const int k0 = partial ? (int)blockIdx.y * chunk : 0;
+  const int count = partial ? min(chunk, count_all - k0) : count_all;
+  const int64_t first_pos = first_pos_all + k0;
+  if (partial && count <= 0) {          // an empty piece: a partial that the combine ignores
+    const int64_t slot = extra_base + (int64_t)blockIdx.x * gridDim.y + blockIdx.y;
+    for (int i = threadIdx.x; i < g * d; i += 512) ws_acc[slot * 16 * d + i] = 0.0f;
+    if (threadIdx.x < g) {
+      ws_m[slot * 16 + threadIdx.x] = -INFINITY;
+      ws_l[slot * 16 + threadIdx.x] = 0.0f;
+    }
+    return;
+  }
   float* qs = sm;                 // [g][d]
   float* sc = sm + g * d;         // [g][count]
-  float* part = sc + ((g * count + 3) & ~3);   // [4][g][d] partial outputs (four slots shared by the sixteen warps), 16-byte aligned
+  float* part = sc + ((g * (partial ? chunk : count) + 3) & ~3);   // [4][g][d] partial outputs (four slots shared by the sixteen warps), 16-byte aligned
+  T* stage_k = reinterpret_cast<T*>(part + 4 * g * d);             // kStaged: [chunk][d], then V [chunk][d]
+  T* stage_v = stage_k + (size_t)chunk * d;
   __shared__ float row_m[16], row_l[16];
   const int zi = blockIdx.x / hk, kh = blockIdx.x % hk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -84,7 +108,25 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
   const T* kb = rk + ((int64_t)(zi * hk + kh) * ring_cap) * d;
   const T* vb = rv + ((int64_t)(zi * hk + kh) * ring_cap) * d;
   const int cap = (int)ring_cap, first = (int)(first_pos % ring_cap);   // slot of key j: first + j, wrapped once
-  auto slot = [&](int j) { const int sl = first + j; return sl >= cap ? sl - cap : sl; };
+  auto gslot = [&](int j) { const int sl = first + j; return sl >= cap ? sl - cap : sl; };
+  if constexpr (kStaged) {
+    const int per_row = d * (int)sizeof(T) / 16;         // 16-byte pieces of a row
+    for (int idx = tid; idx < count * per_row; idx += 512) {
+      const int j = idx / per_row, o = idx - j * per_row;
+      const char* gk = reinterpret_cast<const char*>(kb + (int64_t)gslot(j) * d) + o * 16;
+      const char* gv = reinterpret_cast<const char*>(vb + (int64_t)gslot(j) * d) + o * 16;
+      const uint32_t sk = (uint32_t)__cvta_generic_to_shared(reinterpret_cast<char*>(stage_k) + (size_t)idx * 16);
+      const uint32_t sv = (uint32_t)__cvta_generic_to_shared(reinterpret_cast<char*>(stage_v) + (size_t)idx * 16);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sk), "l"(gk) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sv), "l"(gv) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    kb = stage_k;
+    vb = stage_v;
+  }
+  auto slot = [&](int j) { return kStaged ? j : gslot(j); };
   // scores: a warp takes four keys at a time (four independent row loads in flight), a lane owns
   // four consecutive elements of every 128-element piece of the row; all heads per key
   for (int j0 = warp * 4; j0 < count; j0 += 64) {
@@ -200,6 +242,16 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
       __syncthreads();
     }
   }
+  if (partial) {
+    const int64_t slot = extra_base + (int64_t)blockIdx.x * gridDim.y + blockIdx.y;
+    for (int i = tid; i < g * d; i += 512)
+      ws_acc[slot * 16 * d + i] = part[i] + part[g * d + i] + part[2 * g * d + i] + part[3 * g * d + i];
+    if (tid < g) {
+      ws_m[slot * 16 + tid] = row_m[tid];
+      ws_l[slot * 16 + tid] = row_l[tid];
+    }
+    return;
+  }
   for (int i = tid; i < g * d; i += 512) {
     const int gq = i / d;
     out[((int64_t)(zi * hk + kh) * g) * d + i] =
@@ -291,15 +343,16 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
   const unsigned grid = (unsigned)(z * hk);
 #define NVFP4_WIN(T)                                                                              \
   if (smem > 48 * 1024) {                                                                         \
-    cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T>,                              \
+    cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T, false>,                       \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return fail((int)e, "nvfp4_window_attention: smem attribute: %s", cudaGetErrorString(e)); \
   }                                                                                               \
-  window_attention_kernel<T><<<grid, 512, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh,       \
+  window_attention_kernel<T, false><<<grid, 512, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh, \
                                                       static_cast<const T*>(rk),                  \
                                                       static_cast<const T*>(rv), (int)hk, g, d,   \
-                                                      ring_cap, first_pos, (int)count, scaling,   \
-                                                      out, lse);                                  \
+                                                      ring_cap, first_pos, (int)count, (int)count, \
+                                                      scaling, out, lse, nullptr, nullptr,        \
+                                                      nullptr, 0);                                \
   return launch_result("nvfp4_window_attention")
   switch (dtype) {
     case NVFP4_DT_BF16: NVFP4_WIN(__nv_bfloat16);
@@ -308,6 +361,62 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
     default: return fail(-1, "nvfp4_window_attention: unknown dtype %d", dtype);
   }
 #undef NVFP4_WIN
+}
+
+extern "C" int nvfp4_window_partials(const void* q, int dtype, int64_t s_qz, int64_t s_qh, const void* rk,
+                                     const void* rv, int64_t z, int64_t hk, int g, int d,
+                                     int64_t ring_cap, int64_t first_pos, int64_t count, float scaling,
+                                     int pieces, void* workspace, int64_t total_slots,
+                                     int64_t extra_base, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(q && rk && rv && workspace, "nvfp4_window_partials: null pointer");
+  NVFP4_REQUIRE(count > 0 && count <= ring_cap, "nvfp4_window_partials: count must be in (0, ring_cap]");
+  NVFP4_REQUIRE(g >= 1 && g <= 16, "nvfp4_window_partials: GQA group %d must be <= 16", g);
+  NVFP4_REQUIRE(pieces >= 1 && pieces <= 64, "nvfp4_window_partials: pieces must be in [1, 64]");
+  NVFP4_REQUIRE(z * hk < (1LL << 31) && extra_base >= 0 && extra_base + z * hk * pieces <= total_slots,
+                "nvfp4_window_partials: partial slots out of range");
+  const int chunk = (int)(((count + pieces - 1) / pieces + 3) / 4 * 4);
+  const size_t esz = dtype == NVFP4_DT_FP32 ? 4 : 2;
+  const size_t smem_plain = (size_t)(5 * g * d + g * chunk + 4) * sizeof(float);
+  const size_t smem_staged = smem_plain + 2 * (size_t)chunk * d * esz;
+  const bool staged = smem_staged <= 200 * 1024 && (d * esz) % 16 == 0 && ((uintptr_t)rk % 16) == 0 &&
+                      ((uintptr_t)rv % 16) == 0;
+  const size_t smem = staged ? smem_staged : smem_plain;
+  NVFP4_REQUIRE(smem <= 200 * 1024, "nvfp4_window_partials: window piece too long (%d keys)", chunk);
+  float* ws = static_cast<float*>(workspace);
+  float* ws_acc = ws;
+  float* ws_m = ws + total_slots * 16 * d;
+  float* ws_l = ws_m + total_slots * 16;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((unsigned)(z * hk), (unsigned)pieces);
+  auto launch = [&](auto kern) -> int {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fail((int)e, "nvfp4_window_partials: smem attribute: %s", cudaGetErrorString(e));
+    }
+    return 0;
+  };
+#define NVFP4_WINP(T)                                                                               \
+  {                                                                                                 \
+    int rc = staged ? launch(window_attention_kernel<T, true>) : launch(window_attention_kernel<T, false>); \
+    if (rc) return rc;                                                                              \
+    if (staged)                                                                                     \
+      window_attention_kernel<T, true><<<grid, 512, smem, st>>>(                                    \
+          static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, d, \
+          ring_cap, first_pos, (int)count, chunk, scaling, nullptr, nullptr, ws_acc, ws_m, ws_l, extra_base); \
+    else                                                                                            \
+      window_attention_kernel<T, false><<<grid, 512, smem, st>>>(                                   \
+          static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, d, \
+          ring_cap, first_pos, (int)count, chunk, scaling, nullptr, nullptr, ws_acc, ws_m, ws_l, extra_base); \
+    return launch_result("nvfp4_window_partials");                                                  \
+  }
+  switch (dtype) {
+    case NVFP4_DT_BF16: NVFP4_WINP(__nv_bfloat16)
+    case NVFP4_DT_FP16: NVFP4_WINP(__half)
+    case NVFP4_DT_FP32: NVFP4_WINP(float)
+    default: return fail(-1, "nvfp4_window_partials: unknown dtype %d", dtype);
+  }
+#undef NVFP4_WINP
 }
 
 extern "C" int nvfp4_lse_merge(const void* o1, const float* lse1, const void* o2, const float* lse2,

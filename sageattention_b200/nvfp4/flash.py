@@ -268,8 +268,13 @@ def _decode_plan(s_kv: int, zhk: int, d: int, device):
     return ns.value, sk.value, wb.value
 
 
-def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
-    """Shared body of the decode entry points: plan, allocate scratch, one C-ABI call."""
+def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None, extra=None):
+    """Shared body of the decode entry points: plan, allocate scratch, one C-ABI call.
+
+    ``extra = (n_extra, fill)``: ``n_extra`` more split-K partials per (batch, kv-head) unit are
+    reserved behind the kernel's own; ``fill(workspace, total_slots, extra_base)`` is called to
+    enqueue whatever writes them (the high-precision window of hybrid decode) before the decode,
+    whose combine then merges everything in one pass."""
     _lib.require_cuda(query, "query")
     z, h, s_q, d = query.shape
     assert s_q == 1, "nvfp4_flash_decode is for seqlen_q == 1 (decode)"
@@ -285,6 +290,7 @@ def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
     q3 = query.reshape(z, h, d)
     if q3.stride(2) != 1:
         q3 = q3.contiguous()
+    slot_bytes = (16 * d + 32) * 4
     if split_kv is None:
         nsplit, split_kv, wbytes = _decode_plan(s_kv, zhk, d, dev)
     elif split_kv == 0:
@@ -294,23 +300,28 @@ def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None):
         total = zhk * tiles
         ctas = max(1, min(_sm_count(dev), total // 4 if total // 4 > 0 else 1))
         per = -(-total // ctas)
-        nsplit, wbytes = 0, ctas * ((per + tiles - 2) // tiles + 1) * (16 * d + 32) * 4
+        nsplit, wbytes = 0, ctas * ((per + tiles - 2) // tiles + 1) * slot_bytes
     else:
         assert split_kv % 128 == 0
         nsplit = -(-s_kv // split_kv)
-        wbytes = zhk * nsplit * (16 * d + 32) * 4
+        wbytes = zhk * nsplit * slot_bytes
+    own_slots = wbytes // slot_bytes
+    n_extra = 0 if extra is None else int(extra[0])
+    wbytes = (own_slots + zhk * n_extra) * slot_bytes
     ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+    if n_extra:
+        extra[1](ws, own_slots + zhk * n_extra, own_slots)
     out = torch.empty(z, h, d, dtype=query.dtype, device=dev)
     lse = torch.empty(z, h, dtype=torch.float32, device=dev) if want_lse else None
     for t in (knv, ksc, vnv, vsc):
         assert t.stride(-1) == 1, "packed cache rows must be contiguous"
     assert knv.stride(1) == d // 2 and ksc.stride(1) == d // 16, "K rows must be dense"
-    _lib.call("nvfp4_decode", _lib.same_device(q3, knv, ksc, vnv, vsc),
+    _lib.call("nvfp4_decode_hybrid", _lib.same_device(q3, knv, ksc, vnv, vsc),
               q3.data_ptr(), _lib.dtype_code(q3.dtype), q3.stride(0), q3.stride(1),
               knv.data_ptr(), knv.stride(0), ksc.data_ptr(), ksc.stride(0),
               vnv.data_ptr(), vnv.stride(0), vnv.stride(1), vsc.data_ptr(), vsc.stride(0), vsc.stride(1),
               z, hk, g, d, s_kv, float(scaling), out.data_ptr(),
-              lse.data_ptr() if lse is not None else None, ws.data_ptr(), wbytes, nsplit, split_kv,
+              lse.data_ptr() if lse is not None else None, ws.data_ptr(), wbytes, nsplit, split_kv, n_extra,
               _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return out.reshape(z, h, 1, d), lse
 

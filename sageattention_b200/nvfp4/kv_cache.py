@@ -157,22 +157,31 @@ class NVFP4KVCache:
         qv = query if query.stride(-1) == 1 else query.contiguous()
         if qv.dtype != self.dtype:
             qv = qv.to(self.dtype)
-        out_rec = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
-        lse_rec = torch.empty(z, h, dtype=torch.float32, device=query.device)
-        _lib.call("nvfp4_window_attention", _lib.same_device(qv, self.rk),
-            qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
-            self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling),
-            out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(query.device))
+        dev = query.device
         if cut == 0:
+            # everything is still inside the window: exact attention over the ring alone
+            out_rec = torch.empty(z, h, d, dtype=torch.float32, device=dev)
+            lse_rec = torch.empty(z, h, dtype=torch.float32, device=dev)
+            _lib.call("nvfp4_window_attention", _lib.same_device(qv, self.rk),
+                      qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
+                      self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling),
+                      out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(dev))
             return out_rec.reshape(z, h, 1, d).to(query.dtype)
-        out_old, lse_old = _flash._decode_prequant_with_lse(
-            query.float(), self._packed_upto(cut), scaling, g, block_n=self.block_n)
-        merged = torch.empty(z, h, d, dtype=torch.float32, device=query.device)
-        _lib.call("nvfp4_lse_merge", _lib.same_device(out_old, out_rec),
-            out_old.reshape(z * h, d).data_ptr(), lse_old.data_ptr(), out_rec.data_ptr(),
-            lse_rec.data_ptr(), merged.data_ptr(), None, _lib.DT_FP32, z * h, d,
-            _lib.stream_ptr(query.device))
-        return merged.reshape(z, h, 1, d).to(query.dtype)
+        # The window is cut into a few key ranges per (batch, kv head); each block stages its rows in
+        # shared memory and writes an un-normalised split-K partial behind the FP4 decode's own, and the
+        # decode's combine merges prefix and window in one pass (two launches + the combine; no
+        # intermediate outputs, no copy of the query).
+        # pieces of at most 192 keys: K and V rows of a piece are staged in shared memory in one burst
+        pieces = max(1, min(64, -(-w // 192)))
+
+        def fill(ws, total_slots, extra_base):
+            _lib.call("nvfp4_window_partials", _lib.same_device(qv, self.rk, ws),
+                      qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
+                      self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling), pieces,
+                      ws.data_ptr(), total_slots, extra_base, _lib.stream_ptr(dev))
+
+        out, _ = _flash._decode_core(qv, self._packed_upto(cut), scaling, g, want_lse=False, extra=(pieces, fill))
+        return out.to(query.dtype)
 
     # ------------------------------------------------------------------ checkpoint / resume
     def state_dict(self) -> dict:

@@ -37,6 +37,13 @@ extern "C" {
 
 /* flags of nvfp4_fwd */
 #define NVFP4_FWD_CAUSAL 1
+/* nvfp4_bwd_fp4 only: stochastic rounding of an in-kernel gradient-operand pack (fp4_legacy) */
+#define NVFP4_BWD_SR_DS_DK 16  /* dS^T, the operand of dK  (`stochastic_rounding`)            */
+#define NVFP4_BWD_SR_P_DV 32   /* P^T,  the operand of dV  (`backward_p_dv_stochastic_rounding`) */
+#define NVFP4_BWD_SR_DS_DQ 64  /* dS,   the operand of dQ  (`backward_ds_dq_stochastic_rounding`) */
+/* nvfp4_pack_dual sr_flags */
+#define NVFP4_PACK_SR_ALONG_D 1
+#define NVFP4_PACK_SR_ALONG_S 2
 
 typedef void* nvfp4_stream_t; /* a cudaStream_t */
 
@@ -67,11 +74,15 @@ int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, i
  * calls.  d % 16 == 0, s_pad % 16 == 0, s_pad >= S.  With `prescale_amax` (a device float holding
  * max|x|, e.g. from nvfp4_bwd_prep) every element is first divided by the smallest power of two
  * >= that value (exact), so the packed tensor is x / 2^e with 0.5 < max|.| <= 1 -- the global
- * normalisation of dO in the all-FP4 backward; NULL packs x itself.
+ * normalisation of dO in the all-FP4 backward; NULL packs x itself.  sr_flags
+ * (NVFP4_PACK_SR_ALONG_D | NVFP4_PACK_SR_ALONG_S) round that output's e2m1 codes stochastically
+ * from (seed, position) instead of to nearest (scale bytes unchanged): the dO / dO^T packs of the
+ * fp4_legacy backward (`SR_DO` / `SR_DOT`, flash.py:1352-1394).
  */
 int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
-                    int64_t sxb, int64_t sxs, const float* prescale_amax, uint8_t* dnib,
-                    uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, nvfp4_stream_t stream);
+                    int64_t sxb, int64_t sxs, const float* prescale_amax, int sr_flags,
+                    uint32_t seed, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc,
+                    nvfp4_stream_t stream);
 
 /*
  * Forward pre-pack in ONE launch: Q [bq, s_q, d] and K [bk, s_kv, d] along d, V [bk, s_kv, d] along
@@ -312,7 +323,13 @@ int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, con
  *   lse, delta [Z*H, s_q] fp32 (delta in units of dO);  do_amax: device float, max|dO| (2^e is the
  *   smallest power of two >= it);  key_bias [Z, s_kv] or NULL;  seq_start / seq_end [s] or NULL
  *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
- * sq_pad / skv_pad: multiples of 128.  flags: NVFP4_FWD_CAUSAL.  D is 128 or 256.
+ * sq_pad / skv_pad: multiples of 128.  flags: NVFP4_FWD_CAUSAL | NVFP4_BWD_SR_*.  D is 128 or 256.
+ * The NVFP4_BWD_SR_* bits (the "fp4_legacy" mode's knobs, flash.py:161-176, 4102-4256) make the
+ * e2m1 convert of that in-kernel pack stochastic (cvt.rs: a value goes to one of its two e2m1
+ * neighbours with probability proportional to the distance to the other, so the packed operand is
+ * unbiased); the random bits are a counter-based hash of (seed, tensor, row, column), so a launch
+ * is reproducible from its seed.  The reference draws philox numbers per tile offset; the streams
+ * differ, the distribution of the rounding does not.
  */
 int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const uint8_t* ksc,
                   const uint8_t* vdnv, const uint8_t* vdsc, const uint8_t* donv, const uint8_t* dosc,
@@ -321,8 +338,8 @@ int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, co
                   const float* delta, const float* do_amax, const float* key_bias,
                   const int32_t* seq_start, const int32_t* seq_end, void* dq, void* dk, void* dv,
                   int grad_dtype, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
-                  int64_t sq_pad, int64_t skv_pad, int d, float scaling, int flags, int* status,
-                  nvfp4_stream_t stream);
+                  int64_t sq_pad, int64_t skv_pad, int d, float scaling, int flags, uint32_t seed,
+                  int* status, nvfp4_stream_t stream);
 
 /*
  * Measured pipe rates (no counterpart in the reference): launches a resident-operand micro-kernel

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 
 import torch
 
@@ -23,7 +23,7 @@ SIGNATURES = {
     "nvfp4_pack": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                            c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "nvfp4_pack_dual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int64, c_int64,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvfp4_pack_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -65,7 +65,7 @@ SIGNATURES = {
     "nvfp4_peak_probe": (c_int, [c_int, c_int, POINTER(ctypes.c_double), c_void_p, c_void_p, c_void_p]),
     "nvfp4_selftest_wait_timeout": (c_int, [c_int, ctypes.c_uint, c_void_p, c_void_p]),
     "nvfp4_bwd_fp4": (c_int, [c_void_p] * 23 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                              c_int64, c_int, c_float, c_int, c_void_p, c_void_p]),
+                              c_int64, c_int, c_float, c_int, c_uint32, c_void_p, c_void_p]),
     "nvfp4_fwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "nvfp4_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,
                           c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_int,

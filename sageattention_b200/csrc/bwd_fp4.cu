@@ -89,6 +89,8 @@ struct B4Params {
   int s_q, s_kv, c_pad;  // c_pad: padded column extent of the transposed packs
   float scaling;
   int causal;
+  int sr_p, sr_ds;       // stochastic rounding of the in-kernel P / dS packs (fp4_legacy mode)
+  uint32_t seed;
   int* status;
 };
 
@@ -105,8 +107,10 @@ __device__ __forceinline__ float b4_absmax3(float a, float b, float c) {
 
 // 16 values -> 8 nibble bytes (two words) and the e4m3 scale byte, with the packer's scale rule; the
 // divisions are reciprocal multiplies here (these operands exist only inside the kernel).
+// With sr the e2m1 convert rounds stochastically from the bits of (seed, ca, cb .. cb + 3).
 template <bool kSigned>
-__device__ __forceinline__ uint32_t b4_pack16(const float* x, uint32_t& lo, uint32_t& hi) {
+__device__ __forceinline__ uint32_t b4_pack16(const float* x, uint32_t& lo, uint32_t& hi, bool sr = false,
+                                              uint32_t seed = 0, uint32_t ca = 0, uint32_t cb = 0) {
   float m;
   if constexpr (kSigned) {
     m = fabsf(x[0]);
@@ -134,6 +138,15 @@ __device__ __forceinline__ uint32_t b4_pack16(const float* x, uint32_t& lo, uint
   float2 y[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) y[e] = __fmul2_rn(make_float2(x[2 * e], x[2 * e + 1]), i2);
+  if (sr) {
+    uint32_t q[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      q[e] = e2m1x4_sr(y[2 * e].x, y[2 * e].y, y[2 * e + 1].x, y[2 * e + 1].y, sr_bits(seed, ca, cb + e));
+    lo = q[0] | (q[1] << 16);
+    hi = q[2] | (q[3] << 16);
+    return sb;
+  }
   lo = e2m1x8(y[0].x, y[0].y, y[1].x, y[1].y, y[2].x, y[2].y, y[3].x, y[3].y);
   hi = e2m1x8(y[4].x, y[4].y, y[5].x, y[5].y, y[6].x, y[6].y, y[7].x, y[7].y);
   return sb;
@@ -539,8 +552,14 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
           ds[e] = d2.x; ds[e + 1] = d2.y;
         }
-        if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
-        scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+        // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
+        const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
+        const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
+        if constexpr (kDkdv)
+          scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+                 << (8 * (ch & 1));
+        scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
+               << (8 * (ch & 1));
         if (ch & 1) {
           // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
           if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
@@ -611,7 +630,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
                              const int32_t* seq_end, void* dq, void* dk, void* dv, int grad_dtype,
                              int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
                              int64_t sq_pad, int64_t skv_pad, int d, float scaling, int flags,
-                             int* status, nvfp4_stream_t stream) {
+                             uint32_t seed, int* status, nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_bwd_fp4: head dim must be 128 or 256");
   NVFP4_REQUIRE(z >= 1 && h >= 1 && hk >= 1 && h % hk == 0, "nvfp4_bwd_fp4: bad head counts");
@@ -650,6 +669,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
   p.seq_start = seq_start; p.seq_end = seq_end;
   p.h = (int)h; p.hk = (int)hk; p.g = (int)(h / hk); p.s_q = (int)s_q; p.s_kv = (int)s_kv;
   p.scaling = scaling; p.causal = (flags & NVFP4_FWD_CAUSAL) ? 1 : 0; p.status = status;
+  p.seed = seed; p.sr_p = 0; p.sr_ds = 0;
   const unsigned halves = (unsigned)(d / 128);
   auto launch = [&](auto kdkdv, auto kdq, int smem) -> int {
     cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -660,6 +680,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     B4Params a = p;
     a.x1sc = ksc; a.x2sc = vdsc; a.y1sc = qsc; a.y2sc = dosc; a.t1sc = dotsc; a.t2sc = qtsc;
     a.out1 = dv; a.out2 = dk; a.c_pad = (int)sq_pad;
+    a.sr_p = (flags & NVFP4_BWD_SR_P_DV) ? 1 : 0; a.sr_ds = (flags & NVFP4_BWD_SR_DS_DK) ? 1 : 0;
     dim3 g1((unsigned)zhk, (unsigned)((s_kv + 127) / 128), halves);
     kdkdv<<<g1, kB4Threads, smem, st>>>(t_k, t_vd, t_q, t_do, t_dot, t_qt, a);
     int r1 = launch_result("nvfp4_bwd_fp4(dkdv)");
@@ -668,6 +689,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     B4Params b = p;
     b.x1sc = qsc; b.x2sc = dosc; b.y1sc = ksc; b.y2sc = vdsc; b.t1sc = nullptr; b.t2sc = ktsc;
     b.out1 = nullptr; b.out2 = dq; b.c_pad = (int)skv_pad;
+    b.sr_ds = (flags & NVFP4_BWD_SR_DS_DQ) ? 1 : 0;
     dim3 g2((unsigned)zh, (unsigned)((s_q + 127) / 128), halves);
     kdq<<<g2, kB4Threads, smem, st>>>(t_q, t_do, t_k, t_vd, t_kt, t_kt, b);
     return launch_result("nvfp4_bwd_fp4(dq)");

@@ -53,6 +53,32 @@ __device__ __forceinline__ uint32_t e2m1x8(float x0, float x1, float x2, float x
   return out;
 }
 
+// ---- stochastic rounding (the fp4_legacy backward's gradient operands)
+// 32 random bits for one quad of elements, a counter-based hash of (seed, a, b): the same
+// (seed, position) always draws the same bits, different positions are decorrelated, and no state
+// is kept anywhere.  Two multiply-xorshift rounds over both counters.
+__device__ __forceinline__ uint32_t sr_bits(uint32_t seed, uint32_t a, uint32_t b) {
+  uint32_t h = seed ^ (a * 0x9E3779B1u);
+  h = (h ^ (h >> 15)) * 0x2C1B3C6Du;
+  h += b * 0x85EBCA77u;
+  h = (h ^ (h >> 12)) * 0x297A2D39u;
+  h ^= h >> 15;
+  h *= 0x9E3779B1u;
+  h ^= h >> 16;
+  return h;
+}
+
+// 4 fp32 -> 4 e2m1 codes, stochastically rounded by the hardware convert (each value goes to one
+// of its two e2m1 neighbours with probability proportional to the distance to the other; exact
+// values stay), element 0 in the low nibble.
+__device__ __forceinline__ uint32_t e2m1x4_sr(float x0, float x1, float x2, float x3, uint32_t rbits) {
+  uint16_t d;
+  asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;"
+      : "=h"(d)
+      : "f"(x3), "f"(x2), "f"(x1), "f"(x0), "r"(rbits));
+  return d;
+}
+
 // Correctly rounded x / sf from a correctly rounded reciprocal (one Markstein correction step):
 // q = RN(x * inv), r = x - q * sf (exact in an FMA), result = RN(q + r * inv).  Three FMA-pipe
 // instructions instead of the ~dozen of an IEEE divide.  |x| is clamped so the quotient cannot
@@ -86,6 +112,27 @@ __device__ __forceinline__ uint8_t pack_group16(const float (&x)[16], uint32_t& 
   }
   lo = e2m1x8(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
   hi = e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
+  return sb;
+}
+
+// pack_group16 with the e2m1 convert stochastically rounded (the scale byte is unchanged); the
+// four quads of the group draw their bits from counters (ca, cb .. cb + 3).
+__device__ __forceinline__ uint8_t pack_group16_sr(const float (&x)[16], uint32_t& lo, uint32_t& hi,
+                                                   uint32_t seed, uint32_t ca, uint32_t cb) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  const uint8_t sb = scale_byte_from_amax(amax);
+  const float sf = e4m3_to_f32(sb);
+  const float inv = __frcp_rn(sf);
+  uint32_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    q[i] = e2m1x4_sr(div_by_scale<true>(x[4 * i], sf, inv), div_by_scale<true>(x[4 * i + 1], sf, inv),
+                     div_by_scale<true>(x[4 * i + 2], sf, inv), div_by_scale<true>(x[4 * i + 3], sf, inv),
+                     sr_bits(seed, ca, cb + i));
+  lo = q[0] | (q[1] << 16);
+  hi = q[2] | (q[3] << 16);
   return sb;
 }
 

@@ -157,13 +157,16 @@ struct ColsSmem {
 
 // One 128-key x 64-row tile (tile coordinates bx, by of batch entry b).  With kDual the same tile
 // also yields the pack along the contiguous axis (rows of 16 consecutive elements of each key):
-// dnib [B, keys, R/2], dsc [B, keys, R/16], from the one read of x.
+// dnib [B, keys, R/2], dsc [B, keys, R/16], from the one read of x.  sr_flags (kDual only): bit 0
+// rounds the contiguous-axis pack stochastically, bit 1 the strided-axis pack; the random bits of
+// an element depend only on (seed, which pack, its position in x).
 template <typename T, bool kDual>
 __device__ __forceinline__ void pack_cols_tile(
     ColsSmem& sm, const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
     int64_t ssr, int vec_in, int64_t bx, int64_t by, int64_t b, uint8_t* __restrict__ dnib, int64_t dnb,
-    int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax) {
+    int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax,
+    int sr_flags = 0, uint32_t seed = 0) {
   // exact division by a power of two (1 when no pre-scale is asked for)
   const float pre = (kDual && prescale_amax != nullptr) ? __frcp_rn(pow2_ceil(*prescale_amax)) : 1.0f;
   auto& tile = sm.tile;
@@ -206,7 +209,10 @@ __device__ __forceinline__ void pack_cols_tile(
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = tile[key][g * 16 + j];
         uint32_t lo, hi;
-        const uint8_t sb = pack_group16(v, lo, hi);
+        const uint8_t sb = (sr_flags & 1)
+                               ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * k_read + k0 + key) * 2u,
+                                                 (uint32_t)(r0 / 4 + g * 4))
+                               : pack_group16(v, lo, hi);
         *reinterpret_cast<uint2*>(dnib + b * dnb + (k0 + key) * dnr + (r0 + g * 16) / 2) = make_uint2(lo, hi);
         dsc[b * dsb + (k0 + key) * dsr + (r0 + g * 16) / 16] = sb;
       }
@@ -221,7 +227,10 @@ __device__ __forceinline__ void pack_cols_tile(
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = tile[g * 16 + j][row];
     uint32_t lo, hi;
-    const uint8_t sb = pack_group16(v, lo, hi);
+    const uint8_t sb = (kDual && (sr_flags & 2))
+                           ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
+                                             (uint32_t)(k0 / 4 + g * 4))
+                           : pack_group16(v, lo, hi);
     *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
     osc[row][g] = sb;
   }
@@ -257,10 +266,11 @@ __global__ void __launch_bounds__(256) pack_cols_kernel(
     const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
     int64_t ssr, int vec_in, uint8_t* __restrict__ dnib, int64_t dnb, int64_t dnr,
-    uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax) {
+    uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax,
+    int sr_flags, uint32_t seed) {
   __shared__ ColsSmem sm;
   pack_cols_tile<T, kDual>(sm, x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc, ssb, ssr, vec_in, blockIdx.x,
-                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr, prescale_amax);
+                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr, prescale_amax, sr_flags, seed);
 }
 
 // ---------------------------------------------------------------- Q, K along D and V^T in one launch
@@ -361,7 +371,7 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
     dim3 grid((unsigned)((k_pad + kColsKeys - 1) / kColsKeys),
               (unsigned)((R + kColsRows - 1) / kColsRows), (unsigned)B);
     pack_cols_kernel<T, false><<<grid, 256, 0, st>>>(x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc,
-                                                     ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0, nullptr);
+                                                     ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0, nullptr, 0, 0u);
     return launch_result("nvfp4_pack(cols)");
   }
   const int64_t blocks = (total + 255) / 256;
@@ -403,8 +413,8 @@ namespace nvfp4 {
 
 template <typename T>
 int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, int64_t sxb, int64_t sxs,
-                     const float* prescale_amax, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc,
-                     cudaStream_t st) {
+                     const float* prescale_amax, int sr_flags, uint32_t seed, uint8_t* dnib, uint8_t* dsc,
+                     uint8_t* tnib, uint8_t* tsc, cudaStream_t st) {
   constexpr int64_t kVecElems = 16 / sizeof(T);
   const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && sxb % kVecElems == 0 && sxs % kVecElems == 0;
   dim3 grid((unsigned)((s_pad + kColsKeys - 1) / kColsKeys), (unsigned)((d + kColsRows - 1) / kColsRows),
@@ -412,7 +422,7 @@ int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, 
   pack_cols_kernel<T, true><<<grid, 256, 0, st>>>(
       static_cast<const T*>(x), d, S, s_pad, sxb, sxs, tnib, (int64_t)d * (s_pad / 2), s_pad / 2, tsc,
       (int64_t)d * (s_pad / 16), s_pad / 16, vec, dnib, S * (int64_t)(d / 2), d / 2, dsc, S * (int64_t)(d / 16),
-      d / 16, prescale_amax);
+      d / 16, prescale_amax, sr_flags, seed);
   return launch_result("nvfp4_pack_dual");
 }
 
@@ -434,8 +444,9 @@ int pack_qkv_launch(QkvArgs a, cudaStream_t st) {
 }  // namespace nvfp4
 
 extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
-                               int64_t sxb, int64_t sxs, const float* prescale_amax, uint8_t* dnib,
-                               uint8_t* dsc, uint8_t* tnib, uint8_t* tsc, nvfp4_stream_t stream) {
+                               int64_t sxb, int64_t sxs, const float* prescale_amax, int sr_flags,
+                               uint32_t seed, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc,
+                               nvfp4_stream_t stream) {
   using namespace nvfp4;
   NVFP4_REQUIRE(B >= 0 && S >= 0 && d >= 16 && d % 16 == 0, "nvfp4_pack_dual: head dim must be a positive multiple of 16");
   NVFP4_REQUIRE(s_pad % 16 == 0 && s_pad >= S, "nvfp4_pack_dual: s_pad must be a multiple of 16 >= S");
@@ -445,9 +456,9 @@ extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, i
   NVFP4_REQUIRE(((uintptr_t)dnib & 7) == 0, "nvfp4_pack_dual: nibble buffers must be 8-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case NVFP4_DT_BF16: return pack_dual_launch<__nv_bfloat16>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
-    case NVFP4_DT_FP16: return pack_dual_launch<__half>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
-    case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_BF16: return pack_dual_launch<__nv_bfloat16>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, sr_flags, seed, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP16: return pack_dual_launch<__half>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, sr_flags, seed, dnib, dsc, tnib, tsc, st);
+    case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, sr_flags, seed, dnib, dsc, tnib, tsc, st);
     default: return fail(-1, "nvfp4_pack_dual: unknown dtype %d", dtype);
   }
 }

@@ -142,13 +142,15 @@ def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     return nib, sc.view(torch.float8_e4m3fn)
 
 
-def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None, _prescale_amax: torch.Tensor | None = None):
+def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None, _prescale_amax: torch.Tensor | None = None,
+                      _sr: tuple = (False, False), _seed: int = 0):
     """Both layouts of ``x`` [B, S, D] from one read: along D and along S (padded to ``s_pad``).
 
     Stands in for flash.py:514-561 (one kernel, one pass over ``x``); bytes equal two
     ``_quant_nvfp4`` calls.  Returns ``(nib_d, sc_d, nib_s, sc_s)``.  ``_prescale_amax`` (a device
     float holding max|x|) first divides ``x`` by the smallest power of two >= that value (the global
-    normalisation of dO in the all-FP4 backward).
+    normalisation of dO in the all-FP4 backward).  ``_sr`` = (along D, along S): round that pack's
+    e2m1 codes stochastically from ``_seed`` (the dO packs of the ``fp4_legacy`` backward).
     """
     _lib.require_cuda(x, "x")
     b, s, d = x.shape
@@ -165,7 +167,7 @@ def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None, _prescale_amax:
     if b * sp > 0:
         _lib.call("nvfp4_pack_dual", dev, x.data_ptr(), _lib.dtype_code(x.dtype), b, s, d, sp, x.stride(0),
                   x.stride(1), _prescale_amax.data_ptr() if _prescale_amax is not None else None,
-                  nd.data_ptr(), sd.data_ptr(), ns.data_ptr(), ss.data_ptr(), _lib.stream_ptr(dev))
+                  (1 if _sr[0] else 0) | (2 if _sr[1] else 0), int(_seed) & 0xFFFFFFFF, nd.data_ptr(), sd.data_ptr(), ns.data_ptr(), ss.data_ptr(), _lib.stream_ptr(dev))
     return nd, sd.view(torch.float8_e4m3fn), ns, ss.view(torch.float8_e4m3fn)
 
 
@@ -571,7 +573,8 @@ _FP8_NOTE_SHOWN = False
 
 
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
-             mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, **_unused):
+             mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, sr=False, sr_p_dv=None,
+             sr_dot_dv=None, sr_ds_dq=None, seed=None, **_unused):
     """All-FP4 backward for the ``fp4_rownorm`` / ``fp4_legacy`` modes (stands in for
     flash.py:3811-4265): every GEMM of the backward is a block-scaled NVFP4 tensor-core product.
 
@@ -580,6 +583,11 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     dK/dV kernel (GQA reduced in tensor memory) and the dQ kernel.  ``fp8_rownorm`` (MXFP8 gradient
     operands in the reference) has no kernel of its own here: it runs the high-precision
     gradient-GEMM kernels, which are strictly more accurate; a note is printed once.
+
+    Stochastic rounding (flash.py:3897-3915): only ``fp4_legacy`` honours the knobs; ``sr`` rounds
+    the dO pack along D and the dS^T pack stochastically, ``sr_p_dv`` / ``sr_dot_dv`` / ``sr_ds_dq``
+    (default: ``sr``) the P^T pack, the dO^T pack and the dS pack of the dQ kernel.  ``seed`` is drawn
+    on the host when not given.
     """
     if mode == "fp8_rownorm":
         global _FP8_NOTE_SHOWN
@@ -597,11 +605,20 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     if out_layout == "zshd":          # [Z, Sq, H, D] views as [Z, H, Sq, D] (strided)
         out = out.transpose(1, 2)
         dout = dout.transpose(1, 2)
+    if mode != "fp4_legacy":         # the normalised modes round to nearest only
+        sr = sr_p_dv = sr_dot_dv = sr_ds_dq = False
+    sr = bool(sr)
+    sr_p_dv = sr if sr_p_dv is None else bool(sr_p_dv)
+    sr_dot_dv = sr if sr_dot_dv is None else bool(sr_dot_dv)
+    sr_ds_dq = sr if sr_ds_dq is None else bool(sr_ds_dq)
+    any_sr = sr or sr_p_dv or sr_dot_dv or sr_ds_dq
+    if seed is None:
+        seed = int(torch.randint(0, 2 ** 31 - 1, (1,), device="cpu").item()) if any_sr else 0
     _, delta, amax = _bwd_prep(dout, y=out, want_amax=True)       # strided reads: no copy for the pre-pass
     # the dual pack wants one batch stride: a [Z,S,H,D] gradient viewed per head has two (Z > 1)
     do3 = dout.reshape(z * h, s_q, d) if (dout.is_contiguous() or z == 1) else dout.contiguous().view(z * h, s_q, d)
     sq_pad, skv_pad = _next_mult(s_q, _KEY_TILE), _next_mult(s_kv, _KEY_TILE)
-    donv, dosc, dotnv, dotsc = _quant_nvfp4_dual(do3, sq_pad, _prescale_amax=amax)
+    donv, dosc, dotnv, dotsc = _quant_nvfp4_dual(do3, sq_pad, _prescale_amax=amax, _sr=(sr, sr_dot_dv), _seed=seed)
     q3, k3, v3 = q.reshape(z * h, s_q, d), k.reshape(z * hk, s_kv, d), v.reshape(z * hk, s_kv, d)
     if q_packs is not None:
         qnv, qsc = (t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
@@ -631,7 +648,9 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
               ptr(qnv), ptr(qsc), ptr(knv), ptr(ksc), ptr(vdnv), ptr(vdsc), ptr(donv), ptr(dosc), ptr(dotnv),
               ptr(dotsc), ptr(qtnv), ptr(qtsc), ptr(ktnv), ptr(ktsc), ptr(lse), ptr(delta), ptr(amax), ptr(bias),
               ptr(sst), ptr(sen), ptr(dq), ptr(dk), ptr(dv), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, sq_pad,
-              skv_pad, d, float(scaling), 1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+              skv_pad, d, float(scaling), (1 if causal else 0) | (16 if sr else 0) | (32 if sr_p_dv else 0)
+              | (64 if sr_ds_dq else 0), (int(seed) * 2654435761 + 1) & 0xFFFFFFFF,
+              _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return dq, dk, dv
 
 
@@ -686,13 +705,14 @@ class _NVFP4FlashAttn(torch.autograd.Function):
         bias = key_pad_bias if key_pad_bias is not None else torch.empty(0, device=query.device)
         ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3], bias)
         ctx.meta = (float(scaling), bool(causal), int(num_key_value_groups), varlen, out_layout,
-                    backward_grad_dots, key_pad_bias is not None)
+                    backward_grad_dots, key_pad_bias is not None,
+                    (bool(sr), backward_p_dv_sr, backward_dot_dv_sr, backward_ds_dq_sr))
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         query, key, value, out, lse, qnv, qsc, knv, ksc, bias = ctx.saved_tensors
-        scaling, causal, g, varlen, out_layout, mode, has_bias = ctx.meta
+        scaling, causal, g, varlen, out_layout, mode, has_bias, srk = ctx.meta
         bias = bias if has_bias else None
         if mode == "bf16":
             dq, dk, dv = _run_bwd_hp(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
@@ -700,7 +720,8 @@ class _NVFP4FlashAttn(torch.autograd.Function):
         else:
             dq, dk, dv = _run_bwd(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
                                   out_layout, mode=mode, q_packs=(qnv, qsc), k_packs=(knv, ksc),
-                                  key_pad_bias=bias)
+                                  key_pad_bias=bias, sr=srk[0], sr_p_dv=srk[1], sr_dot_dv=srk[2],
+                                  sr_ds_dq=srk[3])
         return (dq, dk, dv) + (None,) * 23
 
 
@@ -715,8 +736,9 @@ def nvfp4_flash_attn_func(query, key, value, scaling, causal=False, num_key_valu
 
     Same signature as the reference.  ``backward_grad_dots`` in {None (auto), "bf16",
     "fp4_rownorm", "fp8_rownorm", "fp4_legacy"}; ``backward_bf16_grad_dots`` is the legacy boolean
-    spelling of "bf16" (not both).  The stochastic-rounding knobs and tile hints are accepted; the
-    B200 backward always computes its gradient GEMMs in bf16 (see ``_run_bwd``).
+    spelling of "bf16" (not both).  The stochastic-rounding knobs act on the "fp4_legacy" backward
+    only (as in the reference, the normalised modes round to nearest); tile hints are accepted and
+    ignored.
     """
     z, h, s_q, d = query.shape
     hk, s_kv = key.shape[1], key.shape[2]

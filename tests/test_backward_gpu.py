@@ -151,6 +151,58 @@ def test_all_fp4_backward_matches_exact_gradients(z, h, hk, sq, skv, causal, d):
         assert not torch.equal(a, hp), f"{nm}: the all-FP4 mode returned the bf16 kernels' result"
 
 
+def _grads_sr(q, k, v, do, causal, g, **kw):
+    q = q.clone().requires_grad_(True)
+    k = k.clone().requires_grad_(True)
+    v = v.clone().requires_grad_(True)
+    out = _n().nvfp4_flash_attn_func(q, k, v, q.shape[-1] ** -0.5, causal=causal, num_key_value_groups=g,
+                                     backward_grad_dots="fp4_legacy", **kw)
+    out.backward(do)
+    torch.cuda.synchronize()
+    assert _status() == 0
+    return q.grad, k.grad, v.grad
+
+
+def test_fp4_legacy_stochastic_rounding_is_unbiased():
+    """`backward_grad_dots="fp4_legacy"` honours the stochastic-rounding knobs (the reference's
+    tests/test_nvfp4_attention.py:224-244): every draw is finite and above the 0.93 floor, draws
+    differ, `stochastic_rounding=False` is deterministic, and the mean of 16 draws is closer to the
+    exact gradients than one round-to-nearest backward."""
+    z, h, hk, s, d = 1, 4, 2, 512, 128
+    q, qn = seeded_bf16((z, h, s, d), 211)
+    k, kn = seeded_bf16((z, hk, s, d), 212)
+    v, vn = seeded_bf16((z, hk, s, d), 213)
+    do, don = seeded_bf16((z, h, s, d), 214)
+    ref = O.attention_grads(qn, kn, vn, don, d ** -0.5, True, h // hk)
+    rtn = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=False)
+    rtn2 = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=False)
+    rown = _grads(q, k, v, do, True, h // hk, mode="fp4_rownorm")[1:]
+    for a, b, c in zip(rtn, rtn2, rown):
+        assert torch.equal(a, b)
+        assert torch.equal(a, c)          # without the knobs the legacy mode is the normalised kernel
+    acc = [np.zeros_like(r) for r in ref]
+    draws = []
+    for i in range(16):
+        gsr = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=True)
+        draws.append(gsr)
+        for a, gr, r in zip(acc, gsr, ref):
+            gn = gr.float().cpu().numpy()
+            assert np.isfinite(gn).all() and cos(gn, r) >= COS_FP4
+            a += gn
+    assert not torch.equal(draws[0][0], draws[1][0]) and not torch.equal(draws[0][2], draws[1][2])
+    for nm, a, one, r in zip(("dq", "dk", "dv"), acc, rtn, ref):
+        c_mean, c_one = cos(a / 16, r), cos(one.float().cpu().numpy(), r)
+        print(nm, "cos vs exact: mean of 16 stochastic draws", c_mean, " one round-to-nearest", c_one)
+        assert c_mean > 0.95 and c_mean > c_one
+    # single knobs: each changes only what it should feed
+    only_p = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=False, backward_p_dv_stochastic_rounding=True)
+    assert torch.equal(only_p[0], rtn[0]) and torch.equal(only_p[1], rtn[1]) and not torch.equal(only_p[2], rtn[2])
+    only_dq = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=False, backward_ds_dq_stochastic_rounding=True)
+    assert not torch.equal(only_dq[0], rtn[0]) and torch.equal(only_dq[1], rtn[1]) and torch.equal(only_dq[2], rtn[2])
+    only_dot = _grads_sr(q, k, v, do, True, h // hk, stochastic_rounding=False, backward_dot_dv_stochastic_rounding=True)
+    assert torch.equal(only_dot[0], rtn[0]) and torch.equal(only_dot[1], rtn[1]) and not torch.equal(only_dot[2], rtn[2])
+
+
 @pytest.mark.parametrize("d", [128, 256])
 def test_all_fp4_backward_varlen_bias_and_scale_invariance(d):
     h, hk = 4, 2

@@ -214,3 +214,57 @@ def test_gqa_reduce_cast_dkdv():
     ref = a.reshape(z, hk, g, s, d).double().sum(2)
     assert torch.allclose(dk.double(), ref, atol=2e-2, rtol=1e-2)
     assert torch.allclose(dv.double(), b.reshape(z, hk, g, s, d).double().sum(2), atol=2e-2, rtol=1e-2)
+
+
+def test_stochastic_pack_keeps_exact_values_and_scales():
+    """Stochastic rounding leaves e2m1-representable quotients alone, so on such inputs the bytes of
+    both packs equal the round-to-nearest pack whatever the seed (this also pins the nibble order of
+    the hardware's four-wide stochastic convert)."""
+    g = torch.Generator().manual_seed(5)
+    codes = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    b, s, d = 2, 160, 128
+    x = codes[torch.randint(0, 8, (b, s, d), generator=g)] * (torch.randint(0, 2, (b, s, d), generator=g) * 2 - 1)
+    x[:, :, ::16] = 6.0          # every group along D has amax 6 (scale 1)
+    x[:, ::16, :] = 6.0          # and every group along S too
+    x = x.to(torch.bfloat16).cuda()
+    n = _nvfp4()
+    want = n._quant_nvfp4_dual(x, 256)
+    for seed in (1, 77):
+        got = n._quant_nvfp4_dual(x, 256, _sr=(True, True), _seed=seed)
+        for a, w in zip(got, want):
+            assert torch.equal(a.view(torch.uint8), w.view(torch.uint8))
+
+
+def test_stochastic_pack_is_unbiased_and_seeded():
+    """flash.py:161-176 (the reference's dithered pack): scale bytes are those of the plain pack,
+    the same seed repeats the same bytes, another seed differs, and the mean of the dequantised
+    packs over many seeds converges to the input far below the round-to-nearest error."""
+    g = torch.Generator().manual_seed(6)
+    b, s, d = 1, 256, 128
+    x = (torch.randn(b, s, d, generator=g) * 0.7).to(torch.bfloat16).cuda()
+    xf = x.float().cpu().numpy()
+    n = _nvfp4()
+    rn = n._quant_nvfp4_dual(x, 256)
+    a1 = n._quant_nvfp4_dual(x, 256, _sr=(True, True), _seed=11)
+    a2 = n._quant_nvfp4_dual(x, 256, _sr=(True, True), _seed=11)
+    a3 = n._quant_nvfp4_dual(x, 256, _sr=(True, True), _seed=12)
+    only_d = n._quant_nvfp4_dual(x, 256, _sr=(True, False), _seed=11)
+    for i in range(4):
+        assert torch.equal(a1[i].view(torch.uint8), a2[i].view(torch.uint8))
+    assert torch.equal(a1[1].view(torch.uint8), rn[1].view(torch.uint8))      # scales: along D
+    assert torch.equal(a1[3].view(torch.uint8), rn[3].view(torch.uint8))      # scales: along S
+    assert not torch.equal(a1[0], a3[0]) and not torch.equal(a1[2], a3[2])
+    assert not torch.equal(a1[0], rn[0]) and not torch.equal(a1[2], rn[2])
+    assert torch.equal(only_d[0], a1[0]) and torch.equal(only_d[2], rn[2])
+    nseed = 96
+    acc_d = np.zeros((b, s, d), np.float64)
+    acc_s = np.zeros((b, d, s), np.float64)
+    for seed in range(nseed):
+        nd, sd, ns, ss = n._quant_nvfp4_dual(x, 256, _sr=(True, True), _seed=1000 + seed)
+        acc_d += O.unpack(np_u8(nd), np_u8(sd))
+        acc_s += O.unpack(np_u8(ns), np_u8(ss))[:, :, :s]
+    err_rn_d = np.abs(O.unpack(np_u8(rn[0]), np_u8(rn[1])) - xf).mean()
+    err_sr_d = np.abs(acc_d / nseed - xf).mean()
+    err_sr_s = np.abs(acc_s / nseed - np.transpose(xf, (0, 2, 1))).mean()
+    print("mean abs error: round-to-nearest", err_rn_d, "mean of", nseed, "stochastic packs", err_sr_d, err_sr_s)
+    assert err_sr_d < 0.25 * err_rn_d and err_sr_s < 0.25 * err_rn_d

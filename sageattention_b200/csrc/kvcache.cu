@@ -68,11 +68,9 @@ __global__ void kv_append_kernel(const T* __restrict__ k_new, const T* __restric
 // (unit, j) writes the UN-normalised result of its piece -- sum exp(s - m) v, m, sum exp(s - m) -- as
 // one more split-K partial of the unit (slot extra_base + unit * gridDim.y + j, the layout of the
 // FP4 decode's partials), so the decode's combine merges prefix and window in one pass.
-// kStaged (partial mode only): the K and V rows of the piece are first copied to shared memory with
-// one burst of 16-byte cp.async (every byte of the piece in flight at once), because walking them
-// straight from global memory is a chain of dependent DRAM round trips -- 0.7 TB/s on a window that
-// should stream at HBM rate.
-template <typename T, bool kStaged>
+// This scalar kernel serves any dtype, head dim and GQA group <= 16; 16-bit caches with D = 128 / 256
+// take window_mma_kernel below in partial mode.
+template <typename T>
 __global__ void __launch_bounds__(512) window_attention_kernel(
     const T* __restrict__ q, int64_t s_qz, int64_t s_qh, const T* __restrict__ rk,
     const T* __restrict__ rv, int hk, int g, int d, int64_t ring_cap, int64_t first_pos_all,
@@ -95,8 +93,6 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
   float* qs = sm;                 // [g][d]
   float* sc = sm + g * d;         // [g][count]
   float* part = sc + ((g * (partial ? chunk : count) + 3) & ~3);   // [4][g][d] partial outputs (four slots shared by the sixteen warps), 16-byte aligned
-  T* stage_k = reinterpret_cast<T*>(part + 4 * g * d);             // kStaged: [chunk][d], then V [chunk][d]
-  T* stage_v = stage_k + (size_t)chunk * d;
   __shared__ float row_m[16], row_l[16];
   const int zi = blockIdx.x / hk, kh = blockIdx.x % hk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -108,25 +104,7 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
   const T* kb = rk + ((int64_t)(zi * hk + kh) * ring_cap) * d;
   const T* vb = rv + ((int64_t)(zi * hk + kh) * ring_cap) * d;
   const int cap = (int)ring_cap, first = (int)(first_pos % ring_cap);   // slot of key j: first + j, wrapped once
-  auto gslot = [&](int j) { const int sl = first + j; return sl >= cap ? sl - cap : sl; };
-  if constexpr (kStaged) {
-    const int per_row = d * (int)sizeof(T) / 16;         // 16-byte pieces of a row
-    for (int idx = tid; idx < count * per_row; idx += 512) {
-      const int j = idx / per_row, o = idx - j * per_row;
-      const char* gk = reinterpret_cast<const char*>(kb + (int64_t)gslot(j) * d) + o * 16;
-      const char* gv = reinterpret_cast<const char*>(vb + (int64_t)gslot(j) * d) + o * 16;
-      const uint32_t sk = (uint32_t)__cvta_generic_to_shared(reinterpret_cast<char*>(stage_k) + (size_t)idx * 16);
-      const uint32_t sv = (uint32_t)__cvta_generic_to_shared(reinterpret_cast<char*>(stage_v) + (size_t)idx * 16);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sk), "l"(gk) : "memory");
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sv), "l"(gv) : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    kb = stage_k;
-    vb = stage_v;
-  }
-  auto slot = [&](int j) { return kStaged ? j : gslot(j); };
+  auto slot = [&](int j) { const int sl = first + j; return sl >= cap ? sl - cap : sl; };
   // scores: a warp takes four keys at a time (four independent row loads in flight), a lane owns
   // four consecutive elements of every 128-element piece of the row; all heads per key
   for (int j0 = warp * 4; j0 < count; j0 += 64) {
@@ -260,6 +238,214 @@ __global__ void __launch_bounds__(512) window_attention_kernel(
   if (tid < g) lse[(int64_t)(zi * hk + kh) * g + tid] = row_m[tid] + logf(row_l[tid]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Window partials on the (legacy) warp-level tensor path, for 16-bit caches with D = 128 or 256.
+// The window is 34 MB at the decode benchmark's size -- HBM-bound byte work -- and the scalar kernel
+// above spends ~250 issue slots per key on lane reductions.  Here a block (256 threads) owns one
+// piece (<= kWinMaxKeys keys) of one (batch, kv head) unit:
+//   1. all K and V rows of the piece go to shared memory in ONE burst of 16-byte cp.async (every
+//      byte in flight at once; 16-byte chunks XOR-swizzled by the row so ldmatrix is conflict-free);
+//   2. scores = Q[16 x D] K^T with mma.sync m16n8k16 (the <= 16 heads of the group are the M rows),
+//      warps split the 8-key groups;
+//   3. one warp per head: maximum, exponentials, sum; P is kept as a high + low pair of 16-bit
+//      values so the product with V carries ~16 mantissa bits;
+//   4. O = P V with V fragments from ldmatrix.trans, every warp owning D/8 output columns over all
+//      keys, so no cross-warp reduction is needed.
+// The block writes (sum exp(s - m) v, m, sum exp(s - m)) as one split-K partial of the unit.
+template <typename T> struct WinMma;
+template <> struct WinMma<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct WinMma<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+
+constexpr int kWinThreads = 256;
+// bytes of dynamic shared memory for a piece of `keys` (multiple of 16) keys
+__host__ __device__ constexpr size_t win_mma_smem(int d, int keys) {
+  return (size_t)16 * d * 2            // Q rows (16-bit), swizzled
+         + 2 * (size_t)keys * d * 2    // K and V rows, swizzled
+         + (size_t)16 * (keys + 4) * 4       // scores (fp32); P high / low reuse the K rows
+         + 128;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kWinThreads, D == 128 ? 2 : 1) window_mma_kernel(
+    const T* __restrict__ q, int64_t s_qz, int64_t s_qh, const T* __restrict__ rk,
+    const T* __restrict__ rv, int hk, int g, int64_t ring_cap, int64_t first_pos_all, int count_all,
+    int chunk, float scaling, float* __restrict__ ws_acc, float* __restrict__ ws_m,
+    float* __restrict__ ws_l, int64_t extra_base) {
+  constexpr int kRowB = D * 2;            // bytes of a row
+  constexpr int kChunks = D / 8;          // 16-byte chunks of a row
+  extern __shared__ __align__(128) uint8_t wsm[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int k0 = (int)blockIdx.y * chunk;
+  const int count = min(chunk, count_all - k0);
+  const int64_t slot = extra_base + (int64_t)blockIdx.x * gridDim.y + blockIdx.y;
+  if (count <= 0) {                       // an empty piece: a partial that the combine ignores
+    for (int i = tid; i < g * D; i += kWinThreads) ws_acc[slot * 16 * D + i] = 0.0f;
+    if (tid < g) {
+      ws_m[slot * 16 + tid] = -INFINITY;
+      ws_l[slot * 16 + tid] = 0.0f;
+    }
+    return;
+  }
+  const int keys = (count + 15) & ~15;    // rows of the staged tiles that the MMAs touch
+  uint8_t* qs = wsm;
+  uint8_t* ks = qs + 16 * kRowB;
+  uint8_t* vs = ks + (size_t)keys * kRowB;
+  float* sc = reinterpret_cast<float*>(vs + (size_t)keys * kRowB);     // [16][keys + 4]
+  const int scs = keys + 4;
+  T* ph = reinterpret_cast<T*>(ks);            // [16][keys + 8], over the K rows once the scores exist
+  const int ps = keys + 8;
+  T* pl = ph + 16 * ps;
+  __shared__ float row_m[16], row_l[16];
+  const int zi = blockIdx.x / hk, kh = blockIdx.x % hk;
+  const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs), ks_a = (uint32_t)__cvta_generic_to_shared(ks);
+  const uint32_t vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+  const T* kb = rk + ((int64_t)(zi * hk + kh) * ring_cap) * D;
+  const T* vb = rv + ((int64_t)(zi * hk + kh) * ring_cap) * D;
+  const int cap = (int)ring_cap, first = (int)((first_pos_all + k0) % ring_cap);
+  // ---- 1. stage: K first (its own group, so the scores can start while V is still landing)
+  auto stage = [&](const T* base, uint32_t dst) {
+    for (int idx = tid; idx < count * kChunks; idx += kWinThreads) {
+      const int j = idx / kChunks, c = idx - j * kChunks;
+      int sl = first + j;
+      sl = sl >= cap ? sl - cap : sl;
+      const char* src = reinterpret_cast<const char*>(base + (int64_t)sl * D) + c * 16;
+      const uint32_t d_ = dst + j * kRowB + ((c ^ (j & 7)) << 4);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d_), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(kb, ks_a);
+  stage(vb, vs_a);
+  // Q rows (zero rows above the group) and zero V rows behind the last key: 0 * garbage must stay 0
+  for (int idx = tid; idx < 16 * kChunks; idx += kWinThreads) {
+    const int r = idx / kChunks, c = idx - r * kChunks;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < g) v = *reinterpret_cast<const uint4*>(q + zi * s_qz + (int64_t)(kh * g + r) * s_qh + c * 8);
+    *reinterpret_cast<uint4*>(qs + r * kRowB + ((c ^ (r & 7)) << 4)) = v;
+  }
+  for (int idx = tid; idx < (keys - count) * kChunks; idx += kWinThreads) {
+    const int r = count + idx / kChunks, c = idx % kChunks;
+    *reinterpret_cast<uint4*>(vs + (size_t)r * kRowB + ((c ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  asm volatile("cp.async.wait_group 1;" ::: "memory");
+  __syncthreads();
+  // ---- 2. scores, in base-2 units: warp w takes the 8-key groups w, w + 8, ...
+  {
+    uint32_t aq[D / 16][4];
+#pragma unroll
+    for (int s_ = 0; s_ < D / 16; ++s_) {
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * s_ + (lane >> 4);
+      ldsm_x4(aq[s_], qs_a + r * kRowB + ((c ^ (r & 7)) << 4));
+    }
+    const float c2 = scaling * 1.4426950408889634f;
+    for (int grp = warp; grp * 8 < count; grp += kWinThreads / 32) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const int r = grp * 8 + (lane & 7);
+#pragma unroll
+      for (int jj = 0; jj < D / 32; ++jj) {
+        uint32_t b[4];
+        const int c = 4 * jj + (lane >> 3);
+        ldsm_x4(b, ks_a + r * kRowB + ((c ^ (r & 7)) << 4));
+        WinMma<T>::mma(acc, aq[2 * jj], b[0], b[1]);
+        WinMma<T>::mma(acc, aq[2 * jj + 1], b[2], b[3]);
+      }
+      const int key = grp * 8 + 2 * (lane & 3), row = lane >> 2;
+      const float s0 = key < count ? acc[0] * c2 : -INFINITY, s1 = key + 1 < count ? acc[1] * c2 : -INFINITY;
+      const float s2 = key < count ? acc[2] * c2 : -INFINITY, s3 = key + 1 < count ? acc[3] * c2 : -INFINITY;
+      *reinterpret_cast<float2*>(sc + row * scs + key) = make_float2(s0, s1);
+      *reinterpret_cast<float2*>(sc + (row + 8) * scs + key) = make_float2(s2, s3);
+    }
+  }
+  __syncthreads();
+  // ---- 3. one warp per head (two when the group has more than 8): m, p = 2^(s - m) as high + low
+  for (int r = warp; r < 16; r += kWinThreads / 32) {
+    if (r < g) {
+      float m = -INFINITY;
+      for (int j = lane; j < count; j += 32) m = fmaxf(m, sc[r * scs + j]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      float l = 0.0f;
+      for (int j = lane; j < keys; j += 32) {
+        const float e = j < count ? exp2f(sc[r * scs + j] - m) : 0.0f;
+        const T hi = from_f32<T>(e);
+        ph[r * ps + j] = hi;
+        pl[r * ps + j] = from_f32<T>(e - to_f32<T>(hi));
+        l += e;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+      if (lane == 0) { row_m[r] = m * 0.6931471805599453f; row_l[r] = l; }
+    } else {
+      for (int j = lane; j < keys; j += 32) {      // rows without a head: finite, never written out
+        ph[r * ps + j] = from_f32<T>(0.0f);
+        pl[r * ps + j] = from_f32<T>(0.0f);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  // ---- 4. O = P V: warp w owns output columns [w D/8, (w + 1) D/8) over all keys
+  constexpr int kTiles = D / 128;        // pairs of 8-column tiles per warp (one ldmatrix.x4.trans each)
+  float o[2 * kTiles][4];
+#pragma unroll
+  for (int i = 0; i < 2 * kTiles; ++i)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) o[i][x] = 0.0f;
+  const uint32_t ph_a = (uint32_t)__cvta_generic_to_shared(ph), pl_a = (uint32_t)__cvta_generic_to_shared(pl);
+  for (int kb16 = 0; kb16 < keys; kb16 += 16) {
+    uint32_t ah[4], al[4];
+    {
+      const int r = (lane & 7) + ((lane >> 3) & 1) * 8, col = kb16 + (lane >> 4) * 8;
+      ldsm_x4(ah, ph_a + (r * ps + col) * 2);
+      ldsm_x4(al, pl_a + (r * ps + col) * 2);
+    }
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) {
+      uint32_t b[4];
+      const int r = kb16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = warp * (kChunks / 8) + 2 * t + (lane >> 4);
+      ldsm_x4_trans(b, vs_a + r * kRowB + ((c ^ (r & 7)) << 4));
+      WinMma<T>::mma(o[2 * t], ah, b[0], b[1]);
+      WinMma<T>::mma(o[2 * t], al, b[0], b[1]);
+      WinMma<T>::mma(o[2 * t + 1], ah, b[2], b[3]);
+      WinMma<T>::mma(o[2 * t + 1], al, b[2], b[3]);
+    }
+  }
+  {
+    const int row = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 2 * kTiles; ++i) {
+      const int col = warp * (D / 8) + i * 8 + 2 * (lane & 3);
+      if (row < g) *reinterpret_cast<float2*>(ws_acc + slot * 16 * D + row * D + col) = make_float2(o[i][0], o[i][1]);
+      if (row + 8 < g)
+        *reinterpret_cast<float2*>(ws_acc + slot * 16 * D + (row + 8) * D + col) = make_float2(o[i][2], o[i][3]);
+    }
+  }
+  if (tid < g) {
+    ws_m[slot * 16 + tid] = row_m[tid];
+    ws_l[slot * 16 + tid] = row_l[tid];
+  }
+}
+
 template <typename T>
 __global__ void lse_merge_kernel(const T* __restrict__ o1, const float* __restrict__ l1,
                                  const T* __restrict__ o2, const float* __restrict__ l2,
@@ -343,11 +529,11 @@ extern "C" int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, in
   const unsigned grid = (unsigned)(z * hk);
 #define NVFP4_WIN(T)                                                                              \
   if (smem > 48 * 1024) {                                                                         \
-    cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T, false>,                       \
+    cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T>,                              \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return fail((int)e, "nvfp4_window_attention: smem attribute: %s", cudaGetErrorString(e)); \
   }                                                                                               \
-  window_attention_kernel<T, false><<<grid, 512, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh, \
+  window_attention_kernel<T><<<grid, 512, smem, st>>>(static_cast<const T*>(q), s_qz, s_qh,       \
                                                       static_cast<const T*>(rk),                  \
                                                       static_cast<const T*>(rv), (int)hk, g, d,   \
                                                       ring_cap, first_pos, (int)count, (int)count, \
@@ -375,39 +561,51 @@ extern "C" int nvfp4_window_partials(const void* q, int dtype, int64_t s_qz, int
   NVFP4_REQUIRE(pieces >= 1 && pieces <= 64, "nvfp4_window_partials: pieces must be in [1, 64]");
   NVFP4_REQUIRE(z * hk < (1LL << 31) && extra_base >= 0 && extra_base + z * hk * pieces <= total_slots,
                 "nvfp4_window_partials: partial slots out of range");
-  const int chunk = (int)(((count + pieces - 1) / pieces + 3) / 4 * 4);
-  const size_t esz = dtype == NVFP4_DT_FP32 ? 4 : 2;
-  const size_t smem_plain = (size_t)(5 * g * d + g * chunk + 4) * sizeof(float);
-  const size_t smem_staged = smem_plain + 2 * (size_t)chunk * d * esz;
-  const bool staged = smem_staged <= 200 * 1024 && (d * esz) % 16 == 0 && ((uintptr_t)rk % 16) == 0 &&
-                      ((uintptr_t)rv % 16) == 0;
-  const size_t smem = staged ? smem_staged : smem_plain;
-  NVFP4_REQUIRE(smem <= 200 * 1024, "nvfp4_window_partials: window piece too long (%d keys)", chunk);
   float* ws = static_cast<float*>(workspace);
   float* ws_acc = ws;
   float* ws_m = ws + total_slots * 16 * d;
   float* ws_l = ws_m + total_slots * 16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 grid((unsigned)(z * hk), (unsigned)pieces);
-  auto launch = [&](auto kern) -> int {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return fail((int)e, "nvfp4_window_partials: smem attribute: %s", cudaGetErrorString(e));
+  // 16-bit caches with D = 128 / 256: the staged tensor-path kernel, when a piece fits its tiles
+  {
+    const int chunk16 = (int)(((count + pieces - 1) / pieces + 15) / 16 * 16);
+    const size_t smem16 = win_mma_smem(d, chunk16);
+    const bool aligned = ((uintptr_t)q % 16) == 0 && ((uintptr_t)rk % 16) == 0 && ((uintptr_t)rv % 16) == 0 &&
+                         s_qz % 8 == 0 && s_qh % 8 == 0;
+    if ((dtype == NVFP4_DT_BF16 || dtype == NVFP4_DT_FP16) && (d == 128 || d == 256) && aligned &&
+        smem16 <= 200 * 1024) {
+#define NVFP4_WINM(T, DD)                                                                             \
+  {                                                                                                   \
+    cudaError_t e = cudaFuncSetAttribute(window_mma_kernel<T, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem16);                                                \
+    if (e != cudaSuccess) return fail((int)e, "nvfp4_window_partials: smem attribute: %s", cudaGetErrorString(e)); \
+    window_mma_kernel<T, DD><<<grid, kWinThreads, smem16, st>>>(                                      \
+        static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, \
+        ring_cap, first_pos, (int)count, chunk16, scaling, ws_acc, ws_m, ws_l, extra_base);           \
+    return launch_result("nvfp4_window_partials");                                                    \
+  }
+      if (dtype == NVFP4_DT_BF16) {
+        if (d == 128) NVFP4_WINM(__nv_bfloat16, 128) else NVFP4_WINM(__nv_bfloat16, 256)
+      } else {
+        if (d == 128) NVFP4_WINM(__half, 128) else NVFP4_WINM(__half, 256)
+      }
+#undef NVFP4_WINM
     }
-    return 0;
-  };
+  }
+  const int chunk = (int)(((count + pieces - 1) / pieces + 3) / 4 * 4);
+  const size_t smem = (size_t)(5 * g * d + g * chunk + 4) * sizeof(float);
+  NVFP4_REQUIRE(smem <= 200 * 1024, "nvfp4_window_partials: window piece too long (%d keys)", chunk);
 #define NVFP4_WINP(T)                                                                               \
   {                                                                                                 \
-    int rc = staged ? launch(window_attention_kernel<T, true>) : launch(window_attention_kernel<T, false>); \
-    if (rc) return rc;                                                                              \
-    if (staged)                                                                                     \
-      window_attention_kernel<T, true><<<grid, 512, smem, st>>>(                                    \
-          static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, d, \
-          ring_cap, first_pos, (int)count, chunk, scaling, nullptr, nullptr, ws_acc, ws_m, ws_l, extra_base); \
-    else                                                                                            \
-      window_attention_kernel<T, false><<<grid, 512, smem, st>>>(                                   \
-          static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, d, \
-          ring_cap, first_pos, (int)count, chunk, scaling, nullptr, nullptr, ws_acc, ws_m, ws_l, extra_base); \
+    if (smem > 48 * 1024) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T>,                              \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return fail((int)e, "nvfp4_window_partials: smem attribute: %s", cudaGetErrorString(e)); \
+    }                                                                                               \
+    window_attention_kernel<T><<<grid, 512, smem, st>>>(                                            \
+        static_cast<const T*>(q), s_qz, s_qh, static_cast<const T*>(rk), static_cast<const T*>(rv), (int)hk, g, d, \
+        ring_cap, first_pos, (int)count, chunk, scaling, nullptr, nullptr, ws_acc, ws_m, ws_l, extra_base); \
     return launch_result("nvfp4_window_partials");                                                  \
   }
   switch (dtype) {

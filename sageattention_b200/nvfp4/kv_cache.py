@@ -171,8 +171,8 @@ class NVFP4KVCache:
         # shared memory and writes an un-normalised split-K partial behind the FP4 decode's own, and the
         # decode's combine merges prefix and window in one pass (two launches + the combine; no
         # intermediate outputs, no copy of the query).
-        # pieces of at most 192 keys: K and V rows of a piece are staged in shared memory in one burst
-        pieces = max(1, min(64, -(-w // 192)))
+        # pieces of at most 144 keys: K and V rows of a piece are staged in shared memory in one burst
+        pieces = max(1, min(64, -(-w // 144)))
 
         def fill(ws, total_slots, extra_base):
             _lib.call("nvfp4_window_partials", _lib.same_device(qv, self.rk, ws),

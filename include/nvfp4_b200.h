@@ -67,6 +67,22 @@ int nvfp4_pack(const void* x, int dtype, int64_t B, int64_t R, int64_t k_read, i
                uint8_t* sc, int64_t ssb, int64_t ssr, nvfp4_stream_t stream);
 
 /*
+ * V projection with the pack as its epilogue (the "v_proj epilogue" producer asked for in
+ * flash.py:10-13, 2812-2821; the reference itself ships no such kernel): V = X W^T (+ bias) on the
+ * tensor cores (tcgen05.mma kind::f16, fp32 accumulate), rounded once to the operand dtype, and
+ * written as the V^T pack along the keys -- vnv [z*hk, d, s_pad/2], vsc [z*hk, d, s_pad/16],
+ * tokens >= s packed as +0.0 -- and, when v_out is given, as the 16-bit V [z, s, hk*d] itself
+ * (element strides svb, svs; unit stride along the features).  The packed bytes equal nvfp4_pack
+ * of that V.  x [z, s, hidden] (element strides sxb, sxs, multiples of 8; unit stride along
+ * hidden), w [hk*d, hidden] contiguous, bias [hk*d] or NULL, all bf16 or all fp16; hidden % 8 == 0,
+ * s_pad % 16 == 0.
+ */
+int nvfp4_vproj_pack(const void* x, const void* w, const void* bias, int dtype, int64_t z, int64_t s,
+                     int64_t hidden, int64_t hk, int d, int64_t sxb, int64_t sxs, int64_t s_pad,
+                     uint8_t* vnv, uint8_t* vsc, void* v_out, int64_t svb, int64_t svs, int* status,
+                     nvfp4_stream_t stream);
+
+/*
  * Both packs of x [B, S, d] (element strides sxb, sxs; unit stride along d) from ONE read: along d
  * (dnib [B, S, d/2], dsc [B, S, d/16]) and along S as the transposed layout (tnib [B, d, s_pad/2],
  * tsc [B, d, s_pad/16], tokens >= S read as +0.0).  All four outputs contiguous.  Replaces

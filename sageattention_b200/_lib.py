@@ -24,6 +24,9 @@ SIGNATURES = {
                            c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "nvfp4_pack_dual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int64, c_int64,
                                 c_void_p, c_int, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvfp4_vproj_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
+                                 c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                 c_void_p, c_void_p]),
     "nvfp4_pack_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -36,33 +36,6 @@ constexpr int kBwdThreads = 384;
 constexpr float kBwdLog2e = 1.4426950408889634f;
 constexpr int kBwdPrefetch = 8;   // stage loads are prefetched into L2 this many steps ahead
 
-__host__ __device__ inline uint32_t make_idesc_bf16(uint32_t m, uint32_t n, bool b_mn_major) {
-  uint32_t d = 0;
-  d |= 1u << 4;   // accumulator: fp32
-  d |= 1u << 7;   // A: bf16
-  d |= 1u << 10;  // B: bf16
-  if (b_mn_major) d |= 1u << 16;
-  d |= (n >> 3) << 17;
-  d |= (m >> 4) << 24;
-  return d;
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// same, A operand read from TMEM (128 lanes x 8 columns of packed bf16 pairs per K = 16)
-__device__ __forceinline__ void umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // ------------------------------------------------------------------------------------------
 // Pre-pass over rows of x [B1, B2, S, D] (strided, unit stride along D): optional contiguous
 // bf16 copy xc [B1*B2, S, D] and optional delta [B1*B2, S] = rowsum(x o y).  Half a warp per row,
@@ -828,24 +801,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qp, const __grid_constant__
   __syncthreads();
   if (tid == 0 && err != 0 && p.status != nullptr) atomicExch(p.status, err);
   if (warp == 1) tmem_dealloc(tmem, 512);
-}
-
-// bf16 tensor [n2][n1][n0] with 128-byte swizzle, box [1][b1][64 elements]
-inline int make_tmap_bf16_3d_sw128(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
-                                   uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b1, const char* what) {
-  TensorMapEncodeTiledFn enc = tensor_map_encoder();
-  if (!enc) return fail(-1, "%s: cuTensorMapEncodeTiled is unavailable", what);
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1_bytes & 15) || (s2_bytes & 15))
-    return fail(-1, "%s: base and strides must be 16-byte aligned for TMA", what);
-  cuuint64_t dims[3] = {n0, n1, n2};
-  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
-  cuuint32_t box[3] = {64, b1, 1};
-  cuuint32_t es[3] = {1, 1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(-1, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
-  return 0;
 }
 
 template <typename T>

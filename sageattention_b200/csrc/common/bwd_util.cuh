@@ -27,6 +27,33 @@ __device__ __forceinline__ uint64_t desc_sw128_mn(const void* tile, int k16, uin
 __device__ __forceinline__ uint64_t desc_sw64(const void* tile, int k64) {
   return make_smem_desc(smem_u32(tile) + (k64 & 1) * 32, 16, 512, 4);
 }
+// Instruction descriptor of kind::f16 (fp32 accumulate): 16-bit operands, bf16 unless `f16`.
+__host__ __device__ inline uint32_t make_idesc_bf16(uint32_t m, uint32_t n, bool b_mn_major, bool f16 = false) {
+  uint32_t d = 0;
+  d |= 1u << 4;   // accumulator: fp32
+  if (!f16) d |= (1u << 7) | (1u << 10);  // A and B: bf16 (0 = f16)
+  if (b_mn_major) d |= 1u << 16;
+  d |= (n >> 3) << 17;
+  d |= (m >> 4) << 24;
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// same, A operand read from TMEM (128 lanes x 8 columns of packed bf16 pairs per K = 16)
+__device__ __forceinline__ void umma_bf16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&v);

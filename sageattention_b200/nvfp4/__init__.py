@@ -11,6 +11,7 @@ from .flash import (  # noqa: F401
     _run_bwd_hp,
     nvfp4_flash_attn_func,
     rope_quant_nvfp4,
+    vproj_quant_nvfp4,
     _next_mult,
     _quant_nvfp4,
     _quant_nvfp4_dual,

@@ -142,6 +142,44 @@ def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     return nib, sc.view(torch.float8_e4m3fn)
 
 
+def vproj_quant_nvfp4(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, num_kv_heads: int,
+                      head_dim: int, s_pad: int | None = None, return_value: bool = True):
+    """V projection with the NVFP4 pack as its epilogue (the producer the reference asks callers to
+    fuse for V, flash.py:10-13, 2812-2821): ``V = x @ weight.T (+ bias)`` on the tensor cores, written
+    directly as the V^T pack along the keys, so V is never re-read for quantisation.
+
+    ``x`` ``[Z, S, hidden]`` and ``weight`` ``[Hk*D, hidden]`` in bf16 or fp16.  Returns ``(vnv uint8
+    [Z*Hk, D, s_pad/2], vsc float8_e4m3fn [Z*Hk, D, s_pad/16], value)`` where ``value`` is the
+    projected tensor as a ``[Z, Hk, S, D]`` view (``None`` with ``return_value=False``); the packs are
+    bit-identical to ``_quant_nvfp4(value, transpose=True, k_pad=s_pad)`` and feed
+    ``nvfp4_flash_attention_packed`` / ``nvfp4_flash_decode_prequant`` as they are.
+    """
+    _lib.require_cuda(x, "x")
+    z, s, hidden = x.shape
+    feats = num_kv_heads * head_dim
+    assert weight.shape == (feats, hidden), "weight must be [Hk*D, hidden]"
+    assert x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype, "operands must be bf16 or fp16"
+    assert hidden % 8 == 0 and head_dim % 16 == 0
+    if x.stride(2) != 1 or x.stride(0) % 8 or x.stride(1) % 8:
+        x = x.contiguous()
+    weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.to(x.dtype).contiguous()
+        assert bias.numel() == feats
+    sp = _next_mult(s, _KEY_TILE) if s_pad is None else int(s_pad)
+    assert sp % 16 == 0 and sp >= s, "s_pad must be a multiple of 16 covering S"
+    dev = x.device
+    vnv = torch.empty(z * num_kv_heads, head_dim, sp // 2, dtype=torch.uint8, device=dev)
+    vsc = torch.empty(z * num_kv_heads, head_dim, sp // 16, dtype=torch.uint8, device=dev)
+    v = torch.empty(z, s, num_kv_heads, head_dim, dtype=x.dtype, device=dev) if return_value else None
+    _lib.call("nvfp4_vproj_pack", _lib.same_device(x, weight, bias),
+              x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, _lib.dtype_code(x.dtype),
+              z, s, hidden, num_kv_heads, head_dim, x.stride(0), x.stride(1), sp, vnv.data_ptr(), vsc.data_ptr(),
+              v.data_ptr() if v is not None else None, v.stride(0) if v is not None else 0,
+              v.stride(1) if v is not None else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    return vnv, vsc.view(torch.float8_e4m3fn), (v.permute(0, 2, 1, 3) if v is not None else None)
+
+
 def _quant_nvfp4_dual(x: torch.Tensor, s_pad: int | None = None, _prescale_amax: torch.Tensor | None = None,
                       _sr: tuple = (False, False), _seed: int = 0):
     """Both layouts of ``x`` [B, S, D] from one read: along D and along S (padded to ``s_pad``).
@@ -574,7 +612,7 @@ _FP8_NOTE_SHOWN = False
 
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
              mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, sr=False, sr_p_dv=None,
-             sr_dot_dv=None, sr_ds_dq=None, seed=None, **_unused):
+             sr_dot_dv=None, sr_ds_dq=None, seed=None, qt_packs=None, kt_packs=None, vd_packs=None, **_unused):
     """All-FP4 backward for the ``fp4_rownorm`` / ``fp4_legacy`` modes (stands in for
     flash.py:3811-4265): every GEMM of the backward is a block-scaled NVFP4 tensor-core product.
 
@@ -588,6 +626,10 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     the dO pack along D and the dS^T pack stochastically, ``sr_p_dv`` / ``sr_dot_dv`` / ``sr_ds_dq``
     (default: ``sr``) the P^T pack, the dO^T pack and the dS pack of the dQ kernel.  ``seed`` is drawn
     on the host when not given.
+
+    ``qt_packs`` / ``kt_packs`` / ``vd_packs``: the transposed packs of Q and K (padded to 128
+    tokens) and the along-D pack of V saved by the forward under ``save_backward_packs``; given,
+    the pre-pass skips those launches (and the re-read of Q, K and V).
     """
     if mode == "fp8_rownorm":
         global _FP8_NOTE_SHOWN
@@ -622,15 +664,16 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     q3, k3, v3 = q.reshape(z * h, s_q, d), k.reshape(z * hk, s_kv, d), v.reshape(z * hk, s_kv, d)
     if q_packs is not None:
         qnv, qsc = (t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
-        qtnv, qtsc = _quant_nvfp4(q3, transpose=True, k_pad=sq_pad)
+        qtnv, qtsc = qt_packs if qt_packs is not None else _quant_nvfp4(q3, transpose=True, k_pad=sq_pad)
     else:
         qnv, qsc, qtnv, qtsc = _quant_nvfp4_dual(q3, sq_pad)
     if k_packs is not None:
         knv, ksc = (t.contiguous() for t in _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout"))
-        ktnv, ktsc = _quant_nvfp4(k3, transpose=True, k_pad=skv_pad)
+        ktnv, ktsc = kt_packs if kt_packs is not None else _quant_nvfp4(k3, transpose=True, k_pad=skv_pad)
     else:
         knv, ksc, ktnv, ktsc = _quant_nvfp4_dual(k3, skv_pad)
-    vdnv, vdsc = _quant_nvfp4(v3)
+    assert qtnv.shape == (z * h, d, sq_pad // 2) and ktnv.shape == (z * hk, d, skv_pad // 2), "transposed pack layout"
+    vdnv, vdsc = vd_packs if vd_packs is not None else _quant_nvfp4(v3)
     gdt = dout.dtype
     dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
     dk = torch.empty(z, hk, s_kv, d, dtype=gdt, device=dev)
@@ -697,13 +740,24 @@ class _NVFP4FlashAttn(torch.autograd.Function):
                 "q_packs/k_packs are incompatible with save_backward_packs "
                 "(the saved pack set must come from the same fused HP read)")
         out_layout = "zshd" if out_zshd else "zhsd"
+        q_in = (qnv_in, qsc_in) if qnv_in is not None else None
+        k_in = (knv_in, ksc_in) if knv_in is not None else None
+        extra = ()
+        if save_backward_packs and backward_grad_dots in ("fp4_rownorm", "fp4_legacy"):
+            # flash.py:4330-4385: everything the all-FP4 backward needs of Q, K and V is packed here,
+            # from the one read of each operand (along D for the forward, transposed for the backward)
+            z, h, s_q, d = query.shape
+            hk, s_kv = key.shape[1], key.shape[2]
+            qd = _quant_nvfp4_dual(query.reshape(z * h, s_q, d), _next_mult(s_q, _KEY_TILE))
+            kd = _quant_nvfp4_dual(key.reshape(z * hk, s_kv, d), _next_mult(s_kv, _KEY_TILE))
+            q_in, k_in = (qd[0], qd[1]), (kd[0], kd[1])
+            extra = (qd[2], qd[3], kd[2], kd[3], *_quant_nvfp4(value.reshape(z * hk, s_kv, d)))
         out, lse, packs = nvfp4_flash_attention(
             query, key, value, scaling, causal=causal, num_key_value_groups=num_key_value_groups,
             key_pad_bias=key_pad_bias, return_lse=True, return_packs=True, out_layout=out_layout,
-            q_packs=(qnv_in, qsc_in) if qnv_in is not None else None,
-            k_packs=(knv_in, ksc_in) if knv_in is not None else None, _varlen_arrays=varlen)
+            q_packs=q_in, k_packs=k_in, _varlen_arrays=varlen)
         bias = key_pad_bias if key_pad_bias is not None else torch.empty(0, device=query.device)
-        ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3], bias)
+        ctx.save_for_backward(query, key, value, out, lse, packs[0], packs[1], packs[2], packs[3], bias, *extra)
         ctx.meta = (float(scaling), bool(causal), int(num_key_value_groups), varlen, out_layout,
                     backward_grad_dots, key_pad_bias is not None,
                     (bool(sr), backward_p_dv_sr, backward_dot_dv_sr, backward_ds_dq_sr))
@@ -711,7 +765,7 @@ class _NVFP4FlashAttn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out):
-        query, key, value, out, lse, qnv, qsc, knv, ksc, bias = ctx.saved_tensors
+        query, key, value, out, lse, qnv, qsc, knv, ksc, bias, *extra = ctx.saved_tensors
         scaling, causal, g, varlen, out_layout, mode, has_bias, srk = ctx.meta
         bias = bias if has_bias else None
         if mode == "bf16":
@@ -721,7 +775,9 @@ class _NVFP4FlashAttn(torch.autograd.Function):
             dq, dk, dv = _run_bwd(query, key, value, out, lse, grad_out, scaling, causal, g, varlen,
                                   out_layout, mode=mode, q_packs=(qnv, qsc), k_packs=(knv, ksc),
                                   key_pad_bias=bias, sr=srk[0], sr_p_dv=srk[1], sr_dot_dv=srk[2],
-                                  sr_ds_dq=srk[3])
+                                  sr_ds_dq=srk[3], qt_packs=tuple(extra[0:2]) if extra else None,
+                                  kt_packs=tuple(extra[2:4]) if extra else None,
+                                  vd_packs=tuple(extra[4:6]) if extra else None)
         return (dq, dk, dv) + (None,) * 23
 
 

@@ -27,6 +27,72 @@ from . import flash as _flash
 from .flash import _next_mult, _pack_into
 
 
+def append_token(key_new, value_new, knv, ksc, vnv, vsc, v_partial, rk, rv, pos: int) -> None:
+    """One decode token ([Z, Hk, 1, D] or [Z*Hk, D]) into the cache buffers at position ``pos``: one
+    kernel launch (K row pack, V stash and re-pack of the open 16-key V^T group, ring write when
+    ``rk`` / ``rv`` are given).  The buffer-level form of ``NVFP4KVCache.append``."""
+    zhk, _, half = knv.shape
+    d = half * 2
+    dtype = v_partial.dtype
+    _lib.require_cuda(key_new, "key_new")
+    kn = key_new.reshape(zhk, d)
+    vn = value_new.reshape(zhk, d)
+    if kn.dtype != dtype or kn.stride(1) != 1:
+        kn = kn.to(dtype).contiguous()
+    if vn.dtype != dtype or vn.stride(1) != 1:
+        vn = vn.to(dtype).contiguous()
+    if kn.stride(0) != vn.stride(0):
+        kn, vn = kn.contiguous(), vn.contiguous()
+    ring = rk is not None
+    dev = knv.device
+    _lib.call("nvfp4_kv_append", _lib.same_device(kn, vn, knv),
+              kn.data_ptr(), vn.data_ptr(), _lib.dtype_code(dtype), kn.stride(0), zhk, d, int(pos),
+              knv.data_ptr(), knv.stride(0), ksc.data_ptr(), ksc.stride(0),
+              vnv.data_ptr(), vnv.stride(0), vnv.stride(1), vsc.data_ptr(), vsc.stride(0), vsc.stride(1),
+              v_partial.data_ptr(), rk.data_ptr() if ring else None, rv.data_ptr() if ring else None,
+              rk.shape[2] if ring else 0, _lib.stream_ptr(dev))
+
+
+def hybrid_decode_buffers(query, knv, ksc, vnv, vsc, rk, rv, length: int, recent_window: int, scaling: float,
+                          g: int, block_n: int = 128) -> torch.Tensor:
+    """``NVFP4KVCache.hybrid_decode`` on the raw buffers of a cache holding ``length`` tokens."""
+    z, h, _, d = query.shape
+    hk, ring_cap, dtype = rk.shape[1], rk.shape[2], rk.dtype
+    s = int(length)
+    cut = (max(0, s - recent_window) // 16) * 16
+    w = s - cut
+    _lib.require_cuda(query, "query")
+    qv = query if query.stride(-1) == 1 else query.contiguous()
+    if qv.dtype != dtype:
+        qv = qv.to(dtype)
+    dev = query.device
+    if cut == 0:
+        # everything is still inside the window: exact attention over the ring alone
+        out_rec = torch.empty(z, h, d, dtype=torch.float32, device=dev)
+        lse_rec = torch.empty(z, h, dtype=torch.float32, device=dev)
+        _lib.call("nvfp4_window_attention", _lib.same_device(qv, rk),
+                  qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), rk.data_ptr(),
+                  rv.data_ptr(), z, hk, g, d, ring_cap, cut, w, float(scaling),
+                  out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(dev))
+        return out_rec.reshape(z, h, 1, d).to(query.dtype)
+    # The window is cut into a few key ranges per (batch, kv head); each block stages its rows in
+    # shared memory and writes an un-normalised split-K partial behind the FP4 decode's own, and the
+    # decode's combine merges prefix and window in one pass (two launches + the combine; no
+    # intermediate outputs, no copy of the query).  Pieces of at most 144 keys.
+    pieces = max(1, min(64, -(-w // 144)))
+
+    def fill(ws, total_slots, extra_base):
+        _lib.call("nvfp4_window_partials", _lib.same_device(qv, rk, ws),
+                  qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), rk.data_ptr(),
+                  rv.data_ptr(), z, hk, g, d, ring_cap, cut, w, float(scaling), pieces,
+                  ws.data_ptr(), total_slots, extra_base, _lib.stream_ptr(dev))
+
+    s_pad = _next_mult(cut, block_n)
+    packed = (knv[:, :cut], ksc[:, :cut], vnv[:, :, : s_pad // 2], vsc[:, :, : s_pad // 16], cut, s_pad)
+    out, _ = _flash._decode_core(qv, packed, scaling, g, want_lse=False, extra=(pieces, fill))
+    return out.to(query.dtype)
+
+
 class NVFP4KVCache:
     """One layer's GQA KV cache held in NVFP4 and grown one token at a time.
 
@@ -101,24 +167,9 @@ class NVFP4KVCache:
         assert sq == 1 and (z, hk, d) == (self.z, self.hk, self.d)
         t = self.length
         assert t < self.max_seq_len, "append exceeds capacity"
-        _lib.require_cuda(key_new, "key_new")
-        kn = key_new.reshape(self.zhk, d)
-        vn = value_new.reshape(self.zhk, d)
-        if kn.dtype != self.dtype or kn.stride(1) != 1:
-            kn = kn.to(self.dtype).contiguous()
-        if vn.dtype != self.dtype or vn.stride(1) != 1:
-            vn = vn.to(self.dtype).contiguous()
-        if kn.stride(0) != vn.stride(0):
-            kn, vn = kn.contiguous(), vn.contiguous()
         ring = self.recent_window > 0
-        _lib.call("nvfp4_kv_append", _lib.same_device(kn, vn, self.knv),
-            kn.data_ptr(), vn.data_ptr(), _lib.dtype_code(self.dtype), kn.stride(0), self.zhk, d, t,
-            self.knv.data_ptr(), self.knv.stride(0), self.ksc.data_ptr(), self.ksc.stride(0),
-            self.vnv.data_ptr(), self.vnv.stride(0), self.vnv.stride(1),
-            self.vsc.data_ptr(), self.vsc.stride(0), self.vsc.stride(1),
-            self.v_partial_bf16.data_ptr(),
-            self.rk.data_ptr() if ring else None, self.rv.data_ptr() if ring else None,
-            self.ring_cap, _lib.stream_ptr(self.device))
+        append_token(key_new, value_new, self.knv, self.ksc, self.vnv, self.vsc, self.v_partial_bf16,
+                     self.rk if ring else None, self.rv if ring else None, t)
         self.length = t + 1
         self.partial_len = (t % self.GROUP) + 1
         if self.partial_len == self.GROUP:
@@ -149,39 +200,8 @@ class NVFP4KVCache:
                                "(construct NVFP4KVCache with recent_window>0)")
         if self.length == 0:
             raise RuntimeError("hybrid_decode requires at least one token (call prefill/append first)")
-        z, h, _, d = query.shape
-        s = self.length
-        cut = (max(0, s - self.recent_window) // self.GROUP) * self.GROUP
-        w = s - cut
-        _lib.require_cuda(query, "query")
-        qv = query if query.stride(-1) == 1 else query.contiguous()
-        if qv.dtype != self.dtype:
-            qv = qv.to(self.dtype)
-        dev = query.device
-        if cut == 0:
-            # everything is still inside the window: exact attention over the ring alone
-            out_rec = torch.empty(z, h, d, dtype=torch.float32, device=dev)
-            lse_rec = torch.empty(z, h, dtype=torch.float32, device=dev)
-            _lib.call("nvfp4_window_attention", _lib.same_device(qv, self.rk),
-                      qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
-                      self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling),
-                      out_rec.data_ptr(), lse_rec.data_ptr(), _lib.stream_ptr(dev))
-            return out_rec.reshape(z, h, 1, d).to(query.dtype)
-        # The window is cut into a few key ranges per (batch, kv head); each block stages its rows in
-        # shared memory and writes an un-normalised split-K partial behind the FP4 decode's own, and the
-        # decode's combine merges prefix and window in one pass (two launches + the combine; no
-        # intermediate outputs, no copy of the query).
-        # pieces of at most 144 keys: K and V rows of a piece are staged in shared memory in one burst
-        pieces = max(1, min(64, -(-w // 144)))
-
-        def fill(ws, total_slots, extra_base):
-            _lib.call("nvfp4_window_partials", _lib.same_device(qv, self.rk, ws),
-                      qv.data_ptr(), _lib.dtype_code(qv.dtype), qv.stride(0), qv.stride(1), self.rk.data_ptr(),
-                      self.rv.data_ptr(), z, self.hk, g, d, self.ring_cap, cut, w, float(scaling), pieces,
-                      ws.data_ptr(), total_slots, extra_base, _lib.stream_ptr(dev))
-
-        out, _ = _flash._decode_core(qv, self._packed_upto(cut), scaling, g, want_lse=False, extra=(pieces, fill))
-        return out.to(query.dtype)
+        return hybrid_decode_buffers(query, self.knv, self.ksc, self.vnv, self.vsc, self.rk, self.rv, self.length,
+                                     self.recent_window, scaling, g, self.block_n)
 
     # ------------------------------------------------------------------ checkpoint / resume
     def state_dict(self) -> dict:

@@ -163,6 +163,28 @@ def _grads_sr(q, k, v, do, causal, g, **kw):
     return q.grad, k.grad, v.grad
 
 
+@pytest.mark.parametrize("d", [128, 256])
+def test_save_backward_packs_gives_the_same_gradients(d):
+    """`save_backward_packs=True` (flash.py:4330-4385): the forward packs everything the all-FP4
+    backward needs of Q, K and V once; outputs and gradients keep their bits."""
+    z, h, hk, sq, skv = 2, 4, 2, 200, 328
+    q, _ = seeded_bf16((z, h, sq, d), 311)
+    k, _ = seeded_bf16((z, hk, skv, d), 312)
+    v, _ = seeded_bf16((z, hk, skv, d), 313)
+    do, _ = seeded_bf16((z, h, sq, d), 314)
+    res = []
+    for save in (False, True):
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = _n().nvfp4_flash_attn_func(qq, kk, vv, d ** -0.5, causal=True, num_key_value_groups=h // hk,
+                                         backward_grad_dots="fp4_rownorm", save_backward_packs=save)
+        out.backward(do)
+        torch.cuda.synchronize()
+        assert _status() == 0
+        res.append((out.detach(), qq.grad, kk.grad, vv.grad))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
 def test_fp4_legacy_stochastic_rounding_is_unbiased():
     """`backward_grad_dots="fp4_legacy"` honours the stochastic-rounding knobs (the reference's
     tests/test_nvfp4_attention.py:224-244): every draw is finite and above the 0.93 floor, draws

@@ -9,7 +9,8 @@ import sageattention_b200.nvfp4.custom_ops as C  # noqa: F401  (registers the op
 
 def test_ops_are_registered():
     ns = torch.ops.sageattention_b200
-    for name in ("nvfp4_attn_fwd", "nvfp4_attn_bwd", "nvfp4_quant", "nvfp4_decode"):
+    for name in ("nvfp4_attn_fwd", "nvfp4_attn_bwd", "nvfp4_quant", "nvfp4_decode", "nvfp4_attn_ex_fwd",
+                 "nvfp4_attn_ex_bwd", "nvfp4_kv_append", "nvfp4_hybrid_decode"):
         assert hasattr(ns, name)
 
 
@@ -40,3 +41,30 @@ def test_autograd_formula_is_attached_under_fake_mode():
         out = C.nvfp4_attn(q, k, v, 0.088, True, 2)
         out.sum().backward()
         assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+
+
+def test_general_attention_and_cache_ops_under_fake_mode():
+    """Shapes of the zshd / varlen / bias attention ops, their autograd, and the cache ops."""
+    with FakeTensorMode():
+        q = torch.empty(1, 4, 256, 128, dtype=torch.bfloat16, requires_grad=True)
+        k = torch.empty(1, 2, 256, 128, dtype=torch.bfloat16, requires_grad=True)
+        v = torch.empty(1, 2, 256, 128, dtype=torch.bfloat16, requires_grad=True)
+        cu = torch.empty(4, dtype=torch.int32)
+        bias = torch.empty(1, 256)
+        out, lse = torch.ops.sageattention_b200.nvfp4_attn_ex_fwd(q, k, v, 0.088, True, 2, None, cu, True)
+        assert out.shape == (1, 256, 4, 128) and lse.shape == (4, 256)
+        o2 = C.nvfp4_attn_ex(q, k, v, 0.088, True, 2, key_pad_bias=bias, out_layout="zshd",
+                             backward_grad_dots="fp4_rownorm")
+        o2.sum().backward()
+        assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+        knv = torch.empty(4, 1024, 64, dtype=torch.uint8)
+        ksc = torch.empty(4, 1024, 8, dtype=torch.float8_e4m3fn)
+        vnv = torch.empty(4, 128, 512, dtype=torch.uint8)
+        vsc = torch.empty(4, 128, 64, dtype=torch.float8_e4m3fn)
+        part = torch.empty(4, 16, 128, dtype=torch.bfloat16)
+        rk = torch.empty(2, 2, 80, 128, dtype=torch.bfloat16)
+        kn = torch.empty(2, 2, 1, 128, dtype=torch.bfloat16)
+        assert torch.ops.sageattention_b200.nvfp4_kv_append(kn, kn, knv, ksc, vnv, vsc, part, rk, rk, 700) is None
+        qd = torch.empty(2, 8, 1, 128, dtype=torch.bfloat16)
+        o = torch.ops.sageattention_b200.nvfp4_hybrid_decode(qd, knv, ksc, vnv, vsc, rk, rk, 701, 64, 0.088, 4)
+        assert o.shape == qd.shape and o.dtype == torch.bfloat16

@@ -41,6 +41,9 @@ extern "C" {
 #define NVFP4_BWD_SR_DS_DK 16  /* dS^T, the operand of dK  (`stochastic_rounding`)            */
 #define NVFP4_BWD_SR_P_DV 32   /* P^T,  the operand of dV  (`backward_p_dv_stochastic_rounding`) */
 #define NVFP4_BWD_SR_DS_DQ 64  /* dS,   the operand of dQ  (`backward_ds_dq_stochastic_rounding`) */
+/* nvfp4_bwd_fp4 only: the transposed packs (dotnv, qtnv, ktnv) are MXFP8 and the in-kernel gradient
+ * operands are packed as MXFP8 ("fp8_rownorm") */
+#define NVFP4_BWD_MXFP8 128
 /* nvfp4_pack_dual sr_flags */
 #define NVFP4_PACK_SR_ALONG_D 1
 #define NVFP4_PACK_SR_ALONG_S 2
@@ -99,6 +102,18 @@ int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, int d, int64
                     int64_t sxb, int64_t sxs, const float* prescale_amax, int sr_flags,
                     uint32_t seed, uint8_t* dnib, uint8_t* dsc, uint8_t* tnib, uint8_t* tsc,
                     nvfp4_stream_t stream);
+
+/*
+ * MXFP8 pack along the tokens: x [B, S, d] (element strides sxb, sxs; unit stride along d) ->
+ * e4m3 bytes out [B, d, s_pad] and e8m0 scale bytes sc [B, d, s_pad/32], one scale per 32 tokens
+ * (tokens >= S read as +0.0).  The rule of `_pack_mxfp8_along_k` (flash.py:243-257): e = the smallest
+ * integer with amax / 2^e <= 448 (amax floored at 1e-30), bytes = e4m3 RTNE of x / 2^e, scale =
+ * e + 127.  s_pad % 32 == 0.  `prescale_amax` as in nvfp4_pack_dual.  Feeds nvfp4_bwd_fp4 with
+ * NVFP4_BWD_MXFP8 (which wants s_pad % 128 == 0).
+ */
+int nvfp4_pack_mx8_t(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad, int64_t sxb,
+                     int64_t sxs, const float* prescale_amax, uint8_t* out, uint8_t* sc,
+                     nvfp4_stream_t stream);
 
 /*
  * Forward pre-pack in ONE launch: Q [bq, s_q, d] and K [bk, s_kv, d] along d, V [bk, s_kv, d] along
@@ -340,6 +355,11 @@ int nvfp4_bwd_hp(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, con
  *   smallest power of two >= it);  key_bias [Z, s_kv] or NULL;  seq_start / seq_end [s] or NULL
  *   dq [Z*H, s_q, D], dk, dv [Z*Hk, s_kv, D] contiguous in `grad_dtype`
  * sq_pad / skv_pad: multiples of 128.  flags: NVFP4_FWD_CAUSAL | NVFP4_BWD_SR_*.  D is 128 or 256.
+ * With NVFP4_BWD_MXFP8 (the "fp8_rownorm" mode, flash.py:243-257, 3889-3896) the operands of the three
+ * gradient GEMMs are MXFP8 -- e4m3 bytes with one e8m0 scale per 32 (tcgen05.mma kind::mxf8f6f4) --
+ * while S and dP stay NVFP4 products of the along-D packs: dotnv [Z*H, D, sq_pad], qtnv [Z*H, D,
+ * sq_pad], ktnv [Z*Hk, D, skv_pad] are then byte tensors from nvfp4_pack_mx8_t with scales
+ * [.., D, pad/32], and P^T, dS^T, dS are packed as MXFP8 inside the kernels.
  * The NVFP4_BWD_SR_* bits (the "fp4_legacy" mode's knobs, flash.py:161-176, 4102-4256) make the
  * e2m1 convert of that in-kernel pack stochastic (cvt.rs: a value goes to one of its two e2m1
  * neighbours with probability proportional to the distance to the other, so the packed operand is

@@ -134,6 +134,51 @@ def unpack(nib: np.ndarray, sc: np.ndarray) -> np.ndarray:
     return (e2m1_to_f32(codes) * np.repeat(e4m3_to_f32(sc), GROUP, axis=-1)).astype(np.float32)
 
 
+# --------------------------------------------------------------------------- MXFP8 (fp8_rownorm)
+def e4m3_signed_bytes(x: np.ndarray) -> np.ndarray:
+    """fp32 -> float8_e4m3fn bit patterns, round-to-nearest-even, saturating at +-448, signed zero
+    (PTX ``cvt.rn.satfinite.e4m3x2.f32`` per element; Triton's ``.to(tl.float8e4nv)``)."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x).astype(np.float64), 448.0)
+    mant, exp = np.frexp(a)
+    e = np.maximum(exp - 1, -6)
+    q = np.rint(a / np.exp2(e.astype(np.float64) - 3.0)).astype(np.int64)
+    b = np.where(a == 0.0, 0, (e + 6) * 8 + q)
+    b = np.minimum(b, 0x7E)
+    return (b.astype(np.uint8) | (np.signbit(x).astype(np.uint8) << 7)).astype(np.uint8)
+
+
+def e4m3_signed_to_f32(b: np.ndarray) -> np.ndarray:
+    b = np.asarray(b, dtype=np.uint8)
+    return (e4m3_to_f32(b & 0x7F) * np.where(b & 0x80, -1.0, 1.0)).astype(np.float32)
+
+
+def pack_mxfp8(x: np.ndarray, transpose: bool = False, k_pad: int | None = None):
+    """MXFP8 pack along the contraction axis, group 32; restates ``_pack_mxfp8_along_k``
+    (flash.py:243-257): ``e = ceil(log2(max(amax, 1e-30) / 448))`` -- evaluated exactly, as the
+    smallest integer with ``amax / 2**e <= 448`` --, bytes = e4m3(x / 2**e), scale byte = e + 127.
+    ``x`` [B, R, K] (or [B, K, R] with ``transpose``); returns (uint8 [B, R, Kp], uint8 [B, R, Kp/32])."""
+    x = np.asarray(x, dtype=np.float32)
+    if transpose:
+        x = np.swapaxes(x, 1, 2)
+    b, r, k = x.shape
+    kp = k if k_pad is None else int(k_pad)
+    assert kp % 32 == 0 and kp >= k
+    xp = np.zeros((b, r, kp), dtype=np.float32)
+    xp[:, :, :k] = x
+    xb = xp.reshape(b, r, kp // 32, 32)
+    amax = np.maximum(np.max(np.abs(xb), axis=-1), np.float32(1e-30)).astype(np.float32)
+    mant, exp = np.frexp(amax.astype(np.float64))        # amax = mant 2^exp, mant in [0.5, 1)
+    e = (exp - 1) - 8 + (mant * 2.0 > 1.75)
+    q = e4m3_signed_bytes((xb.astype(np.float64) * np.exp2(-e.astype(np.float64))[..., None]).astype(np.float32))
+    return q.reshape(b, r, kp), (e + 127).astype(np.uint8)
+
+
+def unpack_mxfp8(q: np.ndarray, sc: np.ndarray) -> np.ndarray:
+    scale = np.exp2(np.asarray(sc, dtype=np.float64) - 127.0)
+    return (e4m3_signed_to_f32(q).astype(np.float64) * np.repeat(scale, 32, axis=-1)).astype(np.float32)
+
+
 def next_mult(n: int, m: int) -> int:
     return ((n + m - 1) // m) * m
 

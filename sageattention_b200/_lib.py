@@ -27,6 +27,8 @@ SIGNATURES = {
     "nvfp4_vproj_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int,
                                  c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                  c_void_p, c_void_p]),
+    "nvfp4_pack_mx8_t": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_void_p,
+                                 c_void_p, c_void_p, c_void_p]),
     "nvfp4_pack_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

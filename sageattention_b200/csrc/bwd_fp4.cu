@@ -45,20 +45,23 @@ constexpr float kB4PShift = 11.0f;   // P is packed as P * 2^11
 constexpr int kB4Prefetch = 2;       // stages prefetched into L2 ahead of the ring
 
 
-template <int D>
+// kFp8: the gradient GEMMs' operands (P^T, dS^T, dS packed in the kernel; dO'^T, Q^T, K^T from the
+// pre-pass) are MXFP8 -- e4m3 bytes, e8m0 scale per 32 -- instead of NVFP4: tiles of 128-byte rows.
+template <int D, bool kFp8 = false>
 struct B4Cfg {
   static constexpr int KSUB = D / 128;      // 64-byte-wide sub-tiles of a pack row
   static constexpr int KB = D / 64;         // K = 64 MMAs per product over D
   static constexpr int X = KSUB * 8192;     // one pack tile: 128 rows x D/2 bytes
+  static constexpr int AT = kFp8 ? 16384 : 8192;   // an in-kernel operand tile / a transposed-pack tile
   // resident part
-  static constexpr int O_X1 = 0, O_X2 = X, O_A1 = 2 * X, O_A2 = 2 * X + 8192;
-  static constexpr int O_XSF = 2 * X + 16384;             // X1 atoms [KB], X2 atoms [KB]
+  static constexpr int O_X1 = 0, O_X2 = X, O_A1 = 2 * X, O_A2 = 2 * X + AT;
+  static constexpr int O_XSF = 2 * X + 2 * AT;            // X1 atoms [KB], X2 atoms [KB]
   static constexpr int O_ASF = O_XSF + 2 * KB * 512;      // A1 atoms [2 parities], A2 atoms [2]
   static constexpr int RES = ((O_ASF + 2048 + 1023) / 1024) * 1024;
   // one stage = 128 columns
-  static constexpr int S_Y1 = 0, S_Y2 = X, S_T1 = 2 * X, S_T2 = 2 * X + 8192;
-  static constexpr int S_YSF = 2 * X + 16384;             // Y1 atoms [2 steps][KB], then Y2 atoms [2][KB]
-  static constexpr int S_TSF = S_YSF + 4 * KB * 512;      // T1 atoms [2 parities], T2 atoms [2]
+  static constexpr int S_Y1 = 0, S_Y2 = X, S_T1 = 2 * X, S_T2 = 2 * X + AT;
+  static constexpr int S_YSF = 2 * X + 2 * AT;            // Y1 atoms [2 steps][KB], then Y2 atoms [2][KB]
+  static constexpr int S_TSF = S_YSF + 4 * KB * 512;      // T1 atoms [2 parities], T2 atoms [2] (MXFP8: one each)
   static constexpr int S_AUX = S_TSF + 2048;              // two float[128]
   static constexpr int STAGE = ((S_AUX + 1024 + 1023) / 1024) * 1024;
   static constexpr int NSTAGE = D == 128 ? 3 : 2;
@@ -68,7 +71,30 @@ struct B4Cfg {
   static constexpr uint32_t T_SFX1 = 448, T_SFX2 = T_SFX1 + KB * 4, T_SFY = T_SFX2 + KB * 4;
   static constexpr uint32_t T_SFA1 = T_SFY + KB * 4, T_SFT1 = T_SFA1 + 4, T_SFA2 = T_SFT1 + 4, T_SFT2 = T_SFA2 + 4;
   static_assert(T_SFT2 + 4 <= 512, "TMEM budget");
+  static_assert(TOTAL <= 227 * 1024, "shared memory budget");
 };
+
+// kind::mxf8f6f4, e4m3 x e4m3, ue8m0 scale per 32, fp32 accumulate, both operands K-major; a_sf / b_sf
+// pick the byte of the scale word in tensor memory that holds this K = 32 block's scale.
+__host__ __device__ __forceinline__ uint32_t make_idesc_mx8(uint32_t m, uint32_t n, uint32_t a_sf, uint32_t b_sf) {
+  uint32_t d = 0;
+  d |= (b_sf & 3u) << 4;
+  d |= (n >> 3) << 17;
+  d |= 1u << 23;         // scale format: ue8m0
+  d |= (m >> 4) << 24;
+  d |= (a_sf & 3u) << 29;
+  return d;              // A and B format 0 = e4m3
+}
+__device__ __forceinline__ void umma_mx8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], "
+      "p;\n\t}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
 
 struct B4Params {
   const uint8_t* x1sc;   // row side, along D: [RB, R, D/16]   (dK/dV: K scales; dQ: Q scales)
@@ -155,18 +181,21 @@ __device__ __forceinline__ uint32_t b4_pack16(const float* x, uint32_t& lo, uint
 __device__ __forceinline__ void sts_v4(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+__device__ __forceinline__ void sts_b8(uint32_t saddr, uint32_t a) {
+  asm volatile("st.shared.b8 [%0], %1;" ::"r"(saddr), "h"((uint16_t)a) : "memory");
+}
 __device__ __forceinline__ void sts_b16(uint32_t saddr, uint32_t a) {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"((uint16_t)a) : "memory");
 }
 
 // kDkdv = true: the dK/dV pass (rows = keys), false: the dQ pass (rows = queries).
-template <int D, bool kDkdv, typename TG>
+template <int D, bool kDkdv, typename TG, bool kFp8>
 __global__ void __launch_bounds__(kB4Threads, 1)
 bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
             const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
             const __grid_constant__ CUtensorMap tm_t1, const __grid_constant__ CUtensorMap tm_t2,
             const B4Params p) {
-  using C = B4Cfg<D>;
+  using C = B4Cfg<D, kFp8>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -273,8 +302,8 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           tma_prefetch_3d(&tm_y1, c * 64, col0, cb);
           tma_prefetch_3d(&tm_y2, c * 64, col0, cb);
         }
-        if constexpr (kDkdv) tma_prefetch_3d(&tm_t1, col0 / 2, half * 128, cb);
-        tma_prefetch_3d(&tm_t2, col0 / 2, half * 128, cb);
+        if constexpr (kDkdv) tma_prefetch_3d(&tm_t1, kFp8 ? col0 : col0 / 2, half * 128, cb);
+        tma_prefetch_3d(&tm_t2, kFp8 ? col0 : col0 / 2, half * 128, cb);
       };
       for (int sg = C::NSTAGE; sg < min(nstage, C::NSTAGE + kB4Prefetch); ++sg) prefetch(sg);
       for (int sg = 0; sg < nstage; ++sg) {
@@ -284,14 +313,14 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
         if (sg + C::NSTAGE + kB4Prefetch < nstage) prefetch(sg + C::NSTAGE + kB4Prefetch);
         if (sg >= C::NSTAGE) mbar_wait(&empty[s], ((sg / C::NSTAGE) & 1) ^ 1, &err, 1);
         uint8_t* sb = s_stage + s * C::STAGE;
-        mbar_expect_tx(&full_tma[s], 2 * C::X + (kDkdv ? 16384 : 8192));
+        mbar_expect_tx(&full_tma[s], 2 * C::X + (kDkdv ? 2 : 1) * C::AT);
 #pragma unroll
         for (int c = 0; c < C::KSUB; ++c) {
           tma_load_3d(sb + C::S_Y1 + c * 8192, &tm_y1, &full_tma[s], c * 64, col0, cb);
           tma_load_3d(sb + C::S_Y2 + c * 8192, &tm_y2, &full_tma[s], c * 64, col0, cb);
         }
-        if constexpr (kDkdv) tma_load_3d(sb + C::S_T1, &tm_t1, &full_tma[s], col0 / 2, half * 128, cb);
-        tma_load_3d(sb + C::S_T2, &tm_t2, &full_tma[s], col0 / 2, half * 128, cb);
+        if constexpr (kDkdv) tma_load_3d(sb + C::S_T1, &tm_t1, &full_tma[s], kFp8 ? col0 : col0 / 2, half * 128, cb);
+        tma_load_3d(sb + C::S_T2, &tm_t2, &full_tma[s], kFp8 ? col0 : col0 / 2, half * 128, cb);
       }
     }
     __syncwarp();
@@ -316,7 +345,7 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
       __syncwarp();
       if (lane == 0) mbar_arrive(&xsf_full);
       const float inv_gs = 1.0f / gs;
-      const int csc = p.c_pad / 16;      // scale bytes per row of a transposed pack
+      const int csc = p.c_pad / (kFp8 ? 32 : 16);      // scale bytes per row of a transposed pack
       for (int sg = 0; sg < nstage; ++sg) {
         const int s = sg % C::NSTAGE;
         int cb, col0;
@@ -338,11 +367,17 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
             cp_async_4(ysf + ((2 + pp) * C::KB + c) * 512 + sf_atom_offset(rr, 0), p.y2sc + gi + 4 * c, ok ? 4u : 0u);
           }
           // transposed packs: row = feature (this CTA's 128-wide half), 8 scale bytes = this stage's columns
-          const int64_t ti = ((int64_t)cb * D + half * 128 + r) * csc + col0 / 16;
+          if constexpr (kFp8) {     // one word = the four 32-column blocks of the stage
+            const int64_t ti = ((int64_t)cb * D + half * 128 + r) * csc + col0 / 32;
+            if constexpr (kDkdv) cp_async_4(tsf + sf_atom_offset(r, 0), p.t1sc + ti, 4u);
+            cp_async_4(tsf + 2 * 512 + sf_atom_offset(r, 0), p.t2sc + ti, 4u);
+          } else {
+            const int64_t ti = ((int64_t)cb * D + half * 128 + r) * csc + col0 / 16;
 #pragma unroll
-          for (int pq = 0; pq < 2; ++pq) {
-            if constexpr (kDkdv) cp_async_4(tsf + pq * 512 + sf_atom_offset(r, 0), p.t1sc + ti + 4 * pq, 4u);
-            cp_async_4(tsf + (2 + pq) * 512 + sf_atom_offset(r, 0), p.t2sc + ti + 4 * pq, 4u);
+            for (int pq = 0; pq < 2; ++pq) {
+              if constexpr (kDkdv) cp_async_4(tsf + pq * 512 + sf_atom_offset(r, 0), p.t1sc + ti + 4 * pq, 4u);
+              cp_async_4(tsf + (2 + pq) * 512 + sf_atom_offset(r, 0), p.t2sc + ti + 4 * pq, 4u);
+            }
           }
           if constexpr (kDkdv) {
             // per query: -lse * log2e + 11 (exponent offset of P * 2^11) and -delta' * scaling / 4
@@ -375,17 +410,43 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
         tmem_cp_32x128b_warpx4(tmem + C::T_SFX2 + 4 * c, smem_u32(s_res + C::O_XSF + (C::KB + c) * 512));
       }
       const uint64_t d_x1 = desc_sw64(s_res + C::O_X1, 0), d_x2 = desc_sw64(s_res + C::O_X2, 0);
-      const uint64_t d_a1 = desc_sw64(s_res + C::O_A1, 0), d_a2 = desc_sw64(s_res + C::O_A2, 0);
+      const uint64_t d_a1 = kFp8 ? desc_sw128(s_res + C::O_A1, 0) : desc_sw64(s_res + C::O_A1, 0);
+      const uint64_t d_a2 = kFp8 ? desc_sw128(s_res + C::O_A2, 0) : desc_sw64(s_res + C::O_A2, 0);
       const uint64_t d_y1 = desc_sw64(s_stage + C::S_Y1, 0), d_y2 = desc_sw64(s_stage + C::S_Y2, 0);
-      const uint64_t d_t1 = desc_sw64(s_stage + C::S_T1, 0), d_t2 = desc_sw64(s_stage + C::S_T2, 0);
+      const uint64_t d_t1 = kFp8 ? desc_sw128(s_stage + C::S_T1, 0) : desc_sw64(s_stage + C::S_T1, 0);
+      const uint64_t d_t2 = kFp8 ? desc_sw128(s_stage + C::S_T2, 0) : desc_sw64(s_stage + C::S_T2, 0);
       // acc1 += A1 T1^T, acc2 += A2 T2^T for step t (columns [64 pp, 64 pp + 64) of its stage)
       auto grad_gemms = [&](int t) {
         const int pp = t & 1, s = (t >> 1) % C::NSTAGE;
         uint8_t* sb = s_stage + s * C::STAGE;
         mbar_wait(&a_full[pp], (t >> 1) & 1, &err, 8);
         tc_fence_after();
-        const uint64_t so = (uint64_t)(s * (C::STAGE >> 4)) + (uint64_t)(pp * 2);   // stage, then the 32-byte half of a row
         const uint32_t acc = t > 0 ? 1u : 0u;
+        if constexpr (kFp8) {
+          // a step is two K = 32 blocks (32 bytes each) of the 128-byte operand rows; block j of step pp
+          // reads byte j of the A atom (one atom per step parity) and byte 2 pp + j of the T atom
+          const uint64_t sg = (uint64_t)(s * (C::STAGE >> 4));
+          if constexpr (kDkdv) {
+            tmem_cp_32x128b_warpx4(tmem + C::T_SFA1, smem_u32(s_res + C::O_ASF + pp * 512));
+            tmem_cp_32x128b_warpx4(tmem + C::T_SFT1, smem_u32(sb + C::S_TSF));
+          }
+          tmem_cp_32x128b_warpx4(tmem + C::T_SFA2, smem_u32(s_res + C::O_ASF + (2 + pp) * 512));
+          tmem_cp_32x128b_warpx4(tmem + C::T_SFT2, smem_u32(sb + C::S_TSF + 2 * 512));
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint32_t kk = (uint32_t)(pp * 2 + j);
+            const uint32_t id = make_idesc_mx8(128, 128, (uint32_t)j, kk);
+            if constexpr (kDkdv)
+              umma_mx8(tmem + C::T_ACC1, d_a1 + kk * 2, d_t1 + sg + kk * 2, id, tmem + C::T_SFA1, tmem + C::T_SFT1,
+                       j > 0 ? 1u : acc);
+            umma_mx8(tmem + C::T_ACC2, d_a2 + kk * 2, d_t2 + sg + kk * 2, id, tmem + C::T_SFA2, tmem + C::T_SFT2,
+                     j > 0 ? 1u : acc);
+          }
+          umma_commit(&a_free[pp]);
+          if (pp == 1) umma_commit(&empty[s]);
+          return;
+        }
+        const uint64_t so = (uint64_t)(s * (C::STAGE >> 4)) + (uint64_t)(pp * 2);   // stage, then the 32-byte half of a row
         if constexpr (kDkdv) {
           tmem_cp_32x128b_warpx4(tmem + C::T_SFA1, smem_u32(s_res + C::O_ASF + pp * 512));
           tmem_cp_32x128b_warpx4(tmem + C::T_SFT1, smem_u32(sb + C::S_TSF + pp * 512));
@@ -511,6 +572,7 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
       __syncwarp();
       if (lane == 0) mbar_arrive(&g_free);
       uint32_t wp[4], wd[4], scp = 0u, scd = 0u;
+      float pkeep[kFp8 ? 16 : 1], dkeep[kFp8 ? 16 : 1];     // MXFP8: the even chunk of a 32-column group
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t* cur = (ch & 1) ? sb : sa;
@@ -552,6 +614,30 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
           ds[e] = d2.x; ds[e + 1] = d2.y;
         }
+        if constexpr (kFp8) {
+          if (!(ch & 1)) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              if constexpr (kDkdv) pkeep[e] = pf[e];
+              dkeep[e] = ds[e];
+            }
+          } else {
+            if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
+            const int gi = ch >> 1;                       // which 32 columns of the step
+            const uint32_t byte0 = (uint32_t)(pp * 64 + gi * 32);
+            uint32_t w[8];
+            if constexpr (kDkdv) {
+              const uint32_t sb8 = pack_group32_mx8(pkeep, pf, w);
+              sts_v4(a1_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+              sts_v4(a1_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+              sts_b8(asf_s + pp * 512 + sf_atom_offset(row_in, gi), sb8);
+            }
+            const uint32_t sd8 = pack_group32_mx8(dkeep, ds, w);
+            sts_v4(a2_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+            sts_v4(a2_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+            sts_b8(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, gi), sd8);
+          }
+        } else {
         // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
         const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
         const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
@@ -572,6 +658,7 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
           sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
           scd = 0u;
+        }
         }
         if (ch < 3) {
           tmem_ld_wait();
@@ -649,6 +736,9 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
   NVFP4_REQUIRE((((uintptr_t)qsc | (uintptr_t)ksc | (uintptr_t)vdsc | (uintptr_t)dosc | (uintptr_t)dotsc |
                   (uintptr_t)qtsc | (uintptr_t)ktsc) & 3) == 0,
                 "nvfp4_bwd_fp4: scale tensors must be 4-byte aligned");
+  const bool fp8 = (flags & NVFP4_BWD_MXFP8) != 0;
+  NVFP4_REQUIRE(!fp8 || !(flags & (NVFP4_BWD_SR_DS_DK | NVFP4_BWD_SR_P_DV | NVFP4_BWD_SR_DS_DQ)),
+                "nvfp4_bwd_fp4: the MXFP8 operands round to nearest only");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t zh = z * h, zhk = z * hk;
   const uint64_t pb = (uint64_t)d / 2;
@@ -658,12 +748,21 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
   if ((rc = make_tmap_u8_3d_sw64(&t_k, knv, pb, s_kv, zhk, pb, (uint64_t)s_kv * pb, 128, "nvfp4_bwd_fp4(K)"))) return rc;
   if ((rc = make_tmap_u8_3d_sw64(&t_vd, vdnv, pb, s_kv, zhk, pb, (uint64_t)s_kv * pb, 128, "nvfp4_bwd_fp4(V)"))) return rc;
   if ((rc = make_tmap_u8_3d_sw64(&t_do, donv, pb, s_q, zh, pb, (uint64_t)s_q * pb, 128, "nvfp4_bwd_fp4(dO)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_dot, dotnv, (uint64_t)sq_pad / 2, d, zh, (uint64_t)sq_pad / 2,
-                                 (uint64_t)d * (sq_pad / 2), 128, "nvfp4_bwd_fp4(dO^T)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_qt, qtnv, (uint64_t)sq_pad / 2, d, zh, (uint64_t)sq_pad / 2,
-                                 (uint64_t)d * (sq_pad / 2), 128, "nvfp4_bwd_fp4(Q^T)"))) return rc;
-  if ((rc = make_tmap_u8_3d_sw64(&t_kt, ktnv, (uint64_t)skv_pad / 2, d, zhk, (uint64_t)skv_pad / 2,
-                                 (uint64_t)d * (skv_pad / 2), 128, "nvfp4_bwd_fp4(K^T)"))) return rc;
+  if (fp8) {      // transposed operands: one byte per element, 128-byte boxes
+    if ((rc = make_tmap_u8_3d_sw128(&t_dot, dotnv, (uint64_t)sq_pad, d, zh, (uint64_t)sq_pad, (uint64_t)d * sq_pad, 128,
+                                    "nvfp4_bwd_fp4(dO^T)"))) return rc;
+    if ((rc = make_tmap_u8_3d_sw128(&t_qt, qtnv, (uint64_t)sq_pad, d, zh, (uint64_t)sq_pad, (uint64_t)d * sq_pad, 128,
+                                    "nvfp4_bwd_fp4(Q^T)"))) return rc;
+    if ((rc = make_tmap_u8_3d_sw128(&t_kt, ktnv, (uint64_t)skv_pad, d, zhk, (uint64_t)skv_pad, (uint64_t)d * skv_pad, 128,
+                                    "nvfp4_bwd_fp4(K^T)"))) return rc;
+  } else {
+    if ((rc = make_tmap_u8_3d_sw64(&t_dot, dotnv, (uint64_t)sq_pad / 2, d, zh, (uint64_t)sq_pad / 2,
+                                   (uint64_t)d * (sq_pad / 2), 128, "nvfp4_bwd_fp4(dO^T)"))) return rc;
+    if ((rc = make_tmap_u8_3d_sw64(&t_qt, qtnv, (uint64_t)sq_pad / 2, d, zh, (uint64_t)sq_pad / 2,
+                                   (uint64_t)d * (sq_pad / 2), 128, "nvfp4_bwd_fp4(Q^T)"))) return rc;
+    if ((rc = make_tmap_u8_3d_sw64(&t_kt, ktnv, (uint64_t)skv_pad / 2, d, zhk, (uint64_t)skv_pad / 2,
+                                   (uint64_t)d * (skv_pad / 2), 128, "nvfp4_bwd_fp4(K^T)"))) return rc;
+  }
   B4Params p;
   p.lse = lse; p.delta = delta; p.amax = do_amax; p.bias = key_bias;
   p.seq_start = seq_start; p.seq_end = seq_end;
@@ -694,7 +793,9 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     kdq<<<g2, kB4Threads, smem, st>>>(t_q, t_do, t_k, t_vd, t_kt, t_kt, b);
     return launch_result("nvfp4_bwd_fp4(dq)");
   };
-#define NVFP4_B4_LAUNCH(DD, TT) launch(bwd4_kernel<DD, true, TT>, bwd4_kernel<DD, false, TT>, B4Cfg<DD>::TOTAL)
+#define NVFP4_B4_LAUNCH(DD, TT)                                                                                   \
+  (fp8 ? launch(bwd4_kernel<DD, true, TT, true>, bwd4_kernel<DD, false, TT, true>, B4Cfg<DD, true>::TOTAL)        \
+       : launch(bwd4_kernel<DD, true, TT, false>, bwd4_kernel<DD, false, TT, false>, B4Cfg<DD, false>::TOTAL))
   if (d == 128) {
     switch (grad_dtype) {
       case NVFP4_DT_BF16: return NVFP4_B4_LAUNCH(128, __nv_bfloat16);

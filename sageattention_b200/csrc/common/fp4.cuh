@@ -115,6 +115,38 @@ __device__ __forceinline__ uint8_t pack_group16(const float (&x)[16], uint32_t& 
   return sb;
 }
 
+// ---- MXFP8 (e4m3 values, one e8m0 power-of-two scale per 32): the gradient operands of the
+// fp8_rownorm backward.  Scale exponent e = the smallest integer with amax / 2^e <= 448 (the exact
+// form of ceil(log2(amax / 448)), flash.py:243-257), amax floored at 1e-30; stored as e + 127.
+__device__ __forceinline__ uint8_t mx8_scale(float amax, float& inv) {
+  const uint32_t b = __float_as_uint(fmaxf(amax, 1.0e-30f));
+  const int k = (int)(b >> 23) - 127;                    // amax = m 2^k, 1 <= m < 2
+  const int e = k - 8 + ((b & 0x7FFFFFu) > 0x600000u ? 1 : 0);   // 448 = 1.75 * 2^8
+  inv = __uint_as_float((uint32_t)(127 - e) << 23);      // 2^-e, exact
+  return (uint8_t)(e + 127);
+}
+// 4 fp32 -> 4 e4m3 bytes (RTNE, saturating), element 0 in the low byte
+__device__ __forceinline__ uint32_t e4m3x4(float x0, float x1, float x2, float x3) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(x1), "f"(x0));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(x3), "f"(x2));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+// 32 values (two halves of 16) -> 8 words of e4m3 bytes; returns the e8m0 scale byte
+__device__ __forceinline__ uint8_t pack_group32_mx8(const float* x0, const float* x1, uint32_t (&w)[8]) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fmaxf(fabsf(x0[i]), fabsf(x1[i])));
+  float inv;
+  const uint8_t sb = mx8_scale(amax, inv);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    w[i] = e4m3x4(x0[4 * i] * inv, x0[4 * i + 1] * inv, x0[4 * i + 2] * inv, x0[4 * i + 3] * inv);
+    w[4 + i] = e4m3x4(x1[4 * i] * inv, x1[4 * i + 1] * inv, x1[4 * i + 2] * inv, x1[4 * i + 3] * inv);
+  }
+  return sb;
+}
+
 // pack_group16 with the e2m1 convert stochastically rounded (the scale byte is unchanged); the
 // four quads of the group draw their bits from counters (ca, cb .. cb + 3).
 __device__ __forceinline__ uint8_t pack_group16_sr(const float (&x)[16], uint32_t& lo, uint32_t& hi,

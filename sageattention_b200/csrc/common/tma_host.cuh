@@ -66,6 +66,25 @@ inline int make_tmap_u32_3d_prefetch(CUtensorMap* m, const void* base, uint64_t 
   return 0;
 }
 
+// Byte tensor as make_tmap_u8_3d_sw64, with rows of 128 bytes per box and the 128-byte swizzle.
+inline int make_tmap_u8_3d_sw128(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1,
+                                 uint64_t n2, uint64_t s1, uint64_t s2, uint32_t b1,
+                                 const char* what) {
+  TensorMapEncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return fail(-1, "%s: cuTensorMapEncodeTiled is unavailable", what);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1 & 15) || (s2 & 15))
+    return fail(-1, "%s: base and strides must be 16-byte aligned for TMA", what);
+  cuuint64_t dims[3] = {n0, n1, n2};
+  cuuint64_t strides[2] = {s1, s2};
+  cuuint32_t box[3] = {128, b1, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+                   es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-1, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
+  return 0;
+}
+
 // bf16 tensor [n2][n1][n0] with 128-byte swizzle, box [1][b1][64 elements]
 inline int make_tmap_bf16_3d_sw128(CUtensorMap* m, const void* base, uint64_t n0, uint64_t n1, uint64_t n2,
                                    uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b1, const char* what) {

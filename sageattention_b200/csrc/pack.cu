@@ -273,6 +273,57 @@ __global__ void __launch_bounds__(256) pack_cols_kernel(
                            blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr, prescale_amax, sr_flags, seed);
 }
 
+// ---------------------------------------------------------------- MXFP8 along the strided axis
+// x [B, S, R] (rows contiguous) -> e4m3 bytes [B, R, s_pad] + e8m0 scales [B, R, s_pad/32]: the
+// transposed gradient operands (dO^T, Q^T, K^T) of the fp8_rownorm backward.  A 128-token x 64-row
+// tile goes through shared memory; a thread packs one 32-token group of one row.  Tokens >= S read
+// as +0.0; with prescale_amax every element is first divided by the power of two >= that value.
+template <typename T>
+__global__ void __launch_bounds__(256) pack_mx8_cols_kernel(
+    const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
+    uint8_t* __restrict__ out, uint8_t* __restrict__ sc, int vec_in, const float* __restrict__ prescale_amax) {
+  __shared__ float tile[kColsKeys][kColsRows + 1];
+  const float pre = prescale_amax != nullptr ? __frcp_rn(pow2_ceil(*prescale_amax)) : 1.0f;
+  const int tid = threadIdx.x;
+  const int64_t k0 = (int64_t)blockIdx.x * kColsKeys, r0 = (int64_t)blockIdx.y * kColsRows, b = blockIdx.z;
+  const T* xb = x + b * sxb;
+#pragma unroll
+  for (int pass = 0; pass < kColsKeys / 32; ++pass) {
+    const int key = pass * 32 + (tid >> 3);
+    const int rc = (tid & 7) * 8;
+    float v[8];
+    const int64_t kk = k0 + key;
+    int valid = 0;
+    if (kk < k_read) {
+      const int64_t left = R - (r0 + rc);
+      valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
+    }
+    if (valid > 0) {
+      load8<T>(xb + kk * sxk + r0 + rc, vec_in, valid, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tile[key][rc + i] = v[i] * pre;
+  }
+  __syncthreads();
+  const int row = tid & 63, g = tid >> 6;          // 32-token group g of row `row`
+  if (r0 + row >= R || k0 + g * 32 >= k_pad) return;
+  float v0[16], v1[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    v0[j] = tile[g * 32 + j][row];
+    v1[j] = tile[g * 32 + 16 + j][row];
+  }
+  uint32_t w[8];
+  const uint8_t sb = pack_group32_mx8(v0, v1, w);
+  uint8_t* po = out + (b * R + r0 + row) * k_pad + k0 + g * 32;
+  *reinterpret_cast<uint4*>(po) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(po + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+  sc[(b * R + r0 + row) * (k_pad / 32) + (k0 + g * 32) / 32] = sb;
+}
+
 // ---------------------------------------------------------------- Q, K along D and V^T in one launch
 // A flat grid: the first nbq blocks pack Q's 16-groups, the next nbk blocks K's, the rest are the
 // 128-key x 64-row tiles of V -> V^T.  Below a few thousand tokens three launches cost more than
@@ -461,6 +512,34 @@ extern "C" int nvfp4_pack_dual(const void* x, int dtype, int64_t B, int64_t S, i
     case NVFP4_DT_FP32: return pack_dual_launch<float>(x, B, S, d, s_pad, sxb, sxs, prescale_amax, sr_flags, seed, dnib, dsc, tnib, tsc, st);
     default: return fail(-1, "nvfp4_pack_dual: unknown dtype %d", dtype);
   }
+}
+
+extern "C" int nvfp4_pack_mx8_t(const void* x, int dtype, int64_t B, int64_t S, int d, int64_t s_pad,
+                                int64_t sxb, int64_t sxs, const float* prescale_amax, uint8_t* out,
+                                uint8_t* sc, nvfp4_stream_t stream) {
+  using namespace nvfp4;
+  NVFP4_REQUIRE(B >= 0 && S >= 0 && d >= 1, "nvfp4_pack_mx8_t: bad extents");
+  NVFP4_REQUIRE(s_pad % 32 == 0 && s_pad >= S, "nvfp4_pack_mx8_t: s_pad must be a multiple of 32 >= S");
+  if (B == 0 || s_pad == 0) return 0;
+  NVFP4_REQUIRE(x && out && sc, "nvfp4_pack_mx8_t: null pointer");
+  NVFP4_REQUIRE(B < 65536 && ((uintptr_t)out & 15) == 0, "nvfp4_pack_mx8_t: too many batch entries or unaligned output");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((unsigned)((s_pad + kColsKeys - 1) / kColsKeys), (unsigned)((d + kColsRows - 1) / kColsRows), (unsigned)B);
+#define NVFP4_MX8(T)                                                                                    \
+  {                                                                                                     \
+    constexpr int64_t kVecElems = 16 / sizeof(T);                                                       \
+    const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && sxb % kVecElems == 0 && sxs % kVecElems == 0; \
+    pack_mx8_cols_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), d, S, s_pad, sxb, sxs, out, sc, vec, \
+                                                  prescale_amax);                                       \
+    return launch_result("nvfp4_pack_mx8_t");                                                           \
+  }
+  switch (dtype) {
+    case NVFP4_DT_BF16: NVFP4_MX8(__nv_bfloat16)
+    case NVFP4_DT_FP16: NVFP4_MX8(__half)
+    case NVFP4_DT_FP32: NVFP4_MX8(float)
+    default: return fail(-1, "nvfp4_pack_mx8_t: unknown dtype %d", dtype);
+  }
+#undef NVFP4_MX8
 }
 
 extern "C" int nvfp4_pack_qkv(const void* q, const void* k, const void* v, int dtype, int64_t bq,

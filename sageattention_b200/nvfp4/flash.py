@@ -142,6 +142,25 @@ def rope_quant_nvfp4(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, posi
     return nib, sc.view(torch.float8_e4m3fn)
 
 
+def _quant_mxfp8_t(x: torch.Tensor, s_pad: int, _prescale_amax: torch.Tensor | None = None):
+    """MXFP8 pack of ``x`` [B, S, D] along S: e4m3 bytes [B, D, s_pad] and e8m0 scale bytes
+    [B, D, s_pad/32] (one power-of-two scale per 32 tokens); stands in for ``_pack_mxfp8_along_k`` of
+    the transposed operand (flash.py:243-257, 1255-1394).  The gradient operands dO^T, Q^T, K^T of the
+    ``fp8_rownorm`` backward."""
+    _lib.require_cuda(x, "x")
+    b, s, d = x.shape
+    assert s_pad % 32 == 0 and s_pad >= s, "s_pad must be a multiple of 32 covering S"
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    out = torch.empty(b, d, s_pad, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(b, d, s_pad // 32, dtype=torch.uint8, device=x.device)
+    if b * s_pad > 0:
+        _lib.call("nvfp4_pack_mx8_t", x.device, x.data_ptr(), _lib.dtype_code(x.dtype), b, s, d, s_pad, x.stride(0),
+                  x.stride(1), _prescale_amax.data_ptr() if _prescale_amax is not None else None, out.data_ptr(),
+                  sc.data_ptr(), _lib.stream_ptr(x.device))
+    return out, sc
+
+
 def vproj_quant_nvfp4(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, num_kv_heads: int,
                       head_dim: int, s_pad: int | None = None, return_value: bool = True):
     """V projection with the NVFP4 pack as its epilogue (the producer the reference asks callers to
@@ -607,20 +626,17 @@ def _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None,
     return dq, dk, dv
 
 
-_FP8_NOTE_SHOWN = False
-
-
 def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, out_layout="zhsd",
              mode="fp4_rownorm", q_packs=None, k_packs=None, key_pad_bias=None, sr=False, sr_p_dv=None,
              sr_dot_dv=None, sr_ds_dq=None, seed=None, qt_packs=None, kt_packs=None, vd_packs=None, **_unused):
-    """All-FP4 backward for the ``fp4_rownorm`` / ``fp4_legacy`` modes (stands in for
-    flash.py:3811-4265): every GEMM of the backward is a block-scaled NVFP4 tensor-core product.
+    """Block-scaled backward for the ``fp4_rownorm`` / ``fp4_legacy`` / ``fp8_rownorm`` modes (stands
+    in for flash.py:3811-4265): every GEMM of the backward is a block-scaled tensor-core product.
 
     Pre-pass (four small launches): delta = rowsum(dO o O) and max|dO|; dO / 2^e packed along D and
     along the tokens from one read; Q^T and K^T packed along the tokens; V packed along D.  Then the
-    dK/dV kernel (GQA reduced in tensor memory) and the dQ kernel.  ``fp8_rownorm`` (MXFP8 gradient
-    operands in the reference) has no kernel of its own here: it runs the high-precision
-    gradient-GEMM kernels, which are strictly more accurate; a note is printed once.
+    dK/dV kernel (GQA reduced in tensor memory) and the dQ kernel.  In ``fp8_rownorm`` the operands
+    of the three gradient GEMMs (dO^T, Q^T, K^T from the pre-pass; P^T, dS^T, dS packed in the
+    kernels) are MXFP8 -- e4m3 with an e8m0 scale per 32 -- while S and dP stay NVFP4 products.
 
     Stochastic rounding (flash.py:3897-3915): only ``fp4_legacy`` honours the knobs; ``sr`` rounds
     the dO pack along D and the dS^T pack stochastically, ``sr_p_dv`` / ``sr_dot_dv`` / ``sr_ds_dq``
@@ -631,15 +647,7 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     tokens) and the along-D pack of V saved by the forward under ``save_backward_packs``; given,
     the pre-pass skips those launches (and the re-read of Q, K and V).
     """
-    if mode == "fp8_rownorm":
-        global _FP8_NOTE_SHOWN
-        if not _FP8_NOTE_SHOWN:
-            import warnings
-            warnings.warn("backward_grad_dots='fp8_rownorm': no MXFP8 gradient kernels in this build; "
-                          "running the bf16 gradient-GEMM kernels instead", stacklevel=2)
-            _FP8_NOTE_SHOWN = True
-        return _run_bwd_hp(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays, out_layout,
-                           q_packs=q_packs, k_packs=k_packs, key_pad_bias=key_pad_bias)
+    fp8 = mode == "fp8_rownorm"
     z, h, s_q, d = q.shape
     _, hk, s_kv, _ = k.shape
     assert d in (128, 256), "D must be 128 or 256"
@@ -662,17 +670,30 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
     sq_pad, skv_pad = _next_mult(s_q, _KEY_TILE), _next_mult(s_kv, _KEY_TILE)
     donv, dosc, dotnv, dotsc = _quant_nvfp4_dual(do3, sq_pad, _prescale_amax=amax, _sr=(sr, sr_dot_dv), _seed=seed)
     q3, k3, v3 = q.reshape(z * h, s_q, d), k.reshape(z * hk, s_kv, d), v.reshape(z * hk, s_kv, d)
-    if q_packs is not None:
+    if fp8:
+        assert qt_packs is None and kt_packs is None, (
+            "fp8_rownorm repacks Q^T/K^T as MXFP8; incompatible with saved FP4 transposed packs")
+        dotnv, dotsc = _quant_mxfp8_t(do3, sq_pad, _prescale_amax=amax)
+        qnv, qsc = ((t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
+                    if q_packs is not None else _quant_nvfp4(q3))
+        knv, ksc = ((t.contiguous() for t in _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout"))
+                    if k_packs is not None else _quant_nvfp4(k3))
+        qtnv, qtsc = _quant_mxfp8_t(q3, sq_pad)
+        ktnv, ktsc = _quant_mxfp8_t(k3, skv_pad)
+    elif q_packs is not None:
         qnv, qsc = (t.contiguous() for t in _check_packs(q_packs, (z * h, s_q, d), "q_packs layout"))
         qtnv, qtsc = qt_packs if qt_packs is not None else _quant_nvfp4(q3, transpose=True, k_pad=sq_pad)
     else:
         qnv, qsc, qtnv, qtsc = _quant_nvfp4_dual(q3, sq_pad)
-    if k_packs is not None:
+    if fp8:
+        pass
+    elif k_packs is not None:
         knv, ksc = (t.contiguous() for t in _check_packs(k_packs, (z * hk, s_kv, d), "k_packs layout"))
         ktnv, ktsc = kt_packs if kt_packs is not None else _quant_nvfp4(k3, transpose=True, k_pad=skv_pad)
     else:
         knv, ksc, ktnv, ktsc = _quant_nvfp4_dual(k3, skv_pad)
-    assert qtnv.shape == (z * h, d, sq_pad // 2) and ktnv.shape == (z * hk, d, skv_pad // 2), "transposed pack layout"
+    tb = 1 if fp8 else 2          # elements per byte of a transposed pack
+    assert qtnv.shape == (z * h, d, sq_pad // tb) and ktnv.shape == (z * hk, d, skv_pad // tb), "transposed pack layout"
     vdnv, vdsc = vd_packs if vd_packs is not None else _quant_nvfp4(v3)
     gdt = dout.dtype
     dq = torch.empty(z, h, s_q, d, dtype=gdt, device=dev)
@@ -692,7 +713,7 @@ def _run_bwd(q, k, v, out, lse, dout, scaling, causal, g, varlen_arrays=None, ou
               ptr(dotsc), ptr(qtnv), ptr(qtsc), ptr(ktnv), ptr(ktsc), ptr(lse), ptr(delta), ptr(amax), ptr(bias),
               ptr(sst), ptr(sen), ptr(dq), ptr(dk), ptr(dv), _lib.dtype_code(gdt), z, h, hk, s_q, s_kv, sq_pad,
               skv_pad, d, float(scaling), (1 if causal else 0) | (16 if sr else 0) | (32 if sr_p_dv else 0)
-              | (64 if sr_ds_dq else 0), (int(seed) * 2654435761 + 1) & 0xFFFFFFFF,
+              | (64 if sr_ds_dq else 0) | (128 if fp8 else 0), (int(seed) * 2654435761 + 1) & 0xFFFFFFFF,
               _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return dq, dk, dv
 

@@ -151,6 +151,32 @@ def test_all_fp4_backward_matches_exact_gradients(z, h, hk, sq, skv, causal, d):
         assert not torch.equal(a, hp), f"{nm}: the all-FP4 mode returned the bf16 kernels' result"
 
 
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("z,h,hk,sq,skv,causal", FP4_CASES)
+def test_mxfp8_backward_matches_exact_gradients(z, h, hk, sq, skv, causal, d):
+    """`backward_grad_dots="fp8_rownorm"`: MXFP8 operands in the three gradient GEMMs (its own
+    kernels): gradient cosine >= 0.93 against exact attention, closer than the all-FP4 mode on
+    dK / dV's operands, and neither the bf16 nor the FP4 kernels' bits."""
+    q, qn = seeded_bf16((z, h, sq, d), 111)
+    k, kn = seeded_bf16((z, hk, skv, d), 112)
+    v, vn = seeded_bf16((z, hk, skv, d), 113)
+    do, don = seeded_bf16((z, h, sq, d), 114)
+    out, dq, dk, dv = _grads(q, k, v, do, causal, h // hk, mode="fp8_rownorm")
+    _, fq, fk, fv = _grads(q, k, v, do, causal, h // hk, mode="fp4_rownorm")
+    _, hq, hk_, hv = _grads(q, k, v, do, causal, h // hk, mode="bf16")
+    rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, causal, h // hk)
+    for nm, a, b, f4, hp in (("dq", dq, rq, fq, hq), ("dk", dk, rk, fk, hk_), ("dv", dv, rv, fv, hv)):
+        an = a.float().cpu().numpy()
+        assert np.isfinite(an).all(), nm
+        c, c4 = cos(an, b), cos(f4.float().cpu().numpy(), b)
+        print("fp8", d, nm, "cos vs exact", c, " all-FP4", c4, " vs bf16 kernels", cos(an, hp.float().cpu().numpy()))
+        if sq == 1 and nm != "dv":
+            continue
+        assert c >= COS_FP4, (nm, c)
+        assert c >= c4 - 2e-3, (nm, c, c4)
+        assert not torch.equal(a, hp) and not torch.equal(a, f4), nm
+
+
 def _grads_sr(q, k, v, do, causal, g, **kw):
     q = q.clone().requires_grad_(True)
     k = k.clone().requires_grad_(True)

@@ -268,3 +268,26 @@ def test_stochastic_pack_is_unbiased_and_seeded():
     err_sr_s = np.abs(acc_s / nseed - np.transpose(xf, (0, 2, 1))).mean()
     print("mean abs error: round-to-nearest", err_rn_d, "mean of", nseed, "stochastic packs", err_sr_d, err_sr_s)
     assert err_sr_d < 0.25 * err_rn_d and err_sr_s < 0.25 * err_rn_d
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("b,s,d,pad", [(2, 300, 128, 384), (1, 32, 64, 32), (3, 77, 256, 128), (1, 1000, 128, 1024)])
+def test_mxfp8_transposed_pack_matches_oracle(dtype, b, s, d, pad):
+    """MXFP8 pack along the tokens (`_pack_mxfp8_along_k` of the transposed operand,
+    flash.py:243-257): bytes and scale exponents equal the CPU restatement, on magnitudes from
+    denormal-scale to saturating, zeros included; the dequantised tensor is within e4m3 precision."""
+    from sageattention_b200.nvfp4 import flash
+    g = torch.Generator().manual_seed(s * 7 + d)
+    mag = torch.exp2(torch.randint(-30, 20, (b, s // 8 + 1, 1), generator=g).float()).repeat_interleave(8, dim=1)[:, :s]
+    x = (torch.randn(b, s, d, generator=g) * mag).to(dtype)
+    x[0, : min(s, 40), 3] = 0.0                      # an all-zero group
+    if dtype == torch.float32:
+        x[0, 0, 5] = 3.0e38
+    q, sc = flash._quant_mxfp8_t(x.cuda(), pad)
+    oq, osc = O.pack_mxfp8(x.float().numpy(), transpose=True, k_pad=pad)
+    assert np.array_equal(np_u8(sc), osc)
+    assert np.array_equal(np_u8(q), oq)
+    back = O.unpack_mxfp8(np_u8(q), np_u8(sc))[:, :, :s]
+    ref = np.transpose(x.float().numpy(), (0, 2, 1))
+    gmax = np.repeat(np.exp2(np_u8(sc).astype(np.float64) - 127.0) * 448.0, 32, axis=-1)[:, :, :s]
+    assert np.all(np.abs(back - ref) <= gmax * 2.0 ** -4 + 1e-37)

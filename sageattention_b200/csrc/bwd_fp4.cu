@@ -189,12 +189,15 @@ __device__ __forceinline__ void sts_b16(uint32_t saddr, uint32_t a) {
 }
 
 // kDkdv = true: the dK/dV pass (rows = keys), false: the dQ pass (rows = queries).
-template <int D, bool kDkdv, typename TG, bool kFp8>
+// kMode: 0 = NVFP4 gradient operands rounded to nearest, 1 = NVFP4 with the stochastic-rounding
+// flags honoured (a kernel of its own, so the common case carries none of it), 2 = MXFP8.
+template <int D, bool kDkdv, typename TG, int kMode>
 __global__ void __launch_bounds__(kB4Threads, 1)
 bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
             const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
             const __grid_constant__ CUtensorMap tm_t1, const __grid_constant__ CUtensorMap tm_t2,
             const B4Params p) {
+  constexpr bool kFp8 = kMode == 2, kSr = kMode == 1;
   using C = B4Cfg<D, kFp8>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -639,13 +642,18 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           }
         } else {
         // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
-        const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
-        const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
-        if constexpr (kDkdv)
-          scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+        if constexpr (kSr) {
+          const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
+          const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
+          if constexpr (kDkdv)
+            scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+                   << (8 * (ch & 1));
+          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
                  << (8 * (ch & 1));
-        scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
-               << (8 * (ch & 1));
+        } else {
+          if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+        }
         if (ch & 1) {
           // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
           if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
@@ -793,9 +801,11 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     kdq<<<g2, kB4Threads, smem, st>>>(t_q, t_do, t_k, t_vd, t_kt, t_kt, b);
     return launch_result("nvfp4_bwd_fp4(dq)");
   };
+  const bool any_sr = (flags & (NVFP4_BWD_SR_DS_DK | NVFP4_BWD_SR_P_DV | NVFP4_BWD_SR_DS_DQ)) != 0;
 #define NVFP4_B4_LAUNCH(DD, TT)                                                                                   \
-  (fp8 ? launch(bwd4_kernel<DD, true, TT, true>, bwd4_kernel<DD, false, TT, true>, B4Cfg<DD, true>::TOTAL)        \
-       : launch(bwd4_kernel<DD, true, TT, false>, bwd4_kernel<DD, false, TT, false>, B4Cfg<DD, false>::TOTAL))
+  (fp8      ? launch(bwd4_kernel<DD, true, TT, 2>, bwd4_kernel<DD, false, TT, 2>, B4Cfg<DD, true>::TOTAL)         \
+   : any_sr ? launch(bwd4_kernel<DD, true, TT, 1>, bwd4_kernel<DD, false, TT, 1>, B4Cfg<DD, false>::TOTAL)        \
+            : launch(bwd4_kernel<DD, true, TT, 0>, bwd4_kernel<DD, false, TT, 0>, B4Cfg<DD, false>::TOTAL))
   if (d == 128) {
     switch (grad_dtype) {
       case NVFP4_DT_BF16: return NVFP4_B4_LAUNCH(128, __nv_bfloat16);

@@ -275,7 +275,7 @@ def measure_peaks(cx, _lib):
     sink = torch.zeros(4, dtype=torch.float32, device=cx.dev)
     names = {0: "fp4_mma_tflops", 1: "bf16_mma_tflops", 2: "ex2_per_sm_per_s", 3: "cvt_e2m1x2_per_sm_per_s",
              4: "fma_per_sm_per_s", 5: "ex2_plus_cvt_e2m1x2_pairs_per_sm_per_s", 6: "cvt_e4m3x2_per_sm_per_s",
-             7: "cvt_f16x2_from_e4m3x2_per_sm_per_s", 8: "cvt_bf16x2_per_sm_per_s"}
+             7: "cvt_f16x2_from_e4m3x2_per_sm_per_s"}
     out = {}
     sms = torch.cuda.get_device_properties(cx.dev).multi_processor_count
     for what, key in names.items():
@@ -356,7 +356,7 @@ def sharded_prefill(cx, nv, RD, q, k, v, out_full, steps):
 
 
 def train_metrics(cx, nv, RD, peaks, steps):
-    """Config 3: packed varlen forward + backward, both backward modes; the 8 KV groups are dealt
+    """Config 3: packed varlen forward + backward, the three backward modes; the 8 KV groups are dealt
     to the ranks (1 per GPU at 8).  FLOPs: forward 4*H*D*sum(s_i^2)/2, backward 2.5x."""
     torch = cx.torch
     from sageattention_b200.nvfp4 import flash
@@ -379,7 +379,7 @@ def train_metrics(cx, nv, RD, peaks, steps):
     sum_sq = float(sum(n * n for n in lens))
     fwd_flops = 4.0 * h * d * sum_sq / 2.0
     res, clocks, grads = {}, {}, {}
-    for mode in ("bf16", "fp4_rownorm"):
+    for mode in ("bf16", "fp4_rownorm", "fp8_rownorm"):
         def step():
             o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=g,
                                          cu_seqlens=cu, backward_grad_dots=mode)
@@ -401,6 +401,9 @@ def train_metrics(cx, nv, RD, peaks, steps):
                                     q_packs=packs[0:2], k_packs=packs[2:4])
         bwd_ms["bf16"], _, _ = cx.timed(hp, steps, min_seconds=0.2)
         bwd_ms["fp4_rownorm"], _, _ = cx.timed(f4, steps, min_seconds=0.2)
+        f8 = lambda: flash._run_bwd(q, k, v, o, lse, do, d ** -0.5, True, g, arrays, mode="fp8_rownorm",
+                                    q_packs=packs[0:2], k_packs=packs[2:4])
+        bwd_ms["fp8_rownorm"], _, _ = cx.timed(f8, steps, min_seconds=0.2)
     # gradient cosine against bf16 attention on the first sample of this rank's first KV group
     n0 = lens[0]
     qs = q.detach()[:, :g, :n0].clone().requires_grad_(True)
@@ -416,15 +419,18 @@ def train_metrics(cx, nv, RD, peaks, steps):
     bwd_tf = {m: 2.5 * fwd_flops / (bwd_ms[m] * 1e-3) / 1e12 for m in bwd_ms}
     return {"name": "config 3: train fwd+bwd, packed varlen 16384 tokens H32 Hk8 D128, KV groups sharded over the ranks",
             "segments": lens, "sum_len_sq": sum_sq, "kv_groups_per_rank": len(kv_heads), "scaling": "strong",
-            "fwd_bwd_ms": {"hp_grad_dots(bf16)": res["bf16"], "fp4_rownorm": res["fp4_rownorm"]},
+            "fwd_bwd_ms": {"hp_grad_dots(bf16)": res["bf16"], "fp4_rownorm": res["fp4_rownorm"],
+                           "fp8_rownorm": res["fp8_rownorm"]},
             "fwd_bwd_tflops_all_gpus": {"hp_grad_dots(bf16)": 3.5 * fwd_flops / (res["bf16"] * 1e-3) / 1e12,
-                                        "fp4_rownorm": 3.5 * fwd_flops / (res["fp4_rownorm"] * 1e-3) / 1e12},
+                                        "fp4_rownorm": 3.5 * fwd_flops / (res["fp4_rownorm"] * 1e-3) / 1e12,
+                                        "fp8_rownorm": 3.5 * fwd_flops / (res["fp8_rownorm"] * 1e-3) / 1e12},
             "bwd_only_ms": bwd_ms, "grad_cosine_vs_bf16_sdpa": cos,
             "clocks": clocks["bf16"], "clocks_fp4_rownorm": clocks["fp4_rownorm"],
             "roofline": {"bound": "tensor", "achieved": bwd_tf["bf16"], "peak": peak * cx.world, "unit": "TFLOP/s",
                          "frac": bwd_tf["bf16"] / (peak * cx.world), "traffic": None,
                          "kernel": "bwd_dkdv_kernel + bwd_dq_kernel (+ delta pre-pass), hp_grad_dots mode",
                          "achieved_fp4_rownorm": bwd_tf["fp4_rownorm"],
+                         "achieved_fp8_rownorm": bwd_tf["fp8_rownorm"],
                          "note": "2.5 x forward FLOPs (5 GEMMs; the S and dP recompute of the second kernel "
                                  "is not counted) over the bf16 sustained GEMM peak of all ranks"}}
 

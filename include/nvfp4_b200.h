@@ -381,7 +381,7 @@ int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, co
  * Measured pipe rates (no counterpart in the reference): launches a resident-operand micro-kernel
  * on every SM -- what = 0: tcgen05.mma kind::mxf4nvf4 M128 N128 K64; 1: kind::f16 (bf16) M128 N128
  * K16; 2: ex2.approx.f32; 3: cvt e2m1x2; 4: fma.f32; 5: ex2 + cvt e2m1x2 pairs; 6: cvt e4m3x2.f32;
- * 7: cvt f16x2.e4m3x2; 8: cvt bf16x2.f32 -- `iters` operations per issuing thread, and
+ * 7: cvt f16x2.e4m3x2 -- `iters` operations per issuing thread, and
  * stores the work of one launch in *work_per_launch (FLOP for 0/1, thread-instructions for 2-4).
  * The caller times the launch with CUDA events; the result is the roofline denominator benchmarks
  * of this library quote.  `sink` is one device float (never written in practice).

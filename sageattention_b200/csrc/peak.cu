@@ -7,7 +7,7 @@
 //   what = 3   cvt.rn.satfinite.e2m1x2.f32   (the P / gradient packs)
 //   what = 4   fma.rn.f32
 //   what = 5   one ex2 plus one e2m1x2 convert per slot (pipe sharing: counts slots, i.e. pairs)
-//   what = 6   cvt.rn.satfinite.e4m3x2.f32;  7  cvt.rn.f16x2.e4m3x2;  8  cvt.rn.bf16x2.f32
+//   what = 6   cvt.rn.satfinite.e4m3x2.f32;  7  cvt.rn.f16x2.e4m3x2
 // Operands stay in shared memory / registers, so nothing but the pipe under test is exercised.
 #include "common/abi.cuh"
 #include "common/sm100.cuh"
@@ -127,8 +127,6 @@ __global__ void __launch_bounds__(256) peak_alu_kernel(int iters, float seed, fl
         uint32_t h2;
         asm volatile("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)u[i]));
         u[i] = h2;
-      } else if constexpr (kWhat == 8) {
-        asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u[i]) : "f"(x[i]), "f"(x[(i + 1) % kPeakIlp]));
       } else {
         asm volatile("fma.rn.f32 %0, %0, %1, %2;" : "+f"(x[i]) : "f"(1.0001f), "f"(0.5f));
       }
@@ -145,7 +143,7 @@ __global__ void __launch_bounds__(256) peak_alu_kernel(int iters, float seed, fl
 extern "C" int nvfp4_peak_probe(int what, int iters, double* work_per_launch, float* sink, int* status,
                                 nvfp4_stream_t stream) {
   using namespace nvfp4;
-  NVFP4_REQUIRE(what >= 0 && what <= 8, "nvfp4_peak_probe: what must be 0..8");
+  NVFP4_REQUIRE(what >= 0 && what <= 7, "nvfp4_peak_probe: what must be 0..7");
   NVFP4_REQUIRE(iters >= 1 && iters <= (1 << 16), "nvfp4_peak_probe: iters must be in [1, 65536]");
   NVFP4_REQUIRE(sink != nullptr, "nvfp4_peak_probe: sink must not be NULL");
   int dev = 0, sms = 0;
@@ -170,7 +168,6 @@ extern "C" int nvfp4_peak_probe(int what, int iters, double* work_per_launch, fl
   else if (what == 5) peak_alu_kernel<5><<<blocks, 256, 0, st>>>(iters, 1.0f, sink);
   else if (what == 6) peak_alu_kernel<6><<<blocks, 256, 0, st>>>(iters, 1.0f, sink);
   else if (what == 7) peak_alu_kernel<7><<<blocks, 256, 0, st>>>(iters, 1.0f, sink);
-  else if (what == 8) peak_alu_kernel<8><<<blocks, 256, 0, st>>>(iters, 1.0f, sink);
   else peak_alu_kernel<4><<<blocks, 256, 0, st>>>(iters, 1.0f, sink);
   if (work_per_launch) *work_per_launch = (double)blocks * 256 * iters * kPeakIlp;            // thread-instructions
   return launch_result("nvfp4_peak_probe(alu)");

@@ -805,10 +805,19 @@ def run_profile_case(args):
         q = rn(16, 32, 1, 128)
         packed = cache.get_packed()
         fn = lambda: nv.nvfp4_flash_decode_prequant(q, packed, 128 ** -0.5, 4)
-    elif case in ("bwd", "bwd_fp4"):   # Z1 H32 Hk8 S4096 D128 causal fwd+bwd: 0.48 TFLOP per step
+    elif case == "hybrid":     # Z16 Hk8 S8192 + a 512-token bf16 window (34 MB of ring rows per launch)
+        cache = nv.NVFP4KVCache(16, 8, 128, 8192, dev, recent_window=512)
+        cache.prefill(rn(16, 8, 8192, 128), rn(16, 8, 8192, 128))
+        q = rn(16, 32, 1, 128)
+        fn = lambda: cache.hybrid_decode(q, 128 ** -0.5, 4)
+    elif case == "vproj":      # V projection + pack epilogue: 8192 tokens x 4096 hidden -> 8 x 128 features
+        x, w = rn(1, 8192, 4096), rn(1024, 4096) * (4096 ** -0.5)
+        w = w.to(torch.bfloat16)
+        fn = lambda: nv.vproj_quant_nvfp4(x, w, None, 8, 128)
+    elif case in ("bwd", "bwd_fp4", "bwd_fp8"):   # Z1 H32 Hk8 S4096 D128 causal fwd+bwd: 0.48 TFLOP per step
         q, k, v, do = rn(1, 32, 4096, 128), rn(1, 8, 4096, 128), rn(1, 8, 4096, 128), rn(1, 32, 4096, 128)
         q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
-        mode = "bf16" if case == "bwd" else "fp4_rownorm"
+        mode = {"bwd": "bf16", "bwd_fp4": "fp4_rownorm", "bwd_fp8": "fp8_rownorm"}[case]
 
         def fn():
             o = nv.nvfp4_flash_attn_func(q, k, v, 128 ** -0.5, causal=True, num_key_value_groups=4,
@@ -842,7 +851,7 @@ def run_profile_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-case", default=None,
-                    choices=["fwd", "fwd_d256", "decode", "pack", "bwd", "bwd_fp4", "umma_peak"],
+                    choices=["fwd", "fwd_d256", "decode", "pack", "bwd", "bwd_fp4", "bwd_fp8", "hybrid", "vproj", "umma_peak"],
                     help="run one small kernel case --steps times (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

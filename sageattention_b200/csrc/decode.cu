@@ -41,7 +41,7 @@ struct DecodeCfg {
   static constexpr int KSF_BYTES = KB * 512;
   static constexpr int VSF_BYTES = MT * 2 * 512;
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + KSF_BYTES + VSF_BYTES;
-  static constexpr int NSTAGE = (D == 128) ? 11 : 5;
+  static constexpr int NSTAGE = (D == 128) ? 10 : 5;
   static constexpr int STMAX = (D == 128) ? 4 : 2;  // key tiles per softmax round ("super-tile")
   static constexpr int Q_BYTES = KSUB * 1024;     // 16 rows x 64 B per sub-tile
   static constexpr int QSF_BYTES = KB * 512;
@@ -49,9 +49,10 @@ struct DecodeCfg {
   static constexpr int PSF_BYTES = 2 * 512;       // per tile
   static constexpr int MERGE_BYTES = 16 * D * 4;   // one group's O^T partial at the item end
   static constexpr int PBUF_BYTES = 2 * STMAX * (P_BYTES + PSF_BYTES);
+  static constexpr int SSC_BYTES = 16 * 1024;      // scores of one round, [tile][head][128 keys] fp32
   // the merge buffer reuses the P tiles, which are idle once an item's last PV has completed
   static constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 2 * (Q_BYTES + QSF_BYTES) +
-                                    (PBUF_BYTES > MERGE_BYTES ? PBUF_BYTES : MERGE_BYTES) + 1024;
+                                    (PBUF_BYTES > MERGE_BYTES ? PBUF_BYTES : MERGE_BYTES) + SSC_BYTES + 1024;
   // TMEM columns: [buffer][tile of the super-tile][...]
   static constexpr int T_ST = 0;                              // 2 x STMAX x 16
   static constexpr int T_OT = T_ST + 2 * STMAX * 16;          // 2 x STMAX x MT x 16
@@ -117,13 +118,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   uint8_t* s_p = s_qsf + 2 * C::QSF_BYTES;                // [2][STMAX][P_BYTES]
   uint8_t* s_psf = s_p + 2 * C::STMAX * C::P_BYTES;       // [2][STMAX][PSF_BYTES]
   float* s_merge = reinterpret_cast<float*>(s_p);          // [16][D], only at the end of an item
+  float* ssc = reinterpret_cast<float*>(s_p + (C::PBUF_BYTES > C::MERGE_BYTES ? C::PBUF_BYTES : C::MERGE_BYTES));
 
   __shared__ uint64_t full_kv[C::NSTAGE], full_sf[C::NSTAGE], empty[C::NSTAGE];
   __shared__ uint64_t s_full[2], s_free[2], p_full[2], o_full[2], q_full[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int err;
-  __shared__ float xch[2][4][C::STMAX][16];
-  __shared__ float lred[8][16];
+  __shared__ float xch[C::STMAX][16];      // tile maxima of the current round, per head
+  __shared__ float lred[C::STMAX][16];     // row sums at the end of an item, per tile slot and head
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -466,17 +468,23 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int wq = sw & 3;                 // TMEM lane quadrant
     const int ts = (tid - 128) & 127;      // key lane within a tile (softmax) / d row (accumulate)
     const int tall = tid - 128;            // 0..255
+    // pack role: thread `tall` owns (tile ij, head ih, 16-key group ig) of every round
+    constexpr int kItems = ST * NQ * 8;
+    static_assert(kItems <= 256, "one pack item per softmax thread");
+    const bool it_on = tall < kItems;
+    const int ig = tall & 7, ih = (tall >> 3) % NQ, ij = tall / (8 * NQ);
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     uint32_t su = 0;
     for (int wi = 0; wi < my_items; ++wi) {
       int unit, t0, t1;
       item_at(wi, unit, t0, t1);
-      float m_run[NQ], l_run[NQ];             // key-lane role: running max, partial row sum
+      float m_run[NQ];                        // running max of every head (all threads agree)
       float o_run[C::MT][NQ], m_acc[NQ];      // d-row role: accumulated O^T, the max it refers to
       float w_prev[TPG][NQ], m_end_prev[NQ];  // weights of the round whose PV is still in flight
+      float m_it = -INFINITY, l_it = 0.0f;    // pack role: running max of this thread's head, its part of the row sum
 #pragma unroll
       for (int qi = 0; qi < NQ; ++qi) {
-        m_run[qi] = -INFINITY; l_run[qi] = 0.0f; m_acc[qi] = -INFINITY; m_end_prev[qi] = -INFINITY;
+        m_run[qi] = -INFINITY; m_acc[qi] = -INFINITY; m_end_prev[qi] = -INFINITY;
 #pragma unroll
         for (int mt = 0; mt < C::MT; ++mt) o_run[mt][qi] = 0.0f;
 #pragma unroll
@@ -523,7 +531,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const int nt = min(ST, t1 - ts0);
         mbar_wait(&s_full[b], (su >> 1) & 1, &err, 8);
         tc_fence_after();
-        float sv[TPG][NQ];
+        // ---- key-lane role: this thread's key of each of its group's tiles, every head, goes to
+        // the exchange buffer [tile][head][key] (keys permuted within their 16-group so that both
+        // these stores and the 16-byte reads below are free of bank conflicts)
         {
           uint32_t r[TPG][16];
 #pragma unroll
@@ -531,121 +541,109 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             if (grp * TPG + jj < nt)
               tmem_ld16(tmem + lane_addr + C::T_ST + (b * C::STMAX + grp * TPG + jj) * 16, r[jj]);
           tmem_ld_wait();
+          const int kg = ts >> 4, kc = (ts >> 2) & 3, ke = ts & 3;
+          const int kpos = kg * 16 + ((kc ^ (kg >> 1)) & 3) * 4 + ke;
 #pragma unroll
           for (int jj = 0; jj < TPG; ++jj) {
             const int j = grp * TPG + jj;
-            const bool valid = (j < nt) && (((int64_t)(ts0 + j) * 128 + ts) < p.s_kv);
+            if (j < nt) {
+              const bool valid = ((int64_t)(ts0 + j) * 128 + ts) < p.s_kv;
 #pragma unroll
-            for (int qi = 0; qi < NQ; ++qi)
-              sv[jj][qi] = (valid && qi < p.g) ? __uint_as_float(r[jj][qi]) * p.scaling : -INFINITY;
+              for (int qi = 0; qi < NQ; ++qi)
+                ssc[(j * NQ + qi) * 128 + kpos] =
+                    (valid && qi < p.g) ? __uint_as_float(r[jj][qi]) * p.scaling : -INFINITY;
+            }
           }
         }
         tc_fence_before();
         mbar_arrive(&s_free[b]);
-        // maxima: first over each 16-lane key group (kept: exp of it is the group's P amax, since
-        // ex2 is monotonic), then over the warp, then an exchange gives every tile maximum
-        float gmx[TPG][NQ];
-        {
+        named_bar_sync(1, 256);
+        // ---- pack role: thread = (tile ij, head ih, 16-key group ig) of the round; its sixteen
+        // scores are thread-local from here on
+        float sc16[16];
+        float mx16 = -INFINITY;
+        if (it_on && ij < nt) {
+          const float* src = ssc + (ij * NQ + ih) * 128 + ig * 16;
 #pragma unroll
-          for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-            for (int qi = 0; qi < NQ; ++qi) gmx[jj][qi] = sv[jj][qi];
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1)
-#pragma unroll
-            for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-              for (int qi = 0; qi < NQ; ++qi)
-                gmx[jj][qi] = fmaxf(gmx[jj][qi], __shfl_xor_sync(0xffffffffu, gmx[jj][qi], o));
-          float wmx[TPG][NQ];
-#pragma unroll
-          for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-            for (int qi = 0; qi < NQ; ++qi)
-              wmx[jj][qi] = fmaxf(gmx[jj][qi], __shfl_xor_sync(0xffffffffu, gmx[jj][qi], 16));
-          if (lane == 0) {
-#pragma unroll
-            for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-              for (int qi = 0; qi < NQ; ++qi) xch[b][wq][grp * TPG + jj][qi] = wmx[jj][qi];
+          for (int c = 0; c < 4; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(src + ((c ^ (ig >> 1)) & 3) * 4);
+            sc16[4 * c] = v.x; sc16[4 * c + 1] = v.y; sc16[4 * c + 2] = v.z; sc16[4 * c + 3] = v.w;
           }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) mx16 = fmaxf(mx16, sc16[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) sc16[e] = -INFINITY;
+        }
+        {
+          float tm = mx16;      // maximum of the tile for this head: the eight groups sit in adjacent lanes
+          tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+          tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+          tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 4));
+          if (it_on && ig == 0) xch[ij][ih] = tm;
         }
         named_bar_sync(1, 256);
         // running maximum advances tile by tile; weights bring each tile to the round's end
-        float m_mine[TPG][NQ];
+        float w_cur[TPG][NQ];
 #pragma unroll
         for (int qi = 0; qi < NQ; ++qi) {
           float m = m_run[qi];
+          float m_mine[TPG];
 #pragma unroll
           for (int j = 0; j < ST; ++j) {
-            const float tm = fmaxf(fmaxf(xch[b][0][j][qi], xch[b][1][j][qi]),
-                                   fmaxf(xch[b][2][j][qi], xch[b][3][j][qi]));
-            m = (j < nt) ? fmaxf(m, tm) : m;
-            if (j / TPG == grp) m_mine[j % TPG][qi] = m;
+            m = (j < nt) ? fmaxf(m, xch[j][qi]) : m;
+            if (j / TPG == grp) m_mine[j % TPG] = m;
           }
-          const float m_sf = (m == -INFINITY) ? 0.0f : m;
-          l_run[qi] *= ex2f_fast((m_run[qi] - m_sf) * kLog2e);
           m_run[qi] = m;
+          const float m_sf = (m == -INFINITY) ? 0.0f : m;
+#pragma unroll
+          for (int jj = 0; jj < TPG; ++jj)
+            w_cur[jj][qi] = (m_mine[jj] == -INFINITY) ? 0.0f : ex2f_fast((m_mine[jj] - m_sf) * kLog2e);
         }
         // the previous round's PV has had a whole round to finish: fold it into registers now,
         // which also frees its P buffers for rewriting
         if (have_prev) accumulate(su - 1, nt_prev);
-        float w_cur[TPG][NQ], pv[TPG][NQ], am[TPG][NQ];
+        if (it_on) {
+          // this thread's tile maximum and the round's final one, for its head
+          float mj = m_it, mend = m_it;
 #pragma unroll
-        for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-          for (int qi = 0; qi < NQ; ++qi) {
-            const float mj = m_mine[jj][qi];
-            const float mj_sf = (mj == -INFINITY) ? 0.0f : mj;
-            const float m_sf = (m_run[qi] == -INFINITY) ? 0.0f : m_run[qi];
-            pv[jj][qi] = ex2f_fast((sv[jj][qi] - mj_sf) * kLog2e);
-            w_cur[jj][qi] = (mj == -INFINITY) ? 0.0f : ex2f_fast((mj_sf - m_sf) * kLog2e);
-            l_run[qi] += pv[jj][qi] * w_cur[jj][qi];
-            am[jj][qi] = ex2f_fast((gmx[jj][qi] - mj_sf) * kLog2e);   // = max of pv over the 16-lane group
+          for (int j = 0; j < ST; ++j) {
+            if (j < nt) {
+              mend = fmaxf(mend, xch[j][ih]);
+              if (j <= ij) mj = mend;
+            }
           }
-        // NVFP4 pack of P along keys: 16 consecutive lanes form one group
-        uint32_t sbv[TPG][NQ];
-        float y[TPG][NQ], yn[TPG][NQ];
+          const float mend_sf = (mend == -INFINITY) ? 0.0f : mend;
+          l_it *= ex2f_fast((m_it - mend_sf) * kLog2e);
+          m_it = mend;
+          if (ij < nt && ih < p.g) {
+            const float mj_sf = (mj == -INFINITY) ? 0.0f : mj;
+            const float wj = (mj == -INFINITY) ? 0.0f : ex2f_fast((mj_sf - mend_sf) * kLog2e);
+            float pv[16], psum = 0.0f;
 #pragma unroll
-        for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-          for (int qi = 0; qi < NQ; ++qi) {
-            const float s32 = fminf(fmaxf(am[jj][qi] * 0.16666667f, kScaleFloor), kScaleMax);
+            for (int e = 0; e < 16; ++e) {
+              pv[e] = ex2f_fast((sc16[e] - mj_sf) * kLog2e);
+              psum += pv[e];
+            }
+            l_it = fmaf(psum, wj, l_it);
+            // NVFP4 pack of the sixteen probabilities: ex2 is monotonic, so the exponential of the
+            // group's largest score is the group's largest probability
+            const float am = ex2f_fast((mx16 - mj_sf) * kLog2e);
+            const float s32 = fminf(fmaxf(am * 0.16666667f, kScaleFloor), kScaleMax);
             uint16_t sb16;
             asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sb16) : "f"(0.0f), "f"(s32));
-            sbv[jj][qi] = sb16 & 0xFFu;
             float inv;
-            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)sbv[jj][qi])));
-            y[jj][qi] = pv[jj][qi] * inv;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(e4m3_to_f32((uint8_t)(sb16 & 0xFFu))));
+            const uint32_t lo = e2m1x8(pv[0] * inv, pv[1] * inv, pv[2] * inv, pv[3] * inv, pv[4] * inv, pv[5] * inv,
+                                       pv[6] * inv, pv[7] * inv);
+            const uint32_t hi = e2m1x8(pv[8] * inv, pv[9] * inv, pv[10] * inv, pv[11] * inv, pv[12] * inv,
+                                       pv[13] * inv, pv[14] * inv, pv[15] * inv);
+            const uint32_t pt = smem_u32(s_p + (b * C::STMAX + ij) * C::P_BYTES);
+            const uint32_t psf = smem_u32(s_psf + (b * C::STMAX + ij) * C::PSF_BYTES);
+            sts_v2(pt + sw64_offset(ih, ig * 8), lo, hi);
+            asm volatile("st.shared.u8 [%0], %1;" ::"r"(psf + (ig >> 2) * 512 + sf_atom_offset(ih, ig & 3)),
+                         "h"((uint16_t)(sb16 & 0xFFu)) : "memory");
           }
-#pragma unroll
-        for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-          for (int qi = 0; qi < NQ; ++qi) yn[jj][qi] = __shfl_xor_sync(0xffffffffu, y[jj][qi], 1);
-        {
-          const uint32_t pt0 = smem_u32(s_p + (b * C::STMAX) * C::P_BYTES);
-          const uint32_t psf0 = smem_u32(s_psf + (b * C::STMAX) * C::PSF_BYTES);
-          const int gi = ts >> 4;
-#pragma unroll
-          for (int jj = 0; jj < TPG; ++jj)
-#pragma unroll
-            for (int qi = 0; qi < NQ; ++qi) {
-              const int j = grp * TPG + jj;
-              if (j < nt && qi < p.g) {
-                if ((lane & 1) == 0) {
-                  uint16_t byte;
-                  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u16.u8 %0, t;\n\t}\n"
-                      : "=h"(byte)
-                      : "f"(yn[jj][qi]), "f"(y[jj][qi]));
-                  asm volatile("st.shared.u8 [%0], %1;" ::"r"(pt0 + j * C::P_BYTES + sw64_offset(qi, ts >> 1)),
-                               "h"(byte) : "memory");
-                }
-                if ((lane & 15) == 0)
-                  asm volatile("st.shared.u8 [%0], %1;" ::"r"(psf0 + j * C::PSF_BYTES + (gi >> 2) * 512 +
-                                                             sf_atom_offset(qi, gi & 3)),
-                               "h"((uint16_t)sbv[jj][qi]) : "memory");
-              }
-            }
         }
 #pragma unroll
         for (int jj = 0; jj < TPG; ++jj)
@@ -677,12 +675,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
             for (int qi = 0; qi < NQ; ++qi) s_merge[qi * D + mt * 128 + ts] = o_run[mt][qi];
         }
-#pragma unroll
-        for (int qi = 0; qi < NQ; ++qi) {
-          float v = l_run[qi];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (lane == 0) lred[sw][qi] = v;
+        {
+          // row sums: the eight groups of a (tile slot, head) sit in adjacent lanes
+          float v = it_on ? l_it : 0.0f;
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          if (it_on && ig == 0) lred[ij][ih] = v;
         }
         named_bar_sync(1, 256);
         if (grp == 0) {
@@ -699,7 +698,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             for (int qi = 0; qi < NQ; ++qi)
               if (qi == ts) {
 #pragma unroll
-                for (int ww = 0; ww < 8; ++ww) lsum += lred[ww][qi];
+                for (int ww = 0; ww < ST; ++ww) lsum += lred[ww][qi];
                 mfin = m_run[qi];
               }
             p.ws_m[w * 16 + ts] = mfin;

@@ -103,6 +103,9 @@ def check(rc: int, what: str = "nvfp4") -> None:
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
 
 
+_entries: dict = {}
+
+
 def call(name: str, device, *args) -> None:
     """Run the C entry ``name`` with ``device`` current and raise on a non-zero return.
 
@@ -112,11 +115,17 @@ def call(name: str, device, *args) -> None:
     the environment the device status word is read back (a synchronising read) after the call and
     an expired in-kernel wait raises instead of returning undefined tensors.
     """
-    dev = torch.device(device)
+    dev = device if isinstance(device, torch.device) else torch.device(device)
     if dev.type != "cuda":
         raise RuntimeError(f"{name}: operands must live on a CUDA device (got {dev})")
-    with torch.cuda.device(dev):
-        rc = getattr(lib(), name)(*args)
+    fn = _entries.get(name)
+    if fn is None:
+        fn = _entries[name] = getattr(lib(), name)
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        rc = fn(*args)                       # already current: skip the (slow) context manager
+    else:
+        with torch.cuda.device(dev):
+            rc = fn(*args)
     check(rc, name)
     if os.environ.get("NVFP4_CHECK_STATUS", "0") == "1":
         st = read_status(dev)

@@ -16,6 +16,7 @@ D=128 default), so ``block_n`` only has to be 128 where it fixes a visible paddi
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 
 import torch
@@ -316,15 +317,26 @@ def nvfp4_quant_kv_decode(key: torch.Tensor, value: torch.Tensor, block_n: int =
     return knv, ksc, vnv, vsc, s_kv, s_kv_pad
 
 
+@functools.lru_cache(maxsize=64)
+def _sm_count_cached(index: int) -> int:
+    return torch.cuda.get_device_properties(index).multi_processor_count
+
+
 def _sm_count(device) -> int:
-    return torch.cuda.get_device_properties(device).multi_processor_count
+    dev = device if isinstance(device, torch.device) else torch.device(device)
+    return _sm_count_cached(torch.cuda.current_device() if dev.index is None else dev.index)
+
+
+@functools.lru_cache(maxsize=4096)
+def _decode_plan_cached(s_kv: int, zhk: int, d: int, sms: int):
+    ns, sk, wb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_size_t()
+    _lib.check(_lib.lib().nvfp4_decode_plan(s_kv, zhk, d, sms, ctypes.byref(ns), ctypes.byref(sk), ctypes.byref(wb)),
+               "nvfp4_decode_plan")   # host only
+    return ns.value, sk.value, wb.value
 
 
 def _decode_plan(s_kv: int, zhk: int, d: int, device):
-    ns, sk, wb = ctypes.c_int(), ctypes.c_int64(), ctypes.c_size_t()
-    _lib.check(_lib.lib().nvfp4_decode_plan(s_kv, zhk, d, _sm_count(device), ctypes.byref(ns),
-                                            ctypes.byref(sk), ctypes.byref(wb)), "nvfp4_decode_plan")   # host only
-    return ns.value, sk.value, wb.value
+    return _decode_plan_cached(int(s_kv), int(zhk), int(d), _sm_count(device))
 
 
 def _decode_core(query, kv_packed, scaling, g, want_lse, split_kv=None, extra=None):

@@ -251,8 +251,11 @@ def test_fp4_legacy_stochastic_rounding_is_unbiased():
     assert torch.equal(only_dot[0], rtn[0]) and torch.equal(only_dot[1], rtn[1]) and not torch.equal(only_dot[2], rtn[2])
 
 
+@pytest.mark.parametrize("mode", ["fp4_rownorm", "fp8_rownorm"])
 @pytest.mark.parametrize("d", [128, 256])
-def test_all_fp4_backward_varlen_bias_and_scale_invariance(d):
+def test_all_fp4_backward_varlen_bias_and_scale_invariance(d, mode):
+    """Packed varlen rows, exact power-of-two linearity in dO, determinism, and a key bias with
+    masked keys on cross attention, for both block-scaled backward modes."""
     h, hk = 4, 2
     lens = [130, 1, 255, 64, 190]
     s = sum(lens)
@@ -262,18 +265,18 @@ def test_all_fp4_backward_varlen_bias_and_scale_invariance(d):
     do, don = seeded_bf16((1, h, s, d), 124)
     cu_np = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     cu = torch.tensor(cu_np, dtype=torch.int32, device="cuda")
-    _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu, mode="fp4_rownorm")
+    _, dq, dk, dv = _grads(q, k, v, do, True, h // hk, cu=cu, mode=mode)
     rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, True, h // hk, cu_seqlens=cu_np)
     for nm, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
         c = cos(a.float().cpu().numpy(), b)
-        print("fp4 varlen", d, nm, c)
+        print(mode, "varlen", d, nm, c)
         assert c >= COS_FP4, (nm, c)
     # the global power-of-two pre-scale of dO makes the result exactly linear in powers of two
-    _, dq2, dk2, dv2 = _grads(q, k, v, do * 2.0 ** -20, True, h // hk, cu=cu, mode="fp4_rownorm")
+    _, dq2, dk2, dv2 = _grads(q, k, v, do * 2.0 ** -20, True, h // hk, cu=cu, mode=mode)
     for a, b in ((dq, dq2), (dk, dk2), (dv, dv2)):
         assert torch.equal((a.float() * 2.0 ** -20).to(torch.bfloat16), b)
     # deterministic (no atomics on the gradient path)
-    _, dq3, dk3, dv3 = _grads(q, k, v, do, True, h // hk, cu=cu, mode="fp4_rownorm")
+    _, dq3, dk3, dv3 = _grads(q, k, v, do, True, h // hk, cu=cu, mode=mode)
     assert torch.equal(dq, dq3) and torch.equal(dk, dk3) and torch.equal(dv, dv3)
     # key bias with masked keys, cross attention
     z, sq, skv = 2, 200, 333
@@ -287,7 +290,7 @@ def test_all_fp4_backward_varlen_bias_and_scale_invariance(d):
     bias[1, 40:57] = float("-inf")
     qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
     out = _n().nvfp4_flash_attn_func(qq, kk, vv, d ** -0.5, causal=False, num_key_value_groups=h // hk,
-                                     key_pad_bias=bias.cuda(), backward_grad_dots="fp4_rownorm")
+                                     key_pad_bias=bias.cuda(), backward_grad_dots=mode)
     out.backward(do)
     assert _status() == 0
     rq, rk, rv = O.attention_grads(qn, kn, vn, don, d ** -0.5, False, h // hk, key_pad_bias=bias.numpy())

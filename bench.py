@@ -553,14 +553,14 @@ def ring_metrics(cx, nv, RD, _lib, steps, seq):
     q, k, v, do = rn(z, h, s_loc, d), rn(z, hk, s_loc, d), rn(z, hk, s_loc, d), rn(z, h, s_loc, d)
     q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
 
-    def make(comm):
+    def make(comm, mode="bf16"):
         def step():
             if cx.world == 1:
                 o = nv.nvfp4_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
-                                             backward_grad_dots="bf16")
+                                             backward_grad_dots=mode)
             else:
                 o = RD.ring_flash_attn_func(q, k, v, d ** -0.5, causal=True, num_key_value_groups=h // hk,
-                                            _communicate=comm)
+                                            _communicate=comm, backward_grad_dots=mode)
             o.backward(do)
             q.grad = k.grad = v.grad = None
         return step
@@ -570,13 +570,17 @@ def ring_metrics(cx, nv, RD, _lib, steps, seq):
     ms_c = ms
     if cx.world > 1:
         ms_c, _, _ = cx.timed(make(False), n, warm=1)
+    # the all-FP4 backward, which is the faster one at head dim 256
+    ms4, clocks4, _ = cx.timed(make(True, "fp4_rownorm"), n, warm=1)
     flops = 3.5 * 4.0 * z * h * float(seq) * float(seq) * d / 2.0
     return {"name": f"config 5: Z1 H16 Hk4 S{seq} D256 causal fwd+bwd, ring attention over {cx.world} rank(s), "
                     "zigzag chunks (rank r owns chunks r and 2W-1-r)",
             "scaling": "strong", "ms_per_step": ms, "tflops_all_gpus": flops / (ms * 1e-3) / 1e12, "steps": n,
             "compute_only_ms": ms_c, "exposed_comm_ms": max(ms - ms_c, 0.0), "clocks": clocks,
             "kernel_status": _lib.read_status(dev),
-            "dtype": "fp4 forward + fp4 S recompute, bf16 gradient GEMMs"}
+            "dtype": "fp4 forward + fp4 S recompute, bf16 gradient GEMMs",
+            "fp4_rownorm_backward": {"ms_per_step": ms4, "tflops_all_gpus": flops / (ms4 * 1e-3) / 1e12,
+                                     "clocks": clocks4, "dtype": "fp4 forward, all five backward GEMMs in NVFP4"}}
 
 
 # ------------------------------------------------------------------------------ GPU arm

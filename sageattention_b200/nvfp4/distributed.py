@@ -300,12 +300,15 @@ def ring_flash_attention(query, key, value, scaling, causal=True, num_key_value_
 
 def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, causal=True,
                                   num_key_value_groups=1, group=None, schedule="contiguous",
-                                  _communicate=True):
+                                  _communicate=True, backward_grad_dots="bf16"):
     """NVFP4 ring-attention backward on CUDA for the local sequence slices (bf16 tensors).
 
     ``out`` / ``lse`` are the merged results of ``ring_flash_attention``; with them every block's
     probabilities are the globally normalised ones, so the per-block backward kernels give exact
-    contributions.  Returns ``(dq, dk, dv)`` in ``dout.dtype``.
+    contributions.  ``backward_grad_dots``: "bf16" (high-precision gradient GEMMs, the default),
+    "fp4_rownorm" or "fp8_rownorm" (the block-scaled kernels, faster at head dim 256; the
+    transposed packs of a block's K and the along-D pack of its V are made by the rank that holds
+    the block, so the messages stay the same).  Returns ``(dq, dk, dv)`` in ``dout.dtype``.
     """
     from .. import _lib
     from . import flash
@@ -355,6 +358,64 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
         dq[:, :, c:] = dq_hi
         return dq, dk, dv
 
+    if backward_grad_dots != "bf16":
+        assert backward_grad_dots in ("fp4_rownorm", "fp8_rownorm"), backward_grad_dots
+        assert s_loc % 128 == 0 and (not zig or c % 128 == 0), (
+            "the block-scaled ring backward wants local slices (and zigzag chunks) of a multiple of 128 tokens")
+        fp8 = backward_grad_dots == "fp8_rownorm"
+        tpack = (lambda x, pad: flash._quant_mxfp8_t(x, pad)) if fp8 else \
+                (lambda x, pad: flash._quant_nvfp4(x, transpose=True, k_pad=pad))
+
+        def q_side_packs(qt, dot, ot, lse_t):
+            """Everything the block-scaled kernels need of a set of local query rows."""
+            sq = qt.shape[2]
+            _, dl, amax = flash._bwd_prep(dot, y=ot.to(dot.dtype), want_amax=True)
+            do3 = dot.reshape(z * h, sq, d) if dot.is_contiguous() or z == 1 else dot.contiguous().view(z * h, sq, d)
+            donv, dosc, dotnv, dotsc = flash._quant_nvfp4_dual(do3, sq, _prescale_amax=amax)
+            if fp8:
+                dotnv, dotsc = flash._quant_mxfp8_t(do3, sq, _prescale_amax=amax)
+            q3 = qt.reshape(z * h, sq, d)
+            qn, qs_ = flash._quant_nvfp4(q3)
+            qtn, qts = tpack(q3, sq)
+            return (qn, qs_, donv, dosc, dotnv, dotsc, qtn, qts, lse_t.contiguous(), dl, amax)
+
+        qf = q_side_packs(query, dout, out, lse)
+        if zig:
+            qf_hi = q_side_packs(query[:, :, c:], dout[:, :, c:], out[:, :, c:], lse[:, c:])
+
+        def run4(qs, blk, sq, skv, is_causal):
+            kb, vb = blk[0][:, :skv], blk[1][:, :skv]
+            ktn, kts = tpack(kb, skv)
+            vdn, vds = flash._quant_nvfp4(vb)
+            knv_b = blk[2][:, :skv].contiguous()
+            ksc_b = blk[3][:, :skv].contiguous()
+            dq = torch.empty(z, h, sq, d, dtype=torch.float32, device=dev)
+            dk = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
+            dv = torch.empty(z, hk, skv, d, dtype=torch.float32, device=dev)
+            ptr = lambda t: t.data_ptr()
+            _lib.call("nvfp4_bwd_fp4", _lib.same_device(qs[0], kb, vb),
+                      ptr(qs[0]), ptr(qs[1]), ptr(knv_b), ptr(ksc_b), ptr(vdn), ptr(vds), ptr(qs[2]), ptr(qs[3]),
+                      ptr(qs[4]), ptr(qs[5]), ptr(qs[6]), ptr(qs[7]), ptr(ktn), ptr(kts), ptr(qs[8]), ptr(qs[9]),
+                      ptr(qs[10]), None, None, None, ptr(dq), ptr(dk), ptr(dv), _lib.DT_FP32, z, h, hk, sq, skv, sq,
+                      skv, d, float(scaling), (1 if is_causal else 0) | (128 if fp8 else 0), 0,
+                      _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+            return dq, dk, dv
+
+        def block_backward(blk, mode):      # noqa: F811  (the block-scaled twin of the function above)
+            if mode in ("full", "causal"):
+                return run4(qf, blk, s_loc, s_loc, mode == "causal")
+            if mode == "lo_kv":
+                dq, dk_lo, dv_lo = run4(qf, blk, s_loc, c, False)
+                dk = torch.zeros(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+                dv = torch.zeros(z, hk, s_loc, d, dtype=torch.float32, device=dev)
+                dk[:, :, :c] = dk_lo
+                dv[:, :, :c] = dv_lo
+                return dq, dk, dv
+            dq_hi, dk, dv = run4(qf_hi, blk, c, s_loc, False)      # "hi_q"
+            dq = torch.zeros(z, h, s_loc, d, dtype=torch.float32, device=dev)
+            dq[:, :, c:] = dq_hi
+            return dq, dk, dv
+
     like = torch.empty(z, hk, s_loc, d, dtype=torch.float32, device=dev)
     dq, dk, dv = ring_attention_backward(block, [like, like], block_backward, causal, group, schedule,
                                          _communicate)
@@ -364,23 +425,23 @@ def ring_flash_attention_backward(query, key, value, out, lse, dout, scaling, ca
 
 class _RingFlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, query, key, value, scaling, causal, g, group, schedule, communicate):
+    def forward(ctx, query, key, value, scaling, causal, g, group, schedule, communicate, grad_dots="bf16"):
         out, lse = ring_flash_attention(query, key, value, scaling, causal, g, group, schedule, communicate)
         ctx.save_for_backward(query, key, value, out, lse)
-        ctx.meta = (float(scaling), bool(causal), int(g), group, schedule, communicate)
+        ctx.meta = (float(scaling), bool(causal), int(g), group, schedule, communicate, grad_dots)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         query, key, value, out, lse = ctx.saved_tensors
-        scaling, causal, g, group, schedule, communicate = ctx.meta
+        scaling, causal, g, group, schedule, communicate, grad_dots = ctx.meta
         dq, dk, dv = ring_flash_attention_backward(query, key, value, out, lse, grad_out, scaling, causal, g,
-                                                   group, schedule, communicate)
-        return dq, dk, dv, None, None, None, None, None, None
+                                                   group, schedule, communicate, grad_dots)
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_groups=1, group=None,
-                         schedule="zigzag", _communicate=True):
+                         schedule="zigzag", _communicate=True, backward_grad_dots="bf16"):
     """Differentiable context-parallel NVFP4 attention over this rank's slice of the sequence.
 
     ``schedule="zigzag"`` (default, causal only): the slice is chunks r and 2W-1-r of the sequence
@@ -388,4 +449,4 @@ def ring_flash_attn_func(query, key, value, scaling, causal=True, num_key_value_
     rank; with a causal mask the last rank works on every step and the first on one.
     """
     return _RingFlashAttn.apply(query, key, value, scaling, causal, num_key_value_groups, group, schedule,
-                                _communicate)
+                                _communicate, backward_grad_dots)

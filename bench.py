@@ -18,6 +18,8 @@ Printed JSON (one line, rank 0):
              (`nvfp4_peak_probe`) and against 4 x the bf16 figure of MEASURED_PEAKS.json; also the
              MUFU co-bound that actually limits a D=128 FP4 forward
   parity     kernel vs the numpy oracle on one (batch, KV-group) unit of THIS run's inputs
+             (config 2); the config-3 and config-4 entries of `secondary` carry their own
+             `parity` against the oracle (single-GPU runs: the CPU leg runs on one rank only)
   secondary  at every N, each with its own clock sample: config 2 strong-scaled over (batch,
              KV-group) shards with a bit-for-bit check against the unsharded run; config 3 (packed
              varlen training step, KV groups sharded) for both backward modes; config 4 (decode
@@ -355,7 +357,7 @@ def sharded_prefill(cx, nv, RD, q, k, v, out_full, steps):
             "sharded_first_units_bit_identical_to_unsharded": equal, "clocks": clocks}
 
 
-def train_metrics(cx, nv, RD, peaks, steps):
+def train_metrics(cx, nv, RD, peaks, steps, oracle_parity=False):
     """Config 3: packed varlen forward + backward, the three backward modes; the 8 KV groups are dealt
     to the ranks (1 per GPU at 8).  FLOPs: forward 4*H*D*sum(s_i^2)/2, backward 2.5x."""
     torch = cx.torch
@@ -415,6 +417,24 @@ def train_metrics(cx, nv, RD, peaks, steps):
     cosf = lambda a, b: float(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0))
     cos = {m: {"dq": cosf(grads[m][0][:, :g, :n0], qs.grad), "dk": cosf(grads[m][1][:, :1, :n0], ks.grad),
                "dv": cosf(grads[m][2][:, :1, :n0], vs.grad)} for m in grads}
+    parity = None
+    if oracle_parity:
+        # CPU leg (one rank only): the longest packed segment of the first KV group against the
+        # oracle -- forward vs mode B on the kernel's tile alignment, gradients of every backward mode
+        # vs analytic fp64 gradients of exact attention
+        from oracle import parity_checks as PC
+        f = lambda t_: t_.detach().float().cpu().numpy()
+        a, b, a0 = PC.varlen_segment(lens)
+        fw = PC.varlen_forward_segment(f(o[0, :g, a0:b]), f(q[0, :g, a0:b]), f(k[0, 0, a0:b]), f(v[0, 0, a0:b]),
+                                       a - a0, d ** -0.5)
+        parity = {"segment_tokens": b - a,
+                  "forward_vs_oracle_mode_b": {"cosine": fw["cosine"], "max_abs": fw["max_abs"]},
+                  "grad_cosine_vs_fp64_exact": {}}
+        for m in grads:
+            gr = PC.varlen_grads_segment(f(grads[m][0][0, :g, a:b]), f(grads[m][1][0, 0, a:b]), f(grads[m][2][0, 0, a:b]),
+                                         f(q[0, :g, a:b]), f(k[0, 0, a:b]), f(v[0, 0, a:b]), f(do[0, :g, a:b]),
+                                         d ** -0.5)
+            parity["grad_cosine_vs_fp64_exact"][m] = {kk: gr[kk] for kk in ("dq", "dk", "dv")}
     peak = peaks["bf16_tflops_sustained"]
     bwd_tf = {m: 2.5 * fwd_flops / (bwd_ms[m] * 1e-3) / 1e12 for m in bwd_ms}
     return {"name": "config 3: train fwd+bwd, packed varlen 16384 tokens H32 Hk8 D128, KV groups sharded over the ranks",
@@ -424,7 +444,7 @@ def train_metrics(cx, nv, RD, peaks, steps):
             "fwd_bwd_tflops_all_gpus": {"hp_grad_dots(bf16)": 3.5 * fwd_flops / (res["bf16"] * 1e-3) / 1e12,
                                         "fp4_rownorm": 3.5 * fwd_flops / (res["fp4_rownorm"] * 1e-3) / 1e12,
                                         "fp8_rownorm": 3.5 * fwd_flops / (res["fp8_rownorm"] * 1e-3) / 1e12},
-            "bwd_only_ms": bwd_ms, "grad_cosine_vs_bf16_sdpa": cos,
+            "bwd_only_ms": bwd_ms, "grad_cosine_vs_bf16_sdpa": cos, "parity": parity,
             "clocks": clocks["bf16"], "clocks_fp4_rownorm": clocks["fp4_rownorm"],
             "roofline": {"bound": "tensor", "achieved": bwd_tf["bf16"], "peak": peak * cx.world, "unit": "TFLOP/s",
                          "frac": bwd_tf["bf16"] / (peak * cx.world), "traffic": None,
@@ -435,7 +455,7 @@ def train_metrics(cx, nv, RD, peaks, steps):
                                  "is not counted) over the bf16 sustained GEMM peak of all ranks"}}
 
 
-def decode_metrics(cx, nv, peaks, steps):
+def decode_metrics(cx, nv, peaks, steps, oracle_parity=False):
     """Config 4: batch 16 x 8 KV heads = 128 cache units of 32768 tokens, dealt to the ranks by batch
     entry; one decode step streams every unit's packs once.  Plus append, the 64-step serve loop,
     and hybrid decode with a 512-token high-precision window."""
@@ -457,6 +477,28 @@ def decode_metrics(cx, nv, peaks, steps):
     bytes_all = bytes_rank * cx.world
     step = lambda: nv.nvfp4_flash_decode_prequant(q, packed, d ** -0.5, g)
     ms, clocks, n = cx.timed(step, steps, warm=5, min_seconds=0.3)
+    parity = None
+    if oracle_parity:
+        # CPU leg (one rank only): cache unit 0 against the oracle's split-K walk over the very key
+        # ranges the balanced decomposition cuts that unit into
+        import numpy as np
+        from oracle import parity_checks as PC
+        from sageattention_b200.nvfp4 import flash
+        f = lambda t_: t_.detach().float().cpu().numpy()
+        out = step()
+        torch.cuda.synchronize()
+        nsplit, split_kv, _ = flash._decode_plan(s, z * hk, d, dev)
+        sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        if nsplit == 0:
+            pieces = PC.balanced_pieces(z * hk, s, sm, [0])[0]
+        else:
+            pieces = [(i * split_kv, min(s, (i + 1) * split_kv)) for i in range(nsplit)]
+        sel = lambda t_: t_[0:1].cpu().numpy()
+        pk = (sel(packed[0]), sel(packed[1].view(torch.uint8)), sel(packed[2]), sel(packed[3].view(torch.uint8)), s,
+              packed[5])
+        res = PC.decode_units(f(out.reshape(z * hk, g, d)[0:1]), f(q.reshape(z * hk, g, d)[0:1]), pk, d ** -0.5, g,
+                              [pieces])
+        parity = {"unit": 0, "pieces": len(pieces), "cosine_vs_oracle": res["cosine"], "max_abs_vs_oracle": res["max_abs"]}
     gbs = bytes_all / (ms * 1e-3) / 1e9
     graph_us = None
     try:      # the same step replayed from a CUDA graph (no launch overhead between its kernels)
@@ -478,7 +520,7 @@ def decode_metrics(cx, nv, peaks, steps):
     ms_app, _, _ = cx.timed(app, 30)
     entry = {"name": "config 4: decode step Z16 H32 Hk8 D128 S32768, cache units sharded over the ranks by batch entry",
              "cache_units_per_rank": z * hk, "scaling": "strong", "step_us": ms * 1e3, "step_us_cuda_graph": graph_us,
-             "append_us": ms_app * 1e3, "steps": n, "clocks": clocks,
+             "append_us": ms_app * 1e3, "steps": n, "clocks": clocks, "parity": parity,
              "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"] * cx.world, "unit": "GB/s",
                           "frac": gbs / (peaks["hbm_gbs"] * cx.world),
                           # ncu, S=8192 case (balanced decomposition): dram read 163.2 MB for 150.99 MB of
@@ -712,9 +754,10 @@ def run_gpu(args):
     out_unit = out[0, :H // HK].float().cpu().numpy() if rank == 0 else None
     del q, k, v, out
     torch.cuda.empty_cache()
-    secondary.append(train_metrics(cx, nv, RD, peaks, min(args.steps, 10)))
+    cpu_leg = world == 1      # the oracle runs on rank 0 of a single-GPU run only
+    secondary.append(train_metrics(cx, nv, RD, peaks, min(args.steps, 10), oracle_parity=cpu_leg))
     torch.cuda.empty_cache()
-    secondary.append(decode_metrics(cx, nv, peaks, 50))
+    secondary.append(decode_metrics(cx, nv, peaks, 50, oracle_parity=cpu_leg))
     torch.cuda.empty_cache()
     if world == 1:
         secondary.append(pack_metrics(cx, nv, peaks))

@@ -275,12 +275,6 @@ int nvfp4_window_attention(const void* q, int dtype, int64_t s_qz, int64_t s_qh,
                            nvfp4_stream_t stream);
 
 /*
- * Scratch bytes nvfp4_fwd needs for these dimensions (0 if none).
- */
-size_t nvfp4_fwd_workspace_bytes(int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
-                                 int d);
-
-/*
  * Flash-attention forward over packed operands.  Replaces `_flash_fwd_kernel` and its host
  * drivers `_run_flash_packed` / `nvfp4_flash_attention_packed` (flash.py:739-933, 2560-2766).
  *   qnv/qsc  [Z*H,  s_q,  D/2 | D/16]  contiguous
@@ -300,8 +294,7 @@ int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const 
               const uint8_t* vnv, const uint8_t* vsc, const float* bias, const int32_t* seq_id,
               const int32_t* seq_start, void* out, int out_dtype, int64_t so_z, int64_t so_h,
               int64_t so_s, float* lse, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
-              int64_t s_pad, int d, float scaling, int flags, void* workspace,
-              size_t workspace_bytes, int* status, nvfp4_stream_t stream);
+              int64_t s_pad, int d, float scaling, int flags, int* status, nvfp4_stream_t stream);
 
 /*
  * Backward pre-pass over x [nb1, nb2, s, d] (element strides sxb1, sxb2, sxs; unit stride along

@@ -71,10 +71,9 @@ SIGNATURES = {
     "nvfp4_selftest_wait_timeout": (c_int, [c_int, ctypes.c_uint, c_void_p, c_void_p]),
     "nvfp4_bwd_fp4": (c_int, [c_void_p] * 23 + [c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                               c_int64, c_int, c_float, c_int, c_uint32, c_void_p, c_void_p]),
-    "nvfp4_fwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "nvfp4_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int64, c_int64, c_int64, c_void_p, c_int64,
                           c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_int,
-                          c_void_p, c_size_t, c_void_p, c_void_p]),
+                          c_void_p, c_void_p]),
 }
 
 

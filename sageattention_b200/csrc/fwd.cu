@@ -844,19 +844,14 @@ int fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 
 }  // namespace nvfp4
 
-extern "C" size_t nvfp4_fwd_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, int) {
-  return 0;
-}
-
 extern "C" int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv,
                          const uint8_t* ksc, const uint8_t* vnv, const uint8_t* vsc,
                          const float* bias, const int32_t* seq_id, const int32_t* seq_start,
                          void* out, int out_dtype, int64_t so_z, int64_t so_h, int64_t so_s,
                          float* lse, int64_t z, int64_t h, int64_t hk, int64_t s_q, int64_t s_kv,
-                         int64_t s_pad, int d, float scaling, int flags, void* workspace,
-                         size_t workspace_bytes, int* status, nvfp4_stream_t stream) {
+                         int64_t s_pad, int d, float scaling, int flags, int* status,
+                         nvfp4_stream_t stream) {
   using namespace nvfp4;
-  (void)workspace_bytes;
   NVFP4_REQUIRE(d == 128 || d == 256, "nvfp4_fwd: D must be 128 or 256");
   NVFP4_REQUIRE(z >= 1 && h >= 1 && hk >= 1 && h % hk == 0, "nvfp4_fwd: bad head counts");
   NVFP4_REQUIRE(s_q >= 1 && s_kv >= 1, "nvfp4_fwd: empty sequence");

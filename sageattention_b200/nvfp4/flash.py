@@ -461,8 +461,6 @@ def _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scal
     if key_pad_bias is not None:
         bias = key_pad_bias.to(device=dev, dtype=torch.float32).contiguous()
         assert bias.shape == (z, s_kv), "key_pad_bias must be [Z, Skv]"
-    wbytes = _lib.lib().nvfp4_fwd_workspace_bytes(z, h, hk, s_q, s_kv, d)
-    ws = torch.empty(wbytes, dtype=torch.uint8, device=dev) if wbytes else None
     tensors = [t.contiguous() for t in (qnv, qsc, knv, ksc, vnv, vsc)]
     _lib.call("nvfp4_fwd", _lib.same_device(*tensors, bias, seq_id, seq_start),
               *(t.data_ptr() for t in tensors),
@@ -471,8 +469,7 @@ def _run_flash_packed(qnv, qsc, knv, ksc, vnv, vsc, z, h, hk, s_q, s_kv, d, scal
               seq_start.data_ptr() if seq_start is not None else None,
               out.data_ptr(), _lib.dtype_code(out_dtype), so_z, so_h, so_s,
               lse.data_ptr() if lse is not None else None, z, h, hk, s_q, s_kv, s_pad, d, float(scaling),
-              1 if causal else 0, ws.data_ptr() if ws is not None else None, wbytes,
-              _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+              1 if causal else 0, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     return (out, lse) if return_lse else out
 
 

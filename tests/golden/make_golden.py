@@ -8,8 +8,9 @@ hardware primitives it cannot execute:
   * the inline PTX ``cvt.rn.satfinite.e2m1x2.f32`` (sageattention/nvfp4/_fp4_pack.py:38-54):
     per PTX semantics, round-to-nearest-even onto the e2m1 grid, saturating, first source
     operand in the high nibble;
-  * ``tl.dot_scaled`` on e2m1 operands with e4m3 scales (the block-scaled MMA): dequantise and
-    accumulate in fp32.
+  * ``tl.dot_scaled`` on e2m1 operands with e4m3 scales (the block-scaled MMA), and on e4m3
+    operands with e8m0 scales per 32 (the MXFP8 products of the ``fp8_rownorm`` backward):
+    dequantise and accumulate in fp32.
 
 A third override repairs a defect of the interpreter itself: its fp32 -> float8e4nv cast
 rounds half up and drops the mantissa carry (0.487 becomes 0.25), whereas the GPU lowering is
@@ -80,13 +81,20 @@ def _deq(nib, sc):
     return v * np.repeat(_e4m3_f32(sc), 16, axis=1)
 
 
+def _deq_mx8(q, sc):
+    """e4m3 bytes [R, K] with e8m0 scale bytes [R, K/32] -> fp32."""
+    v = torch.from_numpy(np.ascontiguousarray(q).astype(np.uint8)).view(torch.float8_e4m3fn).float().numpy()
+    return v * np.repeat(np.exp2(sc.astype(np.float32) - 127.0), 32, axis=1)
+
+
 def _dot_scaled(self, lhs, lhs_scale, lhs_format, rhs, rhs_scale, rhs_format, acc, fast_math,
                 lhs_k_pack, rhs_k_pack, out_dtype):
     fa = getattr(lhs_format, "value", lhs_format)
     fb = getattr(rhs_format, "value", rhs_format)
-    assert fa == "e2m1" and fb == "e2m1", "only NVFP4 x NVFP4 is emulated"
-    a = _deq(lhs.handle.data.view(np.uint8), lhs_scale.handle.data.view(np.uint8))
-    b = _deq(np.ascontiguousarray(rhs.handle.data.view(np.uint8).T), rhs_scale.handle.data.view(np.uint8))
+    assert fa == fb and fa in ("e2m1", "e4m3"), "only NVFP4 x NVFP4 and MXFP8 x MXFP8 are emulated"
+    deq = _deq if fa == "e2m1" else _deq_mx8
+    a = deq(lhs.handle.data.view(np.uint8), lhs_scale.handle.data.view(np.uint8))
+    b = deq(np.ascontiguousarray(rhs.handle.data.view(np.uint8).T), rhs_scale.handle.data.view(np.uint8))
     r = a.astype(np.float32) @ b.astype(np.float32).T
     if acc is not None:
         r = r + acc.handle.data
@@ -246,6 +254,42 @@ def main(ref_root: str):
         import traceback
         traceback.print_exc()
         print("backward fixtures NOT generated:", repr(e)[:200])
+
+    # ------------------------------------------------------------------ MXFP8 (fp8_rownorm)
+    # (after everything else, so the draws of the fixtures above keep their place in the stream)
+    import triton
+    global _pack_mx8
+    _pack_mx8 = flash._pack_mxfp8_along_k
+
+    @triton.jit
+    def mx8_probe(x_ptr, q_ptr, sc_ptr, ROWS: tl.constexpr, K: tl.constexpr):
+        r = tl.arange(0, ROWS)[:, None]
+        c = tl.arange(0, K)[None, :]
+        x = tl.load(x_ptr + r * K + c)
+        q, sc = _pack_mx8(x, ROWS, K)
+        tl.store(q_ptr + r * K + c, q)
+        cs = tl.arange(0, K // 32)[None, :]
+        tl.store(sc_ptr + r * (K // 32) + cs, sc)
+
+    rows, kk = 64, 128
+    xm = rn(rows, kk).float() * torch.exp2(torch.randint(-20, 12, (rows, 1), generator=g).float())
+    xm[3, :32] = 0.0                                   # an all-zero group
+    xm[5, 32:64] = torch.tensor([448.0, -448.0] * 16)  # amax exactly at the e4m3 maximum
+    xm[7, :] = (torch.randn(kk, generator=g) * 1e-12)
+    xm = xm.to(torch.bfloat16).float().contiguous()
+    qm = torch.zeros(rows, kk, dtype=torch.uint8)
+    scm = torch.zeros(rows, kk // 32, dtype=torch.uint8)
+    mx8_probe[(1,)](xm, qm, scm, ROWS=rows, K=kk)
+    np.savez_compressed(os.path.join(HERE, "mxfp8_pack.npz"), x=bf16_bits(xm.bfloat16()), q=u8(qm), sc=u8(scm))
+    print("mxfp8 pack ok")
+    try:
+        bwd.clear()
+        bwd_case("fp8rn_d128", 1, 2, 1, 192, 128, "fp8_rownorm")
+        np.savez_compressed(os.path.join(HERE, "backward_fp8.npz"), **bwd)
+    except Exception as e:
+        import traceback
+        traceback.print_exc()
+        print("fp8_rownorm backward fixture NOT generated:", repr(e)[:200])
 
 
 if __name__ == "__main__":

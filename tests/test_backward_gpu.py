@@ -81,14 +81,16 @@ def test_backward_matches_exact_gradients(z, h, hk, sq, skv, causal):
 
 
 @pytest.mark.parametrize("name,mode,floor", [("hp_d128", "bf16", 0.995), ("hp_varlen_d128", "bf16", 0.995),
-                                             ("rownorm_d128", "bf16", 0.95), ("rownorm_d128", "fp4_rownorm", 0.97)])
+                                             ("rownorm_d128", "bf16", 0.95), ("rownorm_d128", "fp4_rownorm", 0.97),
+                                             ("fp8rn_d128", "fp8_rownorm", 0.97), ("fp8rn_d128", "bf16", 0.97)])
 def test_backward_matches_reference_fixture(golden, name, mode, floor):
     """Gradients of the reference's own backward kernels on the same inputs (fp32 tensors holding
     bf16 values, so gradients come back in fp32).  The high-precision mode shares this build's
     algorithm (FP4 recompute of P, bf16 gradient GEMMs).  The reference's all-FP4 gradients carry
     their own quantisation noise: this build's all-FP4 kernels (other normalisation factors, same
-    operand precision) must agree with them to 0.97, its bf16 kernels to 0.95."""
-    g = golden("backward")
+    operand precision) must agree with them to 0.97, its bf16 kernels to 0.95.  `fp8rn_d128` holds the
+    gradients of the reference's MXFP8 (`fp8_rownorm`) backward."""
+    g = golden("backward_fp8" if name.startswith("fp8") else "backward")
     z, h, hk, s, d = g[name + "_meta"].tolist()
     q, k, v, do = (_bits_to_cuda(g[f"{name}_{t}"]).float() for t in ("q", "k", "v", "do"))
     cu = torch.from_numpy(g[name + "_cu"]).cuda() if name + "_cu" in g.files else None

@@ -127,11 +127,21 @@ def test_incremental_equals_one_shot_on_valid_region():
     assert np.all(c.vsc[:, :, ng:] == 0) and np.all(vsc[:, :, ng:] == 1)
 
 
+def test_mxfp8_pack_matches_reference(golden):
+    """The oracle's MXFP8 pack against the bytes and scale exponents the reference's own
+    `_pack_mxfp8_along_k` (flash.py:243-257) produced: random magnitudes over 2^-20 .. 2^12, an
+    all-zero group, a group whose maximum is exactly 448, and a row of 1e-12 values."""
+    g = golden("mxfp8_pack")
+    q, sc = O.pack_mxfp8(b2f(g["x"])[None])
+    assert np.array_equal(sc[0], g["sc"])
+    assert np.array_equal(q[0], g["q"])
+
+
 @pytest.mark.parametrize("name,floor", [("hp_d128", 0.985), ("hp_varlen_d128", 0.985),
-                                        ("rownorm_d128", 0.93)])
+                                        ("rownorm_d128", 0.93), ("fp8rn_d128", 0.93)])
 def test_reference_grads_close_to_exact_grads(golden, name, floor):
-    """The reference's own backward (HP and all-FP4) against analytic gradients."""
-    g = golden("backward")
+    """The reference's own backward (HP, all-FP4 and MXFP8) against analytic gradients."""
+    g = golden("backward_fp8" if name.startswith("fp8") else "backward")
     z, h, hk, s, d = g[name + "_meta"].tolist()
     cu = g[name + "_cu"] if name + "_cu" in g.files else None
     q, k, v, do = (b2f(g[f"{name}_{n}"]) for n in ("q", "k", "v", "do"))

@@ -291,3 +291,15 @@ def test_mxfp8_transposed_pack_matches_oracle(dtype, b, s, d, pad):
     ref = np.transpose(x.float().numpy(), (0, 2, 1))
     gmax = np.repeat(np.exp2(np_u8(sc).astype(np.float64) - 127.0) * 448.0, 32, axis=-1)[:, :, :s]
     assert np.all(np.abs(back - ref) <= gmax * 2.0 ** -4 + 1e-37)
+
+
+def test_mxfp8_pack_matches_reference_fixture(golden):
+    """The GPU MXFP8 pack against the bytes of the reference's own `_pack_mxfp8_along_k`
+    (tests/golden/mxfp8_pack.npz): rows of the fixture are packed along their 128 columns, which is
+    the along-S pack of the transposed tensor."""
+    from sageattention_b200.nvfp4 import flash
+    g = golden("mxfp8_pack")
+    x = torch.from_numpy(b2f(g["x"]))                       # [rows, K]
+    q, sc = flash._quant_mxfp8_t(x.t().contiguous()[None].to(torch.bfloat16).cuda(), x.shape[1])
+    assert np.array_equal(np_u8(sc)[0], g["sc"])
+    assert np.array_equal(np_u8(q)[0], g["q"])

@@ -93,19 +93,39 @@ __device__ __forceinline__ float div_by_scale(float x, float sf, float inv) {
   return copysignf(fmaf(r, inv, q), x);
 }
 
+// Two quotients at once with packed fp32x2 instructions (each lane IEEE round-to-nearest, so the
+// results are those of div_by_scale<false>): half the issue slots of the scalar form.
+__device__ __forceinline__ float2 div2_by_scale(float2 x, float2 nsf, float2 inv) {
+  const float2 q = __fmul2_rn(x, inv);
+  const float2 r = __ffma2_rn(q, nsf, x);          // x - q * sf, exact
+  const float2 y = __ffma2_rn(r, inv, q);
+  return make_float2(copysignf(y.x, x.x), copysignf(y.y, x.y));
+}
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Pack one group of 16 fp32 values: returns the scale byte, writes 8 nibble bytes to lo/hi.
 // Bit-exact with amax -> e4m3(clamp(amax / 6)) -> IEEE x / scale -> e2m1 RTNE.
 __device__ __forceinline__ uint8_t pack_group16(const float (&x)[16], uint32_t& lo, uint32_t& hi) {
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  for (int i = 0; i < 16; i += 2) amax = max3f(amax, fabsf(x[i]), fabsf(x[i + 1]));
   const uint8_t sb = scale_byte_from_amax(amax);
   const float sf = e4m3_to_f32(sb);
   const float inv = __frcp_rn(sf);
   float y[16];
   if (amax <= 1.0e30f) {   // the usual case: no quotient can overflow, skip the clamp
+    const float2 nsf2 = make_float2(-sf, -sf), inv2 = make_float2(inv, inv);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) y[i] = div_by_scale<false>(x[i], sf, inv);
+    for (int i = 0; i < 16; i += 2) {
+      const float2 q = div2_by_scale(make_float2(x[i], x[i + 1]), nsf2, inv2);
+      y[i] = q.x;
+      y[i + 1] = q.y;
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < 16; ++i) y[i] = div_by_scale<true>(x[i], sf, inv);

@@ -82,6 +82,63 @@ __device__ __forceinline__ void pack_rows_group(
   sc[b * ssb + r * ssr + g] = sb;
 }
 
+// 32 bytes with one 256-bit load (sm_100): a lane reads a whole 32-byte sector, so a warp whose
+// lanes read consecutive sectors asks L1 for every sector once.
+__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
+}
+
+// Four 16-groups per thread, 32 groups apart: in each of the four rounds the lanes of a warp take
+// consecutive groups, so loads (one or two 256-bit loads per lane), nibble stores (8 bytes per lane)
+// and scale stores (1 byte per lane) of a round cover consecutive memory, and the four rounds' loads
+// are all issued before the first group is packed.  Needs whole groups (no tail), 32-byte aligned
+// rows and a power-of-two group count per row.  `first` = first group of this thread's warp.
+template <typename T>
+__device__ __forceinline__ void pack_rows_quad(const T* __restrict__ x, int ng_log2, int64_t per_batch,
+                                               int64_t sxb, int64_t sxr, uint8_t* __restrict__ nib, int64_t snb,
+                                               int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr,
+                                               int64_t first, int64_t b) {
+  constexpr int kW = 16 * sizeof(T) / 4;          // 32-bit words per group
+  const int lane = threadIdx.x & 31;
+  uint32_t raw[4][kW];
+  int64_t r[4];
+  int g[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t gid = first + i * 32 + lane;
+    const int64_t gc = gid < per_batch ? gid : per_batch - 1;    // the tail re-reads the last group
+    r[i] = gc >> ng_log2;
+    g[i] = (int)(gc - (r[i] << ng_log2));
+    const T* p = x + b * sxb + r[i] * sxr + g[i] * 16;
+#pragma unroll
+    for (int j = 0; j < kW / 8; ++j) ldg256(reinterpret_cast<const uint32_t*>(p) + 8 * j, *reinterpret_cast<uint32_t(*)[8]>(&raw[i][8 * j]));
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float v[16];
+    const T* e = reinterpret_cast<const T*>(raw[i]);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = to_f32<T>(e[j]);
+    uint32_t lo, hi;
+    const uint8_t sb = pack_group16(v, lo, hi);
+    if (first + i * 32 + lane < per_batch) {
+      *reinterpret_cast<uint2*>(nib + b * snb + r[i] * snr + g[i] * 8) = make_uint2(lo, hi);
+      sc[b * ssb + r[i] * ssr + g[i]] = sb;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pack_rows_quad_kernel(
+    const T* __restrict__ x, int ng_log2, int64_t per_batch, int64_t sxb, int64_t sxr,
+    uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb, int64_t ssr) {
+  const int64_t first = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 128;
+  if (first >= per_batch) return;
+  pack_rows_quad<T>(x, ng_log2, per_batch, sxb, sxr, nib, snb, snr, sc, ssb, ssr, first, blockIdx.y);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) pack_rows_kernel(
     const T* __restrict__ x, int64_t R, int64_t k_read, int64_t ngroups, int ngroups_log2,
@@ -333,6 +390,7 @@ struct QkvArgs {
   int64_t rq, rk;            // rows of Q / K per batch entry
   int64_t bq, bk;            // batch entries of Q / K (= V)
   int d, ngroups_log2, vec_q, vec_k, vec_v;
+  int quad_q, quad_k;        // Q / K packed four groups per thread (32-byte aligned rows)
   int64_t sqb, sqr, skb, skr, svb, svk;   // element strides
   int64_t bpq, bpk;          // 256-thread blocks per batch entry
   int64_t nbq, nbk;          // blocks of the Q and K parts
@@ -352,6 +410,17 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const QkvArgs a) {
     const int64_t b = w / bp;
     const int64_t gid = (w - b * bp) * 256 + threadIdx.x;
     const int64_t rows = is_q ? a.rq : a.rk;
+    if (is_q ? a.quad_q : a.quad_k) {
+      const int64_t first = ((w - b * bp) * 8 + (threadIdx.x >> 5)) * 128;    // first group of this warp
+      if (first >= rows * ngroups) return;
+      if (is_q)
+        pack_rows_quad<T>(static_cast<const T*>(a.q), a.ngroups_log2, rows * ngroups, a.sqb, a.sqr, a.qnv,
+                          rows * (a.d / 2), a.d / 2, a.qsc, rows * ngroups, ngroups, first, b);
+      else
+        pack_rows_quad<T>(static_cast<const T*>(a.k), a.ngroups_log2, rows * ngroups, a.skb, a.skr, a.knv,
+                          rows * (a.d / 2), a.d / 2, a.ksc, rows * ngroups, ngroups, first, b);
+      return;
+    }
     if (gid >= rows * ngroups) return;
     if (is_q)
       pack_rows_group<T>(static_cast<const T*>(a.q), a.d, ngroups, a.ngroups_log2, a.sqb, a.sqr, a.qnv,
@@ -412,6 +481,14 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
     NVFP4_REQUIRE(blocks < (1LL << 31), "nvfp4_pack: tensor too large");
     int lg = -1;
     if ((ngroups & (ngroups - 1)) == 0) { lg = 0; while ((1LL << lg) < ngroups) ++lg; }
+    // whole groups, 32-byte aligned rows, a power-of-two group count: four groups per thread
+    constexpr int64_t kVec32 = 32 / sizeof(T);
+    if (lg >= 0 && k_read >= k_pad && (reinterpret_cast<uintptr_t>(x) & 31) == 0 && sxb % kVec32 == 0 &&
+        sxr % kVec32 == 0 && (reinterpret_cast<uintptr_t>(nib) & 7) == 0 && snb % 8 == 0 && snr % 8 == 0) {
+      dim3 qgrid((unsigned)((per_batch + 1023) / 1024), (unsigned)B);
+      pack_rows_quad_kernel<T><<<qgrid, 256, 0, st>>>(x, lg, per_batch, sxb, sxr, nib, snb, snr, sc, ssb, ssr);
+      return launch_result("nvfp4_pack(rows)");
+    }
     dim3 grid((unsigned)blocks, (unsigned)B);
     pack_rows_kernel<T><<<grid, 256, 0, st>>>(x, R, k_read, ngroups, lg, per_batch, sxb, sxr, nib, snb,
                                               snr, sc, ssb, ssr, vec);
@@ -486,6 +563,18 @@ int pack_qkv_launch(QkvArgs a, cudaStream_t st) {
   a.vec_q = vec_ok(a.q, a.sqb, a.sqr);
   a.vec_k = vec_ok(a.k, a.skb, a.skr);
   a.vec_v = vec_ok(a.v, a.svb, a.svk);
+  // four groups per thread (a block covers 1024 groups) where the rows are 32-byte aligned
+  constexpr int64_t kVec32 = 32 / sizeof(T);
+  auto quad_ok = [&](const void* p, int64_t s0, int64_t s1) {
+    return (int)((reinterpret_cast<uintptr_t>(p) & 31) == 0 && s0 % kVec32 == 0 && s1 % kVec32 == 0);
+  };
+  a.quad_q = quad_ok(a.q, a.sqb, a.sqr);
+  a.quad_k = quad_ok(a.k, a.skb, a.skr);
+  const int64_t ng = a.d / 16;
+  a.bpq = (a.rq * ng + (a.quad_q ? 1023 : 255)) / (a.quad_q ? 1024 : 256);
+  a.bpk = (a.rk * ng + (a.quad_k ? 1023 : 255)) / (a.quad_k ? 1024 : 256);
+  a.nbq = a.bpq * a.bq;
+  a.nbk = a.bpk * a.bk;
   const int64_t total = a.nbq + a.nbk + a.bk * a.tx * a.ty;
   NVFP4_REQUIRE(total < (1LL << 31), "nvfp4_pack_qkv: tensors too large");
   pack_qkv_kernel<T><<<(unsigned)total, 256, 0, st>>>(a);
@@ -560,12 +649,11 @@ extern "C" int nvfp4_pack_qkv(const void* q, const void* k, const void* v, int d
   while ((1 << lg) < d / 16) ++lg;
   a.ngroups_log2 = lg;
   a.sqb = sqb; a.sqr = sqr; a.skb = skb; a.skr = skr; a.svb = svb; a.svk = svk;
-  a.bpq = (s_q * (d / 16) + 255) / 256; a.bpk = (s_kv * (d / 16) + 255) / 256;
-  a.nbq = a.bpq * bq; a.nbk = a.bpk * bk;
+  a.bpq = a.bpk = a.nbq = a.nbk = 0;   // set by the launch, which knows the per-dtype alignment
   a.s_kv = s_kv; a.s_pad = s_pad;
   a.tx = (s_pad + kColsKeys - 1) / kColsKeys; a.ty = (d + kColsRows - 1) / kColsRows;
   a.qnv = qnv; a.qsc = qsc; a.knv = knv; a.ksc = ksc; a.vnv = vnv; a.vsc = vsc;
-  a.vec_q = a.vec_k = a.vec_v = 0;
+  a.vec_q = a.vec_k = a.vec_v = a.quad_q = a.quad_k = 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case NVFP4_DT_BF16: return pack_qkv_launch<__nv_bfloat16>(a, st);

@@ -205,34 +205,151 @@ __global__ void __launch_bounds__(256) rope_pack_rows_kernel(
 // ---------------------------------------------------------------- rows contiguous (V^T)
 constexpr int kColsKeys = 128;  // contraction extent of a tile
 constexpr int kColsRows = 64;   // row (head-dim) extent of a tile
+constexpr int kColsRun = 4;     // consecutive key tiles one block walks (the next tile's loads fly under the pack)
 
-struct ColsSmem {
-  float tile[kColsKeys][kColsRows + 1];
-  __align__(16) uint8_t onib[kColsRows][kColsKeys / 2];
+// The input tile: fp32 inputs as floats (one padding column); 16-bit inputs as loaded, two rows per
+// 32-bit word, 144-byte key rows (16-byte aligned, and a quarter warp's 16-byte accesses to
+// consecutive keys fall on different banks).
+template <int kElemBytes> struct ColsTile { float tile[kColsKeys][kColsRows + 1]; };
+template <> struct ColsTile<2> { __align__(16) uint32_t raw[kColsKeys][kColsRows / 2 + 4]; };
+
+template <typename T>
+struct ColsSmem : ColsTile<sizeof(T)> {
+  __align__(16) uint8_t onib[kColsRows][kColsKeys / 2 + 16];
   __align__(8) uint8_t osc[kColsRows][kColsKeys / 16];
 };
 
-// One 128-key x 64-row tile (tile coordinates bx, by of batch entry b).  With kDual the same tile
+// two 16-bit elements of one word -> fp32 (element 0 in the low half)
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t w, float& a, float& b);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& a, float& b) {
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xFFFF0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& a, float& b) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  a = f.x;
+  b = f.y;
+}
+template <> __device__ __forceinline__ void unpack2<float>(uint32_t, float&, float&) {}
+
+// `nt` consecutive 128-key x 64-row tiles (tile coordinates bx .. bx + nt - 1, by of batch entry b);
+// for 16-bit inputs the global loads of the next tile are issued before the current one is packed.
+// With kDual the same tile
 // also yields the pack along the contiguous axis (rows of 16 consecutive elements of each key):
 // dnib [B, keys, R/2], dsc [B, keys, R/16], from the one read of x.  sr_flags (kDual only): bit 0
 // rounds the contiguous-axis pack stochastically, bit 1 the strided-axis pack; the random bits of
 // an element depend only on (seed, which pack, its position in x).
 template <typename T, bool kDual>
 __device__ __forceinline__ void pack_cols_tile(
-    ColsSmem& sm, const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
+    ColsSmem<T>& sm, const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
-    int64_t ssr, int vec_in, int64_t bx, int64_t by, int64_t b, uint8_t* __restrict__ dnib, int64_t dnb,
+    int64_t ssr, int vec_in, int64_t bx, int nt, int64_t by, int64_t b, uint8_t* __restrict__ dnib, int64_t dnb,
     int64_t dnr, uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax,
     int sr_flags = 0, uint32_t seed = 0) {
   // exact division by a power of two (1 when no pre-scale is asked for)
   const float pre = (kDual && prescale_amax != nullptr) ? __frcp_rn(pow2_ceil(*prescale_amax)) : 1.0f;
-  auto& tile = sm.tile;
   auto& onib = sm.onib;
   auto& osc = sm.osc;
   const int tid = threadIdx.x;
-  const int64_t k0 = bx * kColsKeys;
   const int64_t r0 = by * kColsRows;
   const T* xb = x + b * sxb;
+  // 16-bit inputs: 8 threads x 8 elements cover 64 rows of one key, 32 keys per pass, kept in
+  // registers as loaded until the shared tile is free
+  uint4 wreg[kColsKeys / 32];
+  auto load16 = [&](int64_t k0) {
+#pragma unroll
+    for (int pass = 0; pass < kColsKeys / 32; ++pass) {
+      const int key = pass * 32 + (tid >> 3);
+      const int rc = (tid & 7) * 8;
+      const int64_t kk = k0 + key;
+      int valid = 0;
+      if (kk < k_read) {
+        const int64_t left = R - (r0 + rc);
+        valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
+      }
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      const T* src = xb + kk * sxk + r0 + rc;
+      if (valid >= 8 && vec_in) {
+        w = __ldg(reinterpret_cast<const uint4*>(src));
+      } else if (valid > 0) {
+        uint16_t e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = i < valid ? *reinterpret_cast<const uint16_t*>(src + i) : (uint16_t)0;
+        w = make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16), e[4] | ((uint32_t)e[5] << 16),
+                       e[6] | ((uint32_t)e[7] << 16));
+      }
+      wreg[pass] = w;
+    }
+  };
+  if constexpr (sizeof(T) == 2) load16(bx * kColsKeys);
+  // Shared-memory reuse across the tiles of a run needs no extra barrier: the input tile is rewritten
+  // after the second barrier of the tile before (all its readers are past it), the output staging is
+  // rewritten after the first barrier of this tile (its readers, the store phase, are before it).
+  for (int ti = 0; ti < nt; ++ti) {
+  const int64_t k0 = (bx + ti) * kColsKeys;
+  if constexpr (sizeof(T) == 2) {
+    auto& raw = sm.raw;
+    // one 16-byte shared store per 16-byte load; then the next tile's loads are issued
+#pragma unroll
+    for (int pass = 0; pass < kColsKeys / 32; ++pass)
+      *reinterpret_cast<uint4*>(&raw[pass * 32 + (tid >> 3)][(tid & 7) * 4]) = wreg[pass];
+    if (ti + 1 < nt) load16(k0 + kColsKeys);
+    __syncthreads();
+    if constexpr (kDual) {
+      // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2);
+      // the 16 elements of a group are two 16-byte shared loads
+#pragma unroll
+      for (int it = 0; it < 2; ++it) {
+        const int key = tid & 127;
+        const int g = (tid >> 7) + it * 2;
+        if (k0 + key < k_read && r0 + g * 16 < R) {
+          const uint4 w0 = *reinterpret_cast<const uint4*>(&raw[key][g * 8]);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(&raw[key][g * 8 + 4]);
+          const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            unpack2<T>(ww[j], v[2 * j], v[2 * j + 1]);
+            v[2 * j] *= pre;
+            v[2 * j + 1] *= pre;
+          }
+          uint32_t lo, hi;
+          const uint8_t sb = (sr_flags & 1)
+                                 ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * k_read + k0 + key) * 2u,
+                                                   (uint32_t)(r0 / 4 + g * 4))
+                                 : pack_group16(v, lo, hi);
+          *reinterpret_cast<uint2*>(dnib + b * dnb + (k0 + key) * dnr + (r0 + g * 16) / 2) = make_uint2(lo, hi);
+          dsc[b * dsb + (k0 + key) * dsr + (r0 + g * 16) / 16] = sb;
+        }
+      }
+    }
+    // quantise along the keys: thread -> (rows 2 (tid % 32) and the next, 16-key group tid / 32); one
+    // 32-bit shared load brings a key's elements of both rows
+    {
+      const int rp = tid & 31, g = tid >> 5;
+      float v0[16], v1[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        unpack2<T>(raw[g * 16 + j][rp], v0[j], v1[j]);
+        if (kDual) {
+          v0[j] *= pre;
+          v1[j] *= pre;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = 2 * rp + h;
+        uint32_t lo, hi;
+        const uint8_t sb = (kDual && (sr_flags & 2))
+                               ? pack_group16_sr(h ? v1 : v0, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
+                                                 (uint32_t)(k0 / 4 + g * 4))
+                               : pack_group16(h ? v1 : v0, lo, hi);
+        *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
+        osc[row][g] = sb;
+      }
+    }
+  } else {
+  auto& tile = sm.tile;
   // load: 8 threads x 8 elements cover 64 rows of one key; 32 keys per pass
 #pragma unroll
   for (int pass = 0; pass < kColsKeys / 32; ++pass) {
@@ -291,6 +408,7 @@ __device__ __forceinline__ void pack_cols_tile(
     *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
     osc[row][g] = sb;
   }
+  }
   __syncthreads();
   // store: groups of this tile that exist in the output
   const int64_t gleft = (k_pad - k0) / 16;
@@ -316,18 +434,21 @@ __device__ __forceinline__ void pack_cols_tile(
       for (int i = 0; i < ng; ++i) ps[i] = osc[tid][i];
     }
   }
+  }  // tiles of the run
 }
 
 template <typename T, bool kDual>
-__global__ void __launch_bounds__(256) pack_cols_kernel(
+__global__ void __launch_bounds__(256, 3) pack_cols_kernel(
     const T* __restrict__ x, int64_t R, int64_t k_read, int64_t k_pad, int64_t sxb, int64_t sxk,
     uint8_t* __restrict__ nib, int64_t snb, int64_t snr, uint8_t* __restrict__ sc, int64_t ssb,
     int64_t ssr, int vec_in, uint8_t* __restrict__ dnib, int64_t dnb, int64_t dnr,
     uint8_t* __restrict__ dsc, int64_t dsb, int64_t dsr, const float* __restrict__ prescale_amax,
     int sr_flags, uint32_t seed) {
-  __shared__ ColsSmem sm;
-  pack_cols_tile<T, kDual>(sm, x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc, ssb, ssr, vec_in, blockIdx.x,
-                           blockIdx.y, blockIdx.z, dnib, dnb, dnr, dsc, dsb, dsr, prescale_amax, sr_flags, seed);
+  __shared__ ColsSmem<T> sm;
+  const int64_t tx = (k_pad + kColsKeys - 1) / kColsKeys, bx = (int64_t)blockIdx.x * kColsRun;
+  pack_cols_tile<T, kDual>(sm, x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc, ssb, ssr, vec_in, bx,
+                           (int)(tx - bx < kColsRun ? tx - bx : kColsRun), blockIdx.y, blockIdx.z, dnib, dnb, dnr,
+                           dsc, dsb, dsr, prescale_amax, sr_flags, seed);
 }
 
 // ---------------------------------------------------------------- MXFP8 along the strided axis
@@ -399,8 +520,8 @@ struct QkvArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) pack_qkv_kernel(const QkvArgs a) {
-  __shared__ ColsSmem sm;
+__global__ void __launch_bounds__(256, 3) pack_qkv_kernel(const QkvArgs a) {
+  __shared__ ColsSmem<T> sm;
   const int64_t v = blockIdx.x;
   const int ngroups = a.d >> 4;
   if (v < a.nbq + a.nbk) {
@@ -431,13 +552,15 @@ __global__ void __launch_bounds__(256) pack_qkv_kernel(const QkvArgs a) {
     return;
   }
   const int64_t w = v - a.nbq - a.nbk;
-  const int64_t per = a.tx * a.ty;
+  const int64_t runs = (a.tx + kColsRun - 1) / kColsRun;      // runs of key tiles per row of tiles
+  const int64_t per = runs * a.ty;
   const int64_t b = w / per;
   const int64_t rem = w - b * per;
-  const int64_t by = rem / a.tx, bx = rem - by * a.tx;
+  const int64_t by = rem / runs, bx = (rem - by * runs) * kColsRun;
   pack_cols_tile<T, false>(sm, static_cast<const T*>(a.v), a.d, a.s_kv, a.s_pad, a.svb, a.svk, a.vnv,
                            (int64_t)a.d * (a.s_pad / 2), a.s_pad / 2, a.vsc, (int64_t)a.d * (a.s_pad / 16),
-                           a.s_pad / 16, a.vec_v, bx, by, b, nullptr, 0, 0, nullptr, 0, 0, nullptr);
+                           a.s_pad / 16, a.vec_v, bx, (int)(a.tx - bx < kColsRun ? a.tx - bx : kColsRun), by, b,
+                           nullptr, 0, 0, nullptr, 0, 0, nullptr);
 }
 
 // ---------------------------------------------------------------- any strides (scalar)
@@ -496,7 +619,7 @@ int pack_dispatch(const T* x, int64_t B, int64_t R, int64_t k_read, int64_t k_pa
   }
   if (sxr == 1 && B < 65536 && (R + kColsRows - 1) / kColsRows < 65536) {
     const int vec = base_ok && sxb % kVecElems == 0 && sxk % kVecElems == 0;
-    dim3 grid((unsigned)((k_pad + kColsKeys - 1) / kColsKeys),
+    dim3 grid((unsigned)((k_pad + kColsKeys * kColsRun - 1) / (kColsKeys * kColsRun)),
               (unsigned)((R + kColsRows - 1) / kColsRows), (unsigned)B);
     pack_cols_kernel<T, false><<<grid, 256, 0, st>>>(x, R, k_read, k_pad, sxb, sxk, nib, snb, snr, sc,
                                                      ssb, ssr, vec, nullptr, 0, 0, nullptr, 0, 0, nullptr, 0, 0u);
@@ -545,8 +668,8 @@ int pack_dual_launch(const void* x, int64_t B, int64_t S, int d, int64_t s_pad, 
                      uint8_t* tnib, uint8_t* tsc, cudaStream_t st) {
   constexpr int64_t kVecElems = 16 / sizeof(T);
   const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && sxb % kVecElems == 0 && sxs % kVecElems == 0;
-  dim3 grid((unsigned)((s_pad + kColsKeys - 1) / kColsKeys), (unsigned)((d + kColsRows - 1) / kColsRows),
-            (unsigned)B);
+  dim3 grid((unsigned)((s_pad + kColsKeys * kColsRun - 1) / (kColsKeys * kColsRun)),
+            (unsigned)((d + kColsRows - 1) / kColsRows), (unsigned)B);
   pack_cols_kernel<T, true><<<grid, 256, 0, st>>>(
       static_cast<const T*>(x), d, S, s_pad, sxb, sxs, tnib, (int64_t)d * (s_pad / 2), s_pad / 2, tsc,
       (int64_t)d * (s_pad / 16), s_pad / 16, vec, dnib, S * (int64_t)(d / 2), d / 2, dsc, S * (int64_t)(d / 16),
@@ -575,7 +698,7 @@ int pack_qkv_launch(QkvArgs a, cudaStream_t st) {
   a.bpk = (a.rk * ng + (a.quad_k ? 1023 : 255)) / (a.quad_k ? 1024 : 256);
   a.nbq = a.bpq * a.bq;
   a.nbk = a.bpk * a.bk;
-  const int64_t total = a.nbq + a.nbk + a.bk * a.tx * a.ty;
+  const int64_t total = a.nbq + a.nbk + a.bk * ((a.tx + kColsRun - 1) / kColsRun) * a.ty;
   NVFP4_REQUIRE(total < (1LL << 31), "nvfp4_pack_qkv: tensors too large");
   pack_qkv_kernel<T><<<(unsigned)total, 256, 0, st>>>(a);
   return launch_result("nvfp4_pack_qkv");

@@ -39,53 +39,125 @@ constexpr int kBwdPrefetch = 8;   // stage loads are prefetched into L2 this man
 // ------------------------------------------------------------------------------------------
 // Pre-pass over rows of x [B1, B2, S, D] (strided, unit stride along D): optional contiguous
 // bf16 copy xc [B1*B2, S, D] and optional delta [B1*B2, S] = rowsum(x o y).  Half a warp per row,
-// 16 bytes per lane and load, two rows per warp in flight.
+// 16 bytes per lane and load; with D = 128 and aligned rows a warp has eight rows in flight.
 // ------------------------------------------------------------------------------------------
+// eight consecutive elements from a 16-byte aligned address: the loads only (no alignment test, no
+// conversion), so that a thread can issue several before it uses the first
+template <typename T> struct PrepRaw { uint4 q[sizeof(T) / 2]; };
+template <typename T>
+__device__ __forceinline__ void prep_load(const T* src, PrepRaw<T>& r) {
+#pragma unroll
+  for (int i = 0; i < (int)sizeof(T) / 2; ++i) r.q[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+}
+template <typename T>
+__device__ __forceinline__ void prep_unpack(const PrepRaw<T>& r, float (&v)[8]) {
+  const T* t = reinterpret_cast<const T*>(&r);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = to_f32<T>(t[e]);
+}
+
+constexpr int kPrepRows = 4;   // rows per half-warp and trip on the aligned path
+
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ x, int64_t sxb1, int64_t sxb2,
                                                        int64_t sxs, int nb2, const T* __restrict__ y,
                                                        int64_t syb1, int64_t syb2, int64_t sys, int S, int D,
                                                        int64_t rows, __nv_bfloat16* __restrict__ xc,
-                                                       float* __restrict__ delta, float* __restrict__ amax) {
+                                                       float* __restrict__ delta, float* __restrict__ amax,
+                                                       int aligned) {
   const int lane = threadIdx.x & 31, l16 = lane & 15;
-  const int64_t base0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
-  const int64_t nhw = (int64_t)gridDim.x * 16;
   float vmax = 0.0f;   // largest |x| this thread has seen (non-negative floats order like their bit patterns)
-  for (int64_t base = base0; base < rows; base += nhw) {    // both half-warps take every trip (shuffles)
-    const int64_t row0 = base + (lane >> 4);
-    const bool live = row0 < rows;
-    const int64_t row = live ? row0 : rows - 1;
-    const int64_t b = row / S;
-    const int s = (int)(row - b * S);
-    const int64_t b1 = b / nb2, b2 = b - b1 * nb2;
-    const T* xr = x + b1 * sxb1 + b2 * sxb2 + (int64_t)s * sxs;
-    const T* yr = y ? (y + b1 * syb1 + b2 * syb2 + (int64_t)s * sys) : nullptr;
-    float acc = 0.0f;
-    for (int c = l16 * 8; c < D; c += 128) {
-      float v[8], w8[8];
-      load8<T>(xr + c, v);
-      if (amax != nullptr && live) {
+  // 32-bit divisions (the host keeps rows below 2^31): a 64-bit divide costs more instructions than
+  // everything else a thread does for its 16 bytes
+  auto row_ptrs = [&](int64_t row, const T*& xr, const T*& yr) {
+    const uint32_t b = (uint32_t)row / (uint32_t)S;
+    const int s = (int)((uint32_t)row - b * (uint32_t)S);
+    const uint32_t b1 = b / (uint32_t)nb2, b2 = b - b1 * (uint32_t)nb2;
+    xr = x + (int64_t)b1 * sxb1 + (int64_t)b2 * sxb2 + (int64_t)s * sxs;
+    yr = y ? (y + (int64_t)b1 * syb1 + (int64_t)b2 * syb2 + (int64_t)s * sys) : nullptr;
+  };
+  if (aligned && D == 128) {
+    // every row is 16 lanes x 16 bytes, all addresses 16-byte aligned: a warp takes 2 * kPrepRows
+    // rows per trip and issues all their loads (x and y) before it reduces the first
+    const int64_t base0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * (2 * kPrepRows);
+    const int64_t step = (int64_t)gridDim.x * 16 * kPrepRows;
+    for (int64_t base = base0; base < rows; base += step) {
+      int64_t row[kPrepRows];
+      bool live[kPrepRows];
+      PrepRaw<T> rx[kPrepRows], ry[kPrepRows];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
+      for (int j = 0; j < kPrepRows; ++j) {
+        const int64_t row0 = base + 2 * j + (lane >> 4);
+        live[j] = row0 < rows;
+        row[j] = live[j] ? row0 : rows - 1;
+        const T *xr, *yr;
+        row_ptrs(row[j], xr, yr);
+        prep_load<T>(xr + l16 * 8, rx[j]);
+        if (y) prep_load<T>(yr + l16 * 8, ry[j]);
       }
-      if (yr) {
-        load8<T>(yr + c, w8);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc = fmaf(v[e], w8[e], acc);
-      }
-      if (xc && live) {
-        uint4 w;
-        w.x = pack_bf16x2(v[0], v[1]);
-        w.y = pack_bf16x2(v[2], v[3]);
-        w.z = pack_bf16x2(v[4], v[5]);
-        w.w = pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(xc + row * D + c) = w;
+      for (int j = 0; j < kPrepRows; ++j) {
+        float v[8], w8[8];
+        prep_unpack<T>(rx[j], v);
+        if (amax != nullptr && live[j]) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
+        }
+        if (xc && live[j]) {
+          uint4 w;
+          w.x = pack_bf16x2(v[0], v[1]);
+          w.y = pack_bf16x2(v[2], v[3]);
+          w.z = pack_bf16x2(v[4], v[5]);
+          w.w = pack_bf16x2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(xc + row[j] * D + l16 * 8) = w;
+        }
+        if (delta) {
+          float acc = 0.0f;
+          prep_unpack<T>(ry[j], w8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(v[e], w8[e], acc);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+          if (l16 == 0 && live[j]) delta[row[j]] = acc;
+        }
       }
     }
-    if (delta) {
+  } else {
+    const int64_t base0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
+    const int64_t nhw = (int64_t)gridDim.x * 16;
+    for (int64_t base = base0; base < rows; base += nhw) {    // both half-warps take every trip (shuffles)
+      const int64_t row0 = base + (lane >> 4);
+      const bool live = row0 < rows;
+      const int64_t row = live ? row0 : rows - 1;
+      const T *xr, *yr;
+      row_ptrs(row, xr, yr);
+      float acc = 0.0f;
+      for (int c = l16 * 8; c < D; c += 128) {
+        float v[8], w8[8];
+        load8<T>(xr + c, v);
+        if (amax != nullptr && live) {
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (l16 == 0 && live) delta[row] = acc;
+          for (int e = 0; e < 8; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
+        }
+        if (yr) {
+          load8<T>(yr + c, w8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc = fmaf(v[e], w8[e], acc);
+        }
+        if (xc && live) {
+          uint4 w;
+          w.x = pack_bf16x2(v[0], v[1]);
+          w.y = pack_bf16x2(v[2], v[3]);
+          w.z = pack_bf16x2(v[4], v[5]);
+          w.w = pack_bf16x2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(xc + row * D + c) = w;
+        }
+      }
+      if (delta) {
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (l16 == 0 && live) delta[row] = acc;
+      }
     }
   }
   if (amax != nullptr) {
@@ -808,10 +880,18 @@ int prep_launch(const void* x, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t 
                 int64_t syb1, int64_t syb2, int64_t sys, int S, int D, __nv_bfloat16* xc, float* delta,
                 float* amax, cudaStream_t st) {
   const int64_t rows = nb1 * nb2 * S;
-  const int64_t blocks = (rows + 15) / 16;
+  if (rows >= (1LL << 31)) return fail(-1, "nvfp4_bwd_prep: more than 2^31 rows");
+  auto al = [](const void* p, int64_t a, int64_t b, int64_t c) {
+    return p == nullptr || ((reinterpret_cast<uintptr_t>(p) & 15) == 0 && (a * (int64_t)sizeof(T)) % 16 == 0 &&
+                            (b * (int64_t)sizeof(T)) % 16 == 0 && (c * (int64_t)sizeof(T)) % 16 == 0);
+  };
+  const int aligned = al(x, sxb1, sxb2, sxs) && al(y, syb1, syb2, sys) && D == 128;
+  const int64_t per_block = aligned ? 16 * kPrepRows : 16;
+  const int64_t blocks = (rows + per_block - 1) / per_block;
   const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
   bwd_prep_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(x), sxb1, sxb2, sxs, (int)nb2,
-                                           static_cast<const T*>(y), syb1, syb2, sys, S, D, rows, xc, delta, amax);
+                                           static_cast<const T*>(y), syb1, syb2, sys, S, D, rows, xc, delta, amax,
+                                           aligned);
   return launch_result("nvfp4_bwd_prep");
 }
 

@@ -257,6 +257,14 @@ __device__ __forceinline__ void pack_cols_tile(
   // registers as loaded until the shared tile is free
   uint4 wreg[kColsKeys / 32];
   auto load16 = [&](int64_t k0) {
+    if (vec_in && k0 + kColsKeys <= k_read && r0 + kColsRows <= R) {
+      // interior tile: four unconditional 16-byte loads, all in flight together
+      const T* src = xb + (k0 + (tid >> 3)) * sxk + r0 + (tid & 7) * 8;
+#pragma unroll
+      for (int pass = 0; pass < kColsKeys / 32; ++pass)
+        wreg[pass] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)pass * 32 * sxk));
+      return;
+    }
 #pragma unroll
     for (int pass = 0; pass < kColsKeys / 32; ++pass) {
       const int key = pass * 32 + (tid >> 3);

@@ -63,6 +63,16 @@ def test_strided_views_and_zshd_layout():
     nib, sc = _nvfp4()._quant_nvfp4(flat)
     onib, osc = O.pack(xf.reshape(-1)[1: 1 + 4 * 128].reshape(1, 4, 128))
     assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+    # a base that is 16-byte but not 32-byte aligned: 128-bit loads, one group per thread
+    flat = x.reshape(-1)[8: 8 + 40 * 128].reshape(1, 40, 128)
+    nib, sc = _nvfp4()._quant_nvfp4(flat)
+    onib, osc = O.pack(xf.reshape(-1)[8: 8 + 40 * 128].reshape(1, 40, 128))
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
+    # 32-byte aligned rows with a row stride larger than the row (four groups per thread, strided)
+    wide = x.reshape(-1)[: 64 * 256].reshape(1, 64, 256)[:, :, :128]
+    nib, sc = _nvfp4()._quant_nvfp4(wide)
+    onib, osc = O.pack(xf.reshape(-1)[: 64 * 256].reshape(1, 64, 256)[:, :, :128])
+    assert np.array_equal(np_u8(nib), onib) and np.array_equal(np_u8(sc), osc)
 
 
 def test_adversarial_values():

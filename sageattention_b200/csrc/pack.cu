@@ -473,25 +473,50 @@ __global__ void __launch_bounds__(256) pack_mx8_cols_kernel(
   const int tid = threadIdx.x;
   const int64_t k0 = (int64_t)blockIdx.x * kColsKeys, r0 = (int64_t)blockIdx.y * kColsRows, b = blockIdx.z;
   const T* xb = x + b * sxb;
+  bool loaded = false;
+  if constexpr (sizeof(T) == 2) {
+    if (vec_in && k0 + kColsKeys <= k_read && r0 + kColsRows <= R) {
+      // interior tile: four unconditional 16-byte loads, all in flight together
+      const T* src = xb + (k0 + (tid >> 3)) * sxk + r0 + (tid & 7) * 8;
+      uint4 w[kColsKeys / 32];
 #pragma unroll
-  for (int pass = 0; pass < kColsKeys / 32; ++pass) {
-    const int key = pass * 32 + (tid >> 3);
-    const int rc = (tid & 7) * 8;
-    float v[8];
-    const int64_t kk = k0 + key;
-    int valid = 0;
-    if (kk < k_read) {
-      const int64_t left = R - (r0 + rc);
-      valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
+      for (int pass = 0; pass < kColsKeys / 32; ++pass)
+        w[pass] = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)pass * 32 * sxk));
+#pragma unroll
+      for (int pass = 0; pass < kColsKeys / 32; ++pass) {
+        const uint32_t ww[4] = {w[pass].x, w[pass].y, w[pass].z, w[pass].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float a, c;
+          unpack2<T>(ww[i], a, c);
+          tile[pass * 32 + (tid >> 3)][(tid & 7) * 8 + 2 * i] = a * pre;
+          tile[pass * 32 + (tid >> 3)][(tid & 7) * 8 + 2 * i + 1] = c * pre;
+        }
+      }
+      loaded = true;
     }
-    if (valid > 0) {
-      load8<T>(xb + kk * sxk + r0 + rc, vec_in, valid, v);
-    } else {
+  }
+  if (!loaded) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    for (int pass = 0; pass < kColsKeys / 32; ++pass) {
+      const int key = pass * 32 + (tid >> 3);
+      const int rc = (tid & 7) * 8;
+      float v[8];
+      const int64_t kk = k0 + key;
+      int valid = 0;
+      if (kk < k_read) {
+        const int64_t left = R - (r0 + rc);
+        valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
+      }
+      if (valid > 0) {
+        load8<T>(xb + kk * sxk + r0 + rc, vec_in, valid, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tile[key][rc + i] = v[i] * pre;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tile[key][rc + i] = v[i] * pre;
   }
   __syncthreads();
   const int row = tid & 63, g = tid >> 6;          // 32-token group g of row `row`

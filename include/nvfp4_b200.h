@@ -302,7 +302,7 @@ int nvfp4_fwd(const uint8_t* qnv, const uint8_t* qsc, const uint8_t* knv, const 
  * rowsum(x o y) (y has its own strides, same dtype as x); with `amax` (one device float the
  * caller zeroed) also max|x| over the whole tensor by atomic maximum, which the all-FP4 backward
  * turns into its global power-of-two pre-scale of dO.  Replaces the delta part of
- * `_flash_bwd_packprep_kernel` (flash.py:1175-1403).
+ * `_flash_bwd_packprep_kernel` (flash.py:1175-1403).  nb1 * nb2 * s < 2^31 rows.
  */
 int nvfp4_bwd_prep(const void* x, int dtype, int64_t sxb1, int64_t sxb2, int64_t sxs, int64_t nb1,
                    int64_t nb2, const void* y, int64_t syb1, int64_t syb2, int64_t sys, int64_t s,

@@ -1,11 +1,17 @@
 // NVFP4 packer: strided [B, R, K] -> nibbles [B, R, Kp/2] + e4m3 scales [B, R, Kp/16].
 //
-// HBM-bound byte work (2 B read + 0.5625 B written per bf16 element).  Two kernels:
-//   * pack_rows_kernel  -- contraction axis contiguous (Q, K along D): one thread per 16-group,
-//     two 128-bit loads, one 64-bit nibble store;
-//   * pack_cols_kernel  -- contraction axis strided, rows contiguous (V -> V^T along keys): a
-//     128-key x 64-row tile is read with 128-bit loads along the contiguous axis, transposed
-//     through shared memory, and written back as 64-byte row segments.
+// HBM-bound byte work (2 B read + 0.5625 B written per bf16 element).  Kernels:
+//   * pack_rows_quad_kernel -- contraction axis contiguous (Q, K along D), rows 32-byte aligned:
+//     a thread packs four 16-groups that lie 32 groups apart, one 256-bit load per group, so the
+//     lanes of a warp read consecutive sectors and write consecutive nibble words and scale bytes;
+//   * pack_rows_kernel  -- the same axis for rows that are only 16-byte aligned, unaligned or have a
+//     tail: one thread per 16-group;
+//   * pack_cols_kernel  -- contraction axis strided, rows contiguous (V -> V^T along keys): runs of
+//     128-key x 64-row tiles are read with 128-bit loads along the contiguous axis, transposed
+//     through shared memory (16-bit inputs stay as loaded), and written back as 64-byte row
+//     segments; the dual variant also emits the pack along the contiguous axis from the same read;
+//   * pack_qkv_kernel   -- Q, K along D and V^T in one flat-grid launch (the forward's pre-pack);
+//   * pack_mx8_cols_kernel -- MXFP8 (e4m3 + e8m0 per 32) along the strided axis.
 // A scalar kernel covers any other stride combination.
 #include "common/abi.cuh"
 #include "common/fp4.cuh"
@@ -234,8 +240,8 @@ template <> __device__ __forceinline__ void unpack2<float>(uint32_t, float&, flo
 
 // `nt` consecutive 128-key x 64-row tiles (tile coordinates bx .. bx + nt - 1, by of batch entry b);
 // for 16-bit inputs the global loads of the next tile are issued before the current one is packed.
-// With kDual the same tile
-// also yields the pack along the contiguous axis (rows of 16 consecutive elements of each key):
+// With kDual every tile also yields the pack along the contiguous axis (rows of 16 consecutive
+// elements of each key):
 // dnib [B, keys, R/2], dsc [B, keys, R/16], from the one read of x.  sr_flags (kDual only): bit 0
 // rounds the contiguous-axis pack stochastically, bit 1 the strided-axis pack; the random bits of
 // an element depend only on (seed, which pack, its position in x).

@@ -14,11 +14,13 @@
 //               group in turn (dK / dV are reduced over the group in TMEM and written once);
 //   dQ pass     rows = queries of a head, columns = keys.
 // Per step the issuer thread queues S (or S^T) and dP as two N=64 block-scaled MMAs each; a
-// softmax thread owns one row and the step's 64 columns, so the per-16 packs of P and dS along the
-// columns are thread-local: nibbles and scale bytes go to shared memory in the operand layout and
-// feed one M128 N128 K64 MMA per gradient.  Six FP4 MMAs per step replace the twenty bf16 MMAs of
-// the high-precision kernels.  Two teams of four softmax warps alternate steps, so the TMEM loads
-// and barrier waits of one step hide behind the arithmetic of the other.
+// softmax thread owns one row and 16-column chunks of the step's 64 columns, so the per-16 packs of
+// P and dS along the columns are thread-local: nibbles and scale bytes go to shared memory in the
+// operand layout and feed one M128 N128 K64 MMA per gradient.  Six FP4 MMAs per step replace the
+// twenty bf16 MMAs of the high-precision kernels.  Two teams of softmax warps alternate steps, so
+// the TMEM loads and barrier waits of one step hide behind the arithmetic of the other; at D = 128
+// two threads share a row (sixteen softmax warps, four per SM sub-partition: the per-element exp +
+// pack work is bound by how many warps a sub-partition has to interleave), at D = 256 one.
 //
 // Keeping the packed operands inside the e4m3 scale range (2^-9 .. 448) -- the job of the
 // reference's per-row rms normalisation, flash.py:184-228 -- is done with factors that never change
@@ -39,7 +41,6 @@
 
 namespace nvfp4 {
 
-constexpr int kB4Threads = 384;
 constexpr float kB4Log2e = 1.4426950408889634f;
 constexpr float kB4PShift = 11.0f;   // P is packed as P * 2^11
 constexpr int kB4Prefetch = 2;       // stages prefetched into L2 ahead of the ring
@@ -65,6 +66,11 @@ struct B4Cfg {
   static constexpr int S_AUX = S_TSF + 2048;              // two float[128]
   static constexpr int STAGE = ((S_AUX + 1024 + 1023) / 1024) * 1024;
   static constexpr int NSTAGE = D == 128 ? 3 : 2;
+  // softmax threads per row: at D = 128 two (each owns 32 of a step's 64 columns; sixteen softmax
+  // warps, four on every SM sub-partition), at D = 256 one (eight warps: there the MMAs of a step
+  // take long enough to cover one warp per sub-partition and team)
+  static constexpr int NP = D == 128 ? 2 : 1;
+  static constexpr int THREADS = 128 + 256 * NP;
   static constexpr int TOTAL = RES + NSTAGE * STAGE + 1024;
   // TMEM columns
   static constexpr uint32_t T_ACC1 = 0, T_ACC2 = 128, T_S = 256, T_G = 384;
@@ -192,7 +198,7 @@ __device__ __forceinline__ void sts_b16(uint32_t saddr, uint32_t a) {
 // kMode: 0 = NVFP4 gradient operands rounded to nearest, 1 = NVFP4 with the stochastic-rounding
 // flags honoured (a kernel of its own, so the common case carries none of it), 2 = MXFP8.
 template <int D, bool kDkdv, typename TG, int kMode>
-__global__ void __launch_bounds__(kB4Threads, 1)
+__global__ void __launch_bounds__((B4Cfg<D, kMode == 2>::THREADS), 1)
 bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
             const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
             const __grid_constant__ CUtensorMap tm_t1, const __grid_constant__ CUtensorMap tm_t2,
@@ -259,12 +265,12 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
     mbar_init(&x_full, 1);
     mbar_init(&xsf_full, 1);
     mbar_init(&g_full, 1);
-    mbar_init(&g_free, 4);
+    mbar_init(&g_free, 4 * C::NP);
     mbar_init(&acc_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_free[b], 4);
-      mbar_init(&a_full[b], 4);
+      mbar_init(&s_free[b], 4 * C::NP);
+      mbar_init(&a_full[b], 4 * C::NP);
       mbar_init(&a_free[b], 1);
     }
     mbar_fence_init();
@@ -507,12 +513,14 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
     __syncwarp();
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax teams, epilogue
-    // Two teams of four warps alternate steps (team t owns the steps of parity t, hence S slot t and
-    // half t of the operand tiles' rows), so one team's TMEM loads and barrier waits overlap the
-    // other team's arithmetic.  A thread owns one row and the 64 columns of its step, handled as
-    // two chunks of 32 (four 16-column groups packed thread-locally).
-    const int team = (warp - 4) >> 2;
-    const int grp = team;                 // epilogue: which 64 accumulator columns this thread stores
+    // Two teams alternate steps (team t owns the steps of parity t, hence S slot t and half t of the
+    // operand tiles' rows), so one team's TMEM loads and barrier waits overlap the other team's
+    // arithmetic.  NP threads share a row: thread h of a row owns 64 / NP of the step's 64 columns,
+    // as 16-column chunks whose packs are thread-local.
+    constexpr int NP = C::NP, NCH = 4 / NP;               // chunks per thread and step
+    const int team = (warp - 4) / (4 * NP);
+    const int h = ((warp - 4) >> 2) % NP;
+    const int part = team * NP + h;       // epilogue: which 64 / NP accumulator columns this thread stores
     const int wq = warp & 3;
     const int row_in = wq * 32 + lane;
     const int row = row0 + row_in;
@@ -564,148 +572,174 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
       mbar_wait(&s_full[pp], (st >> 1) & 1, &err, 11);
       mbar_wait(&g_full, st & 1, &err, 12);
       tc_fence_after();
-      // dP (or dP^T): all 64 columns at once, so the single slot goes back to the issuer right away;
-      // S in 16-column chunks, the next one in flight while the current one is worked on
-      uint32_t g0[32], g1[32], sa[16], sb[16];
-      tmem_ld32(tmem + lane_addr + C::T_G, g0);
-      tmem_ld32(tmem + lane_addr + C::T_G + 32, g1);
-      tmem_ld16(tmem + lane_addr + C::T_S + pp * 64, sa);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&g_free);
       uint32_t wp[4], wd[4], scp = 0u, scd = 0u;
       float pkeep[kFp8 ? 16 : 1], dkeep[kFp8 ? 16 : 1];     // MXFP8: the even chunk of a 32-column group
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t* cur = (ch & 1) ? sb : sa;
-        if (ch < 3) {
-          if (ch & 1) tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sa);
-          else tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sb);
-        }
-        const uint32_t* gsrc = ch < 2 ? g0 + 16 * ch : g1 + 16 * (ch - 2);
+      // one 16-column chunk: S and dP (or dP^T) values -> P, dS -> packs -> operand tiles
+      auto chunk = [&](int ch, const uint32_t (&cur)[16], const uint32_t* gsrc) {
         const float* aux = aux0 + 16 * ch;
-        float pf[16], ds[16];
+          float pf[16], ds[16];
 #pragma unroll
-        for (int e = 0; e < 16; e += 4) {
-          float2 eo01 = re2, eo23 = re2, nd01 = rnd2, nd23 = rnd2;
-          if constexpr (kDkdv) {
-            const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
-            const float4 n4 = *reinterpret_cast<const float4*>(aux + 128 + e);
-            eo01 = make_float2(a4.x, a4.y); eo23 = make_float2(a4.z, a4.w);
-            nd01 = make_float2(n4.x, n4.y); nd23 = make_float2(n4.z, n4.w);
+          for (int e = 0; e < 16; e += 4) {
+            float2 eo01 = re2, eo23 = re2, nd01 = rnd2, nd23 = rnd2;
+            if constexpr (kDkdv) {
+              const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
+              const float4 n4 = *reinterpret_cast<const float4*>(aux + 128 + e);
+              eo01 = make_float2(a4.x, a4.y); eo23 = make_float2(a4.z, a4.w);
+              nd01 = make_float2(n4.x, n4.y); nd23 = make_float2(n4.z, n4.w);
+            }
+            const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(cur[e]), __uint_as_float(cur[e + 1])), c22, eo01);
+            const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3])), c22, eo23);
+            const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e]), __uint_as_float(gsrc[e + 1])), cds2, nd01);
+            const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e + 2]), __uint_as_float(gsrc[e + 3])), cds2, nd23);
+            pf[e] = t01.x; pf[e + 1] = t01.y; pf[e + 2] = t23.x; pf[e + 3] = t23.y;
+            ds[e] = a01.x; ds[e + 1] = a01.y; ds[e + 2] = a23.x; ds[e + 3] = a23.y;
           }
-          const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(cur[e]), __uint_as_float(cur[e + 1])), c22, eo01);
-          const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3])), c22, eo23);
-          const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e]), __uint_as_float(gsrc[e + 1])), cds2, nd01);
-          const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e + 2]), __uint_as_float(gsrc[e + 3])), cds2, nd23);
-          pf[e] = t01.x; pf[e + 1] = t01.y; pf[e + 2] = t23.x; pf[e + 3] = t23.y;
-          ds[e] = a01.x; ds[e + 1] = a01.y; ds[e + 2] = a23.x; ds[e + 3] = a23.y;
-        }
-        if (has_bias) {           // row bias (dK/dV pass) or column bias (dQ pass), base-2 units
+          if (has_bias) {           // row bias (dK/dV pass) or column bias (dQ pass), base-2 units
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pf[e] += kDkdv ? row_e : aux[e];
-        }
+            for (int e = 0; e < 16; ++e) pf[e] += kDkdv ? row_e : aux[e];
+          }
 #pragma unroll
-        for (int e = 0; e < 16; ++e) pf[e] = ex2_bwd(pf[e]);
-        if (masked) {
+          for (int e = 0; e < 16; ++e) pf[e] = ex2_bwd(pf[e]);
+          if (masked) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pf[e] = (cs0 + 16 * ch + e >= lo && cs0 + 16 * ch + e < hi) ? pf[e] : 0.0f;
-        }
+            for (int e = 0; e < 16; ++e) pf[e] = (cs0 + 16 * ch + e >= lo && cs0 + 16 * ch + e < hi) ? pf[e] : 0.0f;
+          }
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
-          ds[e] = d2.x; ds[e + 1] = d2.y;
-        }
-        if constexpr (kFp8) {
-          if (!(ch & 1)) {
+          for (int e = 0; e < 16; e += 2) {
+            const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
+            ds[e] = d2.x; ds[e + 1] = d2.y;
+          }
+          if constexpr (kFp8) {
+            if (!(ch & 1)) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              if constexpr (kDkdv) pkeep[e] = pf[e];
-              dkeep[e] = ds[e];
+              for (int e = 0; e < 16; ++e) {
+                if constexpr (kDkdv) pkeep[e] = pf[e];
+                dkeep[e] = ds[e];
+              }
+            } else {
+              if (ch == NCH * h + 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
+              const int gi = ch >> 1;                       // which 32 columns of the step
+              const uint32_t byte0 = (uint32_t)(pp * 64 + gi * 32);
+              uint32_t w[8];
+              if constexpr (kDkdv) {
+                const uint32_t sb8 = pack_group32_mx8(pkeep, pf, w);
+                sts_v4(a1_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+                sts_v4(a1_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+                sts_b8(asf_s + pp * 512 + sf_atom_offset(row_in, gi), sb8);
+              }
+              const uint32_t sd8 = pack_group32_mx8(dkeep, ds, w);
+              sts_v4(a2_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+              sts_v4(a2_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+              sts_b8(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, gi), sd8);
             }
           } else {
-            if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
-            const int gi = ch >> 1;                       // which 32 columns of the step
-            const uint32_t byte0 = (uint32_t)(pp * 64 + gi * 32);
-            uint32_t w[8];
-            if constexpr (kDkdv) {
-              const uint32_t sb8 = pack_group32_mx8(pkeep, pf, w);
-              sts_v4(a1_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
-              sts_v4(a1_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
-              sts_b8(asf_s + pp * 512 + sf_atom_offset(row_in, gi), sb8);
-            }
-            const uint32_t sd8 = pack_group32_mx8(dkeep, ds, w);
-            sts_v4(a2_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
-            sts_v4(a2_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
-            sts_b8(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, gi), sd8);
-          }
-        } else {
-        // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
-        if constexpr (kSr) {
-          const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
-          const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
-          if constexpr (kDkdv)
-            scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+          // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
+          if constexpr (kSr) {
+            const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
+            const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
+            if constexpr (kDkdv)
+              scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+                     << (8 * (ch & 1));
+            scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
                    << (8 * (ch & 1));
-          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
-                 << (8 * (ch & 1));
-        } else {
-          if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
-          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
-        }
-        if (ch & 1) {
-          // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
-          if (ch == 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
-          const int c2i = ch >> 1;      // which 32 columns of the step
-          if constexpr (kDkdv) {
-            sts_v4(a1_s + sw64_offset(row_in, pp * 32 + c2i * 16), wp[0], wp[1], wp[2], wp[3]);
-            sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, c2i * 2), scp);
-            scp = 0u;
+          } else {
+            if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+            scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
           }
-          sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
-          sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
-          scd = 0u;
+          if (ch & 1) {
+            // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
+            if (ch == NCH * h + 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
+            const int c2i = ch >> 1;      // which 32 columns of the step
+            if constexpr (kDkdv) {
+              sts_v4(a1_s + sw64_offset(row_in, pp * 32 + c2i * 16), wp[0], wp[1], wp[2], wp[3]);
+              sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, c2i * 2), scp);
+              scp = 0u;
+            }
+            sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
+            sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
+            scd = 0u;
+          }
+          }
+      };
+      if constexpr (NP == 1) {
+        // dP (or dP^T): all 64 columns at once, so the single slot goes back to the issuer right away;
+        // S in 16-column chunks, the next one in flight while the current one is worked on
+        uint32_t g0[32], g1[32], sa[16], sb[16];
+        tmem_ld32(tmem + lane_addr + C::T_G, g0);
+        tmem_ld32(tmem + lane_addr + C::T_G + 32, g1);
+        tmem_ld16(tmem + lane_addr + C::T_S + pp * 64, sa);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&g_free);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          if (ch < 3) {
+            if (ch & 1) tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sa);
+            else tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * (ch + 1), sb);
+          }
+          chunk(ch, (ch & 1) ? sb : sa, ch < 2 ? g0 + 16 * ch : g1 + 16 * (ch - 2));
+          if (ch < 3) {
+            tmem_ld_wait();
+            if (ch == 2) {          // the last chunk of S is in registers: the slot goes back
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&s_free[pp]);
+            }
+          }
         }
-        }
-        if (ch < 3) {
+      } else {
+        // two chunks per thread, one round trip each; both slots go back to the issuer as soon as the
+        // second chunk is in registers
+#pragma unroll
+        for (int cc = 0; cc < NCH; ++cc) {
+          const int ch = NCH * h + cc;
+          uint32_t cur[16], gsrc[16];
+          tmem_ld16(tmem + lane_addr + C::T_G + 16 * ch, gsrc);
+          tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * ch, cur);
           tmem_ld_wait();
-          if (ch == 2) {          // the last chunk of S is in registers: the slot goes back
+          if (cc == NCH - 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[pp]);
+            if (lane == 0) {
+              mbar_arrive(&g_free);
+              mbar_arrive(&s_free[pp]);
+            }
           }
+          chunk(ch, cur, gsrc);
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[pp]);
     }
-    // ---- epilogue: group g writes gradient columns [64 g, 64 g + 64) of this CTA's 128-wide half
+    // ---- epilogue: thread `part` of a row writes gradient columns [EC part, EC part + EC), EC = 64 / NP,
+    // of this CTA's 128-wide half
     const float m1 = gs * 4.8828125e-4f;       // 2^-11
     const float m2 = gs * 1.953125e-3f;        // 2^-9
     TG* o1 = nullptr;
-    TG* o2 = static_cast<TG*>(p.out2) + ((int64_t)rb * R + row) * D + half * 128 + grp * 64;
-    if constexpr (kDkdv) o1 = static_cast<TG*>(p.out1) + ((int64_t)rb * R + row) * D + half * 128 + grp * 64;
+    constexpr int EC = 64 / NP;
+    TG* o2 = static_cast<TG*>(p.out2) + ((int64_t)rb * R + row) * D + half * 128 + part * EC;
+    if constexpr (kDkdv) o1 = static_cast<TG*>(p.out1) + ((int64_t)rb * R + row) * D + half * 128 + part * EC;
     if (nstep > 0) {
       mbar_wait(&acc_done, 0, &err, 14);
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < EC / 32; ++c) {
         uint32_t r[32];
         if constexpr (kDkdv) {
-          tmem_ld32(tmem + lane_addr + C::T_ACC1 + grp * 64 + c * 32, r);
+          tmem_ld32(tmem + lane_addr + C::T_ACC1 + part * EC + c * 32, r);
           tmem_ld_wait();
           if (row_ok) store_row32<TG>(o1 + c * 32, r, m1);
         }
-        tmem_ld32(tmem + lane_addr + C::T_ACC2 + grp * 64 + c * 32, r);
+        tmem_ld32(tmem + lane_addr + C::T_ACC2 + part * EC + c * 32, r);
         tmem_ld_wait();
         if (row_ok) store_row32<TG>(o2 + c * 32, r, m2);
       }
       tc_fence_before();
     } else if (row_ok) {
-      if constexpr (kDkdv) zero_row(o1, 64);
-      zero_row(o2, 64);
+      if constexpr (kDkdv) zero_row(o1, EC);
+      zero_row(o2, EC);
     }
   }
   tc_fence_before();
@@ -778,7 +812,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
   p.scaling = scaling; p.causal = (flags & NVFP4_FWD_CAUSAL) ? 1 : 0; p.status = status;
   p.seed = seed; p.sr_p = 0; p.sr_ds = 0;
   const unsigned halves = (unsigned)(d / 128);
-  auto launch = [&](auto kdkdv, auto kdq, int smem) -> int {
+  auto launch = [&](auto kdkdv, auto kdq, int smem, int threads) -> int {
     cudaError_t e = cudaFuncSetAttribute(kdkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail((int)e, "nvfp4_bwd_fp4: smem attribute: %s", cudaGetErrorString(e));
     e = cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -789,7 +823,7 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     a.out1 = dv; a.out2 = dk; a.c_pad = (int)sq_pad;
     a.sr_p = (flags & NVFP4_BWD_SR_P_DV) ? 1 : 0; a.sr_ds = (flags & NVFP4_BWD_SR_DS_DK) ? 1 : 0;
     dim3 g1((unsigned)zhk, (unsigned)((s_kv + 127) / 128), halves);
-    kdkdv<<<g1, kB4Threads, smem, st>>>(t_k, t_vd, t_q, t_do, t_dot, t_qt, a);
+    kdkdv<<<g1, threads, smem, st>>>(t_k, t_vd, t_q, t_do, t_dot, t_qt, a);
     int r1 = launch_result("nvfp4_bwd_fp4(dkdv)");
     if (r1) return r1;
     // dQ: rows = queries (Q, dO' packs), columns = keys (K, V packs; K^T transposed pack)
@@ -798,14 +832,17 @@ extern "C" int nvfp4_bwd_fp4(const uint8_t* qnv, const uint8_t* qsc, const uint8
     b.out1 = nullptr; b.out2 = dq; b.c_pad = (int)skv_pad;
     b.sr_ds = (flags & NVFP4_BWD_SR_DS_DQ) ? 1 : 0;
     dim3 g2((unsigned)zh, (unsigned)((s_q + 127) / 128), halves);
-    kdq<<<g2, kB4Threads, smem, st>>>(t_q, t_do, t_k, t_vd, t_kt, t_kt, b);
+    kdq<<<g2, threads, smem, st>>>(t_q, t_do, t_k, t_vd, t_kt, t_kt, b);
     return launch_result("nvfp4_bwd_fp4(dq)");
   };
   const bool any_sr = (flags & (NVFP4_BWD_SR_DS_DK | NVFP4_BWD_SR_P_DV | NVFP4_BWD_SR_DS_DQ)) != 0;
 #define NVFP4_B4_LAUNCH(DD, TT)                                                                                   \
-  (fp8      ? launch(bwd4_kernel<DD, true, TT, 2>, bwd4_kernel<DD, false, TT, 2>, B4Cfg<DD, true>::TOTAL)         \
-   : any_sr ? launch(bwd4_kernel<DD, true, TT, 1>, bwd4_kernel<DD, false, TT, 1>, B4Cfg<DD, false>::TOTAL)        \
-            : launch(bwd4_kernel<DD, true, TT, 0>, bwd4_kernel<DD, false, TT, 0>, B4Cfg<DD, false>::TOTAL))
+  (fp8      ? launch(bwd4_kernel<DD, true, TT, 2>, bwd4_kernel<DD, false, TT, 2>, B4Cfg<DD, true>::TOTAL,         \
+                     B4Cfg<DD, true>::THREADS)                                                                    \
+   : any_sr ? launch(bwd4_kernel<DD, true, TT, 1>, bwd4_kernel<DD, false, TT, 1>, B4Cfg<DD, false>::TOTAL,        \
+                     B4Cfg<DD, false>::THREADS)                                                                   \
+            : launch(bwd4_kernel<DD, true, TT, 0>, bwd4_kernel<DD, false, TT, 0>, B4Cfg<DD, false>::TOTAL,        \
+                     B4Cfg<DD, false>::THREADS))
   if (d == 128) {
     switch (grad_dtype) {
       case NVFP4_DT_BF16: return NVFP4_B4_LAUNCH(128, __nv_bfloat16);

@@ -689,24 +689,25 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
           }
         }
       } else {
-        // two chunks per thread, one round trip each; both slots go back to the issuer as soon as the
-        // second chunk is in registers
+        // this thread's 32 columns of dP (or dP^T) arrive with the first S chunk, so the single dP slot
+        // goes back to the issuer after one round trip; the S slot follows with the second chunk
+        uint32_t gq[32];
+        tmem_ld32(tmem + lane_addr + C::T_G + 32 * h, gq);
 #pragma unroll
         for (int cc = 0; cc < NCH; ++cc) {
           const int ch = NCH * h + cc;
-          uint32_t cur[16], gsrc[16];
-          tmem_ld16(tmem + lane_addr + C::T_G + 16 * ch, gsrc);
+          uint32_t cur[16];
           tmem_ld16(tmem + lane_addr + C::T_S + pp * 64 + 16 * ch, cur);
           tmem_ld_wait();
-          if (cc == NCH - 1) {
+          if (cc == 0 || cc == NCH - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-              mbar_arrive(&g_free);
-              mbar_arrive(&s_free[pp]);
+              if (cc == 0) mbar_arrive(&g_free);
+              if (cc == NCH - 1) mbar_arrive(&s_free[pp]);
             }
           }
-          chunk(ch, cur, gsrc);
+          chunk(ch, cur, gq + 16 * cc);
         }
       }
       fence_proxy_async_smem();

@@ -119,7 +119,8 @@ __device__ __forceinline__ void pack_rows_quad(const T* __restrict__ x, int ng_l
     g[i] = (int)(gc - (r[i] << ng_log2));
     const T* p = x + b * sxb + r[i] * sxr + g[i] * 16;
 #pragma unroll
-    for (int j = 0; j < kW / 8; ++j) ldg256(reinterpret_cast<const uint32_t*>(p) + 8 * j, *reinterpret_cast<uint32_t(*)[8]>(&raw[i][8 * j]));
+    for (int j = 0; j < kW / 8; ++j)
+      ldg256(reinterpret_cast<const uint32_t*>(p) + 8 * j, *reinterpret_cast<uint32_t(*)[8]>(&raw[i][8 * j]));
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -300,33 +301,102 @@ __device__ __forceinline__ void pack_cols_tile(
   // after the second barrier of the tile before (all its readers are past it), the output staging is
   // rewritten after the first barrier of this tile (its readers, the store phase, are before it).
   for (int ti = 0; ti < nt; ++ti) {
-  const int64_t k0 = (bx + ti) * kColsKeys;
-  if constexpr (sizeof(T) == 2) {
-    auto& raw = sm.raw;
-    // one 16-byte shared store per 16-byte load; then the next tile's loads are issued
+    const int64_t k0 = (bx + ti) * kColsKeys;
+    if constexpr (sizeof(T) == 2) {
+      auto& raw = sm.raw;
+      // one 16-byte shared store per 16-byte load; then the next tile's loads are issued
 #pragma unroll
-    for (int pass = 0; pass < kColsKeys / 32; ++pass)
-      *reinterpret_cast<uint4*>(&raw[pass * 32 + (tid >> 3)][(tid & 7) * 4]) = wreg[pass];
-    if (ti + 1 < nt) load16(k0 + kColsKeys);
+      for (int pass = 0; pass < kColsKeys / 32; ++pass)
+        *reinterpret_cast<uint4*>(&raw[pass * 32 + (tid >> 3)][(tid & 7) * 4]) = wreg[pass];
+      if (ti + 1 < nt) load16(k0 + kColsKeys);
+      __syncthreads();
+      if constexpr (kDual) {
+        // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2);
+        // the 16 elements of a group are two 16-byte shared loads
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int key = tid & 127;
+          const int g = (tid >> 7) + it * 2;
+          if (k0 + key < k_read && r0 + g * 16 < R) {
+            const uint4 w0 = *reinterpret_cast<const uint4*>(&raw[key][g * 8]);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(&raw[key][g * 8 + 4]);
+            const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              unpack2<T>(ww[j], v[2 * j], v[2 * j + 1]);
+              v[2 * j] *= pre;
+              v[2 * j + 1] *= pre;
+            }
+            uint32_t lo, hi;
+            const uint8_t sb = (sr_flags & 1)
+                                   ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * k_read + k0 + key) * 2u,
+                                                     (uint32_t)(r0 / 4 + g * 4))
+                                   : pack_group16(v, lo, hi);
+            *reinterpret_cast<uint2*>(dnib + b * dnb + (k0 + key) * dnr + (r0 + g * 16) / 2) = make_uint2(lo, hi);
+            dsc[b * dsb + (k0 + key) * dsr + (r0 + g * 16) / 16] = sb;
+          }
+        }
+      }
+      // quantise along the keys: thread -> (rows 2 (tid % 32) and the next, 16-key group tid / 32); one
+      // 32-bit shared load brings a key's elements of both rows
+      {
+        const int rp = tid & 31, g = tid >> 5;
+        float v0[16], v1[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          unpack2<T>(raw[g * 16 + j][rp], v0[j], v1[j]);
+          if (kDual) {
+            v0[j] *= pre;
+            v1[j] *= pre;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int row = 2 * rp + h;
+          uint32_t lo, hi;
+          const uint8_t sb = (kDual && (sr_flags & 2))
+                                 ? pack_group16_sr(h ? v1 : v0, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
+                                                   (uint32_t)(k0 / 4 + g * 4))
+                                 : pack_group16(h ? v1 : v0, lo, hi);
+          *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
+          osc[row][g] = sb;
+        }
+      }
+    } else {
+    auto& tile = sm.tile;
+    // load: 8 threads x 8 elements cover 64 rows of one key; 32 keys per pass
+#pragma unroll
+    for (int pass = 0; pass < kColsKeys / 32; ++pass) {
+      const int key = pass * 32 + (tid >> 3);
+      const int rc = (tid & 7) * 8;
+      float v[8];
+      const int64_t kk = k0 + key;
+      int valid = 0;
+      if (kk < k_read) {
+        const int64_t left = R - (r0 + rc);
+        valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
+      }
+      if (valid > 0) {
+        load8<T>(xb + kk * sxk + r0 + rc, vec_in, valid, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tile[key][rc + i] = kDual ? v[i] * pre : v[i];
+    }
     __syncthreads();
     if constexpr (kDual) {
-      // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2);
-      // the 16 elements of a group are two 16-byte shared loads
+      // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2)
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int key = tid & 127;
         const int g = (tid >> 7) + it * 2;
         if (k0 + key < k_read && r0 + g * 16 < R) {
-          const uint4 w0 = *reinterpret_cast<const uint4*>(&raw[key][g * 8]);
-          const uint4 w1 = *reinterpret_cast<const uint4*>(&raw[key][g * 8 + 4]);
-          const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
           float v[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            unpack2<T>(ww[j], v[2 * j], v[2 * j + 1]);
-            v[2 * j] *= pre;
-            v[2 * j + 1] *= pre;
-          }
+          for (int j = 0; j < 16; ++j) v[j] = tile[key][g * 16 + j];
           uint32_t lo, hi;
           const uint8_t sb = (sr_flags & 1)
                                  ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * k_read + k0 + key) * 2u,
@@ -337,117 +407,48 @@ __device__ __forceinline__ void pack_cols_tile(
         }
       }
     }
-    // quantise along the keys: thread -> (rows 2 (tid % 32) and the next, 16-key group tid / 32); one
-    // 32-bit shared load brings a key's elements of both rows
-    {
-      const int rp = tid & 31, g = tid >> 5;
-      float v0[16], v1[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        unpack2<T>(raw[g * 16 + j][rp], v0[j], v1[j]);
-        if (kDual) {
-          v0[j] *= pre;
-          v1[j] *= pre;
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int row = 2 * rp + h;
-        uint32_t lo, hi;
-        const uint8_t sb = (kDual && (sr_flags & 2))
-                               ? pack_group16_sr(h ? v1 : v0, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
-                                                 (uint32_t)(k0 / 4 + g * 4))
-                               : pack_group16(h ? v1 : v0, lo, hi);
-        *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
-        osc[row][g] = sb;
-      }
-    }
-  } else {
-  auto& tile = sm.tile;
-  // load: 8 threads x 8 elements cover 64 rows of one key; 32 keys per pass
-#pragma unroll
-  for (int pass = 0; pass < kColsKeys / 32; ++pass) {
-    const int key = pass * 32 + (tid >> 3);
-    const int rc = (tid & 7) * 8;
-    float v[8];
-    const int64_t kk = k0 + key;
-    int valid = 0;
-    if (kk < k_read) {
-      const int64_t left = R - (r0 + rc);
-      valid = left >= 8 ? 8 : (left > 0 ? (int)left : 0);
-    }
-    if (valid > 0) {
-      load8<T>(xb + kk * sxk + r0 + rc, vec_in, valid, v);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tile[key][rc + i] = kDual ? v[i] * pre : v[i];
-  }
-  __syncthreads();
-  if constexpr (kDual) {
-    // along the contiguous axis: thread -> (key = tid % 128, groups tid / 128 and tid / 128 + 2)
+    // quantise: thread -> (row = tid % 64, groups tid / 64 and tid / 64 + 4)
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
-      const int key = tid & 127;
-      const int g = (tid >> 7) + it * 2;
-      if (k0 + key < k_read && r0 + g * 16 < R) {
-        float v[16];
+      const int row = tid & 63;
+      const int g = (tid >> 6) + it * 4;
+      float v[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = tile[key][g * 16 + j];
-        uint32_t lo, hi;
-        const uint8_t sb = (sr_flags & 1)
-                               ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * k_read + k0 + key) * 2u,
-                                                 (uint32_t)(r0 / 4 + g * 4))
-                               : pack_group16(v, lo, hi);
-        *reinterpret_cast<uint2*>(dnib + b * dnb + (k0 + key) * dnr + (r0 + g * 16) / 2) = make_uint2(lo, hi);
-        dsc[b * dsb + (k0 + key) * dsr + (r0 + g * 16) / 16] = sb;
+      for (int j = 0; j < 16; ++j) v[j] = tile[g * 16 + j][row];
+      uint32_t lo, hi;
+      const uint8_t sb = (kDual && (sr_flags & 2))
+                             ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
+                                               (uint32_t)(k0 / 4 + g * 4))
+                             : pack_group16(v, lo, hi);
+      *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
+      osc[row][g] = sb;
+    }
+    }
+    __syncthreads();
+    // store: groups of this tile that exist in the output
+    const int64_t gleft = (k_pad - k0) / 16;
+    const int ng = gleft >= 8 ? 8 : (int)gleft;
+    {
+      const int row = tid >> 2, chunk = tid & 3;  // 16-byte chunk = 2 groups
+      if (r0 + row < R) {
+        uint8_t* pn = nib + b * snb + (r0 + row) * snr + k0 / 2 + chunk * 16;
+        const int gv = ng - chunk * 2;  // groups valid in this chunk
+        if (gv >= 2 && (reinterpret_cast<uintptr_t>(pn) & 15) == 0) {
+          *reinterpret_cast<uint4*>(pn) = *reinterpret_cast<const uint4*>(&onib[row][chunk * 16]);
+        } else if (gv > 0) {
+          const int nb = (gv >= 2 ? 2 : gv) * 8;
+          for (int i = 0; i < nb; ++i) pn[i] = onib[row][chunk * 16 + i];
+        }
       }
     }
-  }
-  // quantise: thread -> (row = tid % 64, groups tid / 64 and tid / 64 + 4)
-#pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int row = tid & 63;
-    const int g = (tid >> 6) + it * 4;
-    float v[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = tile[g * 16 + j][row];
-    uint32_t lo, hi;
-    const uint8_t sb = (kDual && (sr_flags & 2))
-                           ? pack_group16_sr(v, lo, hi, seed, (uint32_t)(b * R + r0 + row) * 2u + 1u,
-                                             (uint32_t)(k0 / 4 + g * 4))
-                           : pack_group16(v, lo, hi);
-    *reinterpret_cast<uint2*>(&onib[row][g * 8]) = make_uint2(lo, hi);
-    osc[row][g] = sb;
-  }
-  }
-  __syncthreads();
-  // store: groups of this tile that exist in the output
-  const int64_t gleft = (k_pad - k0) / 16;
-  const int ng = gleft >= 8 ? 8 : (int)gleft;
-  {
-    const int row = tid >> 2, chunk = tid & 3;  // 16-byte chunk = 2 groups
-    if (r0 + row < R) {
-      uint8_t* pn = nib + b * snb + (r0 + row) * snr + k0 / 2 + chunk * 16;
-      const int gv = ng - chunk * 2;  // groups valid in this chunk
-      if (gv >= 2 && (reinterpret_cast<uintptr_t>(pn) & 15) == 0) {
-        *reinterpret_cast<uint4*>(pn) = *reinterpret_cast<const uint4*>(&onib[row][chunk * 16]);
-      } else if (gv > 0) {
-        const int nb = (gv >= 2 ? 2 : gv) * 8;
-        for (int i = 0; i < nb; ++i) pn[i] = onib[row][chunk * 16 + i];
+    if (tid < kColsRows && r0 + tid < R) {
+      uint8_t* ps = sc + b * ssb + (r0 + tid) * ssr + k0 / 16;
+      if (ng == 8 && (reinterpret_cast<uintptr_t>(ps) & 7) == 0) {
+        *reinterpret_cast<uint2*>(ps) = *reinterpret_cast<const uint2*>(&osc[tid][0]);
+      } else {
+        for (int i = 0; i < ng; ++i) ps[i] = osc[tid][i];
       }
     }
-  }
-  if (tid < kColsRows && r0 + tid < R) {
-    uint8_t* ps = sc + b * ssb + (r0 + tid) * ssr + k0 / 16;
-    if (ng == 8 && (reinterpret_cast<uintptr_t>(ps) & 7) == 0) {
-      *reinterpret_cast<uint2*>(ps) = *reinterpret_cast<const uint2*>(&osc[tid][0]);
-    } else {
-      for (int i = 0; i < ng; ++i) ps[i] = osc[tid][i];
-    }
-  }
   }  // tiles of the run
 }
 

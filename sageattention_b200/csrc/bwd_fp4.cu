@@ -577,89 +577,89 @@ bwd4_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ C
       // one 16-column chunk: S and dP (or dP^T) values -> P, dS -> packs -> operand tiles
       auto chunk = [&](int ch, const uint32_t (&cur)[16], const uint32_t* gsrc) {
         const float* aux = aux0 + 16 * ch;
-          float pf[16], ds[16];
+        float pf[16], ds[16];
 #pragma unroll
-          for (int e = 0; e < 16; e += 4) {
-            float2 eo01 = re2, eo23 = re2, nd01 = rnd2, nd23 = rnd2;
-            if constexpr (kDkdv) {
-              const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
-              const float4 n4 = *reinterpret_cast<const float4*>(aux + 128 + e);
-              eo01 = make_float2(a4.x, a4.y); eo23 = make_float2(a4.z, a4.w);
-              nd01 = make_float2(n4.x, n4.y); nd23 = make_float2(n4.z, n4.w);
-            }
-            const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(cur[e]), __uint_as_float(cur[e + 1])), c22, eo01);
-            const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3])), c22, eo23);
-            const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e]), __uint_as_float(gsrc[e + 1])), cds2, nd01);
-            const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e + 2]), __uint_as_float(gsrc[e + 3])), cds2, nd23);
-            pf[e] = t01.x; pf[e + 1] = t01.y; pf[e + 2] = t23.x; pf[e + 3] = t23.y;
-            ds[e] = a01.x; ds[e + 1] = a01.y; ds[e + 2] = a23.x; ds[e + 3] = a23.y;
+        for (int e = 0; e < 16; e += 4) {
+          float2 eo01 = re2, eo23 = re2, nd01 = rnd2, nd23 = rnd2;
+          if constexpr (kDkdv) {
+            const float4 a4 = *reinterpret_cast<const float4*>(aux + e);
+            const float4 n4 = *reinterpret_cast<const float4*>(aux + 128 + e);
+            eo01 = make_float2(a4.x, a4.y); eo23 = make_float2(a4.z, a4.w);
+            nd01 = make_float2(n4.x, n4.y); nd23 = make_float2(n4.z, n4.w);
           }
-          if (has_bias) {           // row bias (dK/dV pass) or column bias (dQ pass), base-2 units
+          const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(cur[e]), __uint_as_float(cur[e + 1])), c22, eo01);
+          const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(cur[e + 2]), __uint_as_float(cur[e + 3])), c22, eo23);
+          const float2 a01 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e]), __uint_as_float(gsrc[e + 1])), cds2, nd01);
+          const float2 a23 = __ffma2_rn(make_float2(__uint_as_float(gsrc[e + 2]), __uint_as_float(gsrc[e + 3])), cds2, nd23);
+          pf[e] = t01.x; pf[e + 1] = t01.y; pf[e + 2] = t23.x; pf[e + 3] = t23.y;
+          ds[e] = a01.x; ds[e + 1] = a01.y; ds[e + 2] = a23.x; ds[e + 3] = a23.y;
+        }
+        if (has_bias) {           // row bias (dK/dV pass) or column bias (dQ pass), base-2 units
 #pragma unroll
-            for (int e = 0; e < 16; ++e) pf[e] += kDkdv ? row_e : aux[e];
-          }
+          for (int e = 0; e < 16; ++e) pf[e] += kDkdv ? row_e : aux[e];
+        }
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pf[e] = ex2_bwd(pf[e]);
-          if (masked) {
+        for (int e = 0; e < 16; ++e) pf[e] = ex2_bwd(pf[e]);
+        if (masked) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) pf[e] = (cs0 + 16 * ch + e >= lo && cs0 + 16 * ch + e < hi) ? pf[e] : 0.0f;
-          }
+          for (int e = 0; e < 16; ++e) pf[e] = (cs0 + 16 * ch + e >= lo && cs0 + 16 * ch + e < hi) ? pf[e] : 0.0f;
+        }
 #pragma unroll
-          for (int e = 0; e < 16; e += 2) {
-            const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
-            ds[e] = d2.x; ds[e + 1] = d2.y;
-          }
-          if constexpr (kFp8) {
-            if (!(ch & 1)) {
+        for (int e = 0; e < 16; e += 2) {
+          const float2 d2 = __fmul2_rn(make_float2(pf[e], pf[e + 1]), make_float2(ds[e], ds[e + 1]));
+          ds[e] = d2.x; ds[e + 1] = d2.y;
+        }
+        if constexpr (kFp8) {
+          if (!(ch & 1)) {
 #pragma unroll
-              for (int e = 0; e < 16; ++e) {
-                if constexpr (kDkdv) pkeep[e] = pf[e];
-                dkeep[e] = ds[e];
-              }
-            } else {
-              if (ch == NCH * h + 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
-              const int gi = ch >> 1;                       // which 32 columns of the step
-              const uint32_t byte0 = (uint32_t)(pp * 64 + gi * 32);
-              uint32_t w[8];
-              if constexpr (kDkdv) {
-                const uint32_t sb8 = pack_group32_mx8(pkeep, pf, w);
-                sts_v4(a1_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
-                sts_v4(a1_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
-                sts_b8(asf_s + pp * 512 + sf_atom_offset(row_in, gi), sb8);
-              }
-              const uint32_t sd8 = pack_group32_mx8(dkeep, ds, w);
-              sts_v4(a2_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
-              sts_v4(a2_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
-              sts_b8(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, gi), sd8);
+            for (int e = 0; e < 16; ++e) {
+              if constexpr (kDkdv) pkeep[e] = pf[e];
+              dkeep[e] = ds[e];
             }
           } else {
-          // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
-          if constexpr (kSr) {
-            const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
-            const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
-            if constexpr (kDkdv)
-              scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
-                     << (8 * (ch & 1));
-            scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
-                   << (8 * (ch & 1));
-          } else {
-            if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
-            scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
-          }
-          if (ch & 1) {
-            // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
             if (ch == NCH * h + 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
-            const int c2i = ch >> 1;      // which 32 columns of the step
+            const int gi = ch >> 1;                       // which 32 columns of the step
+            const uint32_t byte0 = (uint32_t)(pp * 64 + gi * 32);
+            uint32_t w[8];
             if constexpr (kDkdv) {
-              sts_v4(a1_s + sw64_offset(row_in, pp * 32 + c2i * 16), wp[0], wp[1], wp[2], wp[3]);
-              sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, c2i * 2), scp);
-              scp = 0u;
+              const uint32_t sb8 = pack_group32_mx8(pkeep, pf, w);
+              sts_v4(a1_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+              sts_v4(a1_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+              sts_b8(asf_s + pp * 512 + sf_atom_offset(row_in, gi), sb8);
             }
-            sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
-            sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
-            scd = 0u;
+            const uint32_t sd8 = pack_group32_mx8(dkeep, ds, w);
+            sts_v4(a2_s + sw128_offset(row_in, byte0), w[0], w[1], w[2], w[3]);
+            sts_v4(a2_s + sw128_offset(row_in, byte0 + 16), w[4], w[5], w[6], w[7]);
+            sts_b8(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, gi), sd8);
           }
+        } else {
+        // random-bit counters: (tensor, row of the CTA's unit) and the quad's column within the unit
+        if constexpr (kSr) {
+          const uint32_t sr_row = (uint32_t)((int64_t)rb * R + row) * 4u + (kDkdv ? 0u : 2u);
+          const uint32_t sr_col = (uint32_t)(st * 16 + ch * 4);
+          if constexpr (kDkdv)
+            scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1], p.sr_p != 0, p.seed, sr_row + 1u, sr_col)
+                   << (8 * (ch & 1));
+          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1], p.sr_ds != 0, p.seed, sr_row, sr_col)
+                 << (8 * (ch & 1));
+        } else {
+          if constexpr (kDkdv) scp |= b4_pack16<false>(pf, wp[2 * (ch & 1)], wp[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+          scd |= b4_pack16<true>(ds, wd[2 * (ch & 1)], wd[2 * (ch & 1) + 1]) << (8 * (ch & 1));
+        }
+        if (ch & 1) {
+          // the operand tiles of step st - 2 (same half of the rows' bytes) must have been consumed
+          if (ch == NCH * h + 1 && st >= 2) mbar_wait(&a_free[pp], ((st >> 1) - 1) & 1, &err, 13);
+          const int c2i = ch >> 1;      // which 32 columns of the step
+          if constexpr (kDkdv) {
+            sts_v4(a1_s + sw64_offset(row_in, pp * 32 + c2i * 16), wp[0], wp[1], wp[2], wp[3]);
+            sts_b16(asf_s + pp * 512 + sf_atom_offset(row_in, c2i * 2), scp);
+            scp = 0u;
           }
+          sts_v4(a2_s + sw64_offset(row_in, pp * 32 + c2i * 16), wd[0], wd[1], wd[2], wd[3]);
+          sts_b16(asf_s + (2 + pp) * 512 + sf_atom_offset(row_in, c2i * 2), scd);
+          scd = 0u;
+        }
+        }
       };
       if constexpr (NP == 1) {
         // dP (or dP^T): all 64 columns at once, so the single slot goes back to the issuer right away;

@@ -6,7 +6,10 @@ shipped package never does (it fails loudly when the CUDA library is missing).
 
 Pinning: the functions below are checked against fixtures produced by the reference's own
 kernels executed under the Triton CPU interpreter (two hardware primitives emulated: the PTX
-``cvt.rn.satfinite.e2m1x2.f32`` and the block-scaled MMA); see ``tests/golden/make_golden.py``.
+``cvt.rn.satfinite.e2m1x2.f32`` and the block-scaled MMA, for e2m1 and for e4m3 operands); see
+``tests/golden/make_golden.py``.  That covers the NVFP4 pack, the forward, decode, the KV cache,
+the three backward modes and the MXFP8 pack (``tests/golden/mxfp8_pack.npz``: bytes and scale
+exponents of the reference's ``_pack_mxfp8_along_k``).
 
 All ``file:line`` citations are paths inside the reference project
 (thad0ctor/SageAttention), e.g. ``sageattention/nvfp4/flash.py:341-347``.
@@ -157,6 +160,8 @@ def pack_mxfp8(x: np.ndarray, transpose: bool = False, k_pad: int | None = None)
     """MXFP8 pack along the contraction axis, group 32; restates ``_pack_mxfp8_along_k``
     (flash.py:243-257): ``e = ceil(log2(max(amax, 1e-30) / 448))`` -- evaluated exactly, as the
     smallest integer with ``amax / 2**e <= 448`` --, bytes = e4m3(x / 2**e), scale byte = e + 127.
+    Bit-equal to the reference's own function on the ``mxfp8_pack`` fixture (random magnitudes, an
+    all-zero group, a group maximum of exactly 448, 1e-12 values).
     ``x`` [B, R, K] (or [B, K, R] with ``transpose``); returns (uint8 [B, R, Kp], uint8 [B, R, Kp/32])."""
     x = np.asarray(x, dtype=np.float32)
     if transpose:
